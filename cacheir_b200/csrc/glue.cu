@@ -1,0 +1,329 @@
+// Glue ops of the decode graph: RMSNorm (+fused residual add), RoPE, KV page
+// append, SiLU*mul, add, embedding gather, row argmax and the per-step
+// position bookkeeping. All of them touch a few hundred KB per step; they are
+// written as single-pass, 128-bit-access kernels so that their cost is the
+// launch, not the traffic.
+#include "common.cuh"
+
+namespace cb200 {
+namespace {
+
+// ---- RMSNorm ---------------------------------------------------------------------
+// One CTA per row; the row is read once (optionally summed with a residual row,
+// the sum being written back for the later residual connection) and kept in
+// registers between the statistics pass and the scaling pass when it fits.
+template <typename T, int VEC, int PER_THREAD>
+__global__ void __launch_bounds__(256)
+rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ weight,
+                T* __restrict__ sum_out, T* __restrict__ out, int hidden, float eps) {
+  __shared__ float red[8];
+  const size_t row = blockIdx.x;
+  const T* xr = x + row * hidden;
+  const T* rr = residual ? residual + row * hidden : nullptr;
+  const int nvec = hidden / VEC;  // host guarantees hidden % VEC == 0 on this path
+  float cache[PER_THREAD][VEC];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) {
+      VecIO<T, VEC>::ld(xr + c * VEC, cache[i]);
+      if (rr) {
+        float r[VEC];
+        VecIO<T, VEC>::ld(rr + c * VEC, r);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) cache[i][v] += r[v];
+        // the residual stream carries the rounded sum, so normalise what is stored
+        T tmp[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) { Elem<T>::st(&tmp[v], cache[i][v]); cache[i][v] = Elem<T>::ld(&tmp[v]); }
+        VecIO<T, VEC>::st(sum_out + row * hidden + c * VEC, cache[i]);
+      }
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) ss = fmaf(cache[i][v], cache[i][v], ss);
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += red[w];
+  const float inv = rsqrtf(tot / static_cast<float>(hidden) + eps);
+#pragma unroll
+  for (int i = 0; i < PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) {
+      float w[VEC], o[VEC];
+      VecIO<T, VEC>::ld(weight + c * VEC, w);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) o[v] = cache[i][v] * inv * w[v];
+      VecIO<T, VEC>::st(out + row * hidden + c * VEC, o);
+    }
+  }
+}
+
+// Any hidden size / alignment: two passes over global memory, scalar access.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_norm_generic_kernel(const T* __restrict__ x, const T* __restrict__ residual,
+                        const T* __restrict__ weight, T* __restrict__ sum_out, T* __restrict__ out,
+                        int hidden, float eps) {
+  __shared__ float red[8];
+  const size_t row = blockIdx.x;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += 256) {
+    float v = Elem<T>::ld(x + row * hidden + c);
+    if (residual) {
+      v += Elem<T>::ld(residual + row * hidden + c);
+      Elem<T>::st(sum_out + row * hidden + c, v);
+      v = Elem<T>::ld(sum_out + row * hidden + c);
+    }
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += red[w];
+  const float inv = rsqrtf(tot / static_cast<float>(hidden) + eps);
+  const T* src = residual ? sum_out : x;
+  for (int c = threadIdx.x; c < hidden; c += 256)
+    Elem<T>::st(out + row * hidden + c, Elem<T>::ld(src + row * hidden + c) * inv * Elem<T>::ld(weight + c));
+}
+
+template <typename T, int VEC>
+int launch_rms_norm(const void* x, const void* residual, const void* weight, void* sum_out, void* out,
+                    int rows, int hidden, float eps, cudaStream_t st) {
+  const T* xp = static_cast<const T*>(x);
+  const T* rp = static_cast<const T*>(residual);
+  const T* wp = static_cast<const T*>(weight);
+  T* sp = static_cast<T*>(sum_out);
+  T* op = static_cast<T*>(out);
+  const bool vec_ok = hidden % VEC == 0 && aligned_to(x, 16) && aligned_to(weight, 16) &&
+                      aligned_to(out, 16) && (!residual || (aligned_to(residual, 16) && aligned_to(sum_out, 16)));
+  const int nvec = hidden / VEC;
+  if (vec_ok && nvec <= 256 * 2) {
+    rms_norm_kernel<T, VEC, 2><<<rows, 256, 0, st>>>(xp, rp, wp, sp, op, hidden, eps);
+  } else if (vec_ok && nvec <= 256 * 8) {
+    rms_norm_kernel<T, VEC, 8><<<rows, 256, 0, st>>>(xp, rp, wp, sp, op, hidden, eps);
+  } else {
+    rms_norm_generic_kernel<T><<<rows, 256, 0, st>>>(xp, rp, wp, sp, op, hidden, eps);
+  }
+  return launch_status();
+}
+
+// ---- RoPE (interleaved pairs) ----------------------------------------------------
+// angle = pos * theta^(-2i/D); the reference evaluates pow/cos/sin in fp32.
+template <typename T>
+__global__ void rope_inplace_kernel(T* __restrict__ x, const int32_t* __restrict__ positions,
+                                    int num_heads, int head_dim, float theta, long long stride) {
+  const int b = blockIdx.y;
+  const int half = head_dim / 2;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;  // (head, pair)
+  if (idx >= num_heads * half) return;
+  const int h = idx / half;
+  const int i = idx % half;
+  const float freq = 1.0f / powf(theta, static_cast<float>(i) * 2.0f / static_cast<float>(head_dim));
+  const float angle = static_cast<float>(positions[b]) * freq;
+  float s, c;
+  sincosf(angle, &s, &c);
+  T* p = x + static_cast<size_t>(b) * stride + static_cast<size_t>(h) * head_dim + 2 * i;
+  const float e = Elem<T>::ld(p);
+  const float o = Elem<T>::ld(p + 1);
+  Elem<T>::st(p, e * c - o * s);
+  Elem<T>::st(p + 1, e * s + o * c);
+}
+
+// ---- KV append: one new row per (request, kv head) into its page ------------------
+template <typename T>
+__global__ void kv_append_kernel(const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ k_cache,
+                                 T* __restrict__ v_cache, const int32_t* __restrict__ page_table,
+                                 const int32_t* __restrict__ positions, int num_kv_heads, int max_pages,
+                                 int page_size, int head_dim, long long k_stride, long long v_stride) {
+  const int b = blockIdx.y;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;  // (kv head, dim)
+  if (idx >= num_kv_heads * head_dim) return;
+  const int kvh = idx / head_dim;
+  const int d = idx % head_dim;
+  const int pos = positions[b];
+  const int page_idx = pos / page_size;
+  if (pos < 0 || page_idx >= max_pages) return;  // no page reserved: drop rather than write out of range
+  const int page = page_table[static_cast<size_t>(b) * max_pages + page_idx];
+  const size_t dst = ((static_cast<size_t>(page) * num_kv_heads + kvh) * page_size + pos % page_size) *
+                         static_cast<size_t>(head_dim) + d;
+  k_cache[dst] = k[static_cast<size_t>(b) * k_stride + idx];
+  v_cache[dst] = v[static_cast<size_t>(b) * v_stride + idx];
+}
+
+// ---- elementwise ------------------------------------------------------------------
+template <typename T, bool SILU_MUL>
+__global__ void binary_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, size_t total) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float x = Elem<T>::ld(a + i);
+  const float y = Elem<T>::ld(b + i);
+  Elem<T>::st(out + i, SILU_MUL ? (x / (1.f + expf(-x))) * y : x + y);
+}
+
+template <typename T>
+__global__ void embedding_gather_kernel(const T* __restrict__ table, const int64_t* __restrict__ ids,
+                                        T* __restrict__ out, int hidden, int vocab) {
+  const int r = blockIdx.x;
+  long long id = ids[r];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // clamp instead of faulting on a bad id
+  const T* src = table + static_cast<size_t>(id) * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) out[static_cast<size_t>(r) * hidden + c] = src[c];
+}
+
+// Row argmax; ties resolve to the lowest index like torch/numpy argmax.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+argmax_rows_kernel(const T* __restrict__ logits, int64_t* __restrict__ out_ids, int vocab) {
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
+  const T* row = logits + static_cast<size_t>(blockIdx.x) * vocab;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int c = threadIdx.x; c < vocab; c += blockDim.x) {
+    const float v = Elem<T>::ld(row + c);
+    if (v > best || (v == best && c < best_i)) { best = v; best_i = c; }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, off);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = best_i; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int nw = blockDim.x >> 5;
+    best = threadIdx.x < nw ? s_val[threadIdx.x] : -INFINITY;
+    best_i = threadIdx.x < nw ? s_idx[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, off);
+      if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (threadIdx.x == 0) out_ids[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
+  }
+}
+
+__global__ void advance_positions_kernel(int32_t* positions, int32_t* seq_lens, int batch) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < batch) {
+    const int32_t len = seq_lens[b];
+    positions[b] = len;
+    seq_lens[b] = len + 1;
+  }
+}
+
+}  // namespace
+}  // namespace cb200
+
+using namespace cb200;
+
+#define CB200_DISPATCH_DTYPE(dtype, CALL)                 \
+  switch (dtype) {                                        \
+    case CACHEIR_B200_F32: { using T = float; CALL; } break;          \
+    case CACHEIR_B200_F16: { using T = __half; CALL; } break;         \
+    case CACHEIR_B200_BF16: { using T = __nv_bfloat16; CALL; } break; \
+    default: return CACHEIR_B200_EINVAL;                  \
+  }
+
+extern "C" int cacheir_b200_rms_norm(const void* x, const void* residual, const void* weight,
+                                     void* sum_out, void* out, int rows, int hidden, float eps,
+                                     int dtype, void* stream) {
+  if (rows <= 0 || hidden <= 0) return 0;
+  if (!x || !weight || !out) return CACHEIR_B200_EINVAL;
+  if (residual && !sum_out) return CACHEIR_B200_EINVAL;
+  cudaStream_t st = as_stream(stream);
+  switch (dtype) {
+    case CACHEIR_B200_F32: return launch_rms_norm<float, 4>(x, residual, weight, sum_out, out, rows, hidden, eps, st);
+    case CACHEIR_B200_F16: return launch_rms_norm<__half, 8>(x, residual, weight, sum_out, out, rows, hidden, eps, st);
+    case CACHEIR_B200_BF16: return launch_rms_norm<__nv_bfloat16, 8>(x, residual, weight, sum_out, out, rows, hidden, eps, st);
+    default: return CACHEIR_B200_EINVAL;
+  }
+}
+
+extern "C" int cacheir_b200_rope_inplace(void* x, const int32_t* positions, int batch_size,
+                                         int num_heads, int head_dim, float theta, int dtype,
+                                         long long x_batch_stride, void* stream) {
+  if (batch_size <= 0 || num_heads <= 0 || head_dim <= 0) return 0;
+  if (!x || !positions || (head_dim % 2) != 0 || batch_size > 65535) return CACHEIR_B200_EINVAL;
+  const long long stride = x_batch_stride > 0 ? x_batch_stride : static_cast<long long>(num_heads) * head_dim;
+  const int pairs = num_heads * (head_dim / 2);
+  const dim3 grid((pairs + 127) / 128, batch_size);
+  CB200_DISPATCH_DTYPE(dtype, (rope_inplace_kernel<T><<<grid, 128, 0, as_stream(stream)>>>(
+                                  static_cast<T*>(x), positions, num_heads, head_dim, theta, stride)));
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_kv_append(const void* k, const void* v, void* k_cache, void* v_cache,
+                                      const int32_t* page_table, const int32_t* positions,
+                                      int batch_size, int num_kv_heads, int max_pages_per_seq,
+                                      int page_size, int head_dim, int dtype, long long k_batch_stride,
+                                      long long v_batch_stride, void* stream) {
+  if (batch_size <= 0 || num_kv_heads <= 0 || head_dim <= 0) return 0;
+  if (!k || !v || !k_cache || !v_cache || !page_table || !positions || max_pages_per_seq <= 0 ||
+      page_size <= 0 || batch_size > 65535)
+    return CACHEIR_B200_EINVAL;
+  const long long dense = static_cast<long long>(num_kv_heads) * head_dim;
+  const long long ks = k_batch_stride > 0 ? k_batch_stride : dense;
+  const long long vs = v_batch_stride > 0 ? v_batch_stride : dense;
+  const dim3 grid((static_cast<int>(dense) + 127) / 128, batch_size);
+  CB200_DISPATCH_DTYPE(dtype, (kv_append_kernel<T><<<grid, 128, 0, as_stream(stream)>>>(
+                                  static_cast<const T*>(k), static_cast<const T*>(v), static_cast<T*>(k_cache),
+                                  static_cast<T*>(v_cache), page_table, positions, num_kv_heads,
+                                  max_pages_per_seq, page_size, head_dim, ks, vs)));
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_silu_mul(const void* gate, const void* up, void* out, size_t total,
+                                     int dtype, void* stream) {
+  if (total == 0) return 0;
+  if (!gate || !up || !out) return CACHEIR_B200_EINVAL;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  CB200_DISPATCH_DTYPE(dtype, (binary_kernel<T, true><<<blocks, 256, 0, as_stream(stream)>>>(
+                                  static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<T*>(out), total)));
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_add(const void* a, const void* b, void* out, size_t total, int dtype,
+                                void* stream) {
+  if (total == 0) return 0;
+  if (!a || !b || !out) return CACHEIR_B200_EINVAL;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  CB200_DISPATCH_DTYPE(dtype, (binary_kernel<T, false><<<blocks, 256, 0, as_stream(stream)>>>(
+                                  static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), total)));
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_embedding_gather(const void* table, const int64_t* ids, void* out,
+                                             int rows, int hidden, int vocab, int dtype, void* stream) {
+  if (rows <= 0 || hidden <= 0) return 0;
+  if (!table || !ids || !out || vocab <= 0) return CACHEIR_B200_EINVAL;
+  CB200_DISPATCH_DTYPE(dtype, (embedding_gather_kernel<T><<<rows, 256, 0, as_stream(stream)>>>(
+                                  static_cast<const T*>(table), ids, static_cast<T*>(out), hidden, vocab)));
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_argmax_rows(const void* logits, int64_t* out_ids, int rows, int vocab,
+                                        int dtype, void* stream) {
+  if (rows <= 0 || vocab <= 0) return 0;
+  if (!logits || !out_ids) return CACHEIR_B200_EINVAL;
+  CB200_DISPATCH_DTYPE(dtype, (argmax_rows_kernel<T><<<rows, 1024, 0, as_stream(stream)>>>(
+                                  static_cast<const T*>(logits), out_ids, vocab)));
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_advance_positions(int32_t* positions, int32_t* seq_lens, int batch_size,
+                                              void* stream) {
+  if (batch_size <= 0) return 0;
+  if (!positions || !seq_lens) return CACHEIR_B200_EINVAL;
+  advance_positions_kernel<<<(batch_size + 127) / 128, 128, 0, as_stream(stream)>>>(positions, seq_lens, batch_size);
+  return launch_status();
+}

@@ -1,0 +1,36 @@
+// Types shared by the paged decode attention kernels and their launchers.
+#pragma once
+
+#include <stdint.h>
+
+namespace cb200 {
+
+constexpr int kMaxAttentionSplits = 64;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// Kernel arguments of one paged decode attention launch. Split partials live in
+// a caller-provided fp32 workspace: ws_ml[b][h][s] = (row max in the log2
+// domain, softmax denominator), ws_acc[b][h][s][d] = unnormalised output.
+struct AttnParams {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  const int32_t* page_table;
+  const int32_t* seq_lens;
+  void* out;
+  float* ws_ml;
+  float* ws_acc;
+  int batch, heads, kv_heads, max_pages, page_size, head_dim;
+  int group;         // heads / kv_heads
+  int head_chunks;   // CTAs along the query heads of one KV head
+  int splits, chunk_tokens;
+  long long q_stride, out_stride;  // elements between consecutive sequences
+  float scale_log2;                // softmax_scale * log2(e)
+};
+
+// Resolve the number of context splits (requested == 0: choose) and the number
+// of tokens each split covers (a multiple of page_size).
+void resolve_attention_splits(int batch, int heads, int kv_heads, int max_pages, int page_size,
+                              int requested, int* splits, int* chunk_tokens);
+
+}  // namespace cb200

@@ -1,0 +1,228 @@
+// Packed int4/int8 dequant-GEMV on the CUDA cores: y[M,N] = x[M,K] . deq(W)[N,K]^T.
+//
+// One warp owns one output row (or a gate/up row pair for the SwiGLU
+// epilogue) and streams it with 128-bit loads: a lane's 16-byte unit holds 16
+// int8 or 32 int4 codes, unpacked in registers (codes become fp32 through the
+// 2^23 mantissa trick, no integer->float conversion instructions), multiplied
+// against up to MT rows of x and reduced with warp shuffles. This kernel is
+// the path for fp32 activations, for dense (unquantized) weights and for shapes
+// the tensor-core kernel does not take.
+#include "common.cuh"
+#include "qgemv_common.cuh"
+
+namespace cb200 {
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+// 8 consecutive x elements as fp32 (k0 is a multiple of 8 and x rows are 16-byte aligned).
+template <typename XT>
+__device__ __forceinline__ void load_x8(const XT* p, float (&out)[8]) {
+  VecIO<XT, 8>::ld(p, out);
+}
+template <>
+__device__ __forceinline__ void load_x8<float>(const float* p, float (&out)[8]) {
+  float a[4], b[4];
+  VecIO<float, 4>::ld(p, a);
+  VecIO<float, 4>::ld(p + 4, b);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { out[i] = a[i]; out[4 + i] = b[i]; }
+}
+
+__device__ __forceinline__ float code_from_byte(uint32_t word, int i) {
+  // byte i of `word` placed in the mantissa of 2^23: exact integer -> fp32.
+  return __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7540u + i)) - 8388608.f;
+}
+__device__ __forceinline__ float code_from_nibble(uint32_t word, int i) {
+  return __uint_as_float(((word >> (4 * i)) & 0xFu) | 0x4B000000u) - 8388608.f;
+}
+
+template <typename XT>
+__device__ __forceinline__ float scale_at(const void* scales, int scale_dtype, size_t idx) {
+  return scale_dtype == CACHEIR_B200_F16 ? __half2float(static_cast<const __half*>(scales)[idx])
+                                         : static_cast<const float*>(scales)[idx];
+}
+
+// BITS: 8, 4 or 0 (dense weights of type XT).
+template <typename XT, int BITS, int MT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+qgemv_cuda_core_kernel(const QGemvParams p) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_out = blockIdx.x * kWarpsPerBlock + warp;
+  const int n_out_total = p.epilogue == CACHEIR_B200_EPI_SWIGLU ? p.N / 2 : p.N;
+  if (n_out >= n_out_total) return;
+  const int m0 = blockIdx.y * MT;
+  const int K = p.K;
+  const XT* x = static_cast<const XT*>(p.x);
+  const int halves = p.epilogue == CACHEIR_B200_EPI_SWIGLU ? 2 : 1;
+  // elements per lane and iteration: a 16-byte unit of codes, or 8 dense weights
+  constexpr int EPU = BITS == 8 ? 16 : (BITS == 4 ? 32 : 8);
+  const int k_main = p.vector_ok ? (K / EPU) * EPU : 0;
+  const size_t row_bytes = BITS == 8 ? static_cast<size_t>(K)
+                         : BITS == 4 ? static_cast<size_t>((K + 1) / 2)
+                                     : static_cast<size_t>(K) * sizeof(XT);
+  float result[2][MT];
+
+  for (int half = 0; half < halves; ++half) {
+    const int n = n_out + half * (p.N / 2);
+    const uint8_t* wrow = static_cast<const uint8_t*>(p.packed) + static_cast<size_t>(n) * row_bytes;
+    float zp = 0.f;
+    if (BITS != 0) {
+      zp = (p.group_size == 0 && p.zero_points) ? p.zero_points[n] : static_cast<float>(1 << (BITS - 1));
+    }
+    const int groups_per_row = p.group_size > 0 ? K / p.group_size : 1;
+    float acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+
+    for (int k0 = lane * EPU; k0 < k_main; k0 += 32 * EPU) {
+      uint32_t words[4] = {0u, 0u, 0u, 0u};
+      if (BITS != 0) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(wrow + (BITS == 8 ? k0 : k0 / 2));
+        words[0] = raw.x; words[1] = raw.y; words[2] = raw.z; words[3] = raw.w;
+      }
+      float part[MT];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) part[m] = 0.f;
+#pragma unroll
+      for (int c = 0; c < EPU / 8; ++c) {  // 8 weights at a time
+        float w8[8];
+        if (BITS == 8) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w8[i] = code_from_byte(words[c * 2 + i / 4], i % 4) - zp;
+        } else if (BITS == 4) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w8[i] = code_from_nibble(words[c], i) - zp;
+        } else {
+          load_x8<XT>(reinterpret_cast<const XT*>(wrow) + k0 + c * 8, w8);
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          if (m0 + m < p.M) {
+            float x8[8];
+            load_x8<XT>(x + static_cast<size_t>(m0 + m) * p.x_stride + k0 + c * 8, x8);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) part[m] = fmaf(x8[i], w8[i], part[m]);
+          }
+        }
+      }
+      const float gs = p.group_size > 0
+                           ? scale_at<XT>(p.scales, p.scale_dtype, static_cast<size_t>(n) * groups_per_row + k0 / p.group_size)
+                           : 1.f;
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[m] = fmaf(part[m], gs, acc[m]);
+    }
+    // scalar remainder (and the whole row when 128-bit access is not possible)
+    for (int k = k_main + lane; k < K; k += 32) {
+      float w;
+      if (BITS == 8) {
+        w = static_cast<float>(wrow[k]) - zp;
+      } else if (BITS == 4) {
+        w = static_cast<float>((wrow[k >> 1] >> ((k & 1) * 4)) & 0xF) - zp;
+      } else {
+        w = Elem<XT>::ld(reinterpret_cast<const XT*>(wrow) + k);
+      }
+      if (p.group_size > 0)
+        w *= scale_at<XT>(p.scales, p.scale_dtype, static_cast<size_t>(n) * groups_per_row + k / p.group_size);
+#pragma unroll
+      for (int m = 0; m < MT; ++m)
+        if (m0 + m < p.M) acc[m] = fmaf(Elem<XT>::ld(x + static_cast<size_t>(m0 + m) * p.x_stride + k), w, acc[m]);
+    }
+    const float row_scale = (BITS != 0 && p.group_size == 0) ? scale_at<XT>(p.scales, p.scale_dtype, n) : 1.f;
+#pragma unroll
+    for (int m = 0; m < MT; ++m) result[half][m] = warp_sum(acc[m]) * row_scale;
+  }
+
+  if (lane == 0) {
+    XT* y = static_cast<XT*>(p.y);
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      if (m0 + m >= p.M) continue;
+      const size_t o = static_cast<size_t>(m0 + m) * n_out_total + n_out;
+      float v = result[0][m];
+      if (p.epilogue == CACHEIR_B200_EPI_SWIGLU) {
+        v = (v / (1.f + __expf(-v))) * result[1][m];
+      } else if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
+        v += Elem<XT>::ld(static_cast<const XT*>(p.residual) + o);
+      }
+      Elem<XT>::st(y + o, v);
+    }
+  }
+}
+
+template <typename XT, int BITS>
+int launch_mt(const QGemvParams& p, cudaStream_t stream) {
+  const int n_out_total = p.epilogue == CACHEIR_B200_EPI_SWIGLU ? p.N / 2 : p.N;
+  const int mt = p.M >= 8 ? 8 : (p.M > 2 ? 4 : p.M);
+  const dim3 grid((n_out_total + kWarpsPerBlock - 1) / kWarpsPerBlock, (p.M + mt - 1) / mt);
+  if (grid.y > 65535) return CACHEIR_B200_ELIMIT;
+  switch (mt) {
+    case 8: qgemv_cuda_core_kernel<XT, BITS, 8><<<grid, kWarpsPerBlock * 32, 0, stream>>>(p); break;
+    case 4: qgemv_cuda_core_kernel<XT, BITS, 4><<<grid, kWarpsPerBlock * 32, 0, stream>>>(p); break;
+    case 2: qgemv_cuda_core_kernel<XT, BITS, 2><<<grid, kWarpsPerBlock * 32, 0, stream>>>(p); break;
+    default: qgemv_cuda_core_kernel<XT, BITS, 1><<<grid, kWarpsPerBlock * 32, 0, stream>>>(p); break;
+  }
+  return launch_status();
+}
+
+template <typename XT>
+int launch_bits(const QGemvParams& p, cudaStream_t stream) {
+  switch (p.bits) {
+    case 8: return launch_mt<XT, 8>(p, stream);
+    case 4: return launch_mt<XT, 4>(p, stream);
+    default: return launch_mt<XT, 0>(p, stream);
+  }
+}
+
+}  // namespace
+
+int launch_qgemv_cuda_core(const QGemvParams& p, cudaStream_t stream) {
+  switch (p.x_dtype) {
+    case CACHEIR_B200_F32: return launch_bits<float>(p, stream);
+    case CACHEIR_B200_F16: return launch_bits<__half>(p, stream);
+    default: return launch_bits<__nv_bfloat16>(p, stream);
+  }
+}
+
+}  // namespace cb200
+
+using namespace cb200;
+
+extern "C" int cacheir_b200_qgemv(const void* x, const void* packed, const void* scales,
+                                  const float* zero_points, const void* residual, void* y, int M,
+                                  int N, int K, int bits, int group_size, int x_dtype,
+                                  int scale_dtype, long long x_stride, int epilogue, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (!x || !packed || !y) return CACHEIR_B200_EINVAL;
+  const int esize = dtype_size(x_dtype);
+  if (esize == 0) return CACHEIR_B200_EINVAL;
+  if (bits != 0 && bits != 4 && bits != 8) return CACHEIR_B200_EINVAL;
+  if (epilogue < CACHEIR_B200_EPI_NONE || epilogue > CACHEIR_B200_EPI_SWIGLU) return CACHEIR_B200_EINVAL;
+  if (epilogue == CACHEIR_B200_EPI_SWIGLU && (N % 2) != 0) return CACHEIR_B200_EINVAL;
+  if (epilogue == CACHEIR_B200_EPI_RESIDUAL && !residual) return CACHEIR_B200_EINVAL;
+  if (bits != 0) {
+    if (!scales) return CACHEIR_B200_EINVAL;
+    if (scale_dtype != CACHEIR_B200_F32 && scale_dtype != CACHEIR_B200_F16) return CACHEIR_B200_EINVAL;
+    if (group_size < 0) return CACHEIR_B200_EINVAL;
+    if (group_size > 0 && (group_size % 32 != 0 || K % group_size != 0 || zero_points != nullptr))
+      return CACHEIR_B200_EINVAL;
+  } else if (group_size != 0) {
+    return CACHEIR_B200_EINVAL;
+  }
+  QGemvParams p{};
+  p.x = x; p.packed = packed; p.scales = scales; p.zero_points = zero_points;
+  p.residual = residual; p.y = y;
+  p.M = M; p.N = N; p.K = K; p.bits = bits; p.group_size = group_size;
+  p.x_dtype = x_dtype; p.scale_dtype = scale_dtype;
+  p.x_stride = x_stride > 0 ? x_stride : K;
+  p.epilogue = epilogue;
+  const size_t row_bytes = bits == 8 ? static_cast<size_t>(K)
+                         : bits == 4 ? static_cast<size_t>((K + 1) / 2)
+                                     : static_cast<size_t>(K) * esize;
+  p.vector_ok = aligned_to(packed, 16) && row_bytes % 16 == 0 && aligned_to(x, 16) &&
+                (p.x_stride * esize) % 16 == 0;
+  cudaStream_t st = as_stream(stream);
+  if (qgemm_tc_supported(p)) return launch_qgemm_tc(p, st);
+  return launch_qgemv_cuda_core(p, st);
+}

@@ -1,0 +1,206 @@
+/*
+ * cacheir_b200.h -- C ABI of libcacheir_b200.so: the batched decode step of
+ * CacheIR (paged decode attention + packed int4/int8 dequant-GEMV and the
+ * glue ops between them) as hand-written CUDA for sm_100a.
+ *
+ * Conventions shared by every entry point
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer owned
+ *     by the caller for the duration of the launch, `stream` is a
+ *     cudaStream_t passed as void*;
+ *   - nothing here allocates, frees or synchronises;
+ *   - return value: 0 on success, a positive cudaError_t value when the CUDA
+ *     runtime reported one, or a negative CACHEIR_B200_E* validation code.
+ *     Non-positive extents return 0 without launching, exactly like the
+ *     reference launchers (cpp/src/cacheir_cuda_kernels.cu:370-372);
+ *   - `dtype` arguments use the CACHEIR_B200_F32/F16/BF16 codes below.
+ *
+ * Each declaration cites the interface of the reference project
+ * (AhanBhatt/CacheIR, paths relative to its root) that it stands in for.
+ */
+#ifndef CACHEIR_B200_H_
+#define CACHEIR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+#define CACHEIR_B200_F32 0
+#define CACHEIR_B200_F16 1
+#define CACHEIR_B200_BF16 2
+
+/* validation errors (negative so they never collide with cudaError_t) */
+#define CACHEIR_B200_EINVAL (-1)      /* bad extent, dtype or flag            */
+#define CACHEIR_B200_EALIGN (-2)      /* pointer/stride alignment unusable    */
+#define CACHEIR_B200_EWORKSPACE (-3)  /* workspace missing or too small       */
+#define CACHEIR_B200_EUNSUPPORTED (-4)/* shape outside what the kernels cover */
+#define CACHEIR_B200_ELIMIT (-5)      /* beyond a documented fixed maximum    */
+
+/* qgemv epilogues */
+#define CACHEIR_B200_EPI_NONE 0       /* y = x W^T                            */
+#define CACHEIR_B200_EPI_RESIDUAL 1   /* y = residual + x W^T                 */
+#define CACHEIR_B200_EPI_SWIGLU 2     /* W = [gate; up], y = silu(xWg^T)*xWu^T */
+
+/* Library/ABI version (major*100 + minor) and a human readable build line. */
+int cacheir_b200_version(void);
+const char* cacheir_b200_build_info(void);
+/* Text for any return code of this library (never NULL). */
+const char* cacheir_b200_error_string(int code);
+
+/* ------------------------------------------------------------------------
+ * Paged decode attention over a shared page pool.
+ *
+ * Replaces: Triton `paged_attention_decode_batch_kernel`
+ *   (cacheir/backends/triton_kernels.py:174-217, launched from
+ *   cacheir/runtime/cuda.py:1238-1251 and :1166-1179) and its CUDA twin
+ *   `cacheir_cuda_paged_attention_decode_batch`
+ *   (cpp/src/cacheir_cuda_kernels.cu:357-411). Same argument order and
+ *   meaning; the additions are dtype, q/out row strides, softmax_scale,
+ *   and the split-K workspace.
+ *
+ *   out[b,h,:] = sum_t softmax_t(scale * q[b,h,:].K[b,t,kvh(h),:]) V[b,t,kvh(h),:]
+ *   for t < seq_lens[b], kvh(h) = h / (num_heads/num_kv_heads); row t of
+ *   sequence b lives at pool element
+ *   ((page_table[b,t/page_size]*num_kv_heads + kvh)*page_size + t%page_size)*head_dim
+ *   (triton_kernels.py:206). Page-table entries may alias between sequences
+ *   (prefix-shared pages); entries past ceil(seq_len/page_size) are never read.
+ *   A sequence with seq_lens[b] <= 0 produces zeros.
+ *
+ *   q, out:      [batch, num_heads, head_dim], row b at q + b*q_batch_stride
+ *                elements (0 = dense, i.e. num_heads*head_dim)
+ *   k/v_cache:   [slots, num_kv_heads, page_size, head_dim], same dtype as q
+ *   page_table:  int32 [batch, max_pages_per_seq]; seq_lens: int32 [batch]
+ *   softmax_scale: <= 0 selects rsqrt(head_dim) (the reference's constant)
+ *   num_splits:  context splits per sequence (flash-decoding); 0 = choose.
+ *                Partials are merged in split order, so the result is
+ *                bit-identical from run to run for a given num_splits.
+ *   workspace:   fp32 scratch of at least
+ *                cacheir_b200_paged_attention_workspace_bytes(...) bytes;
+ *                may be NULL only when that size is 0 (num_splits == 1).
+ */
+size_t cacheir_b200_paged_attention_workspace_bytes(int batch_size, int num_heads,
+                                                    int head_dim, int num_splits);
+/* The split count that num_splits == 0 resolves to for these extents. */
+int cacheir_b200_paged_attention_auto_splits(int batch_size, int num_heads,
+                                             int num_kv_heads, int max_pages_per_seq,
+                                             int page_size, int head_dim);
+int cacheir_b200_paged_attention_decode_batch(
+    const void* q, const void* k_cache, const void* v_cache,
+    const int32_t* page_table, const int32_t* seq_lens, void* out,
+    int batch_size, int num_heads, int num_kv_heads, int max_pages_per_seq,
+    int page_size, int head_dim, int dtype, long long q_batch_stride,
+    long long out_batch_stride, float softmax_scale, int num_splits,
+    void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Packed int4/int8 dequant-GEMV / small-M GEMM:  y[M,N] = x[M,K] . deq(W)[N,K]^T
+ *
+ * Replaces: `CudaRuntime._quantized_matmul` + `_dequantize_cuda_weight`
+ *   (cacheir/runtime/cuda.py:932-954; CPU twin cacheir/runtime/cpu.py:306-312),
+ *   which materialise the dense weight on every call, and the fused ops built
+ *   on it (cuda.py:812-820 QKV, :867-871 SwiGLU, :795-796 O/Down/lm_head).
+ *   Pack format is the reference's (cacheir/quantization.py:96-139):
+ *     bits 8: packed[n,k] = code;  bits 4: packed[n,j] = code[2j] | code[2j+1]<<4
+ *     (row stride ceil(K/2) bytes, odd K zero padded);
+ *     per-row affine (group_size 0): w = (code - zero_points[n]) * scales[n];
+ *     zero_points are fp32 as uploaded by CudaWeightStore (cuda.py:83), NULL
+ *     means the midpoint 2^(bits-1);
+ *     group-wise symmetric (group_size > 0, a multiple of 32 dividing K):
+ *     w = (code - 2^(bits-1)) * scales[n, k/group_size], zero_points NULL.
+ *   bits 0 selects dense weights W[N,K] of x's dtype (`_matmul`, cuda.py:920-930).
+ *
+ *   x: [M,K] row stride x_stride elements (0 = K); y: [M,N_out] dense,
+ *   N_out = N, or N/2 for EPI_SWIGLU where rows [0,N/2) are gate and
+ *   [N/2,N) are up; residual: [M,N_out] dense, EPI_RESIDUAL only.
+ *   x, y and residual share x_dtype; scales are fp32 or fp16 (scale_dtype).
+ */
+int cacheir_b200_qgemv(const void* x, const void* packed, const void* scales,
+                       const float* zero_points, const void* residual, void* y,
+                       int M, int N, int K, int bits, int group_size,
+                       int x_dtype, int scale_dtype, long long x_stride,
+                       int epilogue, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Quantization loader on the device.
+ *
+ * Replaces: `_asymmetric_pack` / `_pack_int4` (cacheir/quantization.py:96-130)
+ *   as called by `WeightStore._pack_value` (cacheir/runtime/cpu.py:47-58) and
+ *   `dequantize_packed_weight` (quantization.py:74-84). Results are bit-exact
+ *   with the NumPy code: scale = max((max-min)/qmax, 1e-8) in fp32,
+ *   zero = rint(0 - min/scale) (not clipped), code = clip(rint((double)(w/scale)
+ *   + zero), 0, qmax).
+ *   weight: fp32 [N,K]; packed: uint8 [N,K] or [N,ceil(K/2)]; scales: fp32 [N];
+ *   zero_points_i32: int32 [N] (may be NULL); zero_points_f32: fp32 [N] (may be
+ *   NULL) -- the form the GEMV consumes.
+ */
+int cacheir_b200_pack_rows(const float* weight, uint8_t* packed, float* scales,
+                           int32_t* zero_points_i32, float* zero_points_f32,
+                           int N, int K, int bits, void* stream);
+/* out[n,k] = (code - zero_points[n]) * scales[n]   (fp32 math, cast to out_dtype) */
+int cacheir_b200_dequantize_rows(const uint8_t* packed, const float* scales,
+                                 const float* zero_points, void* out, int N, int K,
+                                 int bits, int out_dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Glue ops of the decode graph (one row per request).
+ */
+
+/* Replaces `cacheir_cuda_rms_norm` (cpp/src/cacheir_cuda_kernels.cu:273-284),
+ * Triton `rms_norm_kernel` (triton_kernels.py:40-49), `_rms_norm`
+ * (cuda.py:889-895): out = x * rsqrt(mean(x^2)+eps) * weight, statistics in
+ * fp32. x/out/weight share `dtype`. When `residual` is non-NULL the row that
+ * is normalised is x+residual and that sum is also stored to `sum_out`
+ * (the graph's `add` node, cuda.py:851-852, fused with the following norm). */
+int cacheir_b200_rms_norm(const void* x, const void* residual, const void* weight,
+                          void* sum_out, void* out, int rows, int hidden, float eps,
+                          int dtype, void* stream);
+
+/* Replaces `_rope_with_offsets` / `_rope_offsets_one` (cuda.py:1072-1102; CPU
+ * `_rope_one`, cpu.py:324-340): interleaved even/odd pair rotation in place,
+ * angle = positions[b] * theta^(-2i/head_dim). x: [batch, num_heads, head_dim]
+ * with row stride x_batch_stride elements (0 = dense). */
+int cacheir_b200_rope_inplace(void* x, const int32_t* positions, int batch_size,
+                              int num_heads, int head_dim, float theta, int dtype,
+                              long long x_batch_stride, void* stream);
+
+/* Replaces `TorchPagedKVCache.append` + `TorchKVPageAllocator.write_page`
+ * (cuda.py:322-334, :172-199) for one new token per request: writes
+ * k[b,kvh,:], v[b,kvh,:] to pool row
+ * ((page_table[b,pos/page]*num_kv_heads + kvh)*page + pos%page) with
+ * pos = positions[b]. No contiguous per-session copy is kept. */
+int cacheir_b200_kv_append(const void* k, const void* v, void* k_cache, void* v_cache,
+                           const int32_t* page_table, const int32_t* positions,
+                           int batch_size, int num_kv_heads, int max_pages_per_seq,
+                           int page_size, int head_dim, int dtype,
+                           long long k_batch_stride, long long v_batch_stride,
+                           void* stream);
+
+/* Replaces `cacheir_cuda_fused_swiglu` (cacheir_cuda_kernels.cu:286-295),
+ * Triton `silu_mul_kernel` (triton_kernels.py:51-59), `_silu_mul`
+ * (cuda.py:1025-1030): out = gate/(1+exp(-gate)) * up. */
+int cacheir_b200_silu_mul(const void* gate, const void* up, void* out, size_t total,
+                          int dtype, void* stream);
+/* The graph's `add` node (cuda.py:851-852). */
+int cacheir_b200_add(const void* a, const void* b, void* out, size_t total, int dtype,
+                     void* stream);
+/* The graph's `token_embedding` node (cuda.py:789): out[r,:] = table[ids[r],:]. */
+int cacheir_b200_embedding_gather(const void* table, const int64_t* ids, void* out,
+                                  int rows, int hidden, int vocab, int dtype,
+                                  void* stream);
+/* Replaces `_argmax_tokens` (cacheir/runtime/scheduler.py:535-543) for
+ * device-side greedy feedback: out_ids[r] = first index of the row maximum. */
+int cacheir_b200_argmax_rows(const void* logits, int64_t* out_ids, int rows, int vocab,
+                             int dtype, void* stream);
+/* Per-step request bookkeeping kept on the device (no counterpart kernel in
+ * the reference, which recomputes `_position_offset` on the host each step,
+ * cuda.py:1064-1067): positions[b] = seq_lens[b]; seq_lens[b] += 1. */
+int cacheir_b200_advance_positions(int32_t* positions, int32_t* seq_lens, int batch_size,
+                                   void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CACHEIR_B200_H_ */
