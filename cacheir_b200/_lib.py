@@ -1,0 +1,73 @@
+"""ctypes binding of libcacheir_b200.so (the C ABI declared in include/cacheir_b200.h).
+
+There is no fallback: if the shared library is missing the import of any
+compute entry point raises, telling the user to build it.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libcacheir_b200.so"
+
+# name -> (restype, argtypes); mirrors include/cacheir_b200.h one to one
+SIGNATURES: dict[str, tuple[object, list[object]]] = {
+    "cacheir_b200_version": (c_int, []),
+    "cacheir_b200_build_info": (c_char_p, []),
+    "cacheir_b200_error_string": (c_char_p, [c_int]),
+    "cacheir_b200_paged_attention_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "cacheir_b200_paged_attention_auto_splits": (c_int, [c_int] * 6),
+    "cacheir_b200_paged_attention_decode_batch": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # q k v page_table seq_lens out
+         c_int, c_int, c_int, c_int, c_int, c_int, c_int,              # batch heads kv_heads max_pages page D dtype
+         c_longlong, c_longlong, c_float, c_int,                       # q_stride out_stride scale num_splits
+         c_void_p, c_size_t, c_void_p]),                               # workspace bytes stream
+    "cacheir_b200_qgemv": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # x packed scales zero_points residual y
+         c_int, c_int, c_int, c_int, c_int, c_int, c_int,              # M N K bits group x_dtype scale_dtype
+         c_longlong, c_int, c_void_p]),                                # x_stride epilogue stream
+    "cacheir_b200_pack_rows": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_void_p]),
+    "cacheir_b200_dequantize_rows": (c_int, [c_void_p] * 4 + [c_int, c_int, c_int, c_int, c_void_p]),
+    "cacheir_b200_rms_norm": (c_int, [c_void_p] * 5 + [c_int, c_int, c_float, c_int, c_void_p]),
+    "cacheir_b200_rope_inplace": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p]),
+    "cacheir_b200_kv_append": (
+        c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p]),
+    "cacheir_b200_silu_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "cacheir_b200_add": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "cacheir_b200_embedding_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "cacheir_b200_argmax_rows": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "cacheir_b200_advance_positions": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
+}
+
+_LIB: ctypes.CDLL | None = None
+
+
+class CacheIRB200Error(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once and attach the prototypes. Raises if it is not built."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not LIB_PATH.exists():
+        raise CacheIRB200Error(
+            f"{LIB_PATH} is missing: build the CUDA library first (python -m cacheir_b200.build). "
+            "cacheir_b200 has no CPU or PyTorch fallback.")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means header and library disagree
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _LIB = lib
+    return lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        text = load().cacheir_b200_error_string(int(code)).decode("utf-8", "replace")
+        raise CacheIRB200Error(f"{what} failed with status {code}: {text}")

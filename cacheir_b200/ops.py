@@ -1,0 +1,272 @@
+"""Torch-tensor wrappers over the C ABI (include/cacheir_b200.h).
+
+PyTorch supplies device memory and the current stream, nothing else: every
+function below validates its arguments, passes raw device pointers to
+libcacheir_b200.so on `torch.cuda.current_stream()`, and raises
+`CacheIRB200Error` on a non-zero status. Output tensors can be passed in (no
+allocation, CUDA-graph friendly) or are allocated here.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+from ._lib import CacheIRB200Error, check
+
+F32, F16, BF16 = 0, 1, 2
+EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+
+_DTYPE_CODES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODES[dtype]
+    except KeyError:
+        raise TypeError(f"cacheir_b200 supports float32/float16/bfloat16 activations, got {dtype}") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _require_cuda(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise CacheIRB200Error("cacheir_b200 kernels run on CUDA tensors only; there is no CPU fallback")
+
+
+def _rows_dense(t: torch.Tensor, what: str) -> None:
+    if t.stride(-1) != 1:
+        raise ValueError(f"{what}: innermost dimension must be contiguous")
+
+
+# ------------------------------------------------------------------------------
+def attention_auto_splits(batch: int, heads: int, kv_heads: int, max_pages: int, page_size: int, head_dim: int) -> int:
+    return int(_lib.load().cacheir_b200_paged_attention_auto_splits(batch, heads, kv_heads, max_pages, page_size, head_dim))
+
+
+def attention_workspace_bytes(batch: int, heads: int, head_dim: int, num_splits: int) -> int:
+    return int(_lib.load().cacheir_b200_paged_attention_workspace_bytes(batch, heads, head_dim, num_splits))
+
+
+def paged_attention_decode_batch(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                                 page_table: torch.Tensor, seq_lens: torch.Tensor, *,
+                                 out: torch.Tensor | None = None, softmax_scale: float | None = None,
+                                 num_splits: int = 0, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """out[b,h,:] = softmax(scale * q[b,h].K_b^T) V_b over the pages of sequence b.
+
+    q: [B, H, D] (rows may be strided views of a wider buffer); k_cache/v_cache:
+    [slots, KVH, page, D] contiguous, same dtype as q; page_table: int32
+    [B, max_pages]; seq_lens: int32 [B]. Same contract as the reference's
+    Triton launch (cacheir/runtime/cuda.py:1238-1251)."""
+    _require_cuda(q, k_cache, v_cache, page_table, seq_lens, out, workspace)
+    if q.dim() != 3 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape:
+        raise ValueError("expected q [B,H,D] and k_cache/v_cache [slots,KVH,page,D]")
+    batch, heads, head_dim = (int(s) for s in q.shape)
+    _, kv_heads, page_size, pool_dim = (int(s) for s in k_cache.shape)
+    if pool_dim != head_dim or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise ValueError("q and the KV pool must share head_dim and dtype")
+    if page_table.dtype != torch.int32 or seq_lens.dtype != torch.int32:
+        raise TypeError("page_table and seq_lens must be int32")
+    if page_table.dim() != 2 or page_table.shape[0] != batch or seq_lens.numel() != batch:
+        raise ValueError("page_table must be [B, max_pages] and seq_lens [B]")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous() and page_table.is_contiguous() and seq_lens.is_contiguous()):
+        raise ValueError("KV pool, page_table and seq_lens must be contiguous")
+    if q.stride(2) != 1 or q.stride(1) != head_dim:
+        raise ValueError("q heads must be dense: only the batch stride may differ from H*D")
+    if out is None:
+        out = torch.empty((batch, heads, head_dim), device=q.device, dtype=q.dtype)
+    elif out.shape != q.shape or out.dtype != q.dtype or out.stride(2) != 1 or out.stride(1) != head_dim:
+        raise ValueError("out must match q's shape/dtype with dense heads")
+    max_pages = int(page_table.shape[1])
+    lib = _lib.load()
+    splits = num_splits if num_splits > 0 else attention_auto_splits(batch, heads, kv_heads, max_pages, page_size, head_dim)
+    need = attention_workspace_bytes(batch, heads, head_dim, splits)
+    if need > 0 and workspace is None:
+        workspace = torch.empty((need + 3) // 4, device=q.device, dtype=torch.float32)
+    ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    check(lib.cacheir_b200_paged_attention_decode_batch(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(),
+        out.data_ptr(), batch, heads, kv_heads, max_pages, page_size, head_dim, dtype_code(q.dtype),
+        q.stride(0), out.stride(0), float(softmax_scale or 0.0), int(splits), _ptr(workspace), ws_bytes, _stream()),
+        "paged_attention_decode_batch")
+    return out
+
+
+def qgemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor | None, zero_points: torch.Tensor | None, *,
+          bits: int, n: int, k: int, group_size: int = 0, epilogue: int = EPI_NONE,
+          residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y[M, N_out] = x[M, K] . deq(W)[N, K]^T with the reference's pack format
+    (bits 8/4; bits 0 = dense weights of x's dtype). x: [..., K] with dense rows."""
+    _require_cuda(x, packed, scales, zero_points, residual, out)
+    if x.shape[-1] != k:
+        raise ValueError(f"x has {x.shape[-1]} input features, weight expects {k}")
+    _rows_dense(x, "x")
+    x2 = x.reshape(-1, k) if x.is_contiguous() else x
+    if x2.dim() != 2:
+        raise ValueError("non-contiguous x must be 2-D [M, K] with a row stride")
+    m = int(x2.shape[0])
+    n_out = n // 2 if epilogue == EPI_SWIGLU else n
+    if bits == 0:
+        if packed.dtype != x.dtype or tuple(packed.shape) != (n, k) or not packed.is_contiguous():
+            raise ValueError("dense weights must be a contiguous [N, K] tensor of x's dtype")
+    else:
+        row_bytes = k if bits == 8 else (k + 1) // 2
+        if packed.dtype != torch.uint8 or tuple(packed.shape) != (n, row_bytes) or not packed.is_contiguous():
+            raise ValueError(f"packed int{bits} weights must be contiguous uint8 [{n}, {row_bytes}]")
+        if scales is None or scales.dtype not in (torch.float32, torch.float16) or not scales.is_contiguous():
+            raise ValueError("scales must be a contiguous float32 or float16 tensor")
+        want = n * (k // group_size) if group_size else n
+        if scales.numel() != want:
+            raise ValueError(f"scales has {scales.numel()} entries, expected {want}")
+        if zero_points is not None and (zero_points.dtype != torch.float32 or zero_points.numel() != n):
+            raise ValueError("zero_points must be float32 [N] (the reference's device format)")
+    if out is None:
+        out = torch.empty((m, n_out), device=x.device, dtype=x.dtype)
+    elif out.numel() != m * n_out or out.dtype != x.dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [M, N_out] tensor of x's dtype")
+    if residual is not None and (residual.numel() != m * n_out or residual.dtype != x.dtype or not residual.is_contiguous()):
+        raise ValueError("residual must be a contiguous [M, N_out] tensor of x's dtype")
+    check(_lib.load().cacheir_b200_qgemv(
+        x2.data_ptr(), packed.data_ptr(), _ptr(scales), _ptr(zero_points), _ptr(residual), out.data_ptr(),
+        m, n, k, bits, group_size, dtype_code(x.dtype),
+        F16 if (scales is not None and scales.dtype == torch.float16) else F32,
+        x2.stride(0), epilogue, _stream()), "qgemv")
+    return out
+
+
+def pack_rows(weight: torch.Tensor, bits: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Device quantization loader: fp32 [N,K] -> (packed uint8, scales f32, zero_points i32, zero_points f32),
+    bit-exact with the reference's NumPy packer (cacheir/quantization.py:96-130)."""
+    _require_cuda(weight)
+    if weight.dim() != 2 or weight.dtype != torch.float32 or not weight.is_contiguous():
+        raise ValueError("pack_rows expects a contiguous float32 [N, K] CUDA tensor")
+    n, k = (int(s) for s in weight.shape)
+    row_bytes = k if bits == 8 else (k + 1) // 2
+    packed = torch.empty((n, row_bytes), device=weight.device, dtype=torch.uint8)
+    scales = torch.empty((n,), device=weight.device, dtype=torch.float32)
+    zp_i = torch.empty((n,), device=weight.device, dtype=torch.int32)
+    zp_f = torch.empty((n,), device=weight.device, dtype=torch.float32)
+    check(_lib.load().cacheir_b200_pack_rows(weight.data_ptr(), packed.data_ptr(), scales.data_ptr(), zp_i.data_ptr(),
+                                             zp_f.data_ptr(), n, k, bits, _stream()), "pack_rows")
+    return packed, scales, zp_i, zp_f
+
+
+def dequantize_rows(packed: torch.Tensor, scales: torch.Tensor, zero_points: torch.Tensor | None, *, bits: int,
+                    k: int, dtype: torch.dtype) -> torch.Tensor:
+    _require_cuda(packed, scales, zero_points)
+    n = int(packed.shape[0])
+    out = torch.empty((n, k), device=packed.device, dtype=dtype)
+    check(_lib.load().cacheir_b200_dequantize_rows(packed.data_ptr(), scales.data_ptr(), _ptr(zero_points),
+                                                   out.data_ptr(), n, k, bits, dtype_code(dtype), _stream()),
+          "dequantize_rows")
+    return out
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, residual: torch.Tensor | None = None,
+             sum_out: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = rmsnorm(x [+ residual]) * weight; with a residual the rounded sum is stored to sum_out."""
+    _require_cuda(x, weight, residual, sum_out, out)
+    hidden = int(x.shape[-1])
+    if not x.is_contiguous() or weight.numel() != hidden or weight.dtype != x.dtype:
+        raise ValueError("rms_norm expects contiguous x and a weight of x's dtype and width")
+    rows = x.numel() // hidden
+    if out is None:
+        out = torch.empty_like(x)
+    if residual is not None:
+        if residual.shape != x.shape or not residual.is_contiguous():
+            raise ValueError("residual must match x")
+        if sum_out is None:
+            sum_out = torch.empty_like(x)
+    check(_lib.load().cacheir_b200_rms_norm(x.data_ptr(), _ptr(residual), weight.data_ptr(), _ptr(sum_out),
+                                            out.data_ptr(), rows, hidden, float(eps), dtype_code(x.dtype), _stream()),
+          "rms_norm")
+    return out
+
+
+def rope_inplace(x: torch.Tensor, positions: torch.Tensor, *, num_heads: int, head_dim: int, theta: float) -> torch.Tensor:
+    """Interleaved-pair RoPE applied in place to x [B, num_heads*head_dim] (row-strided views allowed)."""
+    _require_cuda(x, positions)
+    if positions.dtype != torch.int32 or x.dim() != 2 or x.stride(1) != 1 or x.shape[1] != num_heads * head_dim:
+        raise ValueError("rope_inplace expects x [B, H*D] with dense rows and int32 positions")
+    check(_lib.load().cacheir_b200_rope_inplace(x.data_ptr(), positions.data_ptr(), int(x.shape[0]), num_heads,
+                                                head_dim, float(theta), dtype_code(x.dtype), x.stride(0), _stream()),
+          "rope_inplace")
+    return x
+
+
+def kv_append(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              page_table: torch.Tensor, positions: torch.Tensor) -> None:
+    """Write one new K/V row per request (k, v: [B, KVH*D], row-strided views allowed) into the page pool."""
+    _require_cuda(k, v, k_cache, v_cache, page_table, positions)
+    _, kv_heads, page_size, head_dim = (int(s) for s in k_cache.shape)
+    batch = int(k.shape[0])
+    if k.shape != v.shape or k.shape[1] != kv_heads * head_dim or k.stride(1) != 1 or v.stride(1) != 1:
+        raise ValueError("k and v must be [B, KVH*D] with dense rows")
+    if k.dtype != k_cache.dtype or page_table.dtype != torch.int32 or positions.dtype != torch.int32:
+        raise TypeError("dtype mismatch in kv_append")
+    check(_lib.load().cacheir_b200_kv_append(k.data_ptr(), v.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                             page_table.data_ptr(), positions.data_ptr(), batch, kv_heads,
+                                             int(page_table.shape[1]), page_size, head_dim, dtype_code(k.dtype),
+                                             k.stride(0), v.stride(0), _stream()), "kv_append")
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _require_cuda(gate, up, out)
+    if gate.shape != up.shape or not gate.is_contiguous() or not up.is_contiguous():
+        raise ValueError("silu_mul expects contiguous tensors of equal shape")
+    out = torch.empty_like(gate) if out is None else out
+    check(_lib.load().cacheir_b200_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(),
+                                            dtype_code(gate.dtype), _stream()), "silu_mul")
+    return out
+
+
+def add(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _require_cuda(a, b, out)
+    if a.shape != b.shape or not a.is_contiguous() or not b.is_contiguous():
+        raise ValueError("add expects contiguous tensors of equal shape")
+    out = torch.empty_like(a) if out is None else out
+    check(_lib.load().cacheir_b200_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), dtype_code(a.dtype),
+                                       _stream()), "add")
+    return out
+
+
+def embedding_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _require_cuda(table, ids, out)
+    if ids.dtype != torch.int64 or not ids.is_contiguous() or not table.is_contiguous():
+        raise ValueError("embedding_gather expects contiguous int64 ids and a contiguous table")
+    rows, hidden = ids.numel(), int(table.shape[1])
+    out = torch.empty((rows, hidden), device=table.device, dtype=table.dtype) if out is None else out
+    check(_lib.load().cacheir_b200_embedding_gather(table.data_ptr(), ids.data_ptr(), out.data_ptr(), rows, hidden,
+                                                    int(table.shape[0]), dtype_code(table.dtype), _stream()),
+          "embedding_gather")
+    return out
+
+
+def argmax_rows(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _require_cuda(logits, out)
+    vocab = int(logits.shape[-1])
+    rows = logits.numel() // vocab
+    if not logits.is_contiguous():
+        raise ValueError("argmax_rows expects contiguous logits")
+    out = torch.empty((rows,), device=logits.device, dtype=torch.int64) if out is None else out
+    check(_lib.load().cacheir_b200_argmax_rows(logits.data_ptr(), out.data_ptr(), rows, vocab, dtype_code(logits.dtype),
+                                               _stream()), "argmax_rows")
+    return out
+
+
+def advance_positions(positions: torch.Tensor, seq_lens: torch.Tensor) -> None:
+    _require_cuda(positions, seq_lens)
+    check(_lib.load().cacheir_b200_advance_positions(positions.data_ptr(), seq_lens.data_ptr(), seq_lens.numel(),
+                                                     _stream()), "advance_positions")
+
+
+def default_softmax_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(float(head_dim))

@@ -1,0 +1,110 @@
+"""Device-side quantized weights in the reference's pack format.
+
+`B200PackedWeight` is the GPU counterpart of the reference's
+`CudaPackedQuantizedTensor` (cacheir/runtime/cuda.py:96-105): uint8 codes
+(`packed_values`: [N, K] for int8, [N, ceil(K/2)] for int4 with the even
+column in the low nibble), fp32 `scales` [N] and fp32 `zero_points` [N]
+(the reference uploads its int32 zero points as fp32, cuda.py:83). The codes
+are exactly what `cacheir/quantization.py:_asymmetric_pack` produces; packing
+runs on the GPU (`ops.pack_rows`). Group-wise symmetric weights (scales
+[N, K/group], zero point 2^(bits-1)) use the same code layout.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+from . import ops
+
+
+def quant_bits(quant: str | None) -> int | None:
+    """Bit width by quant name, the rule of cacheir/quantization.py:63-71."""
+    if not quant:
+        return None
+    name = quant.lower()
+    if "int4" in name or "awq" in name or "gptq" in name:
+        return 4
+    if "int8" in name or "8bit" in name:
+        return 8
+    return None
+
+
+@dataclass
+class B200PackedWeight:
+    packed_values: torch.Tensor          # uint8 [N, K] or [N, ceil(K/2)]
+    scales: torch.Tensor                 # f32 [N]  |  f16/f32 [N, K/group]
+    zero_points: torch.Tensor | None     # f32 [N]  |  None (midpoint)
+    bits: int
+    shape: tuple[int, int]
+    axis: int = 1
+    group_size: int | None = None
+    zero_points_i32: torch.Tensor | None = None   # the reference's int32 form, kept for parity checks
+
+    @property
+    def nbytes(self) -> int:
+        total = self.packed_values.numel() + self.scales.numel() * self.scales.element_size()
+        if self.zero_points is not None:
+            total += self.zero_points.numel() * 4
+        return int(total)
+
+
+def pack_weight_device(weight: torch.Tensor, quant: str | None) -> B200PackedWeight | None:
+    """`pack_quantized_weight` (cacheir/quantization.py:63-71) on the GPU; None when `quant` names no packed format."""
+    bits = quant_bits(quant)
+    if bits is None:
+        return None
+    w = weight.to(dtype=torch.float32).contiguous()
+    if w.dim() != 2:
+        raise ValueError("packed quantization expects a 2D out_features x in_features weight")
+    packed, scales, zp_i, zp_f = ops.pack_rows(w, bits)
+    return B200PackedWeight(packed, scales, zp_f, bits, (int(w.shape[0]), int(w.shape[1])), zero_points_i32=zp_i)
+
+
+def upload_reference_pack(packed: Any, device: torch.device | str) -> B200PackedWeight:
+    """Upload a host `PackedQuantizedTensor`-like object (numpy fields packed_values, scales, zero_points, bits,
+    shape, group_size) the way `CudaWeightStore.get_quantized` does (cacheir/runtime/cuda.py:77-94)."""
+    values = torch.from_numpy(packed.packed_values).to(device).contiguous()
+    group = int(packed.group_size) if getattr(packed, "group_size", None) else None
+    if group:
+        scales = torch.from_numpy(packed.scales).to(device).contiguous()   # keeps fp16 scales as fp16
+        zero_points = None
+    else:
+        scales = torch.from_numpy(packed.scales).to(device=device, dtype=torch.float32).contiguous()
+        zero_points = torch.from_numpy(packed.zero_points).to(device=device, dtype=torch.float32).contiguous()
+    return B200PackedWeight(values, scales, zero_points, int(packed.bits), (int(packed.shape[0]), int(packed.shape[1])),
+                            group_size=group)
+
+
+def concat_rows(weights: list[B200PackedWeight]) -> B200PackedWeight:
+    """Stack packed weights along the output dimension (Q|K|V, gate|up): same K, bits and grouping."""
+    first = weights[0]
+    for w in weights[1:]:
+        if w.bits != first.bits or w.shape[1] != first.shape[1] or w.group_size != first.group_size:
+            raise ValueError("cannot concatenate packed weights of different formats")
+    zero_points = None
+    if first.zero_points is not None:
+        zero_points = torch.cat([w.zero_points for w in weights]).contiguous()
+    return B200PackedWeight(
+        packed_values=torch.cat([w.packed_values for w in weights], dim=0).contiguous(),
+        scales=torch.cat([w.scales for w in weights], dim=0).contiguous(),
+        zero_points=zero_points,
+        bits=first.bits,
+        shape=(sum(w.shape[0] for w in weights), first.shape[1]),
+        group_size=first.group_size,
+    )
+
+
+def dequantize_device(w: B200PackedWeight, dtype: torch.dtype) -> torch.Tensor:
+    """`dequantize_packed_weight` (cacheir/quantization.py:74-84) on the GPU, per-row affine weights only."""
+    if w.group_size:
+        raise NotImplementedError("dequantize_device covers the per-row affine format")
+    return ops.dequantize_rows(w.packed_values, w.scales, w.zero_points, bits=w.bits, k=w.shape[1], dtype=dtype)
+
+
+def quantized_matmul(x: torch.Tensor, w: B200PackedWeight, *, epilogue: int = ops.EPI_NONE,
+                     residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """`_quantized_matmul` (cacheir/runtime/cuda.py:932-940) without materialising the dense weight."""
+    return ops.qgemv(x, w.packed_values, w.scales, w.zero_points, bits=w.bits, n=w.shape[0], k=w.shape[1],
+                     group_size=w.group_size or 0, epilogue=epilogue, residual=residual, out=out)

@@ -1,0 +1,669 @@
+"""B200 decode runtime: drop-in for the reference's `CudaRuntime` on the batched
+decode path.
+
+`B200DecodeRuntime` exposes the duck type the reference's dispatcher,
+scheduler, benchmark and server use (cacheir/runtime/cuda.py:430-714,
+cacheir/runtime/scheduler.py:508-577): `run`, `fork`, `run_decode_batch`,
+`run_prefill_batch`, `prefill_tokens`, `generate`, `cache_stats`,
+`synchronize`, `tokenizer`, `artifact`, `kv_cache`, `prefix_cache`,
+`kernel_counts`. It walks the same lowered graph and dispatches on the same
+`node.op` strings (cuda.py:779-874), but:
+
+  * every op is a hand-written sm_100a kernel called through the C ABI; there
+    is no torch math, no Triton and no CPU fallback on the path;
+  * the graph walk happens once per batch composition: it is lowered to a flat
+    launch list over static buffers ("plan") and, after the first step,
+    captured in a CUDA graph that later steps replay;
+  * request state lives on the device (token ids, positions, sequence lengths,
+    page table); the host only mirrors lengths and pushes page-table rows when
+    a sequence crosses a page boundary;
+  * K/V rows are written straight into the shared page pool, and sessions can
+    alias the pages of a common prefix.
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+from pathlib import Path
+from typing import Any, Callable, Iterable
+
+import numpy as np
+import torch
+
+from . import ops
+from .artifact import CompileArtifact
+from .kv_cache import B200KVPageAllocator, B200PagedKVCache
+from .quantization import B200PackedWeight, concat_rows, quant_bits
+from .weights import B200WeightStore, TensorSource
+
+
+def b200_runtime_available() -> bool:
+    return bool(torch.cuda.is_available())
+
+
+def _dtype_from_name(name: str | None) -> torch.dtype | None:
+    if name in {None, "auto"}:
+        return None
+    table = {"float16": torch.float16, "fp16": torch.float16, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+             "float32": torch.float32, "fp32": torch.float32}
+    try:
+        return table[str(name).lower()]
+    except KeyError as exc:
+        raise ValueError(f"Unsupported CUDA runtime dtype {name!r}") from exc
+
+
+class ByteTokenizer:
+    """Byte-mod tokenizer of the reference's tiny models (cacheir/runtime/tokenizer.py:7-24)."""
+
+    def __init__(self, vocab_size: int):
+        self.vocab_size = max(1, int(vocab_size))
+
+    def encode(self, text: str) -> list[int]:
+        if not isinstance(text, str):
+            raise TypeError("tokenizer.encode expects a string prompt")
+        data = text.encode("utf-8") or b"\x00"
+        return [int(byte) % self.vocab_size for byte in data]
+
+    def decode(self, token_ids: list[int]) -> str:
+        out = []
+        for token_id in token_ids:
+            value = int(token_id) % self.vocab_size
+            out.append(chr(value) if 32 <= value <= 126 else f"<{value}>")
+        return "".join(out)
+
+
+class B200PrefixCache:
+    """LRU of reusable prompt prefixes, keyed by token tuple like the reference's
+    `PrefixCache` (cacheir/runtime/kv_cache.py:262-307), but an entry holds
+    references to the prefix's full KV pages instead of a copy of the tensors."""
+
+    def __init__(self, allocator: B200KVPageAllocator, num_layers: int, capacity: int = 8):
+        self.capacity = max(1, int(capacity))
+        self.allocator = allocator
+        self.num_layers = num_layers
+        self._entries: OrderedDict[tuple[int, ...], B200PagedKVCache] = OrderedDict()
+        self.hits = self.misses = self.evictions = 0
+
+    def put(self, token_ids, cache: B200PagedKVCache) -> None:
+        page = cache.page_size
+        key = tuple(int(t) for t in token_ids)[: (min(len(token_ids), cache.tokens) // page) * page]
+        if not key:
+            return
+        if key in self._entries:
+            self._entries.pop(key).clear()
+        holder = B200PagedKVCache(self.allocator, self.num_layers)
+        holder.share_prefix(cache, len(key))
+        self._entries[key] = holder
+        while len(self._entries) > self.capacity:
+            _, old = self._entries.popitem(last=False)
+            old.clear()
+            self.evictions += 1
+
+    def longest_prefix(self, token_ids) -> tuple[tuple[int, ...], B200PagedKVCache | None]:
+        query = tuple(int(t) for t in token_ids)
+        best_key: tuple[int, ...] = ()
+        best = None
+        for key, value in self._entries.items():
+            if len(key) > len(best_key) and query[: len(key)] == key:
+                best_key, best = key, value
+        if best is not None:
+            self._entries.move_to_end(best_key)
+            self.hits += 1
+        else:
+            self.misses += 1
+        return best_key, best
+
+    def stats(self) -> dict[str, int]:
+        return {"capacity": self.capacity, "entries": len(self._entries), "hits": self.hits,
+                "misses": self.misses, "evictions": self.evictions}
+
+
+class _Engine:
+    """State shared by every fork of a runtime: weights, page pools, plans."""
+
+    def __init__(self, artifact: Any, *, device: torch.device, dtype: torch.dtype, weights: B200WeightStore | None,
+                 tensor_source: Any, kv_allocator: B200KVPageAllocator | None, max_seq_len: int | None,
+                 use_cuda_graph: bool, attention_splits: int, max_plans: int):
+        self.artifact = artifact
+        self.device = device
+        self.dtype = dtype
+        self.graph = artifact.graph("decode")
+        self.config = artifact.config
+        self.quant = artifact.quant
+        if self.quant and quant_bits(self.quant) is None:
+            raise ValueError(f"Unsupported quantization mode {self.quant!r}")
+        source = tensor_source if tensor_source is not None else artifact.model_path
+        self.weights = weights or B200WeightStore(TensorSource(source), self.graph.weights, self.quant,
+                                                  device=device, dtype=dtype)
+        hints = self.graph.attrs.get("execution_hints", {}) if isinstance(self.graph.attrs, dict) else {}
+        self.page_size = int(hints.get("page_size", 16))
+        self.allocator = kv_allocator or B200KVPageAllocator(page_size=self.page_size)
+        if self.allocator.page_size != self.page_size:
+            raise ValueError("kv_allocator page_size differs from the artifact's decode page size")
+        self.allocator.configure(torch=torch, device=device, dtype=dtype, num_layers=int(self.config.num_layers),
+                                 kv_heads=int(self.config.num_key_value_heads), head_dim=int(self.config.head_dim))
+        self.max_seq_len = int(max_seq_len or self.config.max_position_embeddings)
+        self.use_cuda_graph = use_cuda_graph
+        self.attention_splits = int(attention_splits)
+        self.max_plans = max(1, int(max_plans))
+        self.plans: OrderedDict[tuple[str, ...], "_DecodePlan"] = OrderedDict()
+        self.kernel_counts: OrderedDict[str, int] = OrderedDict()
+        self.gemm_plans: OrderedDict[str, str] = OrderedDict()
+        self.fused_weights: dict[tuple[str, ...], B200PackedWeight | torch.Tensor] = {}
+        self.prefix_cache = B200PrefixCache(self.allocator, int(self.config.num_layers))
+        self.tokenizer = ByteTokenizer(int(self.config.vocab_size))
+
+    def count(self, name: str, n: int = 1) -> None:
+        self.kernel_counts[name] = self.kernel_counts.get(name, 0) + n
+
+    # -- weights as the kernels want them -------------------------------------------
+    def matmul_weight(self, names: tuple[str, ...], quantized: bool) -> B200PackedWeight | torch.Tensor:
+        """One (row-concatenated) weight for a matmul-family node: packed when the
+        node is a quantized op, dense [N, K] otherwise (cuda.py:1017-1023 caches the
+        same concatenation for its unquantized fused ops)."""
+        if names in self.fused_weights:
+            return self.fused_weights[names]
+        if quantized:
+            parts = [self.weights.get_quantized(n) for n in names]
+            fused = parts[0] if len(parts) == 1 else concat_rows(parts)
+            if len(parts) > 1:   # the concatenation replaces the parts: keep one copy of the codes in HBM
+                for n in names:
+                    self.weights.release(n)
+        else:
+            dense = [self.weights.get(n) for n in names]
+            fused = dense[0] if len(dense) == 1 else torch.cat(dense, dim=0).contiguous()
+            if len(dense) > 1:
+                for n in names:
+                    self.weights.release(n)
+        self.fused_weights[names] = fused
+        return fused
+
+    def plan_for(self, sessions: list["B200DecodeRuntime"]) -> "_DecodePlan":
+        key = tuple(s.kv_cache.owner_id for s in sessions)
+        plan = self.plans.get(key)
+        needed_pages = max((s.kv_cache.tokens + 1 + self.page_size - 1) // self.page_size for s in sessions)
+        if plan is not None and (plan.pool_generation != self.allocator.generation or plan.width < needed_pages):
+            self.plans.pop(key)
+            plan = None
+        if plan is None:
+            width = max(needed_pages, (self.max_seq_len + self.page_size - 1) // self.page_size)
+            plan = _DecodePlan(self, len(sessions), width)
+            self.plans[key] = plan
+            while len(self.plans) > self.max_plans:
+                self.plans.popitem(last=False)
+        else:
+            self.plans.move_to_end(key)
+        return plan
+
+
+class _DecodePlan:
+    """Static device buffers and the flat launch list of one decode step for a
+    fixed batch size; optionally a CUDA graph of that list."""
+
+    def __init__(self, engine: _Engine, batch: int, width: int):
+        self.engine = engine
+        self.batch = batch
+        self.width = width
+        self.pool_generation = engine.allocator.generation
+        dev = engine.device
+        self.ids = torch.zeros((batch,), device=dev, dtype=torch.int64)
+        self.positions = torch.zeros((batch,), device=dev, dtype=torch.int32)
+        self.seq_lens = torch.zeros((batch,), device=dev, dtype=torch.int32)
+        self.page_table = torch.zeros((batch, width), device=dev, dtype=torch.int32)
+        self.host_ids = torch.zeros((batch,), dtype=torch.int64).pin_memory()
+        self.host_lens = torch.zeros((batch,), dtype=torch.int32).pin_memory()
+        self.host_table = torch.zeros((batch, width), dtype=torch.int32).pin_memory()
+        self.synced_owner_state: list[tuple[str, int, int, int]] | None = None
+        self.program: list[Callable[[], None]] = []
+        self.launches_per_step = 0
+        self.cuda_graph: torch.cuda.CUDAGraph | None = None
+        self.feedback_graph: torch.cuda.CUDAGraph | None = None
+        self.h2d_done = torch.cuda.Event()
+        self.steps_run = 0
+        self.logits: torch.Tensor | None = None
+        self._lower()
+
+    # -- graph lowering --------------------------------------------------------------
+    def _emit(self, fn: Callable[[], None], count_key: str, launches: int = 1) -> None:
+        self.program.append(fn)
+        self.launches_per_step += launches
+        self._count_keys.append((count_key, 1))
+
+    def _buf(self, cols: int) -> torch.Tensor:
+        return torch.empty((self.batch, cols), device=self.engine.device, dtype=self.engine.dtype)
+
+    def _lower(self) -> None:
+        eng = self.engine
+        nodes = list(eng.graph.nodes)
+        env: dict[str, Any] = {}
+        self._count_keys: list[tuple[str, int]] = []
+        uses: dict[str, int] = {}
+        for node in nodes:
+            for name in node.inputs:
+                uses[name] = uses.get(name, 0) + 1
+        for name in eng.graph.outputs:
+            uses[name] = uses.get(name, 0) + 1
+
+        self._emit(lambda: ops.advance_positions(self.positions, self.seq_lens), "b200.advance_positions")
+        skip: set[int] = set()
+        for idx, node in enumerate(nodes):
+            if idx in skip:
+                continue
+            op = node.op
+            attrs = node.attrs
+            if op == "token_embedding":
+                table = eng.weights.get(node.inputs[1])
+                out = self._buf(int(table.shape[1]))
+                self._emit(lambda table=table, out=out: ops.embedding_gather(table, self.ids, out), "b200.embedding_gather")
+                env[node.outputs[0]] = out
+            elif op == "rms_norm":
+                x, w = env[node.inputs[0]], eng.weights.get(node.inputs[1])
+                out = self._buf(int(x.shape[1]))
+                eps = float(attrs.get("eps", 1e-6))
+                self._emit(lambda x=x, w=w, out=out, eps=eps: ops.rms_norm(x, w, eps, out=out), "b200.rms_norm")
+                env[node.outputs[0]] = out
+            elif op in {"matmul", "quantized_matmul"}:
+                x = env[node.inputs[0]]
+                weight = eng.matmul_weight((node.inputs[1],), op == "quantized_matmul")
+                out_name = node.outputs[0]
+                nxt = nodes[idx + 1] if idx + 1 < len(nodes) else None
+                residual = None
+                if (nxt is not None and nxt.op == "add" and out_name in nxt.inputs and uses.get(out_name, 0) == 1
+                        and nxt.inputs[0] != nxt.inputs[1]):
+                    other = nxt.inputs[0] if nxt.inputs[1] == out_name else nxt.inputs[1]
+                    residual = env[other]
+                    skip.add(idx + 1)
+                    out_name = nxt.outputs[0]
+                out = self._matmul(x, weight, residual=residual)
+                env[out_name] = out
+            elif op in {"fused_rmsnorm_qkv_rope", "quantized_fused_rmsnorm_qkv_rope"}:
+                x, norm_w = env[node.inputs[0]], eng.weights.get(node.inputs[1])
+                weight = eng.matmul_weight(tuple(node.inputs[2:5]), op.startswith("quantized_"))
+                eps = float(attrs.get("eps", 1e-6))
+                normed = self._buf(int(x.shape[1]))
+                self._emit(lambda x=x, w=norm_w, out=normed, eps=eps: ops.rms_norm(x, w, eps, out=out), "b200.rms_norm")
+                qkv = self._matmul(normed, weight)
+                q_dim = self._rows_of(node.inputs[2])
+                k_dim = self._rows_of(node.inputs[3])
+                head_dim = int(attrs["head_dim"])
+                theta = float(attrs.get("rope_theta", 10000.0))
+                qk = qkv[:, : q_dim + k_dim]   # q and k heads are adjacent: one RoPE launch covers both
+                self._emit(lambda qk=qk, hd=head_dim, theta=theta, nh=(q_dim + k_dim) // head_dim:
+                           ops.rope_inplace(qk, self.positions, num_heads=nh, head_dim=hd, theta=theta), "b200.rope")
+                env[node.outputs[0]] = qkv[:, :q_dim]
+                env[node.outputs[1]] = qkv[:, q_dim:q_dim + k_dim]
+                env[node.outputs[2]] = qkv[:, q_dim + k_dim:]
+            elif op == "qkv_projection":
+                x = env[node.inputs[0]]
+                for w_name, out_name in zip(node.inputs[1:4], node.outputs[:3]):
+                    env[out_name] = self._matmul(x, eng.matmul_weight((w_name,), False))
+            elif op == "rope":
+                head_dim = int(attrs["head_dim"])
+                theta = float(attrs.get("rope_theta", 10000.0))
+                for in_name, out_name in zip(node.inputs[:2], node.outputs[:2]):
+                    t = env[in_name]
+                    self._emit(lambda t=t, hd=head_dim, theta=theta:
+                               ops.rope_inplace(t, self.positions, num_heads=int(t.shape[1]) // hd, head_dim=hd, theta=theta),
+                               "b200.rope")
+                    env[out_name] = t
+            elif op in {"paged_attention_decode", "grouped_query_attention"}:
+                env[node.outputs[0]] = self._attention(env[node.inputs[0]], env[node.inputs[1]], env[node.inputs[2]], attrs)
+            elif op == "add":
+                a, b = env[node.inputs[0]], env[node.inputs[1]]
+                out = self._buf(int(a.shape[1]))
+                self._emit(lambda a=a, b=b, out=out: ops.add(a, b, out), "b200.add")
+                env[node.outputs[0]] = out
+            elif op in {"fused_swiglu", "quantized_fused_swiglu"}:
+                x = env[node.inputs[0]]
+                weight = eng.matmul_weight(tuple(node.inputs[1:3]), op.startswith("quantized_"))
+                env[node.outputs[0]] = self._matmul(x, weight, epilogue=ops.EPI_SWIGLU)
+            elif op == "elementwise_mul" and idx > 0 and nodes[idx - 1].op == "silu" and nodes[idx - 1].outputs[0] in node.inputs:
+                gate = env["__silu_in__" + nodes[idx - 1].outputs[0]]
+                up = env[node.inputs[1] if node.inputs[0] == nodes[idx - 1].outputs[0] else node.inputs[0]]
+                out = self._buf(int(gate.shape[1]))
+                self._emit(lambda g=gate, u=up, out=out: ops.silu_mul(g, u, out), "b200.silu_mul")
+                env[node.outputs[0]] = out
+            elif op == "silu" and idx + 1 < len(nodes) and nodes[idx + 1].op == "elementwise_mul":
+                env["__silu_in__" + node.outputs[0]] = env[node.inputs[0]]
+            elif op == "paged_attention_prefill":
+                raise NotImplementedError("the B200 runtime executes the decode graph; prefill runs as decode steps")
+            else:
+                raise NotImplementedError(f"B200 decode runtime does not implement op {op}")
+        logits = env[eng.graph.outputs[0]]
+        self.logits = logits
+        # Greedy feedback variant: the row argmax overwrites `ids` (already consumed by the
+        # embedding gather of this step), so the next replay needs nothing from the host.
+        self.feedback_tail = lambda: ops.argmax_rows(logits, self.ids)
+
+    def _rows_of(self, weight_name: str) -> int:
+        spec = self.engine.graph.weights[weight_name]
+        shape = getattr(spec, "shape", None) or spec.tensor_type.shape
+        return int(shape[0])
+
+    def _matmul(self, x: torch.Tensor, weight: B200PackedWeight | torch.Tensor, *, epilogue: int = ops.EPI_NONE,
+                residual: torch.Tensor | None = None) -> torch.Tensor:
+        eng = self.engine
+        if residual is not None:
+            epilogue = ops.EPI_RESIDUAL
+        if isinstance(weight, B200PackedWeight):
+            n, k, bits = weight.shape[0], weight.shape[1], weight.bits
+            out = self._buf(n // 2 if epilogue == ops.EPI_SWIGLU else n)
+            fn = lambda: ops.qgemv(x, weight.packed_values, weight.scales, weight.zero_points, bits=bits, n=n, k=k,
+                                   group_size=weight.group_size or 0, epilogue=epilogue, residual=residual, out=out)
+            key = f"b200.qgemv.int{bits}" + (".swiglu" if epilogue == ops.EPI_SWIGLU else ".residual" if residual is not None else "")
+            eng.gemm_plans[f"q{bits}:{(self.batch, 1, k)}x{weight.shape}"] = key
+        else:
+            n, k = int(weight.shape[0]), int(weight.shape[1])
+            out = self._buf(n // 2 if epilogue == ops.EPI_SWIGLU else n)
+            fn = lambda: ops.qgemv(x, weight, None, None, bits=0, n=n, k=k, epilogue=epilogue, residual=residual, out=out)
+            key = "b200.gemv.dense" + (".swiglu" if epilogue == ops.EPI_SWIGLU else ".residual" if residual is not None else "")
+            eng.gemm_plans[f"{(self.batch, 1, k)}x{(n, k)}"] = key
+        self._emit(fn, key)
+        return out
+
+    def _attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attrs: dict[str, Any]) -> torch.Tensor:
+        eng = self.engine
+        layer = int(attrs.get("layer", 0))
+        heads, kv_heads, head_dim = int(attrs["num_heads"]), int(attrs["num_kv_heads"]), int(attrs["head_dim"])
+        pool = eng.allocator.pool_for_layer(layer)
+        if pool is None:
+            raise RuntimeError(f"no KV page pool for layer {layer}")
+        k_pool, v_pool = pool["keys"], pool["values"]
+        out = self._buf(heads * head_dim)
+        q3 = q.as_strided((self.batch, heads, head_dim), (q.stride(0), head_dim, 1), q.storage_offset())
+        out3 = out.view(self.batch, heads, head_dim)
+        splits = eng.attention_splits or ops.attention_auto_splits(self.batch, heads, kv_heads, self.width,
+                                                                  eng.page_size, head_dim)
+        ws_bytes = ops.attention_workspace_bytes(self.batch, heads, head_dim, splits)
+        if not hasattr(self, "_attn_ws") or self._attn_ws.numel() * 4 < ws_bytes:
+            self._attn_ws = torch.empty((max(1, (ws_bytes + 3) // 4),), device=eng.device, dtype=torch.float32)
+        ws = self._attn_ws if ws_bytes else None
+        self._emit(lambda: ops.kv_append(k, v, k_pool, v_pool, self.page_table, self.positions), "b200.kv_append")
+        self._emit(lambda: ops.paged_attention_decode_batch(q3, k_pool, v_pool, self.page_table, self.seq_lens, out=out3,
+                                                            num_splits=splits, workspace=ws),
+                   "b200.paged_attention_decode_batch.persistent_shared", launches=2 if splits > 1 else 1)
+        return out
+
+    # -- stepping --------------------------------------------------------------------
+    def sync_sessions(self, sessions: list["B200DecodeRuntime"]) -> None:
+        """Make the device copy of lengths and page tables match the host bookkeeping
+        (which already accounts for the token about to be decoded)."""
+        state = [(s.kv_cache.owner_id, s.kv_cache.tokens, len(s.kv_cache.pages), s.kv_cache.epoch) for s in sessions]
+        previous = self.synced_owner_state
+        lens_ok = previous is not None and all(p[0] == c[0] and p[3] == c[3] and p[1] + 1 == c[1] for p, c in zip(previous, state))
+        pages_ok = previous is not None and all(p[0] == c[0] and p[3] == c[3] and p[2] == c[2] for p, c in zip(previous, state))
+        self.h2d_done.synchronize()   # the pinned staging buffers must not change under a pending copy
+        if not pages_ok:
+            table = self.host_table.numpy()
+            for row, s in enumerate(sessions):
+                table[row] = s.kv_cache.page_table_row(self.width)
+            self.page_table.copy_(self.host_table, non_blocking=True)
+        if not lens_ok:
+            lens = self.host_lens.numpy()
+            for row, s in enumerate(sessions):
+                lens[row] = s.kv_cache.tokens - 1   # the step itself advances the device copy by one
+            self.seq_lens.copy_(self.host_lens, non_blocking=True)
+        self.synced_owner_state = state
+
+    def run_program(self, *, feedback: bool = False) -> None:
+        """One decode step: eager launches on the first step, CUDA-graph replay afterwards."""
+        eng = self.engine
+        if eng.use_cuda_graph and self.steps_run >= 1:
+            attr = "feedback_graph" if feedback else "cuda_graph"
+            graph = getattr(self, attr)
+            if graph is None:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    for fn in self.program:
+                        fn()
+                    if feedback:
+                        self.feedback_tail()
+                setattr(self, attr, graph)
+            graph.replay()
+        else:
+            for fn in self.program:
+                fn()
+            if feedback:
+                self.feedback_tail()
+        self.steps_run += 1
+        for key, n in self._count_keys:
+            eng.count(key, n)
+        if feedback:
+            eng.count("b200.argmax_rows")
+
+    def run_feedback_steps(self, steps: int) -> torch.Tensor:
+        """`steps` greedy decode steps with the argmax fed back on the device (no host
+        round trip between steps). Returns the generated tokens [steps, B]."""
+        out = torch.empty((steps, self.batch), device=self.engine.device, dtype=torch.int64)
+        for i in range(steps):
+            self.run_program(feedback=True)
+            out[i].copy_(self.ids, non_blocking=True)
+        return out
+
+
+class B200DecodeRuntime:
+    """Execute compiled CacheIR decode graphs on a B200 (see module docstring)."""
+
+    supports_variable_prefill_batch = True
+
+    def __init__(
+        self,
+        artifact: CompileArtifact | Any | str | Path,
+        *,
+        device: str = "cuda",
+        dtype: str | None = "auto",
+        weights: B200WeightStore | None = None,
+        tensor_source: Any = None,
+        kv_allocator: B200KVPageAllocator | None = None,
+        max_seq_len: int | None = None,
+        use_cuda_graph: bool = True,
+        attention_splits: int = 0,
+        max_plans: int = 8,
+        clone_outputs: bool = True,
+        _engine: _Engine | None = None,
+    ):
+        if isinstance(artifact, (str, Path)):
+            artifact = CompileArtifact.load(artifact)
+        if _engine is None:
+            if not torch.cuda.is_available():
+                raise RuntimeError("B200DecodeRuntime needs a CUDA device; cacheir_b200 has no CPU fallback")
+            dev = torch.device(device)
+            if dev.type != "cuda":
+                raise RuntimeError("B200DecodeRuntime runs on CUDA devices only")
+            if dev.index is None:
+                dev = torch.device("cuda", torch.cuda.current_device())
+            selected = _dtype_from_name(dtype)
+            if selected is None:
+                selected = torch.float16 if str(artifact.config.dtype).lower() in {"float16", "fp16", "bfloat16", "bf16"} else torch.float32
+            with torch.cuda.device(dev):
+                _engine = _Engine(artifact, device=dev, dtype=selected, weights=weights, tensor_source=tensor_source,
+                                  kv_allocator=kv_allocator, max_seq_len=max_seq_len, use_cuda_graph=use_cuda_graph,
+                                  attention_splits=attention_splits, max_plans=max_plans)
+        self._engine = _engine
+        self.artifact = _engine.artifact
+        self.device = _engine.device
+        self.dtype = _engine.dtype
+        self.weights = _engine.weights
+        self.tokenizer = _engine.tokenizer
+        self.kv_allocator = _engine.allocator
+        self.prefix_cache = _engine.prefix_cache
+        self.kernel_counts = _engine.kernel_counts
+        self.gemm_plans = _engine.gemm_plans
+        self.kv_cache = B200PagedKVCache(_engine.allocator, int(_engine.config.num_layers))
+        self.clone_outputs = clone_outputs
+        self.oom_recoveries = 0
+
+    @classmethod
+    def available(cls) -> bool:
+        return b200_runtime_available()
+
+    def fork(self) -> "B200DecodeRuntime":
+        """Independent KV session sharing weights, page pools, plans and prefix cache (cuda.py:491-506)."""
+        return B200DecodeRuntime(self.artifact, clone_outputs=self.clone_outputs, _engine=self._engine)
+
+    # -- decode ----------------------------------------------------------------------
+    def run_decode_batch(self, sessions: list["B200DecodeRuntime"], token_ids: list[int] | tuple[int, ...]) -> torch.Tensor:
+        """Advance one decode token for several sessions; returns logits [N, 1, vocab] (cuda.py:541-582)."""
+        plan = self._prepare_batch(sessions, token_ids)
+        with torch.cuda.device(self.device):
+            plan.run_program()
+        self._engine.count("cacheir.b200_decode_batch_graph")
+        logits = plan.logits.view(len(sessions), 1, -1)
+        return logits.clone() if self.clone_outputs else logits
+
+    def _prepare_batch(self, sessions, token_ids) -> _DecodePlan:
+        if not sessions:
+            raise ValueError("run_decode_batch requires at least one session")
+        if len(sessions) != len(token_ids):
+            raise ValueError("sessions and token_ids must have the same length")
+        for session in sessions:
+            if not isinstance(session, B200DecodeRuntime):
+                raise TypeError("run_decode_batch only accepts B200DecodeRuntime sessions")
+            if session._engine is not self._engine:
+                raise ValueError("all sessions must be forks of the same runtime (same artifact, weights and device)")
+        if len({s.kv_cache.owner_id for s in sessions}) != len(sessions):
+            raise ValueError("a session may appear only once in a decode batch")
+        with torch.cuda.device(self.device):
+            for session in sessions:
+                session.kv_cache.extend(1)      # opens a page when the new token starts one
+            plan = self._engine.plan_for(list(sessions))
+            plan.sync_sessions(list(sessions))
+            ids = plan.host_ids.numpy()
+            ids[:] = [int(t) for t in token_ids]
+            plan.ids.copy_(plan.host_ids, non_blocking=True)
+            plan.h2d_done.record()
+        return plan
+
+    def decode_greedy_batch(self, sessions: list["B200DecodeRuntime"], token_ids, steps: int) -> torch.Tensor:
+        """`steps` greedy tokens per session with on-device argmax feedback
+        (no per-step host round trip). Returns int64 tokens [steps, N] on the device."""
+        steps = int(steps)
+        if steps <= 0:
+            raise ValueError("steps must be positive")
+        plan = self._prepare_batch(sessions, token_ids)
+        with torch.cuda.device(self.device):
+            for session in sessions:          # reserve the pages of the remaining steps up front
+                session.kv_cache.extend(steps - 1)
+            if any(len(s.kv_cache.pages) > plan.width for s in sessions):
+                raise RuntimeError("decode_greedy_batch would outgrow the plan's page table; raise max_seq_len")
+            if plan.pool_generation != self._engine.allocator.generation:
+                raise RuntimeError("the KV page pool grew while reserving pages; pre-size it with reserve_slots()")
+            plan.h2d_done.synchronize()
+            table = plan.host_table.numpy()
+            for row, s in enumerate(sessions):
+                table[row] = s.kv_cache.page_table_row(plan.width)
+            plan.page_table.copy_(plan.host_table, non_blocking=True)
+            plan.h2d_done.record()
+            tokens = plan.run_feedback_steps(steps)
+            plan.synced_owner_state = [(s.kv_cache.owner_id, s.kv_cache.tokens, len(s.kv_cache.pages), s.kv_cache.epoch)
+                                       for s in sessions]
+        self._engine.count("cacheir.b200_decode_batch_graph", steps)
+        return tokens
+
+    def run(self, input_ids: Iterable[Iterable[int]] | np.ndarray, *, mode: str = "prefill",
+            reset_kv: bool | None = None) -> torch.Tensor:
+        """`CudaRuntime.run` (cuda.py:508-539). Prefill is executed as decode steps
+        over the prompt (identical results: causal attention over an append-only cache)."""
+        if reset_kv is None:
+            reset_kv = mode == "prefill"
+        if mode == "prefill" and reset_kv:
+            self.kv_cache.clear()
+        ids = np.asarray(input_ids, dtype=np.int64)
+        if ids.ndim == 1:
+            ids = ids[None, :]
+        if ids.shape[0] != 1:
+            raise ValueError("B200DecodeRuntime.run handles one sequence; use run_decode_batch / run_prefill_batch for batches")
+        if ids.shape[1] == 0:
+            raise ValueError("run needs at least one token")
+        steps = []
+        keep = self.clone_outputs
+        self.clone_outputs = True
+        try:
+            for token in ids[0]:
+                steps.append(self.run_decode_batch([self], [int(token)]))
+        finally:
+            self.clone_outputs = keep
+        return torch.cat(steps, dim=1) if len(steps) > 1 else steps[0]
+
+    def run_prefill_batch(self, sessions: list["B200DecodeRuntime"], token_id_batches: list[list[int]]) -> torch.Tensor:
+        """Variable-length batched prefill (cuda.py:584-629): returns zero-padded logits [N, max_len, vocab]."""
+        if not sessions:
+            raise ValueError("run_prefill_batch requires at least one session")
+        if len(sessions) != len(token_id_batches):
+            raise ValueError("sessions and token_id_batches must have the same length")
+        lens = [len(t) for t in token_id_batches]
+        if any(n <= 0 for n in lens):
+            raise ValueError("run_prefill_batch requires non-empty token batches")
+        for session in sessions:
+            session.kv_cache.clear()
+        vocab = int(self._engine.config.vocab_size)
+        out = torch.zeros((len(sessions), max(lens), vocab), device=self.device, dtype=self.dtype)
+        for pos in range(max(lens)):
+            rows = [i for i, n in enumerate(lens) if pos < n]
+            logits = self.run_decode_batch([sessions[i] for i in rows], [token_id_batches[i][pos] for i in rows])
+            out[rows, pos] = logits[:, 0]
+        self._engine.count("cacheir.b200_prefill_batch_graph")
+        return out
+
+    def prefill_tokens(self, token_ids, *, use_prefix_cache: bool = False, remember_prefix: bool = False):
+        """cuda.py:631-653. A reused prefix aliases the stored pages instead of copying a snapshot."""
+        ids = [int(t) for t in token_ids]
+        reused: tuple[int, ...] = ()
+        if use_prefix_cache and ids:
+            prefix, holder = self.prefix_cache.longest_prefix(ids)
+            if holder is not None and 0 < len(prefix) < len(ids):
+                self.kv_cache.clear()
+                self.kv_cache.share_prefix(holder, len(prefix))
+                reused = prefix
+                logits = self.run([ids[len(prefix):]], mode="prefill", reset_kv=False)
+            else:
+                logits = self.run([ids], mode="prefill", reset_kv=True)
+        else:
+            logits = self.run([ids], mode="prefill", reset_kv=True)
+        if remember_prefix and ids:
+            self.remember_prefix(ids)
+        return logits, reused
+
+    def generate(self, prompt: str, *, max_new_tokens: int = 16, use_prefix_cache: bool = False,
+                 remember_prefix: bool = True) -> Iterable[str]:
+        token_ids = self.tokenizer.encode(prompt)
+        logits, _ = self.prefill_tokens(token_ids, use_prefix_cache=use_prefix_cache,
+                                        remember_prefix=remember_prefix and use_prefix_cache)
+        vocab = int(self._engine.config.vocab_size)
+        for _ in range(max_new_tokens):
+            next_id = int(torch.argmax(logits[0, -1]).item()) % vocab
+            yield self.tokenizer.decode([next_id])
+            logits = self.run([[next_id]], mode="decode")
+
+    def remember_prefix(self, token_ids) -> None:
+        self.prefix_cache.put(token_ids, self.kv_cache)
+
+    def load_longest_prefix(self, token_ids) -> tuple[int, ...]:
+        prefix, holder = self.prefix_cache.longest_prefix(token_ids)
+        if holder is not None:
+            self.kv_cache.clear()
+            self.kv_cache.share_prefix(holder, len(prefix))
+        return prefix
+
+    def _position_offset(self, layer: int) -> int:
+        return self.kv_cache.length(layer)
+
+    def cache_stats(self) -> dict[str, object]:
+        stats = self.kv_cache.stats()
+        stats["device"] = str(self.device)
+        stats["prefix_cache"] = self.prefix_cache.stats()
+        stats["kernel_counts"] = dict(self.kernel_counts)
+        stats["gemm_plans"] = dict(self.gemm_plans)
+        stats["oom_recoveries"] = self.oom_recoveries
+        stats["memory_limit_mb"] = None
+        return stats
+
+    def synchronize(self) -> None:
+        torch.cuda.synchronize(self.device)
+
+
+def create_runtime(artifact: Any, *, backend: str = "auto", **kwargs) -> B200DecodeRuntime:
+    """The `cuda` branch of the reference dispatcher (cacheir/runtime/__init__.py:10-24).
+    `auto` and `cuda` select the B200 runtime; there is no CPU backend in this package."""
+    if backend not in {"auto", "cuda", "cuda-b200"}:
+        raise ValueError(f"Unknown CacheIR runtime backend {backend!r} (cacheir_b200 provides the CUDA backend only)")
+    return B200DecodeRuntime(artifact, **kwargs)

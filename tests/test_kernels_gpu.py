@@ -1,0 +1,313 @@
+"""Parity of every CUDA kernel, called through the C ABI, against the CPU oracle.
+
+Bars: integer/byte/index results bit-exact; floating point rel-L2 <= 2e-3 in
+fp16/bf16 (the tolerance of the decode path's acceptance gate) and <= 2e-5 in fp32.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 2e-5, torch.float16: 2e-3, torch.bfloat16: 2e-3}
+DTYPES = [torch.float32, torch.float16, torch.bfloat16]
+
+
+def _ops():
+    from cacheir_b200 import ops
+    return ops
+
+
+def _rel(got: torch.Tensor, want: np.ndarray) -> float:
+    return oracle.rel_l2(got.detach().float().cpu().numpy(), want)
+
+
+def _make_paged(rng, batch, heads, kv_heads, head_dim, page, lens, dtype, extra_slots=3, shared_prefix_pages=0):
+    """Random q / pools / permuted page table. Inputs are rounded to `dtype` first so the
+    oracle sees exactly what the kernel sees."""
+    pages_per_seq = [(n + page - 1) // page for n in lens]
+    max_pages = max(1, max(pages_per_seq))
+    total = sum(pages_per_seq) + extra_slots
+    perm = rng.permutation(total).astype(np.int32)
+    table = np.zeros((batch, max_pages), dtype=np.int32)   # padding aliases slot 0, as in the reference test
+    cursor = 0
+    for b, n in enumerate(pages_per_seq):
+        table[b, :n] = perm[cursor:cursor + n]
+        cursor += n
+    if shared_prefix_pages:
+        for b in range(1, batch):
+            k = min(shared_prefix_pages, pages_per_seq[b], pages_per_seq[0])
+            table[b, :k] = table[0, :k]
+    q = torch.from_numpy(rng.standard_normal((batch, heads, head_dim)).astype(np.float32)).to(dtype)
+    k_pool = torch.from_numpy(rng.standard_normal((total, kv_heads, page, head_dim)).astype(np.float32)).to(dtype)
+    v_pool = torch.from_numpy(rng.standard_normal((total, kv_heads, page, head_dim)).astype(np.float32)).to(dtype)
+    return q, k_pool, v_pool, table, np.asarray(lens, dtype=np.int32)
+
+
+def _run_attention(q, k_pool, v_pool, table, lens, **kw):
+    ops = _ops()
+    out = ops.paged_attention_decode_batch(q.cuda(), k_pool.cuda(), v_pool.cuda(), torch.from_numpy(table).cuda(),
+                                           torch.from_numpy(lens).cuda(), **kw)
+    want = oracle.paged_attention_decode(q.float().numpy(), k_pool.float().numpy(), v_pool.float().numpy(), table, lens)
+    return out, want
+
+
+def test_attention_reference_test_shape():
+    # B=2, H=4, KVH=2, page=2, max_pages=3, D=8 fp32, page table [[0,1,2],[3,4,0]], seq_lens [5,3]:
+    # the case of the reference's tests/test_advanced_experiments.py:519-558 (atol 1e-4 there)
+    rng = np.random.default_rng(0)
+    q = torch.from_numpy(rng.standard_normal((2, 4, 8)).astype(np.float32))
+    k_pool = torch.from_numpy(rng.standard_normal((5, 2, 2, 8)).astype(np.float32))
+    v_pool = torch.from_numpy(rng.standard_normal((5, 2, 2, 8)).astype(np.float32))
+    table = np.asarray([[0, 1, 2], [3, 4, 0]], dtype=np.int32)
+    lens = np.asarray([5, 3], dtype=np.int32)
+    for splits in (0, 1, 2, 3):
+        out, want = _run_attention(q, k_pool, v_pool, table, lens, num_splits=splits)
+        np.testing.assert_allclose(out.cpu().numpy(), want, atol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [
+    (4, 2, 64, 16), (32, 8, 128, 16), (8, 1, 128, 16), (4, 4, 16, 4), (6, 2, 40, 8), (16, 2, 256, 16), (7, 7, 4, 1),
+])
+def test_attention_matches_oracle(dtype, heads, kv_heads, head_dim, page):
+    rng = np.random.default_rng(heads * 1000 + head_dim)
+    lens = [1, page, page + 1, 5 * page - 1, 333, 64]
+    q, k_pool, v_pool, table, lens = _make_paged(rng, len(lens), heads, kv_heads, head_dim, page, lens, dtype)
+    for splits in (0, 1, 4):
+        out, want = _run_attention(q, k_pool, v_pool, table, lens, num_splits=splits)
+        assert _rel(out, want) <= TOL[dtype], (dtype, splits)
+
+
+def test_attention_empty_and_ragged_sequences():
+    rng = np.random.default_rng(7)
+    lens = [0, 1, 17, 0, 200]
+    q, k_pool, v_pool, table, lens = _make_paged(rng, 5, 8, 2, 64, 16, lens, torch.float16)
+    out, want = _run_attention(q, k_pool, v_pool, table, lens, num_splits=3)
+    assert torch.isfinite(out).all()
+    assert float(out[0].abs().max()) == 0.0 and float(out[3].abs().max()) == 0.0
+    assert _rel(out, want) <= TOL[torch.float16]
+
+
+def test_attention_prefix_shared_pages_and_strided_q():
+    rng = np.random.default_rng(9)
+    lens = [96, 80, 130, 64]
+    q, k_pool, v_pool, table, lens = _make_paged(rng, 4, 8, 2, 128, 16, lens, torch.float16, shared_prefix_pages=4)
+    assert (table[1:, :4] == table[0, :4]).all()
+    out, want = _run_attention(q, k_pool, v_pool, table, lens)
+    assert _rel(out, want) <= TOL[torch.float16]
+    # q as a strided view of a wider [B, (H+2KVH)*D] projection buffer
+    wide = torch.zeros((4, (8 + 4) * 128), dtype=torch.float16, device="cuda")
+    wide[:, : 8 * 128] = q.cuda().reshape(4, -1)
+    q_view = wide.as_strided((4, 8, 128), (wide.stride(0), 128, 1))
+    ops = _ops()
+    out2 = ops.paged_attention_decode_batch(q_view, k_pool.cuda(), v_pool.cuda(), torch.from_numpy(table).cuda(),
+                                            torch.from_numpy(lens).cuda())
+    assert torch.equal(out2, out)
+
+
+def test_attention_split_combine_is_deterministic():
+    rng = np.random.default_rng(3)
+    lens = list(rng.integers(100, 3000, 6))
+    q, k_pool, v_pool, table, lens = _make_paged(rng, 6, 32, 8, 128, 16, lens, torch.float16)
+    a, want = _run_attention(q, k_pool, v_pool, table, lens, num_splits=0)
+    b, _ = _run_attention(q, k_pool, v_pool, table, lens, num_splits=0)
+    assert torch.equal(a, b)
+    assert _rel(a, want) <= TOL[torch.float16]
+
+
+def test_attention_workspace_contract():
+    from cacheir_b200._lib import CacheIRB200Error
+    ops = _ops()
+    rng = np.random.default_rng(4)
+    q, k_pool, v_pool, table, lens = _make_paged(rng, 2, 4, 2, 64, 16, [40, 50], torch.float16)
+    tiny_ws = torch.empty(4, dtype=torch.float32, device="cuda")
+    with pytest.raises(CacheIRB200Error):
+        ops.paged_attention_decode_batch(q.cuda(), k_pool.cuda(), v_pool.cuda(), torch.from_numpy(table).cuda(),
+                                         torch.from_numpy(lens).cuda(), num_splits=2, workspace=tiny_ws)
+    with pytest.raises((ValueError, TypeError)):
+        ops.paged_attention_decode_batch(q.cuda(), k_pool.cuda(), v_pool.cuda(), torch.from_numpy(table).long().cuda(),
+                                         torch.from_numpy(lens).cuda())
+
+
+# ---- dequant GEMV -------------------------------------------------------------------
+def _qgemv_case(rng, m, n, k, bits, dtype, group=0, reference_pack=True):
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(dtype)
+    if group:
+        codes = rng.integers(0, 1 << bits, (n, k)).astype(np.uint8)
+        scales = rng.uniform(0.005, 0.02, (n, k // group)).astype(np.float16)
+        packed = oracle.symmetric_group_pack_from_codes(codes, scales, bits, group)
+    elif reference_pack:
+        w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+        packed = oracle.asymmetric_pack(w, bits)
+    else:   # codes uniform, fp16 per-channel scale, zero point at the midpoint
+        codes = rng.integers(0, 1 << bits, (n, k)).astype(np.uint8)
+        packed = oracle.PackedQuantizedTensor(oracle.pack_int4(codes) if bits == 4 else codes,
+                                              rng.uniform(0.005, 0.02, n).astype(np.float16),
+                                              np.full(n, 1 << (bits - 1), dtype=np.int32), bits, (n, k))
+    return x, packed
+
+
+def _device_pack(packed):
+    from cacheir_b200.quantization import upload_reference_pack
+    return upload_reference_pack(packed, "cuda")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("m,n,k", [(1, 64, 256), (3, 96, 688), (8, 40, 1024), (32, 128, 512), (64, 24, 96), (2, 17, 53)])
+def test_qgemv_per_row_affine_matches_oracle(dtype, bits, m, n, k):
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(m * 7 + n + k + bits)
+    x, packed = _qgemv_case(rng, m, n, k, bits, dtype)
+    y = quantized_matmul(x.cuda(), _device_pack(packed))
+    want = oracle.quantized_matmul(x.float().numpy(), packed)
+    assert y.shape == (m, n)
+    assert _rel(y, want) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m", [1, 8, 32])
+def test_qgemv_group128_int4_matches_oracle(dtype, m):
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(100 + m)
+    x, packed = _qgemv_case(rng, m, 192, 1024, 4, dtype, group=128)
+    y = quantized_matmul(x.cuda(), _device_pack(packed))
+    want = oracle.quantized_matmul(x.float().numpy(), packed)
+    assert _rel(y, want) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_qgemv_fp16_scales_and_epilogues(dtype):
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(21)
+    m, n, k = 4, 128, 512
+    x, packed = _qgemv_case(rng, m, n, k, 8, dtype, reference_pack=False)
+    dev = _device_pack(packed)
+    dev.scales = torch.from_numpy(packed.scales).cuda()         # keep the fp16 per-channel scales
+    base = oracle.quantized_matmul(x.float().numpy(), packed)
+    assert _rel(quantized_matmul(x.cuda(), dev), base) <= TOL[dtype]
+    res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).to(dtype)
+    y = quantized_matmul(x.cuda(), dev, epilogue=ops.EPI_RESIDUAL, residual=res.cuda())
+    assert _rel(y, base + res.float().numpy()) <= TOL[dtype]
+    y = quantized_matmul(x.cuda(), dev, epilogue=ops.EPI_SWIGLU)
+    assert y.shape == (m, n // 2)
+    assert _rel(y, oracle.silu_mul(base[:, : n // 2], base[:, n // 2:])) <= TOL[dtype] * 2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_dense_gemv_matches_oracle(dtype):
+    ops = _ops()
+    rng = np.random.default_rng(5)
+    for m, n, k in [(1, 64, 256), (5, 33, 100), (16, 1024, 256)]:
+        x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(dtype)
+        w = torch.from_numpy((rng.standard_normal((n, k)) * 0.05).astype(np.float32)).to(dtype)
+        y = ops.qgemv(x.cuda(), w.cuda(), None, None, bits=0, n=n, k=k)
+        assert _rel(y, oracle.matmul(x.float().numpy(), w.float().numpy())) <= TOL[dtype]
+
+
+# ---- quantization loader: bit-exact -------------------------------------------------
+def test_pack_rows_is_bit_exact_with_reference_golden(golden_dir):
+    ops = _ops()
+    g = np.load(golden_dir / "pack.npz")
+    for prefix in ("lin", "rnd", "even"):
+        w = torch.from_numpy(g[f"{prefix}_w"]).cuda()
+        for bits, tag in ((4, "q4"), (8, "q8")):
+            packed, scales, zp_i, zp_f = ops.pack_rows(w, bits)
+            np.testing.assert_array_equal(packed.cpu().numpy(), g[f"{prefix}_{tag}_packed"])
+            np.testing.assert_array_equal(zp_i.cpu().numpy(), g[f"{prefix}_{tag}_zero_points"])
+            np.testing.assert_array_equal(scales.cpu().numpy(), g[f"{prefix}_{tag}_scales"])
+            np.testing.assert_array_equal(zp_f.cpu().numpy(), g[f"{prefix}_{tag}_zero_points"].astype(np.float32))
+            deq = ops.dequantize_rows(packed, scales, zp_f, bits=bits, k=w.shape[1], dtype=torch.float32)
+            np.testing.assert_array_equal(deq.cpu().numpy(), g[f"{prefix}_{tag}_dequant"])
+
+
+def test_pack_rows_matches_oracle_on_model_sized_rows():
+    ops = _ops()
+    rng = np.random.default_rng(12)
+    w = (rng.standard_normal((64, 4096)) * 0.02).astype(np.float32)
+    for bits in (4, 8):
+        want = oracle.asymmetric_pack(w, bits)
+        packed, scales, zp_i, _ = ops.pack_rows(torch.from_numpy(w).cuda(), bits)
+        np.testing.assert_array_equal(packed.cpu().numpy(), want.packed_values)
+        np.testing.assert_array_equal(scales.cpu().numpy(), want.scales)
+        np.testing.assert_array_equal(zp_i.cpu().numpy(), want.zero_points)
+
+
+# ---- glue ops -------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [48, 256, 4096, 8192, 1000])
+def test_rms_norm_and_fused_residual(dtype, hidden):
+    ops = _ops()
+    rng = np.random.default_rng(hidden)
+    x = torch.from_numpy(rng.standard_normal((5, hidden)).astype(np.float32)).to(dtype)
+    r = torch.from_numpy(rng.standard_normal((5, hidden)).astype(np.float32)).to(dtype)
+    w = torch.from_numpy(rng.standard_normal((hidden,)).astype(np.float32)).to(dtype)
+    out = ops.rms_norm(x.cuda(), w.cuda(), 1e-5)
+    assert _rel(out, oracle.rms_norm(x.float().numpy(), w.float().numpy(), 1e-5)) <= TOL[dtype]
+    summed = torch.empty_like(x, device="cuda")
+    out = ops.rms_norm(x.cuda(), w.cuda(), 1e-5, residual=r.cuda(), sum_out=summed)
+    want_sum = (x.float() + r.float()).to(dtype)
+    assert torch.equal(summed.cpu(), want_sum)          # the residual stream is the rounded sum, exactly
+    assert _rel(out, oracle.rms_norm(want_sum.float().numpy(), w.float().numpy(), 1e-5)) <= TOL[dtype]
+
+
+def test_rope_matches_reference_golden(golden_dir):
+    ops = _ops()
+    g = np.load(golden_dir / "numerics.npz")
+    x = g["rope_x"]                                      # [2, 3, 4*16]; every (batch, seq) row gets its own position
+    for off, key in ((7, "rope_out_off7"), (0, "rope_out_off0")):
+        rows = torch.from_numpy(x.reshape(6, 64).copy()).cuda()
+        pos = torch.tensor([off, off + 1, off + 2] * 2, dtype=torch.int32, device="cuda")
+        ops.rope_inplace(rows, pos, num_heads=4, head_dim=16, theta=10000.0)
+        np.testing.assert_allclose(rows.cpu().numpy().reshape(2, 3, 64), g[key], rtol=2e-5, atol=2e-5)
+
+
+def test_kv_append_writes_the_right_page_rows():
+    ops = _ops()
+    rng = np.random.default_rng(2)
+    batch, kvh, d, page = 3, 2, 8, 4
+    k_pool = torch.zeros((10, kvh, page, d), device="cuda")
+    v_pool = torch.zeros_like(k_pool)
+    table = torch.tensor([[5, 1, 0], [2, 7, 9], [3, 0, 0]], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([6, 11, 0], dtype=torch.int32, device="cuda")
+    wide = torch.from_numpy(rng.standard_normal((batch, 3 * kvh * d)).astype(np.float32)).cuda()
+    k, v = wide[:, kvh * d: 2 * kvh * d], wide[:, 2 * kvh * d:]
+    ops.kv_append(k, v, k_pool, v_pool, table, pos)
+    want_k = np.zeros((10, kvh, page, d), dtype=np.float32)
+    want_v = np.zeros_like(want_k)
+    for b, (slot, off) in enumerate([(1, 2), (9, 3), (3, 0)]):
+        want_k[slot, :, off] = k[b].cpu().numpy().reshape(kvh, d)
+        want_v[slot, :, off] = v[b].cpu().numpy().reshape(kvh, d)
+    np.testing.assert_array_equal(k_pool.cpu().numpy(), want_k)
+    np.testing.assert_array_equal(v_pool.cpu().numpy(), want_v)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_elementwise_embedding_argmax(dtype):
+    ops = _ops()
+    rng = np.random.default_rng(8)
+    a = torch.from_numpy(rng.standard_normal((3, 1000)).astype(np.float32)).to(dtype)
+    b = torch.from_numpy(rng.standard_normal((3, 1000)).astype(np.float32)).to(dtype)
+    assert torch.equal(ops.add(a.cuda(), b.cuda()).cpu(), (a.float() + b.float()).to(dtype))
+    assert _rel(ops.silu_mul(a.cuda(), b.cuda()), oracle.silu_mul(a.float().numpy(), b.float().numpy())) <= TOL[dtype]
+    table = torch.from_numpy(rng.standard_normal((50, 24)).astype(np.float32)).to(dtype)
+    ids = torch.tensor([3, 49, 0, 3], dtype=torch.int64)
+    assert torch.equal(ops.embedding_gather(table.cuda(), ids.cuda()).cpu(), table[ids])
+    logits = torch.from_numpy(rng.standard_normal((4, 5000)).astype(np.float32)).to(dtype)
+    logits[1, 77] = 100.0
+    logits[2, 10] = logits[2, 4000] = 50.0             # tie -> lowest index
+    got = ops.argmax_rows(logits.cuda()).cpu()
+    assert torch.equal(got, logits.float().argmax(dim=-1))
+    assert got[1] == 77 and got[2] == 10
+
+
+def test_advance_positions():
+    ops = _ops()
+    lens = torch.tensor([0, 5, 31], dtype=torch.int32, device="cuda")
+    pos = torch.zeros_like(lens)
+    ops.advance_positions(pos, lens)
+    assert pos.tolist() == [0, 5, 31] and lens.tolist() == [1, 6, 32]
