@@ -1,0 +1,546 @@
+#!/usr/bin/env python
+"""Decode-throughput benchmark of the CacheIR batched decode step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (default): the Llama-3-8B-shaped random-init decoder of the reference's
+headline configuration -- 32 layers, hidden 4096, 32 query / 8 KV heads,
+head_dim 128, FFN 14336, vocab 128256, int8 per-channel weights (fp32 scale +
+zero point per row, the reference's pack format), fp16 activations and KV pages
+of 16 tokens; batch 32 requests, each with 2048 cached context tokens; greedy
+decode. Weights are N(0, 0.02) generated and packed on the device, the KV cache
+is pre-filled with N(0,1): synthetic data of the benchmark's shapes.
+
+One "step" is one decode step of the whole batch. Reported on one JSON line:
+  value         tokens/s with all state resident in HBM (CUDA-graph replay with
+                on-device argmax feedback), timed with CUDA events, max over ranks
+  e2e           tokens/s through `run_decode_batch(sessions, token_ids)` with host
+                token lists in and host argmax ids out every step (H2D/D2H inside)
+  roofline      achieved HBM GB/s of the dominant kernel (paged decode attention),
+                timed alone with CUDA events over all layers' page pools, against
+                the measured copy bandwidth in MEASURED_PEAKS.json
+  cpu_baseline  the reference's CPU algorithm (NumPy dequantize-then-matmul +
+                gather attention) timed on this host on a bounded sample
+With --gpus N (launched under torchrun) every rank runs its own batch of 32
+requests on its own weight replica: data parallel by sequence, no collective in
+the step ("scaling": "weak").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "decode_tokens_per_s"
+UNIT = "tokens/s"
+
+WORKLOADS = {
+    # name: layers hidden heads kv_heads ffn vocab batch ctx
+    "llama3-8b-int8-b32-ctx2048": dict(layers=32, hidden=4096, heads=32, kv_heads=8, ffn=14336, vocab=128256,
+                                       batch=32, ctx=2048, quant="int8"),
+    "small": dict(layers=2, hidden=1024, heads=8, kv_heads=2, ffn=2816, vocab=4096, batch=8, ctx=256, quant="int8"),
+}
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms during the timed region."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.rows: list[list[str]] = []
+        self.proc: subprocess.Popen | None = None
+        self.thread: threading.Thread | None = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump() -> None:
+            assert self.proc is not None and self.proc.stdout is not None
+            for line in self.proc.stdout:
+                self.rows.append([c.strip() for c in line.split(",")])
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        sm, sm_max, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            if len(row) < 9:
+                continue
+            try:
+                sm.append(float(row[1]))
+                sm_max.append(float(row[2]))
+            except ValueError:
+                continue
+            for name, cell in zip(names, row[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------
+def build_runtime(cfg: dict, device_index: int, extra_tokens: int):
+    import torch
+
+    from cacheir_b200 import B200DecodeRuntime, B200KVPageAllocator, ModelConfig, build_decoder_artifact
+
+    head_dim = cfg["hidden"] // cfg["heads"]
+    mc = ModelConfig(architecture="LlamaForCausalLM", hidden_size=cfg["hidden"], intermediate_size=cfg["ffn"],
+                     num_layers=cfg["layers"], num_attention_heads=cfg["heads"], num_key_value_heads=cfg["kv_heads"],
+                     vocab_size=cfg["vocab"], max_position_embeddings=cfg["ctx"] + extra_tokens, rope_theta=500000.0,
+                     rms_norm_eps=1e-5, dtype="float16")
+    art = build_decoder_artifact(mc, target="cuda", quant=cfg["quant"], modes=("decode",))
+    dev = torch.device("cuda", device_index)
+    gen = torch.Generator(device=dev)
+
+    def synth(key: str, shape: tuple[int, ...]) -> "torch.Tensor":
+        # random-init weights of the reference's tiny-model recipe at full shape: N(0, 0.02), norms = 1
+        if len(shape) == 1:
+            return torch.ones(shape, device=dev, dtype=torch.float32)
+        gen.manual_seed(abs(hash(key)) % (2 ** 31))
+        return torch.randn(shape, device=dev, dtype=torch.float32, generator=gen) * 0.02
+
+    page = 16
+    pages_per_seq = (cfg["ctx"] + extra_tokens + page - 1) // page + 1
+    alloc = B200KVPageAllocator(page_size=page, initial_slots=cfg["batch"] * pages_per_seq + 8)
+    rt = B200DecodeRuntime(art, device=f"cuda:{device_index}", dtype="float16", tensor_source=synth,
+                           kv_allocator=alloc, max_seq_len=cfg["ctx"] + extra_tokens, clone_outputs=False)
+    del head_dim
+    return rt, art
+
+
+def prefill_synthetic_context(rt, cfg: dict):
+    """`batch` sessions with `ctx` cached tokens each: pages are allocated through the
+    allocator, their contents are N(0,1) (stand-in for a real prompt's K/V)."""
+    import torch
+
+    sessions = [rt.fork() for _ in range(cfg["batch"])]
+    for s in sessions:
+        s.kv_cache.extend(cfg["ctx"])
+    gen = torch.Generator(device=rt.device)
+    gen.manual_seed(1234)
+    for layer in range(cfg["layers"]):
+        pool = rt.kv_allocator.pool_for_layer(layer)
+        pool["keys"].normal_(generator=gen)
+        pool["values"].normal_(generator=gen)
+    return sessions
+
+
+def step_bytes(cfg: dict, ctx: int) -> dict:
+    """Algorithmic HBM bytes of one decode step: every weight byte once, every cached K/V row once."""
+    h, f, v, L = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["layers"]
+    hd = h // cfg["heads"]
+    kvd = cfg["kv_heads"] * hd
+    bits = 8 if cfg["quant"] == "int8" else 4
+    rows = (h + 2 * kvd) + h + 2 * f + h          # q,k,v | o | gate,up | down
+    layer_w = ((h + 2 * kvd) * h + h * h + 2 * f * h + h * f) * bits // 8 + rows * 8
+    weights = L * layer_w + v * h * bits // 8 + v * 8
+    kv = L * cfg["batch"] * ctx * kvd * 2 * 2
+    return {"weights": weights, "kv": kv, "total": weights + kv}
+
+
+def time_attention_kernel(rt, sessions, cfg: dict, iters: int = 3) -> dict:
+    """The dominant kernel alone: one launch per layer over that layer's page pool (each
+    pool is larger than L2, so every launch streams from HBM), CUDA events on the launch stream."""
+    import torch
+
+    from cacheir_b200 import ops
+
+    B, H, KVH = cfg["batch"], cfg["heads"], cfg["kv_heads"]
+    hd = cfg["hidden"] // H
+    plan = rt._engine.plan_for(sessions)
+    lens = torch.tensor([s.kv_cache.tokens for s in sessions], dtype=torch.int32, device=rt.device)
+    q = torch.randn((B, H, hd), device=rt.device, dtype=torch.float16)
+    out = torch.empty_like(q)
+    splits = ops.attention_auto_splits(B, H, KVH, plan.width, 16, hd)
+    ws = torch.empty(max(1, ops.attention_workspace_bytes(B, H, hd, splits) // 4), device=rt.device, dtype=torch.float32)
+    pools = [rt.kv_allocator.pool_for_layer(l) for l in range(cfg["layers"])]
+
+    def sweep() -> None:
+        for pool in pools:
+            ops.paged_attention_decode_batch(q, pool["keys"], pool["values"], plan.page_table, lens, out=out,
+                                             num_splits=splits, workspace=ws)
+
+    sweep()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        sweep()
+    end.record()
+    torch.cuda.synchronize()
+    per_launch_s = start.elapsed_time(end) * 1e-3 / (iters * len(pools))
+    total_ctx = int(lens.sum().item())
+    algo = total_ctx * KVH * hd * 2 * 2 + 2 * B * H * hd * 2 + B * plan.width * 4 + B * 4
+    return {"kernel": "paged_attention_decode_batch", "seconds": per_launch_s, "bytes": algo, "splits": splits}
+
+
+def time_gemv_kernels(rt, cfg: dict, iters: int = 3) -> list[dict]:
+    """Each projection shape alone, cycling over the layers' weights (cold in L2)."""
+    import torch
+
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul
+
+    eng = rt._engine
+    B = cfg["batch"]
+    groups: dict[str, list] = {"qkv": [], "o": [], "gate_up": [], "down": []}
+    for names, w in eng.fused_weights.items():
+        n0 = names[0]
+        if n0.endswith("_q_w"):
+            groups["qkv"].append(w)
+        elif n0.endswith("_o_w"):
+            groups["o"].append(w)
+        elif n0.endswith("_gate_w"):
+            groups["gate_up"].append(w)
+        elif n0.endswith("_down_w"):
+            groups["down"].append(w)
+    results = []
+    for name, ws in groups.items():
+        if not ws:
+            continue
+        n, k = ws[0].shape
+        epi = ops.EPI_SWIGLU if name == "gate_up" else ops.EPI_NONE
+        x = torch.randn((B, k), device=rt.device, dtype=torch.float16)
+        out = torch.empty((B, n // 2 if epi == ops.EPI_SWIGLU else n), device=rt.device, dtype=torch.float16)
+        for w in ws:
+            quantized_matmul(x, w, epilogue=epi, out=out)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(iters):
+            for w in ws:
+                quantized_matmul(x, w, epilogue=epi, out=out)
+        end.record()
+        torch.cuda.synchronize()
+        sec = start.elapsed_time(end) * 1e-3 / (iters * len(ws))
+        algo = ws[0].nbytes + B * k * 2 + out.numel() * 2
+        results.append({"kernel": f"qgemv_int{ws[0].bits}_{name}", "shape": [B, n, k], "seconds": sec, "bytes": algo})
+    return results
+
+
+# --------------------------------------------------------------------------------------
+def cpu_reference_layer_step(cfg: dict, rng: np.random.Generator, weights: dict, kv: dict, x: np.ndarray,
+                             rows_fraction: float = 1.0) -> np.ndarray:
+    """One decoder layer of one decode step with the reference's CPU algorithm (dequantize the
+    whole weight, then matmul; gather K/V, attention), batch `x.shape[0]`."""
+    from oracle import oracle, ref_native
+
+    h = cfg["hidden"]
+    heads, kv_heads = cfg["heads"], cfg["kv_heads"]
+    hd = h // heads
+    use_native = ref_native.available()
+    norm = (lambda a, w: ref_native.rms_norm(a, w, 1e-5)) if use_native else (lambda a, w: oracle.rms_norm(a, w, 1e-5))
+    xn = norm(x, weights["norm"])
+    q = oracle.quantized_matmul(xn, weights["q"])
+    k = oracle.quantized_matmul(xn, weights["k"])
+    v = oracle.quantized_matmul(xn, weights["v"])
+    offsets = kv["lens"]
+    q = oracle.rope_one(q, hd, 500000.0, offsets)
+    k = oracle.rope_one(k, hd, 500000.0, offsets)
+    del v
+    attn = oracle.paged_attention_decode(q.reshape(-1, heads, hd), kv["k_pool"], kv["v_pool"], kv["table"], kv["lens"])
+    attn = attn.reshape(x.shape[0], 1, heads * hd)
+    hidden = x + oracle.quantized_matmul(attn, weights["o"])
+    hn = norm(hidden, weights["norm"])
+    gate = oracle.quantized_matmul(hn, weights["gate"])
+    up = oracle.quantized_matmul(hn, weights["up"])
+    gated = ref_native.silu_mul(gate, up) if use_native else oracle.silu_mul(gate, up)
+    return hidden + oracle.quantized_matmul(gated, weights["down"])
+
+
+def make_cpu_sample(cfg: dict, batch: int, ctx: int, seed: int = 0):
+    from oracle import oracle
+
+    rng = np.random.default_rng(seed)
+    h, f = cfg["hidden"], cfg["ffn"]
+    hd = h // cfg["heads"]
+    kvd = cfg["kv_heads"] * hd
+    bits = 8 if cfg["quant"] == "int8" else 4
+
+    def packed(n: int, k: int):
+        codes = rng.integers(0, 1 << bits, (n, k), dtype=np.uint8)
+        return oracle.PackedQuantizedTensor(oracle.pack_int4(codes) if bits == 4 else codes,
+                                            rng.uniform(1e-4, 2e-4, n).astype(np.float32),
+                                            np.full(n, 1 << (bits - 1), dtype=np.int32), bits, (n, k))
+
+    weights = {"norm": np.ones(h, dtype=np.float32), "q": packed(h, h), "k": packed(kvd, h), "v": packed(kvd, h),
+               "o": packed(h, h), "gate": packed(f, h), "up": packed(f, h), "down": packed(h, f)}
+    pages = (ctx + 15) // 16
+    kv = {"k_pool": rng.standard_normal((batch * pages, cfg["kv_heads"], 16, hd), dtype=np.float32),
+          "v_pool": rng.standard_normal((batch * pages, cfg["kv_heads"], 16, hd), dtype=np.float32),
+          "table": rng.permutation(batch * pages).astype(np.int32).reshape(batch, pages),
+          "lens": np.full(batch, ctx, dtype=np.int32)}
+    x = rng.standard_normal((batch, 1, h), dtype=np.float32)
+    return rng, weights, kv, x
+
+
+def cpu_threads() -> int:
+    try:
+        from threadpoolctl import threadpool_info
+        counts = [int(p.get("num_threads", 1)) for p in threadpool_info()]
+        if counts:
+            return max(counts)
+    except Exception:
+        pass
+    return os.cpu_count() or 1
+
+
+def run_cpu_baseline(cfg: dict, budget_s: float = 20.0) -> dict:
+    """Tokens/s of the reference's CPU algorithm, from a bounded sample: repeated single-layer
+    decode steps at full batch and context, extrapolated linearly to all layers (the lm_head is
+    charged as vocab/ffn-proportional extra matmul rows)."""
+    from oracle import ref_native
+
+    rng, weights, kv, x = make_cpu_sample(cfg, cfg["batch"], cfg["ctx"])
+    cpu_reference_layer_step(cfg, rng, weights, kv, x)   # warm
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while time.perf_counter() < t_end and len(times) < 8:
+        t0 = time.perf_counter()
+        cpu_reference_layer_step(cfg, rng, weights, kv, x)
+        times.append(time.perf_counter() - t0)
+    layer_s = float(np.median(times))
+    layer_rows = 2 * cfg["hidden"] + 2 * cfg["kv_heads"] * (cfg["hidden"] // cfg["heads"]) + 3 * cfg["ffn"]
+    lm_head_s = layer_s * cfg["vocab"] / (layer_rows * 1.6)   # matmul share of a layer step, by rows
+    step_s = layer_s * cfg["layers"] + lm_head_s
+    return {"value": cfg["batch"] / step_s, "unit": UNIT, "cores": cpu_threads(), "kind": "port",
+            "sample": (f"{len(times)} x one decoder layer of one decode step (batch {cfg['batch']}, ctx {cfg['ctx']}; "
+                       f"NumPy dequantize-then-matmul + gather attention"
+                       f"{', reference C++/OpenMP rms_norm+silu_mul' if ref_native.available() else ''}), "
+                       f"median {layer_s:.3f} s/layer, extrapolated to {cfg['layers']} layers + lm_head")}
+
+
+def run_reference_arm(args, cfg: dict, workload: str) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import ref_native
+
+    total_steps = args.steps + args.warmup
+    budget = 150.0
+    rng, weights, kv, x = make_cpu_sample(cfg, cfg["batch"], cfg["ctx"])
+    t0 = time.perf_counter()
+    cpu_reference_layer_step(cfg, rng, weights, kv, x)
+    first = time.perf_counter() - t0
+    # A step of this arm is one decoder layer of one decode step at full batch/context; if even that
+    # would overrun the time budget for K+W steps, shrink the batch of the sample (time is ~linear in it
+    # for the attention part and constant for the dequantisation, so the extrapolation is conservative).
+    sample_batch = cfg["batch"]
+    while first * total_steps > budget and sample_batch > 1:
+        sample_batch //= 2
+        rng, weights, kv, x = make_cpu_sample(cfg, sample_batch, cfg["ctx"])
+        t0 = time.perf_counter()
+        cpu_reference_layer_step(cfg, rng, weights, kv, x)
+        first = time.perf_counter() - t0
+    for _ in range(args.warmup):
+        cpu_reference_layer_step(cfg, rng, weights, kv, x)
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(args.steps):
+        cpu_reference_layer_step(cfg, rng, weights, kv, x)
+        done += 1
+    elapsed = time.perf_counter() - t0
+    layer_s = elapsed / max(1, done)
+    layer_rows = 2 * cfg["hidden"] + 2 * cfg["kv_heads"] * (cfg["hidden"] // cfg["heads"]) + 3 * cfg["ffn"]
+    step_s = layer_s * cfg["layers"] + layer_s * cfg["vocab"] / (layer_rows * 1.6)
+    value = sample_batch / step_s
+    sample = (f"each step = one decoder layer of one decode step (batch {sample_batch} of {cfg['batch']}, ctx {cfg['ctx']}) with "
+              f"the reference CPU algorithm (NumPy dequantize-then-matmul, gather attention"
+              f"{', reference C++/OpenMP rms_norm+silu_mul' if ref_native.available() else ''}); "
+              f"tokens/s extrapolated to {cfg['layers']} layers + lm_head")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload, "batch": cfg["batch"], "context": cfg["ctx"], "layers": cfg["layers"],
+                       "l2_policy": "inputs larger than L2"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cpu_threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--warmup", type=int, default=4)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--workload", default="llama3-8b-int8-b32-ctx2048", choices=sorted(WORKLOADS))
+    parser.add_argument("--e2e-steps", type=int, default=32)
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    cfg = dict(WORKLOADS[args.workload])
+    warmup = max(3, args.warmup)
+
+    if args.impl == "reference":
+        run_reference_arm(args, cfg, args.workload)
+        return
+
+    import torch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: cacheir_b200 has no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # type: ignore[no-redef]
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+
+    e2e_steps = max(4, args.e2e_steps)
+    extra = warmup + args.steps + e2e_steps + 3 + 48
+    rt, _ = build_runtime(cfg, local_rank, extra)
+    sessions = prefill_synthetic_context(rt, cfg)
+    first_tokens = [int(t) for t in np.random.default_rng(rank).integers(0, cfg["vocab"], cfg["batch"])]
+
+    def barrier() -> None:
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident loop: `value` ------------------------------------------------
+    toks = rt.decode_greedy_batch(sessions, first_tokens, warmup)     # eager step, graph capture, replays
+    last = [int(t) for t in toks[-1].tolist()]
+    plan = rt._engine.plan_for(sessions)
+    launches_per_step = plan.launches_per_step + 1                    # + the feedback argmax
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    toks = rt.decode_greedy_batch(sessions, last, args.steps)
+    end.record()
+    barrier()
+    elapsed_s = start.elapsed_time(end) * 1e-3
+    clocks = sampler.stop()
+    last = [int(t) for t in toks[-1].tolist()]
+    ctx_mid = cfg["ctx"] + warmup + args.steps // 2
+    if dist is not None:
+        t = torch.tensor([elapsed_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_s = float(t.item())
+    tokens_total = world * cfg["batch"] * args.steps
+    value = tokens_total / elapsed_s
+
+    # ---- host-facing loop: `e2e` ------------------------------------------------------
+    from cacheir_b200.scheduler import argmax_tokens
+
+    token_ids = last
+    for _ in range(2):
+        token_ids = argmax_tokens(rt.run_decode_batch(sessions, token_ids))
+    barrier()
+    h2d = d2h = 0
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        pages_before = sum(len(s.kv_cache.pages) for s in sessions)
+        logits = rt.run_decode_batch(sessions, token_ids)             # host ids in (pinned staging + H2D)
+        token_ids = argmax_tokens(logits)                             # argmax ids out (D2H)
+        h2d += cfg["batch"] * 8
+        if sum(len(s.kv_cache.pages) for s in sessions) != pages_before:
+            h2d += plan.page_table.numel() * 4
+        d2h += cfg["batch"] * 8
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = world * cfg["batch"] * e2e_steps / e2e_s
+
+    # ---- per-kernel roofline (rank 0 reports) -------------------------------------------
+    peak, peak_kind = measured_peaks()
+    attn = time_attention_kernel(rt, sessions, cfg)
+    gemvs = time_gemv_kernels(rt, cfg)
+    kernels = []
+    for k in [attn] + gemvs:
+        gbs = k["bytes"] / k["seconds"] / 1e9
+        kernels.append({"kernel": k["kernel"], "us": round(k["seconds"] * 1e6, 2), "algorithmic_bytes": int(k["bytes"]),
+                        "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4), **({"shape": k["shape"]} if "shape" in k else {})})
+    sb = step_bytes(cfg, ctx_mid)
+    step_gbs = sb["total"] / (elapsed_s / args.steps) / 1e9
+
+    if rank == 0:
+        traffic = None
+        prof = ROOT / "profiles" / "attention_traffic.json"
+        if prof.exists():
+            try:
+                traffic = json.loads(prof.read_text()).get("dram_bytes_per_launch_scaled")
+            except Exception:
+                traffic = None
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": elapsed_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": cfg["batch"], "context": cfg["ctx"],
+                       "layers": cfg["layers"], "weights": "int8 per-row affine (fp32 scale+zero)", "kv": "fp16 pages of 16",
+                       "parallelism": f"dp{world} by sequence, no collective", "l2_policy": "inputs larger than L2 (16 GB/step)"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d // e2e_steps, "d2h_bytes_per_step": d2h // e2e_steps,
+                    "steps": e2e_steps, "api": "B200DecodeRuntime.run_decode_batch + argmax_tokens"},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": attn["kernel"], "achieved": kernels[0]["achieved_gbs"], "peak": peak,
+                         "unit": "GB/s", "frac": kernels[0]["frac"], "traffic": traffic, "peak_source": f"of {peak_kind}",
+                         "algorithmic_bytes_per_launch": int(attn["bytes"]), "us_per_launch": kernels[0]["us"]},
+            "kernels": kernels,
+            "step": {"algorithmic_bytes": int(sb["total"]), "weight_bytes": int(sb["weights"]), "kv_bytes": int(sb["kv"]),
+                     "achieved_gbs": round(step_gbs, 1), "frac_of_hbm_roofline": round(step_gbs / peak, 4),
+                     "roofline_tokens_per_s": round(cfg["batch"] * peak * 1e9 / sb["total"], 1),
+                     "launches_per_step": launches_per_step},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = run_cpu_baseline(cfg)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -11,7 +11,9 @@ from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
-TOL = {torch.float32: 2e-5, torch.float16: 2e-3, torch.bfloat16: 2e-3}
+# bf16 keeps 8 significant bits: rounding the OUTPUT alone costs up to 2^-8 = 3.9e-3 relative
+# (about 1.6e-3 rms), so 2e-3 is not reachable on small outputs whatever the kernel does.
+TOL = {torch.float32: 2e-5, torch.float16: 2e-3, torch.bfloat16: 4e-3}
 DTYPES = [torch.float32, torch.float16, torch.bfloat16]
 
 

@@ -120,3 +120,26 @@ def test_tiny_model_greedy_tokens_match_reference(golden_dir):
         np.testing.assert_allclose(logits[0], g[f"{tag}_prefill_logits_last"], rtol=1e-4, atol=1e-5)
         np.testing.assert_array_equal(
             np.asarray([[p.page_id, p.start, p.length] for p in rt.pages[0]]), g[f"{tag}_pages_layer0"])
+
+
+def test_oracle_agrees_with_reference_native_kernels():
+    # the reference's own native-vs-NumPy check (tests/test_advanced_experiments.py:440-452,
+    # tests/test_runtime.py:34-41), run against its C++ kernels compiled from its sources
+    import pytest
+    from oracle import ref_native
+
+    if not ref_native.available():
+        pytest.skip("oracle/_ref not built (needs the reference checkout: make -C oracle)")
+    assert ref_native.simd_backend() in {"avx512", "avx2", "scalar"}
+    x = (np.arange(24, dtype=np.float32).reshape(1, 3, 8) / 10.0).astype(np.float32)
+    w = np.ones(8, dtype=np.float32)
+    np.testing.assert_allclose(ref_native.rms_norm(x, w, 1e-6), oracle.rms_norm(x, w, 1e-6), rtol=1e-5, atol=1e-6)
+    weight = (np.arange(32, dtype=np.float32).reshape(4, 8) / 100.0).astype(np.float32)
+    np.testing.assert_allclose(ref_native.matmul_out_in(x, weight), oracle.matmul(x, weight), rtol=1e-5, atol=1e-6)
+    gate = np.linspace(-3.0, 3.0, num=24, dtype=np.float32).reshape(2, 3, 4)
+    up = np.linspace(0.5, 2.0, num=24, dtype=np.float32).reshape(2, 3, 4)
+    np.testing.assert_allclose(ref_native.silu_mul(gate, up), oracle.silu_mul(gate, up), rtol=1e-6, atol=1e-6)
+    rng = np.random.default_rng(0)
+    xb = rng.standard_normal((2, 5, 300)).astype(np.float32)
+    wb = rng.standard_normal((77, 300)).astype(np.float32)
+    np.testing.assert_allclose(ref_native.matmul_out_in(xb, wb), oracle.matmul(xb, wb), rtol=1e-4, atol=1e-4)
