@@ -346,3 +346,48 @@ extern "C" int cacheir_b200_paged_attention_decode_batch(
     default: return launch_combine<__nv_bfloat16>(p, st);
   }
 }
+
+// ---- allocation-free variant -------------------------------------------------------
+// Split-K scratch that lives inside the library image: callers that cannot obtain
+// device memory themselves use this instead of passing a workspace.
+#define CB200_NOALLOC_WORKSPACE_BYTES (16u * 1024u * 1024u)
+static __device__ __align__(256) float g_noalloc_attention_workspace[CB200_NOALLOC_WORKSPACE_BYTES / sizeof(float)];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of the array above, looked up once per device. In host code the
+// array's name is only a handle for the runtime, never a pointer a kernel may use.
+void* g_noalloc_ws_ptr[kMaxDevices] = {};
+}  // namespace
+
+extern "C" size_t cacheir_b200_paged_attention_noalloc_max_workspace_bytes(void) {
+  return CB200_NOALLOC_WORKSPACE_BYTES;
+}
+
+extern "C" int cacheir_b200_paged_attention_decode_batch_noalloc(
+    const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
+    const int32_t* seq_lens, void* out, int batch_size, int num_heads, int num_kv_heads,
+    int max_pages_per_seq, int page_size, int head_dim, int dtype, long long q_batch_stride,
+    long long out_batch_stride, float softmax_scale, int num_splits, void* stream) {
+  if (batch_size <= 0 || num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0) return 0;
+  if (max_pages_per_seq <= 0 || page_size <= 0 || num_splits < 0) return CACHEIR_B200_EINVAL;
+  int splits = 1, chunk = 0;
+  resolve_attention_splits(batch_size, num_heads, num_kv_heads, max_pages_per_seq, page_size, num_splits,
+                           &splits, &chunk);
+  const size_t need = cacheir_b200_paged_attention_workspace_bytes(batch_size, num_heads, head_dim, splits);
+  if (need > CB200_NOALLOC_WORKSPACE_BYTES) return CACHEIR_B200_ELIMIT;
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  if (device < 0 || device >= kMaxDevices) return CACHEIR_B200_ELIMIT;
+  void* ws = g_noalloc_ws_ptr[device];
+  if (ws == nullptr) {  // first call on this device: resolve the symbol with this device current
+    err = cudaGetSymbolAddress(&ws, g_noalloc_attention_workspace);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    g_noalloc_ws_ptr[device] = ws;
+  }
+  return cacheir_b200_paged_attention_decode_batch(
+      q, k_cache, v_cache, page_table, seq_lens, out, batch_size, num_heads, num_kv_heads,
+      max_pages_per_seq, page_size, head_dim, dtype, q_batch_stride, out_batch_stride, softmax_scale,
+      num_splits, ws, CB200_NOALLOC_WORKSPACE_BYTES, stream);
+}

@@ -95,6 +95,37 @@ int cacheir_b200_paged_attention_decode_batch(
     long long out_batch_stride, float softmax_scale, int num_splits,
     void* workspace, size_t workspace_bytes, void* stream);
 
+/* Allocation-free variant of cacheir_b200_paged_attention_decode_batch. It has no
+ * counterpart in the reference; it exists for callers that have inputs and outputs
+ * but no way to get scratch memory on the device: code bound to the reference's own
+ * launcher signature (cpp/src/cacheir_cuda_kernels.cu:357-369 carries no workspace
+ * argument), plug-ins of a serving process that handed all of HBM to its weight and
+ * KV arenas at start-up, and hosts that run under a fixed device-memory budget and
+ * treat any later cudaMalloc as an error. Same arguments and results as the entry
+ * point above, minus the workspace: the split-K partials go to a 16 MiB array that is
+ * part of the library image (every GPU that loads the library holds those 16 MiB
+ * until the process exits). The call performs no cudaMalloc/cudaFree and calls no
+ * allocating routine.
+ *   - Limit: extents whose partials need more than
+ *     cacheir_b200_paged_attention_noalloc_max_workspace_bytes() return
+ *     CACHEIR_B200_ELIMIT and launch nothing; pass a smaller num_splits (1 needs no
+ *     scratch at all) or use the workspace entry point.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call before
+ *     any stream capture begins.
+ *   - All calls share the one array. It keeps whatever the previous call left in it;
+ *     nothing in it has to start at zero, because every partial that the combine step
+ *     reads is written earlier in the same call. Two calls that overlap on the GPU
+ *     (different streams, or different threads without ordering) race on it: issue
+ *     them on one stream or order them with events. */
+size_t cacheir_b200_paged_attention_noalloc_max_workspace_bytes(void);
+int cacheir_b200_paged_attention_decode_batch_noalloc(
+    const void* q, const void* k_cache, const void* v_cache,
+    const int32_t* page_table, const int32_t* seq_lens, void* out,
+    int batch_size, int num_heads, int num_kv_heads, int max_pages_per_seq,
+    int page_size, int head_dim, int dtype, long long q_batch_stride,
+    long long out_batch_stride, float softmax_scale, int num_splits, void* stream);
+
 /* ------------------------------------------------------------------------
  * Packed int4/int8 dequant-GEMV / small-M GEMM:  y[M,N] = x[M,K] . deq(W)[N,K]^T
  *
