@@ -1,8 +1,466 @@
-// Tensor-core small-M dequant-GEMM (placeholder until the tcgen05 kernel lands).
+// Small-M dequant-GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
+//
+//   y[M, N] = x[M, K] . deq(W)[N, K]^T        M <= 64, fp16 activations
+//
+// The weight matrix is the 128-row MMA operand ("swap-AB"): one CTA owns 128
+// weight rows and the whole K range, the M activation rows are the MMA's N
+// dimension (padded to MP = 16/32/64), the fp32 accumulator D[128 x MP] lives
+// in tensor memory. Weight codes never exist in HBM in any other form than the
+// reference's packed bytes:
+//
+//   warp 0      TMA producer: raw code tile [128 rows x 128 k] (16 KB int8 / 8 KB
+//               int4, hardware-swizzled so that row-per-thread reads are
+//               conflict free) + the x tile [MP x 128 k] per pipeline stage
+//   warps 4-7   converters: thread r owns weight row r of the tile; unpacks its
+//               codes in registers (byte/nibble -> fp16 through the 0x6400
+//               mantissa trick, zero point removed exactly) and writes the fp16
+//               operand tile in the canonical no-swizzle UMMA layout
+//   warp 1      one thread issues tcgen05.mma (M=128, N=MP, K=16) x 8 per stage and
+//               commits to the barriers that recycle the stages
+//   warps 4-7   epilogue: tcgen05.ld the accumulator row, apply the row scale,
+//               residual add or SiLU*mul, store y
+//
+// Every wait is bounded: a barrier that does not complete within the poll budget
+// raises a device status flag and the CTA drains and exits instead of hanging.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "qgemv_common.cuh"
 
 namespace cb200 {
-bool qgemm_tc_supported(const QGemvParams&) { return false; }
-int launch_qgemm_tc(const QGemvParams&, cudaStream_t) { return CACHEIR_B200_EUNSUPPORTED; }
+namespace {
+
+constexpr int kBlockN = 128;      // weight rows per CTA (UMMA M)
+constexpr int kBlockK = 128;      // k elements per pipeline stage
+constexpr int kStages = 4;        // raw-code + x stages in flight
+constexpr int kAStages = 2;       // converted fp16 operand tiles
+constexpr int kThreads = 256;
+constexpr int kATileBytes = kBlockN * kBlockK * 2;      // 32 KB
+constexpr uint32_t kPollLimit = 8u * 1000u * 1000u;
+
+__device__ int g_qgemm_status = 0;   // 0 ok; otherwise (code << 8 | barrier id) of the first wait that gave up
+
+// ---- PTX wrappers ------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+// Bounded wait. Returns false (and records which barrier) when the poll budget runs out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int id) {
+  for (uint32_t i = 0; i < kPollLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) __nanosleep(32);
+  }
+  atomicCAS(&g_qgemm_status, 0, (1 << 8) | id);
+  return false;
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (64 bit): start address, leading/stride byte offsets
+// (all >> 4), descriptor version 1 at bit 46, swizzle mode at bits 61-63.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(layout_type & 0x7) << 61;
+  return d;
+}
+
+struct TcParams {
+  const void* scales;
+  const float* zero_points;
+  const void* residual;
+  void* y;
+  int M, N, K;
+  int n_out;        // output columns (N, or N/2 with the SwiGLU epilogue)
+  int group_size;
+  int scale_dtype;
+  int epilogue;
+  int n_tiles;
+};
+
+__device__ __forceinline__ float load_scale(const void* scales, int scale_dtype, size_t idx) {
+  return scale_dtype == CACHEIR_B200_F16 ? __half2float(static_cast<const __half*>(scales)[idx])
+                                         : static_cast<const float*>(scales)[idx];
+}
+
+// Unpack 16 bytes of one weight row into fp16 and store them as UMMA core-matrix rows.
+// BITS 8: 16 codes -> k-chunks 2c, 2c+1.   BITS 4: 32 codes -> k-chunks 4c .. 4c+3.
+template <int BITS>
+__device__ __forceinline__ void convert_chunk_fast(const uint4 raw, int c, uint8_t* a_row_base, __half2 sub8, __half2 mul4,
+                                                   __half2 sub4, bool scaled, __half2 gscale) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  if (BITS == 8) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t o[4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t word = w[half * 2 + i];
+        const uint32_t lo = __byte_perm(word, 0x64646464u, 0x5140);   // (1024+b0, 1024+b1)
+        const uint32_t hi = __byte_perm(word, 0x64646464u, 0x5342);   // (1024+b2, 1024+b3)
+        __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&lo), sub8);
+        __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&hi), sub8);
+        if (scaled) { a = __hmul2(a, gscale); b = __hmul2(b, gscale); }
+        o[i * 2] = *reinterpret_cast<uint32_t*>(&a);
+        o[i * 2 + 1] = *reinterpret_cast<uint32_t*>(&b);
+      }
+      *reinterpret_cast<uint4*>(a_row_base + (2 * c + half) * 2048) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        // byte q -> (0x6400 | low nibble, 0x6400 | high nibble << 4) = (1024 + n0, 1024 + 16*n1)
+        const uint32_t t = __byte_perm(w[i], 0x64646464u, 0x4040 + 0x101 * q) & 0x64F0640Fu;
+        __half2 a = __hfma2(*reinterpret_cast<const __half2*>(&t), mul4, sub4);   // exact (n0 - z, n1 - z)
+        if (scaled) a = __hmul2(a, gscale);
+        o[q] = *reinterpret_cast<uint32_t*>(&a);
+      }
+      *reinterpret_cast<uint4*>(a_row_base + (4 * c + i) * 2048) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// Rows whose zero point is not a small integer: plain fp32 arithmetic, scale folded in.
+template <int BITS>
+__device__ __forceinline__ void convert_chunk_slow(const uint4 raw, int c, uint8_t* a_row_base, float zero, float scale) {
+  const uint8_t* bytes = reinterpret_cast<const uint8_t*>(&raw);
+  constexpr int CHUNKS = BITS == 8 ? 2 : 4;
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    __half vals[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int idx = j * 8 + e;
+      const float code = BITS == 8 ? static_cast<float>(bytes[idx])
+                                   : static_cast<float>((bytes[idx >> 1] >> ((idx & 1) * 4)) & 0xF);
+      vals[e] = __float2half_rn((code - zero) * scale);
+    }
+    *reinterpret_cast<uint4*>(a_row_base + (CHUNKS * c + j) * 2048) = *reinterpret_cast<const uint4*>(vals);
+  }
+}
+
+template <int BITS, int MP>
+__global__ void __launch_bounds__(kThreads, 1)
+qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
+  constexpr int kRawBytes = BITS == 8 ? kBlockN * 128 : kBlockN * 64;   // per stage
+  constexpr int kXBytes = MP * kBlockK * 2;
+  constexpr int kRawRow = BITS == 8 ? 128 : 64;
+  constexpr int kChunks = kRawRow / 16;                                  // 16-byte chunks per row per stage
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* s_raw = smem;                                   // kStages x kRawBytes
+  uint8_t* s_x = s_raw + kStages * kRawBytes;              // kStages x kXBytes      (1024-aligned: sizes are multiples of 1024)
+  uint8_t* s_a = s_x + kStages * kXBytes;                  // kAStages x 32 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_a + kAStages * kATileBytes);
+  uint64_t* full = bars;                                   // [kStages]   TMA landed
+  uint64_t* empty = bars + kStages;                        // [kStages]   converters (128) + MMA commit (1)
+  uint64_t* a_full = bars + 2 * kStages;                   // [kAStages]  converters (128)
+  uint64_t* a_empty = a_full + kAStages;                   // [kAStages]  MMA commit (1)
+  uint64_t* acc_full = a_empty + kAStages;                 // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const bool swiglu = p.epilogue == CACHEIR_B200_EPI_SWIGLU;
+  const int passes = swiglu ? 2 : 1;
+  const int kblocks = p.K / kBlockK;
+  const int total = kblocks * passes;
+  const int n0 = blockIdx.x * kBlockN;
+  constexpr int kTmemCols = (2 * MP) < 32 ? 32 : 2 * MP;   // power of two >= 32; two accumulators for SwiGLU
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 129); }
+    for (int t = 0; t < kAStages; ++t) { mbar_init(smem_u32(&a_full[t]), 128); mbar_init(smem_u32(&a_empty[t]), 1); }
+    mbar_init(smem_u32(acc_full), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // TMEM allocation is a warp-wide operation
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer ----------------
+      for (int i = 0; i < total; ++i) {
+        const int s = i % kStages;
+        const uint32_t ph = (i / kStages) & 1;
+        if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1, 1)) break;
+        const int pass = i / kblocks;
+        const int kb = i % kblocks;
+        const int row0 = n0 + pass * (p.N / 2);
+        const uint32_t bar = smem_u32(&full[s]);
+        mbar_expect_tx(bar, kRawBytes + kXBytes);
+        tma_load_2d(smem_u32(s_raw + s * kRawBytes), &tmap_w, bar, kb * kRawRow, row0);
+        tma_load_2d(smem_u32(s_x + s * kXBytes), &tmap_x, bar, kb * kBlockK, 0);
+        tma_load_2d(smem_u32(s_x + s * kXBytes + MP * 128), &tmap_x, bar, kb * kBlockK + 64, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer ----------------
+      // instruction descriptor: D=f32, A=B=f16, both K-major, N=MP, M=128
+      const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(MP >> 3) << 17) | (static_cast<uint32_t>(kBlockN >> 4) << 24);
+      bool ok = true;
+      for (int i = 0; i < total && ok; ++i) {
+        const int s = i % kStages;
+        const int t = i % kAStages;
+        ok = mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, 2) && mbar_wait(smem_u32(&a_full[t]), (i / kAStages) & 1, 3);
+        if (!ok) break;
+        tc_fence_after();
+        const int pass = i / kblocks;
+        const int kb = i % kblocks;
+        const uint32_t d = tmem_base + pass * MP;
+        const uint32_t a_base = smem_u32(s_a + t * kATileBytes);
+        const uint32_t x_base = smem_u32(s_x + s * kXBytes);
+#pragma unroll
+        for (int j = 0; j < kBlockK / 16; ++j) {
+          // A: no-swizzle K-major, core matrices 128 B; k-chunks 2048 B apart (LBO), 8-row groups 128 B apart (SBO)
+          const uint64_t a_desc = smem_desc(a_base + (2 * j) * 2048, 2048, 128, 0);
+          // B: 128-byte swizzled rows (TMA), 8-row groups 1024 B apart; 32 B per k step inside the 64-element span
+          const uint64_t b_desc = smem_desc(x_base + (j / 4) * (MP * 128) + (j % 4) * 32, 16, 1024, 2);
+          tc_mma_f16(d, a_desc, b_desc, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&a_empty[t]));   // operand tile and stage are free once these MMAs retire
+        tc_commit(smem_u32(&empty[s]));
+      }
+      tc_commit(smem_u32(acc_full));
+    }
+  } else if (warp >= 4) {
+    // ---------------- converters, then epilogue ----------------
+    const int r = threadIdx.x - 128;              // row of the tile owned by this thread (= TMEM lane)
+    const int swz = BITS == 8 ? (r & 7) : ((r >> 1) & 3);
+    bool ok = true;
+    float row_scale[2] = {1.f, 1.f};
+    for (int pass = 0; pass < passes && ok; ++pass) {
+      const int n = n0 + pass * (p.N / 2) + r;
+      const bool row_valid = n < (swiglu ? (pass + 1) * (p.N / 2) : p.N);
+      float zero = static_cast<float>(1 << (BITS - 1));
+      float scale = 1.f;
+      if (row_valid && p.group_size == 0) {
+        scale = load_scale(p.scales, p.scale_dtype, n);
+        if (p.zero_points) zero = p.zero_points[n];
+      }
+      // exact in-register zero-point removal needs an integer zero point that fp16 can offset exactly
+      const bool fast = (zero == rintf(zero)) && fabsf(zero) <= 960.f;
+      row_scale[pass] = (p.group_size == 0 && fast) ? scale : 1.f;
+      const __half2 sub8 = __float2half2_rn(1024.f + zero);
+      const __half2 mul4 = __floats2half2_rn(1.f, 0.0625f);
+      const __half2 sub4 = __floats2half2_rn(-(1024.f + zero), -(64.f + zero));
+      for (int kb = 0; kb < kblocks; ++kb) {
+        const int i = pass * kblocks + kb;
+        const int s = i % kStages;
+        const int t = i % kAStages;
+        ok = mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, 4) &&
+             mbar_wait(smem_u32(&a_empty[t]), ((i / kAStages) & 1) ^ 1, 5);
+        if (!ok) break;
+        const uint8_t* raw_row = s_raw + s * kRawBytes + r * kRawRow;
+        uint8_t* a_row = s_a + t * kATileBytes + (r >> 3) * 128 + (r & 7) * 16;
+        __half2 gscale = __float2half2_rn(1.f);
+        const bool scaled = p.group_size > 0;
+        if (scaled && row_valid) {
+          const int groups_per_row = p.K / p.group_size;
+          gscale = __float2half2_rn(load_scale(p.scales, p.scale_dtype,
+                                               static_cast<size_t>(n) * groups_per_row + (kb * kBlockK) / p.group_size));
+        }
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(raw_row + ((c ^ swz) * 16));
+          if (fast) convert_chunk_fast<BITS>(raw, c, a_row, sub8, mul4, sub4, scaled, gscale);
+          else convert_chunk_slow<BITS>(raw, c, a_row, zero, scale);
+        }
+        fence_proxy_async();                       // generic-proxy stores -> visible to the tensor core
+        mbar_arrive(smem_u32(&a_full[t]));
+        mbar_arrive(smem_u32(&empty[s]));
+      }
+    }
+    // ---- epilogue ----
+    if (ok && mbar_wait(smem_u32(acc_full), 0, 6)) {
+      tc_fence_after();
+      const int q = warp - 4;
+      const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      const int n_out_idx = n0 + r;
+      const bool store = n_out_idx < p.n_out;
+      __half* y = static_cast<__half*>(p.y);
+      const __half* res = static_cast<const __half*>(p.residual);
+#pragma unroll
+      for (int c0 = 0; c0 < MP; c0 += 16) {
+        uint32_t acc0[16], acc1[16];
+        tc_ld_x16(lane_base + c0, acc0);
+        if (swiglu) tc_ld_x16(lane_base + MP + c0, acc1);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = c0 + j;
+          if (m < p.M && store) {
+            float v = __uint_as_float(acc0[j]) * row_scale[0];
+            const size_t o = static_cast<size_t>(m) * p.n_out + n_out_idx;
+            if (swiglu) {
+              const float u = __uint_as_float(acc1[j]) * row_scale[1];
+              v = (v / (1.f + __expf(-v))) * u;
+            } else if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
+              v += __half2float(res[o]);
+            }
+            y[o] = __float2half_rn(v);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  }
+  return fn;
+}
+
+bool encode_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t inner, uint64_t outer,
+               uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  return fn(map, type, 2, const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BITS, int MP>
+int launch_tc(const QGemvParams& q, cudaStream_t stream) {
+  constexpr int kRawBytes = BITS == 8 ? kBlockN * 128 : kBlockN * 64;
+  constexpr int kXBytes = MP * kBlockK * 2;
+  constexpr size_t kSmem = 1024 + kStages * (kRawBytes + kXBytes) + kAStages * kATileBytes + 256;
+  CUtensorMap tmap_w, tmap_x;
+  const uint64_t row_bytes = BITS == 8 ? static_cast<uint64_t>(q.K) : static_cast<uint64_t>(q.K / 2);
+  if (!encode_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, q.packed, row_bytes, static_cast<uint64_t>(q.N), row_bytes,
+                 BITS == 8 ? 128 : 64, kBlockN, BITS == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
+    return CACHEIR_B200_EUNSUPPORTED;
+  if (!encode_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, q.x, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.M),
+                 static_cast<uint64_t>(q.x_stride) * 2, 64, MP, CU_TENSOR_MAP_SWIZZLE_128B))
+    return CACHEIR_B200_EUNSUPPORTED;
+  TcParams p{};
+  p.scales = q.scales; p.zero_points = q.zero_points; p.residual = q.residual; p.y = q.y;
+  p.M = q.M; p.N = q.N; p.K = q.K;
+  p.n_out = q.epilogue == CACHEIR_B200_EPI_SWIGLU ? q.N / 2 : q.N;
+  p.group_size = q.group_size; p.scale_dtype = q.scale_dtype; p.epilogue = q.epilogue;
+  p.n_tiles = (p.n_out + kBlockN - 1) / kBlockN;
+  auto kern = qgemm_tc_kernel<BITS, MP>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  kern<<<p.n_tiles, kThreads, kSmem, stream>>>(tmap_w, tmap_x, p);
+  return launch_status();
+}
+
+template <int BITS>
+int launch_tc_mp(const QGemvParams& q, cudaStream_t stream) {
+  if (q.M <= 16) return launch_tc<BITS, 16>(q, stream);
+  if (q.M <= 32) return launch_tc<BITS, 32>(q, stream);
+  return launch_tc<BITS, 64>(q, stream);
+}
+
+}  // namespace
+
+bool qgemm_tc_supported(const QGemvParams& q) {
+  if (q.x_dtype != CACHEIR_B200_F16) return false;
+  if (q.bits != 4 && q.bits != 8) return false;
+  if (q.M < 1 || q.M > 64) return false;
+  if (q.K % kBlockK != 0 || q.K < kBlockK) return false;
+  if (q.group_size != 0 && q.group_size % kBlockK != 0) return false;   // one scale per row and k block
+  if (q.epilogue == CACHEIR_B200_EPI_SWIGLU && (q.N / 2) % kBlockN != 0) return false;
+  if (!aligned_to(q.packed, 16) || !aligned_to(q.x, 16) || (q.x_stride * 2) % 16 != 0) return false;
+  return get_encode_fn() != nullptr;
+}
+
+int launch_qgemm_tc(const QGemvParams& q, cudaStream_t stream) {
+  return q.bits == 8 ? launch_tc_mp<8>(q, stream) : launch_tc_mp<4>(q, stream);
+}
+
+int qgemm_tc_device_status(bool reset) {
+  int status = 0;
+  if (cudaMemcpyFromSymbol(&status, g_qgemm_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && status != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_qgemm_status, &zero, sizeof(int));
+  }
+  return status;
+}
+
 }  // namespace cb200

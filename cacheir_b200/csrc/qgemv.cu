@@ -226,3 +226,5 @@ extern "C" int cacheir_b200_qgemv(const void* x, const void* packed, const void*
   if (qgemm_tc_supported(p)) return launch_qgemm_tc(p, st);
   return launch_qgemv_cuda_core(p, st);
 }
+
+extern "C" int cacheir_b200_device_status(int reset) { return qgemm_tc_device_status(reset != 0); }

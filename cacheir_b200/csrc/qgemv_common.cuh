@@ -27,5 +27,7 @@ int launch_qgemv_cuda_core(const QGemvParams& p, cudaStream_t stream);
 // Tensor-core (tcgen05) small-M GEMM: weights are the 128-row MMA operand.
 bool qgemm_tc_supported(const QGemvParams& p);
 int launch_qgemm_tc(const QGemvParams& p, cudaStream_t stream);
+// Device-side status word of the tensor-core kernel (0 = no bounded wait ever gave up).
+int qgemm_tc_device_status(bool reset);
 
 }  // namespace cb200

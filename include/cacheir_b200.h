@@ -154,6 +154,12 @@ int cacheir_b200_qgemv(const void* x, const void* packed, const void* scales,
                        int x_dtype, int scale_dtype, long long x_stride,
                        int epilogue, void* stream);
 
+/* Status word of the kernels that wait on hardware barriers (the tensor-core GEMM):
+ * 0, or a non-zero code recorded by the first wait that ran out of its poll budget
+ * (the kernel then drains and returns instead of hanging; its output is undefined).
+ * Synchronises with the device. `reset` != 0 clears the word after reading it. */
+int cacheir_b200_device_status(int reset);
+
 /* ------------------------------------------------------------------------
  * Quantization loader on the device.
  *

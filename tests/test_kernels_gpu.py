@@ -313,3 +313,76 @@ def test_advance_positions():
     pos = torch.zeros_like(lens)
     ops.advance_positions(pos, lens)
     assert pos.tolist() == [0, 5, 31] and lens.tolist() == [1, 6, 32]
+
+
+# ---- tensor-core (tcgen05) small-M dequant-GEMM: fp16 activations, K % 128 == 0 -----------
+def _device_status_ok():
+    from cacheir_b200 import _lib
+    status = _lib.load().cacheir_b200_device_status(1)
+    assert status == 0, f"a bounded device wait gave up: status {status:#x}"
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 32, 64])
+@pytest.mark.parametrize("n,k", [(512, 1024), (200, 256), (128, 4096)])
+def test_qgemm_tensor_core_per_row_affine(bits, m, n, k):
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(bits * 1000 + m * 10 + n + k)
+    x, packed = _qgemv_case(rng, m, n, k, bits, torch.float16)
+    y = quantized_matmul(x.cuda(), _device_pack(packed))
+    torch.cuda.synchronize()
+    _device_status_ok()
+    want = oracle.quantized_matmul(x.float().numpy(), packed)
+    assert _rel(y, want) <= TOL[torch.float16]
+
+
+@pytest.mark.parametrize("m", [1, 32, 64])
+def test_qgemm_tensor_core_group128_int4_and_midpoint_int8(m):
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(300 + m)
+    x, packed = _qgemv_case(rng, m, 384, 2048, 4, torch.float16, group=128)
+    y = quantized_matmul(x.cuda(), _device_pack(packed))
+    assert _rel(y, oracle.quantized_matmul(x.float().numpy(), packed)) <= TOL[torch.float16]
+    x, packed = _qgemv_case(rng, m, 256, 1024, 8, torch.float16, reference_pack=False)   # fp16 scales, zero = 128
+    dev = _device_pack(packed)
+    dev.scales = torch.from_numpy(packed.scales).cuda()
+    y = quantized_matmul(x.cuda(), dev)
+    torch.cuda.synchronize()
+    _device_status_ok()
+    assert _rel(y, oracle.quantized_matmul(x.float().numpy(), packed)) <= TOL[torch.float16]
+
+
+def test_qgemm_tensor_core_epilogues_and_odd_zero_points():
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(77)
+    m, n, k = 32, 512, 1024
+    x, packed = _qgemv_case(rng, m, n, k, 8, torch.float16)
+    # rows the fast in-register path cannot take: huge and fractional zero points
+    packed.zero_points = packed.zero_points.astype(np.float64)
+    dev = _device_pack(packed)
+    zp = dev.zero_points.clone()
+    zp[3] = 25000.0
+    zp[5] = 100.5
+    dev.zero_points = zp
+    host = oracle.PackedQuantizedTensor(packed.packed_values, packed.scales, zp.cpu().numpy(), 8, (n, k))
+    base = oracle.quantized_matmul(x.float().numpy(), host)
+    keep = [i for i in range(n) if i != 3]      # row 3 saturates fp16 by construction; compare the rest
+    y = quantized_matmul(x.cuda(), dev)
+    assert _rel(y[:, keep], base[:, keep]) <= TOL[torch.float16]
+    x, packed = _qgemv_case(rng, m, n, k, 8, torch.float16)
+    dev = _device_pack(packed)
+    base = oracle.quantized_matmul(x.float().numpy(), packed)
+    res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).half()
+    y = quantized_matmul(x.cuda(), dev, epilogue=ops.EPI_RESIDUAL, residual=res.cuda())
+    assert _rel(y, base + res.float().numpy()) <= TOL[torch.float16]
+    y = quantized_matmul(x.cuda(), dev, epilogue=ops.EPI_SWIGLU)
+    assert y.shape == (m, n // 2)
+    assert _rel(y, oracle.silu_mul(base[:, : n // 2], base[:, n // 2:])) <= TOL[torch.float16] * 2
+    # x as a strided view of a wider buffer
+    wide = torch.zeros((m, k + 256), dtype=torch.float16, device="cuda")
+    wide[:, :k] = x.cuda()
+    y2 = quantized_matmul(wide[:, :k], dev)
+    assert _rel(y2, base) <= TOL[torch.float16]
+    torch.cuda.synchronize()
+    _device_status_ok()
