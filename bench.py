@@ -403,6 +403,83 @@ def run_reference_arm(args, cfg: dict, workload: str) -> None:
 
 
 # --------------------------------------------------------------------------------------
+def run_micro(args) -> None:
+    """Single-kernel runs for profiling (`ncu ... python bench.py --micro qgemv ...`): prints one JSON
+    line with the CUDA-event time per launch; inputs rotate over `--copies` buffers so that every launch
+    streams from HBM."""
+    import torch
+
+    from cacheir_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0)
+    peak, kind = measured_peaks()
+    if args.micro == "qgemv":
+        m, n, k, bits = args.m, args.n, args.k, args.bits
+        row_bytes = k if bits == 8 else k // 2
+        copies = max(1, args.copies)
+        packed = [torch.randint(0, 256, (n, row_bytes), device=dev, dtype=torch.uint8, generator=gen) for _ in range(copies)]
+        if args.group:
+            scales = torch.rand((n, k // args.group), device=dev, generator=gen).mul_(0.015).add_(0.005).half()
+            zeros = None
+        else:
+            scales = torch.rand((n,), device=dev, generator=gen).mul_(0.015).add_(0.005)
+            zeros = torch.full((n,), float(1 << (bits - 1)), device=dev)
+        x = torch.randn((m, k), device=dev, dtype=torch.float16, generator=gen)
+        epi = {"none": ops.EPI_NONE, "swiglu": ops.EPI_SWIGLU}[args.epilogue]
+        out = torch.empty((m, n // 2 if epi == ops.EPI_SWIGLU else n), device=dev, dtype=torch.float16)
+
+        def launch(i: int) -> None:
+            ops.qgemv(x, packed[i % copies], scales, zeros, bits=bits, n=n, k=k, group_size=args.group, epilogue=epi, out=out)
+
+        algo = n * row_bytes + scales.numel() * scales.element_size() + (n * 4 if zeros is not None else 0) + m * k * 2 + out.numel() * 2
+        name = f"qgemv_int{bits}" + (f"_g{args.group}" if args.group else "")
+        shape = {"M": m, "N": n, "K": k}
+    else:
+        batch, heads, kv_heads, hd, page = args.batch, 32, 8, 128, 16
+        rng = np.random.default_rng(0)
+        lens_np = rng.integers(args.ctx_min, args.ctx_max + 1, batch).astype(np.int32)
+        pages = (lens_np + page - 1) // page
+        total = int(pages.sum())
+        table_np = np.zeros((batch, int(pages.max())), dtype=np.int32)
+        perm = np.random.default_rng(1).permutation(total).astype(np.int32)
+        cur = 0
+        for b in range(batch):
+            table_np[b, : pages[b]] = perm[cur:cur + pages[b]]
+            cur += int(pages[b])
+        k_pool = torch.randn((total, kv_heads, page, hd), device=dev, dtype=torch.float16, generator=gen)
+        v_pool = torch.randn((total, kv_heads, page, hd), device=dev, dtype=torch.float16, generator=gen)
+        q = torch.randn((batch, heads, hd), device=dev, dtype=torch.float16, generator=gen)
+        table = torch.from_numpy(table_np).to(dev)
+        lens = torch.from_numpy(lens_np).to(dev)
+        out = torch.empty_like(q)
+        splits = args.splits or ops.attention_auto_splits(batch, heads, kv_heads, table.shape[1], page, hd)
+        ws = torch.empty(max(1, ops.attention_workspace_bytes(batch, heads, hd, splits) // 4), device=dev, dtype=torch.float32)
+
+        def launch(i: int) -> None:
+            ops.paged_attention_decode_batch(q, k_pool, v_pool, table, lens, out=out, num_splits=splits, workspace=ws)
+
+        algo = int(lens_np.sum()) * kv_heads * hd * 2 * 2 + 2 * batch * heads * hd * 2 + table.numel() * 4 + batch * 4
+        name = "paged_attention_decode_batch"
+        shape = {"batch": batch, "heads": heads, "kv_heads": kv_heads, "head_dim": hd, "total_ctx": int(lens_np.sum()), "splits": splits}
+    for i in range(max(1, args.warmup)):
+        launch(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        launch(i)
+    end.record()
+    torch.cuda.synchronize()
+    sec = start.elapsed_time(end) * 1e-3 / args.steps
+    from cacheir_b200 import _lib
+    print(json.dumps({"micro": name, **shape, "us_per_launch": round(sec * 1e6, 2), "algorithmic_bytes": int(algo),
+                      "achieved_gbs": round(algo / sec / 1e9, 1), "frac": round(algo / sec / 1e9 / peak, 4),
+                      "peak": peak, "peak_source": f"of {kind}", "device_status": _lib.load().cacheir_b200_device_status(0)}), flush=True)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
@@ -412,7 +489,22 @@ def main() -> None:
     parser.add_argument("--workload", default="llama3-8b-int8-b32-ctx2048", choices=sorted(WORKLOADS))
     parser.add_argument("--e2e-steps", type=int, default=32)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--micro", choices=["qgemv", "attention"], help="time one kernel alone (profiling aid)")
+    parser.add_argument("--m", type=int, default=32)
+    parser.add_argument("--n", type=int, default=14336)
+    parser.add_argument("--k", type=int, default=4096)
+    parser.add_argument("--bits", type=int, default=8)
+    parser.add_argument("--group", type=int, default=0)
+    parser.add_argument("--epilogue", default="none", choices=["none", "swiglu"])
+    parser.add_argument("--copies", type=int, default=4)
+    parser.add_argument("--batch", type=int, default=64)
+    parser.add_argument("--ctx-min", type=int, default=512)
+    parser.add_argument("--ctx-max", type=int, default=8192)
+    parser.add_argument("--splits", type=int, default=0)
     args = parser.parse_args()
+    if args.micro:
+        run_micro(args)
+        return
     cfg = dict(WORKLOADS[args.workload])
     warmup = max(3, args.warmup)
 

@@ -3,22 +3,24 @@
 //   y[M, N] = x[M, K] . deq(W)[N, K]^T        M <= 64, fp16 activations
 //
 // The weight matrix is the 128-row MMA operand ("swap-AB"): one CTA owns 128
-// weight rows and the whole K range, the M activation rows are the MMA's N
-// dimension (padded to MP = 16/32/64), the fp32 accumulator D[128 x MP] lives
-// in tensor memory. Weight codes never exist in HBM in any other form than the
-// reference's packed bytes:
+// weight rows and a K range, the M activation rows are the MMA's N dimension
+// (padded to MP = 16/32/64), the fp32 accumulator D[128 x MP] lives in tensor
+// memory. Weight codes exist in HBM only as the reference's packed bytes:
 //
 //   warp 0      TMA producer: raw code tile [128 rows x 128 k] (16 KB int8 / 8 KB
-//               int4, hardware-swizzled so that row-per-thread reads are
-//               conflict free) + the x tile [MP x 128 k] per pipeline stage
-//   warps 4-7   converters: thread r owns weight row r of the tile; unpacks its
-//               codes in registers (byte/nibble -> fp16 through the 0x6400
-//               mantissa trick, zero point removed exactly) and writes the fp16
-//               operand tile in the canonical no-swizzle UMMA layout
-//   warp 1      one thread issues tcgen05.mma (M=128, N=MP, K=16) x 8 per stage and
-//               commits to the barriers that recycle the stages
-//   warps 4-7   epilogue: tcgen05.ld the accumulator row, apply the row scale,
-//               residual add or SiLU*mul, store y
+//               int4, hardware-swizzled so that row-per-thread reads are conflict
+//               free) + the x tile [MP x 128 k] per pipeline stage
+//   warps 4-11  converters: thread (r, half) owns half of weight row r of the tile;
+//               unpacks its codes in registers (byte/nibble -> fp16 through the
+//               0x6400 mantissa trick, zero point removed exactly) and stores the
+//               fp16 operand straight into TENSOR MEMORY (tcgen05.st, row r = TMEM
+//               lane r): the dequantised weights never touch shared memory
+//   warp 1      one thread issues tcgen05.mma with A from TMEM and B (x) from shared
+//               memory (M=128, N=MP, K=16; 8 per stage) and commits to the barriers
+//               that recycle the stages
+//   warps 4-11  epilogue: tcgen05.ld the accumulator, split-K reduction across the
+//               CTAs of a cluster through distributed shared memory in rank order
+//               (deterministic), row scale, residual add or SiLU*mul, store y
 //
 // Every wait is bounded: a barrier that does not complete within the poll budget
 // raises a device status flag and the CTA drains and exits instead of hanging.
@@ -32,10 +34,21 @@ namespace {
 
 constexpr int kBlockN = 128;      // weight rows per CTA (UMMA M)
 constexpr int kBlockK = 128;      // k elements per pipeline stage
-constexpr int kStages = 4;        // raw-code + x stages in flight
-constexpr int kAStages = 2;       // converted fp16 operand tiles
-constexpr int kThreads = 256;
-constexpr int kATileBytes = kBlockN * kBlockK * 2;      // 32 KB
+constexpr int kAStages = 4;       // converted fp16 operand tiles in tensor memory
+constexpr int kAStageCols = kBlockK / 2;                // 64 TMEM columns: two fp16 per 32-bit column
+constexpr int kAColBase = 128;                          // accumulators use columns [0, 128)
+constexpr int kTmemCols = 512;
+constexpr int kConvThreads = 256;                       // warps 4..11
+constexpr int kThreads = 128 + kConvThreads;
+constexpr int kMaxSplitK = 4;
+constexpr int kRingBudget = 192 * 1024;                 // shared memory for the raw/x ring
+
+__host__ __device__ constexpr int stage_bytes(int bits, int mp) {
+  return (bits == 8 ? kBlockN * 128 : kBlockN * 64) + mp * kBlockK * 2;
+}
+__host__ __device__ constexpr int num_stages(int bits, int mp) {
+  return kRingBudget / stage_bytes(bits, mp) > 8 ? 8 : kRingBudget / stage_bytes(bits, mp);
+}
 constexpr uint32_t kPollLimit = 8u * 1000u * 1000u;
 
 __device__ int g_qgemm_status = 0;   // 0 ok; otherwise (code << 8 | barrier id) of the first wait that gave up
@@ -71,9 +84,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int id)
   atomicCAS(&g_qgemm_status, 0, (1 << 8) | id);
   return false;
 }
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -84,19 +94,35 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void tc_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr) : "memory");
+__device__ __forceinline__ void tc_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t local_addr, uint32_t rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -122,7 +148,7 @@ struct TcParams {
   int group_size;
   int scale_dtype;
   int epilogue;
-  int n_tiles;
+  int split_k;      // CTAs per cluster along K (1 = no split)
 };
 
 __device__ __forceinline__ float load_scale(const void* scales, int scale_dtype, size_t idx) {
@@ -130,98 +156,84 @@ __device__ __forceinline__ float load_scale(const void* scales, int scale_dtype,
                                          : static_cast<const float*>(scales)[idx];
 }
 
-// Unpack 16 bytes of one weight row into fp16 and store them as UMMA core-matrix rows.
-// BITS 8: 16 codes -> k-chunks 2c, 2c+1.   BITS 4: 32 codes -> k-chunks 4c .. 4c+3.
-template <int BITS>
-__device__ __forceinline__ void convert_chunk_fast(const uint4 raw, int c, uint8_t* a_row_base, __half2 sub8, __half2 mul4,
-                                                   __half2 sub4, bool scaled, __half2 gscale) {
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  if (BITS == 8) {
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+
+// 8 int8 codes (two 32-bit words) -> 8 fp16 (four registers, k order), zero point removed exactly.
+__device__ __forceinline__ void unpack8_int8(uint32_t w0, uint32_t w1, __half2 sub, bool scaled, __half2 gscale, uint32_t* o) {
+  __half2 v[4];
+  v[0] = __hsub2(bits_h2(__byte_perm(w0, 0x64646464u, 0x5140)), sub);   // (1024+b0, 1024+b1) - (1024+z)
+  v[1] = __hsub2(bits_h2(__byte_perm(w0, 0x64646464u, 0x5342)), sub);
+  v[2] = __hsub2(bits_h2(__byte_perm(w1, 0x64646464u, 0x5140)), sub);
+  v[3] = __hsub2(bits_h2(__byte_perm(w1, 0x64646464u, 0x5342)), sub);
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint32_t o[4];
+  for (int i = 0; i < 4; ++i) o[i] = h2_bits(scaled ? __hmul2(v[i], gscale) : v[i]);
+}
+// 8 int4 codes (one 32-bit word) -> 8 fp16: byte q -> (0x6400 | low nibble, 0x6400 | high nibble << 4)
+// = (1024 + n0, 1024 + 16*n1); one fma maps both to (n0 - z, n1 - z) exactly.
+__device__ __forceinline__ void unpack8_int4(uint32_t w, __half2 mul, __half2 sub, bool scaled, __half2 gscale, uint32_t* o) {
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const uint32_t word = w[half * 2 + i];
-        const uint32_t lo = __byte_perm(word, 0x64646464u, 0x5140);   // (1024+b0, 1024+b1)
-        const uint32_t hi = __byte_perm(word, 0x64646464u, 0x5342);   // (1024+b2, 1024+b3)
-        __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&lo), sub8);
-        __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&hi), sub8);
-        if (scaled) { a = __hmul2(a, gscale); b = __hmul2(b, gscale); }
-        o[i * 2] = *reinterpret_cast<uint32_t*>(&a);
-        o[i * 2 + 1] = *reinterpret_cast<uint32_t*>(&b);
-      }
-      *reinterpret_cast<uint4*>(a_row_base + (2 * c + half) * 2048) = make_uint4(o[0], o[1], o[2], o[3]);
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint32_t o[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        // byte q -> (0x6400 | low nibble, 0x6400 | high nibble << 4) = (1024 + n0, 1024 + 16*n1)
-        const uint32_t t = __byte_perm(w[i], 0x64646464u, 0x4040 + 0x101 * q) & 0x64F0640Fu;
-        __half2 a = __hfma2(*reinterpret_cast<const __half2*>(&t), mul4, sub4);   // exact (n0 - z, n1 - z)
-        if (scaled) a = __hmul2(a, gscale);
-        o[q] = *reinterpret_cast<uint32_t*>(&a);
-      }
-      *reinterpret_cast<uint4*>(a_row_base + (4 * c + i) * 2048) = make_uint4(o[0], o[1], o[2], o[3]);
-    }
+  for (int q = 0; q < 4; ++q) {
+    const uint32_t t = __byte_perm(w, 0x64646464u, 0x4040 + 0x101 * q) & 0x64F0640Fu;
+    const __half2 v = __hfma2(bits_h2(t), mul, sub);
+    o[q] = h2_bits(scaled ? __hmul2(v, gscale) : v);
   }
 }
-
 // Rows whose zero point is not a small integer: plain fp32 arithmetic, scale folded in.
 template <int BITS>
-__device__ __forceinline__ void convert_chunk_slow(const uint4 raw, int c, uint8_t* a_row_base, float zero, float scale) {
-  const uint8_t* bytes = reinterpret_cast<const uint8_t*>(&raw);
-  constexpr int CHUNKS = BITS == 8 ? 2 : 4;
+__device__ __forceinline__ void unpack8_slow(const uint8_t* bytes, int first, float zero, float scale, uint32_t* o) {
 #pragma unroll
-  for (int j = 0; j < CHUNKS; ++j) {
-    __half vals[8];
+  for (int e = 0; e < 4; ++e) {
+    float f[2];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int idx = j * 8 + e;
+    for (int h = 0; h < 2; ++h) {
+      const int idx = first + 2 * e + h;
       const float code = BITS == 8 ? static_cast<float>(bytes[idx])
                                    : static_cast<float>((bytes[idx >> 1] >> ((idx & 1) * 4)) & 0xF);
-      vals[e] = __float2half_rn((code - zero) * scale);
+      f[h] = (code - zero) * scale;
     }
-    *reinterpret_cast<uint4*>(a_row_base + (CHUNKS * c + j) * 2048) = *reinterpret_cast<const uint4*>(vals);
+    o[e] = h2_bits(__floats2half2_rn(f[0], f[1]));
   }
 }
 
 template <int BITS, int MP>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
+  constexpr int kStages = num_stages(BITS, MP);
   constexpr int kRawBytes = BITS == 8 ? kBlockN * 128 : kBlockN * 64;   // per stage
   constexpr int kXBytes = MP * kBlockK * 2;
-  constexpr int kRawRow = BITS == 8 ? 128 : 64;
-  constexpr int kChunks = kRawRow / 16;                                  // 16-byte chunks per row per stage
+  constexpr int kRawRow = BITS == 8 ? 128 : 64;                          // bytes of one row per stage
+  constexpr int kChunksPerThread = kRawRow / 16 / 2;                     // 16-byte chunks per converter thread
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* s_raw = smem;                                   // kStages x kRawBytes
-  uint8_t* s_x = s_raw + kStages * kRawBytes;              // kStages x kXBytes      (1024-aligned: sizes are multiples of 1024)
-  uint8_t* s_a = s_x + kStages * kXBytes;                  // kAStages x 32 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_a + kAStages * kATileBytes);
+  uint8_t* s_x = s_raw + kStages * kRawBytes;              // kStages x kXBytes (all sizes are multiples of 1024)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_x + kStages * kXBytes);
   uint64_t* full = bars;                                   // [kStages]   TMA landed
-  uint64_t* empty = bars + kStages;                        // [kStages]   converters (128) + MMA commit (1)
-  uint64_t* a_full = bars + 2 * kStages;                   // [kAStages]  converters (128)
+  uint64_t* empty = bars + kStages;                        // [kStages]   converters (256) + MMA commit (1)
+  uint64_t* a_full = bars + 2 * kStages;                   // [kAStages]  converters (256)
   uint64_t* a_empty = a_full + kAStages;                   // [kAStages]  MMA commit (1)
   uint64_t* acc_full = a_empty + kAStages;                 // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  float* s_partial = reinterpret_cast<float*>(smem);       // split-K partials reuse the ring once it has drained
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const bool swiglu = p.epilogue == CACHEIR_B200_EPI_SWIGLU;
   const int passes = swiglu ? 2 : 1;
-  const int kblocks = p.K / kBlockK;
+  const int split = p.split_k;
+  const int krank = split > 1 ? static_cast<int>(cluster_ctarank()) : 0;
+  const int kblocks_all = p.K / kBlockK;
+  const int kb_begin = (kblocks_all * krank) / split;
+  const int kb_end = (kblocks_all * (krank + 1)) / split;
+  const int kblocks = kb_end - kb_begin;
   const int total = kblocks * passes;
   const int n0 = blockIdx.x * kBlockN;
-  constexpr int kTmemCols = (2 * MP) < 32 ? 32 : 2 * MP;   // power of two >= 32; two accumulators for SwiGLU
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 129); }
-    for (int t = 0; t < kAStages; ++t) { mbar_init(smem_u32(&a_full[t]), 128); mbar_init(smem_u32(&a_empty[t]), 1); }
+    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), kConvThreads + 1); }
+    for (int t = 0; t < kAStages; ++t) { mbar_init(smem_u32(&a_full[t]), kConvThreads); mbar_init(smem_u32(&a_empty[t]), 1); }
     mbar_init(smem_u32(acc_full), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -242,7 +254,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         const uint32_t ph = (i / kStages) & 1;
         if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1, 1)) break;
         const int pass = i / kblocks;
-        const int kb = i % kblocks;
+        const int kb = kb_begin + i % kblocks;
         const int row0 = n0 + pass * (p.N / 2);
         const uint32_t bar = smem_u32(&full[s]);
         mbar_expect_tx(bar, kRawBytes + kXBytes);
@@ -256,34 +268,36 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       // ---------------- MMA issuer ----------------
       // instruction descriptor: D=f32, A=B=f16, both K-major, N=MP, M=128
       const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(MP >> 3) << 17) | (static_cast<uint32_t>(kBlockN >> 4) << 24);
-      bool ok = true;
-      for (int i = 0; i < total && ok; ++i) {
+      for (int i = 0; i < total; ++i) {
         const int s = i % kStages;
         const int t = i % kAStages;
-        ok = mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, 2) && mbar_wait(smem_u32(&a_full[t]), (i / kAStages) & 1, 3);
-        if (!ok) break;
+        if (!mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, 2)) break;
+        if (!mbar_wait(smem_u32(&a_full[t]), (i / kAStages) & 1, 3)) break;
         tc_fence_after();
         const int pass = i / kblocks;
         const int kb = i % kblocks;
         const uint32_t d = tmem_base + pass * MP;
-        const uint32_t a_base = smem_u32(s_a + t * kATileBytes);
+        const uint32_t a_tmem = tmem_base + kAColBase + t * kAStageCols;
         const uint32_t x_base = smem_u32(s_x + s * kXBytes);
 #pragma unroll
         for (int j = 0; j < kBlockK / 16; ++j) {
-          // A: no-swizzle K-major, core matrices 128 B; k-chunks 2048 B apart (LBO), 8-row groups 128 B apart (SBO)
-          const uint64_t a_desc = smem_desc(a_base + (2 * j) * 2048, 2048, 128, 0);
-          // B: 128-byte swizzled rows (TMA), 8-row groups 1024 B apart; 32 B per k step inside the 64-element span
+          // A: tensor memory, row r in lane r, 16 fp16 of this k step in 8 columns.
+          // B: 128-byte swizzled rows (TMA), 8-row groups 1024 B apart; 32 B per k step inside a 64-element span.
           const uint64_t b_desc = smem_desc(x_base + (j / 4) * (MP * 128) + (j % 4) * 32, 16, 1024, 2);
-          tc_mma_f16(d, a_desc, b_desc, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          tc_mma_f16_ts(d, a_tmem + j * 8, b_desc, idesc, (kb > 0 || j > 0) ? 1u : 0u);
         }
-        tc_commit(smem_u32(&a_empty[t]));   // operand tile and stage are free once these MMAs retire
+        tc_commit(smem_u32(&a_empty[t]));   // operand columns and the x stage are free once these MMAs retire
         tc_commit(smem_u32(&empty[s]));
       }
       tc_commit(smem_u32(acc_full));
     }
   } else if (warp >= 4) {
     // ---------------- converters, then epilogue ----------------
-    const int r = threadIdx.x - 128;              // row of the tile owned by this thread (= TMEM lane)
+    const int cw = warp - 4;                      // 0..7
+    const int q = cw & 3;                         // TMEM lane quarter this warp may access (= warp % 4)
+    const int hsel = cw >> 2;                     // which half of the row's k range / of the output columns
+    const int r = q * 32 + lane;                  // row of the tile owned by this thread (= TMEM lane)
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const int swz = BITS == 8 ? (r & 7) : ((r >> 1) & 3);
     bool ok = true;
     float row_scale[2] = {1.f, 1.f};
@@ -302,65 +316,132 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const __half2 sub8 = __float2half2_rn(1024.f + zero);
       const __half2 mul4 = __floats2half2_rn(1.f, 0.0625f);
       const __half2 sub4 = __floats2half2_rn(-(1024.f + zero), -(64.f + zero));
-      for (int kb = 0; kb < kblocks; ++kb) {
-        const int i = pass * kblocks + kb;
+      const bool scaled = p.group_size > 0;
+      for (int kbi = 0; kbi < kblocks; ++kbi) {
+        const int i = pass * kblocks + kbi;
         const int s = i % kStages;
         const int t = i % kAStages;
         ok = mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, 4) &&
              mbar_wait(smem_u32(&a_empty[t]), ((i / kAStages) & 1) ^ 1, 5);
         if (!ok) break;
+        tc_fence_after();
         const uint8_t* raw_row = s_raw + s * kRawBytes + r * kRawRow;
-        uint8_t* a_row = s_a + t * kATileBytes + (r >> 3) * 128 + (r & 7) * 16;
+        const uint32_t a_cols = tmem_base + lane_addr + kAColBase + t * kAStageCols;
         __half2 gscale = __float2half2_rn(1.f);
-        const bool scaled = p.group_size > 0;
         if (scaled && row_valid) {
           const int groups_per_row = p.K / p.group_size;
           gscale = __float2half2_rn(load_scale(p.scales, p.scale_dtype,
-                                               static_cast<size_t>(n) * groups_per_row + (kb * kBlockK) / p.group_size));
+                                               static_cast<size_t>(n) * groups_per_row + ((kb_begin + kbi) * kBlockK) / p.group_size));
+        }
+        uint4 raw[kChunksPerThread];
+#pragma unroll
+        for (int cc = 0; cc < kChunksPerThread; ++cc) {
+          const int c = hsel * kChunksPerThread + cc;
+          raw[cc] = *reinterpret_cast<const uint4*>(raw_row + ((c ^ swz) * 16));
         }
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(raw_row + ((c ^ swz) * 16));
-          if (fast) convert_chunk_fast<BITS>(raw, c, a_row, sub8, mul4, sub4, scaled, gscale);
-          else convert_chunk_slow<BITS>(raw, c, a_row, zero, scale);
+        for (int cc = 0; cc < kChunksPerThread; ++cc) {
+          const int c = hsel * kChunksPerThread + cc;
+          const uint32_t w[4] = {raw[cc].x, raw[cc].y, raw[cc].z, raw[cc].w};
+          if (BITS == 8) {      // 16 codes -> 8 columns starting at 8c
+            uint32_t o[8];
+            if (fast) {
+              unpack8_int8(w[0], w[1], sub8, scaled, gscale, o);
+              unpack8_int8(w[2], w[3], sub8, scaled, gscale, o + 4);
+            } else {
+              unpack8_slow<8>(reinterpret_cast<const uint8_t*>(w), 0, zero, scale, o);
+              unpack8_slow<8>(reinterpret_cast<const uint8_t*>(w), 8, zero, scale, o + 4);
+            }
+            tc_st_x8(a_cols + 8 * c, reinterpret_cast<const uint32_t(&)[8]>(o));
+          } else {              // 32 codes -> 16 columns starting at 16c
+#pragma unroll
+            for (int hw = 0; hw < 2; ++hw) {
+              uint32_t o[8];
+              if (fast) {
+                unpack8_int4(w[2 * hw], mul4, sub4, scaled, gscale, o);
+                unpack8_int4(w[2 * hw + 1], mul4, sub4, scaled, gscale, o + 4);
+              } else {
+                unpack8_slow<4>(reinterpret_cast<const uint8_t*>(w), 16 * hw, zero, scale, o);
+                unpack8_slow<4>(reinterpret_cast<const uint8_t*>(w), 16 * hw + 8, zero, scale, o + 4);
+              }
+              tc_st_x8(a_cols + 16 * c + 8 * hw, reinterpret_cast<const uint32_t(&)[8]>(o));
+            }
+          }
         }
-        fence_proxy_async();                       // generic-proxy stores -> visible to the tensor core
+        tc_wait_st();
+        tc_fence_before();                         // order the TMEM stores before the arrive the MMA thread waits on
         mbar_arrive(smem_u32(&a_full[t]));
         mbar_arrive(smem_u32(&empty[s]));
       }
     }
-    // ---- epilogue ----
-    if (ok && mbar_wait(smem_u32(acc_full), 0, 6)) {
+    // ---- epilogue: this warp owns rows [32q, 32q+32) and output columns [hsel*MP/2, (hsel+1)*MP/2) ----
+    constexpr int kColsPerWarp = MP / 2;
+    float acc[2][kColsPerWarp];
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int j = 0; j < kColsPerWarp; ++j) acc[a][j] = 0.f;
+    ok = ok && mbar_wait(smem_u32(acc_full), 0, 6);
+    if (ok && total > 0) {
       tc_fence_after();
-      const int q = warp - 4;
-      const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll
+      for (int a = 0; a < 2; ++a) {
+        if (a == 1 && !swiglu) break;
+#pragma unroll
+        for (int c0 = 0; c0 < kColsPerWarp; c0 += 8) {
+          uint32_t v[8];
+          tc_ld_x8(tmem_base + lane_addr + a * MP + hsel * kColsPerWarp + c0, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[a][c0 + j] = __uint_as_float(v[j]);
+        }
+      }
+    }
+    if (split > 1) {
+      // Deterministic split-K: ranks 1.. send their partial rows to rank 0's shared memory
+      // (the pipeline ring, idle by now), rank 0 adds them in rank order.
+      cluster_sync_all();
+      if (krank != 0) {
+#pragma unroll
+        for (int j = 0; j < kColsPerWarp; ++j) {
+          const int col = hsel * kColsPerWarp + j;
+          st_cluster_f32(smem_u32(s_partial + (static_cast<size_t>(krank - 1) * MP + col) * kBlockN + r), 0, acc[0][j]);
+        }
+      }
+      cluster_sync_all();
+      if (krank == 0) {
+        for (int k = 1; k < split; ++k)
+#pragma unroll
+          for (int j = 0; j < kColsPerWarp; ++j)
+            acc[0][j] += s_partial[(static_cast<size_t>(k - 1) * MP + hsel * kColsPerWarp + j) * kBlockN + r];
+      }
+    }
+    if (ok && krank == 0) {
       const int n_out_idx = n0 + r;
       const bool store = n_out_idx < p.n_out;
       __half* y = static_cast<__half*>(p.y);
       const __half* res = static_cast<const __half*>(p.residual);
 #pragma unroll
-      for (int c0 = 0; c0 < MP; c0 += 16) {
-        uint32_t acc0[16], acc1[16];
-        tc_ld_x16(lane_base + c0, acc0);
-        if (swiglu) tc_ld_x16(lane_base + MP + c0, acc1);
-        tc_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int m = c0 + j;
-          if (m < p.M && store) {
-            float v = __uint_as_float(acc0[j]) * row_scale[0];
-            const size_t o = static_cast<size_t>(m) * p.n_out + n_out_idx;
-            if (swiglu) {
-              const float u = __uint_as_float(acc1[j]) * row_scale[1];
-              v = (v / (1.f + __expf(-v))) * u;
-            } else if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
-              v += __half2float(res[o]);
-            }
-            y[o] = __float2half_rn(v);
+      for (int j = 0; j < kColsPerWarp; ++j) {
+        const int m = hsel * kColsPerWarp + j;
+        if (m < p.M && store) {
+          float v = acc[0][j] * row_scale[0];
+          const size_t o = static_cast<size_t>(m) * p.n_out + n_out_idx;
+          if (swiglu) {
+            const float u = acc[1][j] * row_scale[1];
+            v = (v / (1.f + __expf(-v))) * u;
+          } else if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
+            v += __half2float(res[o]);
           }
+          y[o] = __float2half_rn(v);
         }
       }
     }
+  } 
+  if (warp < 4 && split > 1) {   // warps without an epilogue still take part in the two cluster barriers
+    __syncwarp();
+    cluster_sync_all();
+    cluster_sync_all();
   }
   tc_fence_before();
   __syncthreads();
@@ -403,11 +484,22 @@ bool encode_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, uin
             swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// CTAs per cluster along K: enough to put about one CTA on every SM, never for the SwiGLU form
+// (it has two accumulators and plenty of row tiles).
+int choose_split_k(int n_tiles, int kblocks, int epilogue) {
+  if (epilogue == CACHEIR_B200_EPI_SWIGLU) return 1;
+  int s = kNumSMs / n_tiles;
+  if (s > kMaxSplitK) s = kMaxSplitK;
+  if (s > kblocks / 4) s = kblocks / 4;     // keep at least four k blocks per CTA
+  return s < 1 ? 1 : s;
+}
+
 template <int BITS, int MP>
 int launch_tc(const QGemvParams& q, cudaStream_t stream) {
-  constexpr int kRawBytes = BITS == 8 ? kBlockN * 128 : kBlockN * 64;
-  constexpr int kXBytes = MP * kBlockK * 2;
-  constexpr size_t kSmem = 1024 + kStages * (kRawBytes + kXBytes) + kAStages * kATileBytes + 256;
+  constexpr int kStages = num_stages(BITS, MP);
+  constexpr size_t kSmem = 1024 + static_cast<size_t>(kStages) * stage_bytes(BITS, MP) + 512;
+  static_assert(static_cast<size_t>(kMaxSplitK - 1) * MP * kBlockN * 4 <= static_cast<size_t>(kStages) * stage_bytes(BITS, MP),
+                "split-K partials must fit in the pipeline ring");
   CUtensorMap tmap_w, tmap_x;
   const uint64_t row_bytes = BITS == 8 ? static_cast<uint64_t>(q.K) : static_cast<uint64_t>(q.K / 2);
   if (!encode_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, q.packed, row_bytes, static_cast<uint64_t>(q.N), row_bytes,
@@ -421,11 +513,25 @@ int launch_tc(const QGemvParams& q, cudaStream_t stream) {
   p.M = q.M; p.N = q.N; p.K = q.K;
   p.n_out = q.epilogue == CACHEIR_B200_EPI_SWIGLU ? q.N / 2 : q.N;
   p.group_size = q.group_size; p.scale_dtype = q.scale_dtype; p.epilogue = q.epilogue;
-  p.n_tiles = (p.n_out + kBlockN - 1) / kBlockN;
+  const int n_tiles = (p.n_out + kBlockN - 1) / kBlockN;
+  p.split_k = choose_split_k(n_tiles, q.K / kBlockK, q.epilogue);
   auto kern = qgemm_tc_kernel<BITS, MP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
   if (e != cudaSuccess) return static_cast<int>(e);
-  kern<<<p.n_tiles, kThreads, kSmem, stream>>>(tmap_w, tmap_x, p);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(n_tiles, p.split_k, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = p.split_k;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kern, tmap_w, tmap_x, p);
+  if (e != cudaSuccess) return static_cast<int>(e);
   return launch_status();
 }
 
