@@ -36,7 +36,7 @@ constexpr int kBlockN = 128;      // weight rows per CTA (UMMA M)
 constexpr int kBlockK = 128;      // k elements per pipeline stage
 constexpr int kAStages = 4;       // converted fp16 operand tiles in tensor memory
 constexpr int kAStageCols = kBlockK / 2;                // 64 TMEM columns: two fp16 per 32-bit column
-constexpr int kAColBase = 128;                          // accumulators use columns [0, 128)
+constexpr int kAColBase = 256;                          // accumulators use columns [0, 256)
 constexpr int kTmemCols = 512;
 constexpr int kConvThreads = 256;                       // warps 4..11
 constexpr int kThreads = 128 + kConvThreads;
@@ -51,7 +51,16 @@ __host__ __device__ constexpr int num_stages(int bits, int mp) {
 }
 constexpr uint32_t kPollLimit = 8u * 1000u * 1000u;
 
-__device__ int g_qgemm_status = 0;   // 0 ok; otherwise (code << 8 | barrier id) of the first wait that gave up
+__device__ int g_qgemm_status = 0;
+
+// Optional pipeline trace (compile with -DCB200_QGEMM_TRACE): CTA 0 records clock64() at the
+// hand-over points of each role so that stage times can be read back and compared.
+#ifdef CB200_QGEMM_TRACE
+__device__ long long g_trace[4][256][4];
+#define CB200_TRACE(role, i, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 256) g_trace[role][i][slot] = clock64(); } while (0)
+#else
+#define CB200_TRACE(role, i, slot) do { } while (0)
+#endif   // 0 ok; otherwise (code << 8 | barrier id) of the first wait that gave up
 
 // ---- PTX wrappers ------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -88,6 +97,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -230,6 +244,9 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   const int kblocks = kb_end - kb_begin;
   const int total = kblocks * passes;
   const int n0 = blockIdx.x * kBlockN;
+  // Back-to-back MMAs into one accumulator serialise on it; k steps rotate over `nacc`
+  // independent accumulators (summed in a fixed order in the epilogue).
+  const int nacc = (kAColBase / (passes * MP)) > 4 ? 4 : (kAColBase / (passes * MP));
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), kConvThreads + 1); }
@@ -252,15 +269,18 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       for (int i = 0; i < total; ++i) {
         const int s = i % kStages;
         const uint32_t ph = (i / kStages) & 1;
+        CB200_TRACE(0, i, 0);
         if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1, 1)) break;
+        CB200_TRACE(0, i, 1);
         const int pass = i / kblocks;
         const int kb = kb_begin + i % kblocks;
         const int row0 = n0 + pass * (p.N / 2);
         const uint32_t bar = smem_u32(&full[s]);
         mbar_expect_tx(bar, kRawBytes + kXBytes);
         tma_load_2d(smem_u32(s_raw + s * kRawBytes), &tmap_w, bar, kb * kRawRow, row0);
-        tma_load_2d(smem_u32(s_x + s * kXBytes), &tmap_x, bar, kb * kBlockK, 0);
-        tma_load_2d(smem_u32(s_x + s * kXBytes + MP * 128), &tmap_x, bar, kb * kBlockK + 64, 0);
+        // x viewed as [K/64 spans][M rows][64 elements]: both 64-element halves of the k block in one copy
+        tma_load_3d(smem_u32(s_x + s * kXBytes), &tmap_x, bar, 0, 0, kb * 2);
+        CB200_TRACE(0, i, 2);
       }
     }
   } else if (warp == 1) {
@@ -271,12 +291,15 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       for (int i = 0; i < total; ++i) {
         const int s = i % kStages;
         const int t = i % kAStages;
+        CB200_TRACE(1, i, 0);
         if (!mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, 2)) break;
+        CB200_TRACE(1, i, 1);
         if (!mbar_wait(smem_u32(&a_full[t]), (i / kAStages) & 1, 3)) break;
+        CB200_TRACE(1, i, 2);
         tc_fence_after();
         const int pass = i / kblocks;
         const int kb = i % kblocks;
-        const uint32_t d = tmem_base + pass * MP;
+        const uint32_t d = tmem_base + pass * nacc * MP;
         const uint32_t a_tmem = tmem_base + kAColBase + t * kAStageCols;
         const uint32_t x_base = smem_u32(s_x + s * kXBytes);
 #pragma unroll
@@ -284,10 +307,11 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           // A: tensor memory, row r in lane r, 16 fp16 of this k step in 8 columns.
           // B: 128-byte swizzled rows (TMA), 8-row groups 1024 B apart; 32 B per k step inside a 64-element span.
           const uint64_t b_desc = smem_desc(x_base + (j / 4) * (MP * 128) + (j % 4) * 32, 16, 1024, 2);
-          tc_mma_f16_ts(d, a_tmem + j * 8, b_desc, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          tc_mma_f16_ts(d + (j & (nacc - 1)) * MP, a_tmem + j * 8, b_desc, idesc, (kb > 0 || j >= nacc) ? 1u : 0u);
         }
         tc_commit(smem_u32(&a_empty[t]));   // operand columns and the x stage are free once these MMAs retire
         tc_commit(smem_u32(&empty[s]));
+        CB200_TRACE(1, i, 3);
       }
       tc_commit(smem_u32(acc_full));
     }
@@ -321,9 +345,12 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         const int i = pass * kblocks + kbi;
         const int s = i % kStages;
         const int t = i % kAStages;
-        ok = mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, 4) &&
-             mbar_wait(smem_u32(&a_empty[t]), ((i / kAStages) & 1) ^ 1, 5);
+        if (threadIdx.x == 128) CB200_TRACE(2, i, 0);
+        ok = mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, 4);
+        if (threadIdx.x == 128) CB200_TRACE(2, i, 1);
+        ok = ok && mbar_wait(smem_u32(&a_empty[t]), ((i / kAStages) & 1) ^ 1, 5);
         if (!ok) break;
+        if (threadIdx.x == 128) CB200_TRACE(2, i, 2);
         tc_fence_after();
         const uint8_t* raw_row = s_raw + s * kRawBytes + r * kRawRow;
         const uint32_t a_cols = tmem_base + lane_addr + kAColBase + t * kAStageCols;
@@ -372,6 +399,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         tc_fence_before();                         // order the TMEM stores before the arrive the MMA thread waits on
         mbar_arrive(smem_u32(&a_full[t]));
         mbar_arrive(smem_u32(&empty[s]));
+        if (threadIdx.x == 128) CB200_TRACE(2, i, 3);
       }
     }
     // ---- epilogue: this warp owns rows [32q, 32q+32) and output columns [hsel*MP/2, (hsel+1)*MP/2) ----
@@ -387,13 +415,15 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
       for (int a = 0; a < 2; ++a) {
         if (a == 1 && !swiglu) break;
+        for (int part = 0; part < nacc; ++part) {
 #pragma unroll
-        for (int c0 = 0; c0 < kColsPerWarp; c0 += 8) {
-          uint32_t v[8];
-          tc_ld_x8(tmem_base + lane_addr + a * MP + hsel * kColsPerWarp + c0, v);
-          tc_wait_ld();
+          for (int c0 = 0; c0 < kColsPerWarp; c0 += 8) {
+            uint32_t v[8];
+            tc_ld_x8(tmem_base + lane_addr + (a * nacc + part) * MP + hsel * kColsPerWarp + c0, v);
+            tc_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[a][c0 + j] = __uint_as_float(v[j]);
+            for (int j = 0; j < 8; ++j) acc[a][c0 + j] += __uint_as_float(v[j]);
+          }
         }
       }
     }
@@ -484,6 +514,20 @@ bool encode_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, uin
             swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// x[M, K] fp16 as a 3-D tensor [K/64][M][64]: a box {64, MP, 2} brings both 128-byte-swizzled
+// halves of a 128-element k block in one copy, laid out as [half][row][64].
+bool encode_x_3d(CUtensorMap* map, const void* base, uint64_t K, uint64_t M, uint64_t row_stride_bytes, uint32_t mp) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {64, M, K / 64};
+  const cuuint64_t strides[2] = {row_stride_bytes, 128};
+  const cuuint32_t box[3] = {64, mp, 2};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem_strides,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // CTAs per cluster along K: enough to put about one CTA on every SM, never for the SwiGLU form
 // (it has two accumulators and plenty of row tiles).
 int choose_split_k(int n_tiles, int kblocks, int epilogue) {
@@ -505,8 +549,8 @@ int launch_tc(const QGemvParams& q, cudaStream_t stream) {
   if (!encode_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, q.packed, row_bytes, static_cast<uint64_t>(q.N), row_bytes,
                  BITS == 8 ? 128 : 64, kBlockN, BITS == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
     return CACHEIR_B200_EUNSUPPORTED;
-  if (!encode_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, q.x, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.M),
-                 static_cast<uint64_t>(q.x_stride) * 2, 64, MP, CU_TENSOR_MAP_SWIZZLE_128B))
+  if (!encode_x_3d(&tmap_x, q.x, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.M),
+                   static_cast<uint64_t>(q.x_stride) * 2, MP))
     return CACHEIR_B200_EUNSUPPORTED;
   TcParams p{};
   p.scales = q.scales; p.zero_points = q.zero_points; p.residual = q.residual; p.y = q.y;
@@ -558,6 +602,12 @@ bool qgemm_tc_supported(const QGemvParams& q) {
 int launch_qgemm_tc(const QGemvParams& q, cudaStream_t stream) {
   return q.bits == 8 ? launch_tc_mp<8>(q, stream) : launch_tc_mp<4>(q, stream);
 }
+
+#ifdef CB200_QGEMM_TRACE
+extern "C" int cacheir_b200_debug_trace(long long* out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 4 * 256 * 4));
+}
+#endif
 
 int qgemm_tc_device_status(bool reset) {
   int status = 0;
