@@ -334,6 +334,9 @@ extern "C" int cacheir_b200_paged_attention_decode_batch(
                          (p.q_stride * esize) % 16 == 0 &&
                          (static_cast<long long>(head_dim) * esize) % 16 == 0;
   int rc;
+  if (paged_attention_fast_supported(p, dtype)) {
+    rc = launch_paged_attention_fast(p, dtype, st);
+  } else
   switch (dtype) {
     case CACHEIR_B200_F32: rc = launch_general<float, 4>(p, vector_ok, st); break;
     case CACHEIR_B200_F16: rc = launch_general<__half, 8>(p, vector_ok, st); break;

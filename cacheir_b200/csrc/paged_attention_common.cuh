@@ -1,6 +1,7 @@
 // Types shared by the paged decode attention kernels and their launchers.
 #pragma once
 
+#include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace cb200 {
@@ -32,5 +33,10 @@ struct AttnParams {
 // of tokens each split covers (a multiple of page_size).
 void resolve_attention_splits(int batch, int heads, int kv_heads, int max_pages, int page_size,
                               int requested, int* splits, int* chunk_tokens);
+
+// Tensor-core path (fp16/bf16, head_dim 64/128, 16-token pages, GQA group <= 16).
+bool paged_attention_fast_supported(const AttnParams& p, int dtype);
+int launch_paged_attention_fast(const AttnParams& p, int dtype, cudaStream_t stream);
+int paged_attention_device_status(bool reset);
 
 }  // namespace cb200

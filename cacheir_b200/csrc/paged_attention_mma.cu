@@ -1,0 +1,400 @@
+// Paged decode attention, fast path: fp16/bf16 pools, head_dim 64 or 128, 16-token pages.
+//
+// One CTA per (context split, KV head, sequence). A producer warp walks the
+// sequence's page table and brings each (page, kv head) chunk -- 16 rows of K and 16
+// rows of V, 4 KB each at head_dim 128 -- into shared memory with TMA tensor copies
+// (128-byte swizzle, so that the ldmatrix reads below are bank-conflict free),
+// through a ring of stages guarded by mbarriers. Four consumer warps each take one
+// page of a stage: S = Q K^T and O += P V run on the tensor cores (mma.sync
+// m16n8k16, fp32 accumulation) with all query heads of the GQA group as the 16-row
+// M dimension, so every K/V byte is read from HBM once for the whole group. The
+// online softmax keeps its running max / sum per row in registers (quad shuffles);
+// the four warps' states are merged once per CTA in warp order, and context splits
+// are merged by the combine kernel in split order: bit-reproducible.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "paged_attention_common.cuh"
+
+namespace cb200 {
+namespace {
+
+constexpr int kPage = 16;
+constexpr int kPagesPerStage = 4;
+constexpr int kConsumerWarps = 4;
+constexpr int kFastThreads = (kConsumerWarps + 1) * 32;
+constexpr uint32_t kPollLimit = 8u * 1000u * 1000u;
+
+__device__ int g_attn_status = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int id) {
+  for (uint32_t i = 0; i < kPollLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) __nanosleep(32);
+  }
+  atomicCAS(&g_attn_status, 0, (2 << 8) | id);
+  return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+template <typename T>
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma_16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kFastThreads)
+paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                        const AttnParams p, const int stages) {
+  constexpr int kTileBytes = kPage * D * 2;       // one K or V page chunk: 4 KB at D=128
+  constexpr int kPageBytes = 2 * kTileBytes;      // K + V
+  constexpr int kStageBytes = kPagesPerStage * kPageBytes;
+  constexpr int kKSteps = D / 16;                 // k steps of the QK^T product
+  constexpr int kDimTiles = D / 8;                // n tiles of the PV product
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + stages * kStageBytes);
+  uint64_t* empty = full + stages;
+
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int b = blockIdx.z;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int seq_len = p.seq_lens[b];
+  const int t_begin = split * p.chunk_tokens;
+  if (p.splits > 1 && t_begin >= seq_len) return;      // combine never reads this split
+  const int t_end = min(seq_len, t_begin + p.chunk_tokens);
+  const int page_begin = t_begin / kPage;              // chunk_tokens is a multiple of the page size
+  const int n_pages = t_end > t_begin ? (t_end - t_begin + kPage - 1) / kPage : 0;
+  const int n_iters = (n_pages + kPagesPerStage - 1) / kPagesPerStage;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&full[s]), 1);
+      mbar_init(smem_u32(&empty[s]), kConsumerWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  // per-thread softmax / output state of the two rows (heads) this thread owns: g and g + 8
+  const int g = lane >> 2;
+  const int t4 = lane & 3;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  float o[kDimTiles][4];
+#pragma unroll
+  for (int i = 0; i < kDimTiles; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  bool ok = true;
+
+  if (warp == kConsumerWarps) {
+    // ---------------- producer warp: lane j copies page j of each stage ----------------
+    const int32_t* pt = p.page_table + static_cast<size_t>(b) * p.max_pages + page_begin;
+    int next_id = lane < min(kPagesPerStage, n_pages) ? pt[lane] : 0;   // page ids are fetched one stage ahead
+    for (int it = 0; it < n_iters && ok; ++it) {
+      const int s = it % stages;
+      const uint32_t ph = (it / stages) & 1;
+      const int first = it * kPagesPerStage;
+      const int cnt = min(kPagesPerStage, n_pages - first);
+      const int page_id = next_id;
+      if (first + kPagesPerStage + lane < n_pages && lane < kPagesPerStage) next_id = pt[first + kPagesPerStage + lane];
+      if (lane == 0) {
+        ok = mbar_wait(smem_u32(&empty[s]), ph ^ 1, 1);
+        if (ok) mbar_expect_tx(smem_u32(&full[s]), cnt * kPageBytes);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (ok && lane < cnt) {
+        const uint32_t dst = smem_u32(smem + s * kStageBytes + lane * kPageBytes);
+        const int row = (page_id * p.kv_heads + kvh) * kPage;
+        tma_load_3d(dst, &tmap_k, smem_u32(&full[s]), 0, row, 0);
+        tma_load_3d(dst + kTileBytes, &tmap_v, smem_u32(&full[s]), 0, row, 0);
+      }
+    }
+  } else {
+    // ---------------- consumer warps ----------------
+    // Q as the A operand: rows = heads of the group (zero beyond the group), 16 dims per k step
+    uint32_t qa[kKSteps][4];
+    {
+      const T* qb = static_cast<const T*>(p.q) + static_cast<size_t>(b) * p.q_stride + static_cast<size_t>(kvh) * p.group * D;
+#pragma unroll
+      for (int ks = 0; ks < kKSteps; ++ks) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int row = g + (r & 1) * 8;
+          const int col = ks * 16 + 2 * t4 + (r >> 1) * 8;
+          qa[ks][r] = row < p.group ? *reinterpret_cast<const uint32_t*>(qb + static_cast<size_t>(row) * D + col) : 0u;
+        }
+      }
+    }
+    const uint32_t lrow = lane & 7;        // row supplied by this lane to ldmatrix
+    const uint32_t lmat = lane >> 3;       // which of the four 8x8 matrices
+    for (int it = 0; it < n_iters && ok; ++it) {
+      const int s = it % stages;
+      ok = mbar_wait(smem_u32(&full[s]), (it / stages) & 1, 2);
+      if (!ok) break;
+      const int pg = it * kPagesPerStage + warp;       // this warp's page of the stage
+      if (pg < n_pages) {
+        const uint32_t kbase = smem_u32(smem + s * kStageBytes + warp * kPageBytes);
+        const uint32_t vbase = kbase + kTileBytes;
+        // ---- S = Q K^T for the 16 tokens of the page: two n tiles of 8 tokens ----
+        float sc[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+          const uint32_t token = nt * 8 + lrow;
+#pragma unroll
+          for (int kk = 0; kk < kKSteps / 2; ++kk) {
+            const uint32_t c = 4 * kk + lmat;          // 16-byte chunk of the row
+            uint32_t kb[4];
+            ldmatrix_x4(kbase + (c >> 3) * (kPage * 128) + token * 128 + (((c & 7) ^ (token & 7)) << 4), kb);
+            mma_16816<T>(sc[nt], qa[2 * kk], kb[0], kb[1]);
+            mma_16816<T>(sc[nt], qa[2 * kk + 1], kb[2], kb[3]);
+          }
+        }
+        // ---- online softmax over the page (rows g and g+8; columns 2*t4, 2*t4+1 of each tile) ----
+        const int tok0 = t_begin + pg * kPage;
+        float pmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int tok = tok0 + nt * 8 + 2 * t4 + (e & 1);
+            const float v = tok < t_end ? sc[nt][e] * p.scale_log2 : -INFINITY;
+            sc[nt][e] = v;
+            pmax[e >> 1] = fmaxf(pmax[e >> 1], v);
+          }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          pmax[r] = fmaxf(pmax[r], __shfl_xor_sync(0xffffffffu, pmax[r], 1));
+          pmax[r] = fmaxf(pmax[r], __shfl_xor_sync(0xffffffffu, pmax[r], 2));
+        }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const float m_new = fmaxf(m_run[r], pmax[r]);    // finite: every loaded page has a valid token
+          corr[r] = exp2f(m_run[r] - m_new);               // first page: exp2(-inf) = 0
+          m_run[r] = m_new;
+        }
+        uint32_t pa[4];
+        {
+          float pr[2][4];
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pr[nt][e] = exp2f(sc[nt][e] - m_run[e >> 1]);
+#pragma unroll
+          for (int r = 0; r < 2; ++r)
+            l_run[r] = l_run[r] * corr[r] + (pr[0][2 * r] + pr[0][2 * r + 1] + pr[1][2 * r] + pr[1][2 * r + 1]);
+          // P as the A operand of the PV product (16 heads x 16 tokens)
+          pa[0] = pack2<T>(pr[0][0], pr[0][1]);
+          pa[1] = pack2<T>(pr[0][2], pr[0][3]);
+          pa[2] = pack2<T>(pr[1][0], pr[1][1]);
+          pa[3] = pack2<T>(pr[1][2], pr[1][3]);
+        }
+        // ---- O = O * corr + P V ----
+#pragma unroll
+        for (int j = 0; j < kDimTiles / 2; ++j) {
+          o[2 * j][0] *= corr[0]; o[2 * j][1] *= corr[0]; o[2 * j][2] *= corr[1]; o[2 * j][3] *= corr[1];
+          o[2 * j + 1][0] *= corr[0]; o[2 * j + 1][1] *= corr[0]; o[2 * j + 1][2] *= corr[1]; o[2 * j + 1][3] *= corr[1];
+          const uint32_t token = (lmat & 1) * 8 + lrow;
+          const uint32_t c = 2 * j + (lmat >> 1);
+          uint32_t vb[4];
+          ldmatrix_x4_trans(vbase + (c >> 3) * (kPage * 128) + token * 128 + (((c & 7) ^ (token & 7)) << 4), vb);
+          mma_16816<T>(o[2 * j], pa, vb[0], vb[1]);
+          mma_16816<T>(o[2 * j + 1], pa, vb[2], vb[3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty[s]));
+    }
+    // the row sums were kept per thread: finish them across the quad
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+  }
+
+  // ---------------- merge the consumer warps in warp order ----------------
+  __syncthreads();                        // every stage is consumed: the ring can be reused
+  float* s_m = reinterpret_cast<float*>(smem);                  // [warps][16]
+  float* s_l = s_m + kConsumerWarps * 16;                       // [warps][16]
+  float* s_o = s_l + kConsumerWarps * 16;                       // [warps][16][D]
+  if (warp < kConsumerWarps) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + r * 8;
+      if (t4 == 0) { s_m[warp * 16 + row] = m_run[r]; s_l[warp * 16 + row] = l_run[r]; }
+#pragma unroll
+      for (int i = 0; i < kDimTiles; ++i) {
+        s_o[(warp * 16 + row) * D + i * 8 + 2 * t4] = o[i][2 * r];
+        s_o[(warp * 16 + row) * D + i * 8 + 2 * t4 + 1] = o[i][2 * r + 1];
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < p.group * D; idx += kFastThreads) {
+    const int row = idx / D;
+    const int d = idx % D;
+    float m_tot = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) m_tot = fmaxf(m_tot, s_m[w * 16 + row]);
+    float l_tot = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) {
+      const float mi = s_m[w * 16 + row];
+      const float wgt = (mi == -INFINITY) ? 0.f : exp2f(mi - m_tot);
+      l_tot = fmaf(s_l[w * 16 + row], wgt, l_tot);
+      acc = fmaf(s_o[(w * 16 + row) * D + d], wgt, acc);
+    }
+    const int h = kvh * p.group + row;
+    if (p.splits == 1) {
+      T* ob = static_cast<T*>(p.out) + static_cast<size_t>(b) * p.out_stride;
+      Elem<T>::st(ob + static_cast<size_t>(h) * D + d, l_tot > 0.f ? acc / l_tot : 0.f);
+    } else {
+      const size_t unit = (static_cast<size_t>(b) * p.heads + h) * p.splits + split;
+      p.ws_acc[unit * D + d] = acc;
+      if (d == 0) {
+        p.ws_ml[unit * 2] = m_tot;
+        p.ws_ml[unit * 2 + 1] = l_tot;
+      }
+    }
+  }
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// The pool [slots, kv_heads, 16, D] as a 3-D tensor [D/64 spans][rows][64 elements]: one box
+// {64, 16, D/64} is one (page, kv head) chunk, landing as [span][16 rows][128 B] with the 128-byte swizzle.
+bool encode_pool(CUtensorMap* map, const void* base, int dtype, uint64_t rows, int head_dim) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {64, rows, static_cast<cuuint64_t>(head_dim / 64)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 2, 128};
+  const cuuint32_t box[3] = {64, kPage, static_cast<cuuint32_t>(head_dim / 64)};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUtensorMapDataType type = dtype == CACHEIR_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  return fn(map, type, 3, const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int D>
+int launch_fast(const AttnParams& p, int dtype, uint64_t pool_rows, cudaStream_t stream) {
+  CUtensorMap tmap_k, tmap_v;
+  if (!encode_pool(&tmap_k, p.k_cache, dtype, pool_rows, D) || !encode_pool(&tmap_v, p.v_cache, dtype, pool_rows, D))
+    return CACHEIR_B200_EUNSUPPORTED;
+  constexpr int kStageBytes = kPagesPerStage * 2 * kPage * D * 2;
+  const int stages = D == 128 ? 3 : 4;
+  size_t smem = 1024 + static_cast<size_t>(stages) * kStageBytes + 256;
+  const size_t merge = static_cast<size_t>(kConsumerWarps) * 16 * (D + 2) * sizeof(float) + 1024;
+  if (smem < merge) smem = merge;
+  auto kern = paged_decode_mma_kernel<T, D>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const dim3 grid(p.splits, p.kv_heads, p.batch);
+  kern<<<grid, kFastThreads, smem, stream>>>(tmap_k, tmap_v, p, stages);
+  return launch_status();
+}
+
+}  // namespace
+
+bool paged_attention_fast_supported(const AttnParams& p, int dtype) {
+  if (dtype != CACHEIR_B200_F16 && dtype != CACHEIR_B200_BF16) return false;
+  if (p.head_dim != 64 && p.head_dim != 128) return false;
+  if (p.page_size != kPage || p.group > 16) return false;
+  if (p.chunk_tokens % kPage != 0) return false;
+  if (!aligned_to(p.k_cache, 16) || !aligned_to(p.v_cache, 16) || !aligned_to(p.q, 4) || (p.q_stride % 2) != 0) return false;
+  return encode_fn() != nullptr;
+}
+
+int launch_paged_attention_fast(const AttnParams& p, int dtype, cudaStream_t stream) {
+  // The C ABI (like the reference's) does not carry the slot count of the pool; the tensor map only
+  // needs an upper bound for its bounds check, and page ids are trusted exactly as in every other kernel.
+  const uint64_t rows = 1ull << 30;
+  if (dtype == CACHEIR_B200_F16)
+    return p.head_dim == 128 ? launch_fast<__half, 128>(p, dtype, rows, stream) : launch_fast<__half, 64>(p, dtype, rows, stream);
+  return p.head_dim == 128 ? launch_fast<__nv_bfloat16, 128>(p, dtype, rows, stream)
+                           : launch_fast<__nv_bfloat16, 64>(p, dtype, rows, stream);
+}
+
+int paged_attention_device_status(bool reset) {
+  int status = 0;
+  if (cudaMemcpyFromSymbol(&status, g_attn_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && status != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int));
+  }
+  return status;
+}
+
+}  // namespace cb200

@@ -8,6 +8,7 @@
 // the path for fp32 activations, for dense (unquantized) weights and for shapes
 // the tensor-core kernel does not take.
 #include "common.cuh"
+#include "paged_attention_common.cuh"
 #include "qgemv_common.cuh"
 
 namespace cb200 {
@@ -227,4 +228,8 @@ extern "C" int cacheir_b200_qgemv(const void* x, const void* packed, const void*
   return launch_qgemv_cuda_core(p, st);
 }
 
-extern "C" int cacheir_b200_device_status(int reset) { return qgemm_tc_device_status(reset != 0); }
+extern "C" int cacheir_b200_device_status(int reset) {
+  const int gemm = qgemm_tc_device_status(reset != 0);
+  const int attn = paged_attention_device_status(reset != 0);
+  return gemm != 0 ? gemm : attn;
+}
