@@ -251,13 +251,14 @@ void resolve_attention_splits(int batch, int heads, int kv_heads, int max_pages,
   const long long max_ctx = static_cast<long long>(max_pages) * page_size;
   int s = requested;
   if (s <= 0) {
-    // ~1024-token chunks bound the tail of the longest sequence; small batches get
-    // more splits so that at least two waves of CTAs cover the 148 SMs.
-    s = static_cast<int>((max_ctx + 1023) / 1024);
-    const long long units = static_cast<long long>(batch) * kv_heads * ((heads / kv_heads + 7) / 8);
-    const long long want = (2LL * kNumSMs + units - 1) / units;
+    // Every extra split costs a few microseconds (partials + the combine launch), so split only as
+    // far as needed: chunks of at most 4096 tokens bound the tail of the longest sequence of a
+    // ragged batch, and small batches get enough splits to put one CTA on each of the 148 SMs.
+    s = static_cast<int>((max_ctx + 4095) / 4096);
+    const long long units = static_cast<long long>(batch) * kv_heads * ((heads / kv_heads + 15) / 16);
+    const long long want = (kNumSMs + units - 1) / units;
     if (s < want) s = static_cast<int>(want);
-    const int cap = static_cast<int>((max_ctx + 127) / 128);
+    const int cap = static_cast<int>((max_ctx + 255) / 256);
     if (s > cap) s = cap;
   }
   if (s > kMaxAttentionSplits) s = kMaxAttentionSplits;
