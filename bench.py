@@ -182,6 +182,27 @@ def step_bytes(cfg: dict, ctx: int) -> dict:
     return {"weights": weights, "kv": kv, "total": weights + kv}
 
 
+def time_graph(fn, iters: int) -> float:
+    """Seconds per call of `fn`, timed with CUDA events around the replay of a CUDA graph that
+    holds `iters` calls (host launch cost would otherwise dominate kernels of a few microseconds)."""
+    import torch
+
+    fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(iters):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) * 1e-3 / iters
+
+
 def time_attention_kernel(rt, sessions, cfg: dict, iters: int = 3) -> dict:
     """The dominant kernel alone: one launch per layer over that layer's page pool (each
     pool is larger than L2, so every launch streams from HBM), CUDA events on the launch stream."""
@@ -204,15 +225,7 @@ def time_attention_kernel(rt, sessions, cfg: dict, iters: int = 3) -> dict:
             ops.paged_attention_decode_batch(q, pool["keys"], pool["values"], plan.page_table, lens, out=out,
                                              num_splits=splits, workspace=ws)
 
-    sweep()
-    torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(iters):
-        sweep()
-    end.record()
-    torch.cuda.synchronize()
-    per_launch_s = start.elapsed_time(end) * 1e-3 / (iters * len(pools))
+    per_launch_s = time_graph(sweep, iters) / len(pools)
     total_ctx = int(lens.sum().item())
     algo = total_ctx * KVH * hd * 2 * 2 + 2 * B * H * hd * 2 + B * plan.width * 4 + B * 4
     return {"kernel": "paged_attention_decode_batch", "seconds": per_launch_s, "bytes": algo, "splits": splits}
@@ -246,17 +259,13 @@ def time_gemv_kernels(rt, cfg: dict, iters: int = 3) -> list[dict]:
         epi = ops.EPI_SWIGLU if name == "gate_up" else ops.EPI_NONE
         x = torch.randn((B, k), device=rt.device, dtype=torch.float16)
         out = torch.empty((B, n // 2 if epi == ops.EPI_SWIGLU else n), device=rt.device, dtype=torch.float16)
-        for w in ws:
-            quantized_matmul(x, w, epilogue=epi, out=out)
-        torch.cuda.synchronize()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(iters):
+        scratch = torch.empty(ops.qgemv_workspace_bytes(B, k), device=rt.device, dtype=torch.uint8)
+
+        def sweep(ws=ws, x=x, out=out, epi=epi, scratch=scratch) -> None:
             for w in ws:
-                quantized_matmul(x, w, epilogue=epi, out=out)
-        end.record()
-        torch.cuda.synchronize()
-        sec = start.elapsed_time(end) * 1e-3 / (iters * len(ws))
+                quantized_matmul(x, w, epilogue=epi, out=out, workspace=scratch)
+
+        sec = time_graph(sweep, iters) / len(ws)
         algo = ws[0].nbytes + B * k * 2 + out.numel() * 2
         results.append({"kernel": f"qgemv_int{ws[0].bits}_{name}", "shape": [B, n, k], "seconds": sec, "bytes": algo})
     return results
@@ -431,8 +440,13 @@ def run_micro(args) -> None:
         epi = {"none": ops.EPI_NONE, "swiglu": ops.EPI_SWIGLU}[args.epilogue]
         out = torch.empty((m, n // 2 if epi == ops.EPI_SWIGLU else n), device=dev, dtype=torch.float16)
 
+        ws = None
+        if args.workspace:
+            ws = torch.empty(ops.qgemv_workspace_bytes(m, k), device=dev, dtype=torch.uint8)
+
         def launch(i: int) -> None:
-            ops.qgemv(x, packed[i % copies], scales, zeros, bits=bits, n=n, k=k, group_size=args.group, epilogue=epi, out=out)
+            ops.qgemv(x, packed[i % copies], scales, zeros, bits=bits, n=n, k=k, group_size=args.group, epilogue=epi,
+                      out=out, workspace=ws)
 
         algo = n * row_bytes + scales.numel() * scales.element_size() + (n * 4 if zeros is not None else 0) + m * k * 2 + out.numel() * 2
         name = f"qgemv_int{bits}" + (f"_g{args.group}" if args.group else "")
@@ -467,10 +481,17 @@ def run_micro(args) -> None:
     for i in range(max(1, args.warmup)):
         launch(i)
     torch.cuda.synchronize()
+    # The launches are captured in a CUDA graph so that the host's launch cost (tens of
+    # microseconds from Python) does not hide kernels that take a few microseconds.
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(args.steps):
+            launch(i)
+    graph.replay()
+    torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for i in range(args.steps):
-        launch(i)
+    graph.replay()
     end.record()
     torch.cuda.synchronize()
     sec = start.elapsed_time(end) * 1e-3 / args.steps
@@ -497,6 +518,7 @@ def main() -> None:
     parser.add_argument("--group", type=int, default=0)
     parser.add_argument("--epilogue", default="none", choices=["none", "swiglu"])
     parser.add_argument("--copies", type=int, default=4)
+    parser.add_argument("--workspace", action="store_true", help="give qgemv its scratch (integer tensor-core path)")
     parser.add_argument("--batch", type=int, default=64)
     parser.add_argument("--ctx-min", type=int, default=512)
     parser.add_argument("--ctx-max", type=int, default=8192)

@@ -35,6 +35,12 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # x packed scales zero_points residual y
          c_int, c_int, c_int, c_int, c_int, c_int, c_int,              # M N K bits group x_dtype scale_dtype
          c_longlong, c_int, c_void_p]),                                # x_stride epilogue stream
+    "cacheir_b200_qgemv_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "cacheir_b200_qgemv_ex": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+         c_longlong, c_int, c_void_p, c_size_t, c_void_p]),
     "cacheir_b200_device_status": (c_int, [c_int]),
     "cacheir_b200_pack_rows": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_void_p]),
     "cacheir_b200_dequantize_rows": (c_int, [c_void_p] * 4 + [c_int, c_int, c_int, c_int, c_void_p]),

@@ -70,7 +70,7 @@ qgemv_cuda_core_kernel(const QGemvParams p) {
     const uint8_t* wrow = static_cast<const uint8_t*>(p.packed) + static_cast<size_t>(n) * row_bytes;
     float zp = 0.f;
     if (BITS != 0) {
-      zp = (p.group_size == 0 && p.zero_points) ? p.zero_points[n] : static_cast<float>(1 << (BITS - 1));
+      zp = (p.group_size == 0 && p.zero_points) ? p.zero_points[n] : static_cast<float>(BITS > 0 ? (1 << (BITS > 0 ? BITS - 1 : 0)) : 0);
     }
     const int groups_per_row = p.group_size > 0 ? K / p.group_size : 1;
     float acc[MT];
@@ -190,10 +190,13 @@ int launch_qgemv_cuda_core(const QGemvParams& p, cudaStream_t stream) {
 
 using namespace cb200;
 
-extern "C" int cacheir_b200_qgemv(const void* x, const void* packed, const void* scales,
-                                  const float* zero_points, const void* residual, void* y, int M,
-                                  int N, int K, int bits, int group_size, int x_dtype,
-                                  int scale_dtype, long long x_stride, int epilogue, void* stream) {
+extern "C" size_t cacheir_b200_qgemv_workspace_bytes(int M, int K) { return qgemm_i8_workspace_bytes(M, K); }
+
+extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const void* scales,
+                                     const float* zero_points, const void* residual, void* y, int M,
+                                     int N, int K, int bits, int group_size, int x_dtype,
+                                     int scale_dtype, long long x_stride, int epilogue,
+                                     void* workspace, size_t workspace_bytes, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (!x || !packed || !y) return CACHEIR_B200_EINVAL;
   const int esize = dtype_size(x_dtype);
@@ -224,12 +227,22 @@ extern "C" int cacheir_b200_qgemv(const void* x, const void* packed, const void*
   p.vector_ok = aligned_to(packed, 16) && row_bytes % 16 == 0 && aligned_to(x, 16) &&
                 (p.x_stride * esize) % 16 == 0;
   cudaStream_t st = as_stream(stream);
+  if (qgemm_i8_supported(p, workspace, workspace_bytes)) return launch_qgemm_i8(p, workspace, st);
   if (qgemm_tc_supported(p)) return launch_qgemm_tc(p, st);
   return launch_qgemv_cuda_core(p, st);
+}
+
+extern "C" int cacheir_b200_qgemv(const void* x, const void* packed, const void* scales,
+                                  const float* zero_points, const void* residual, void* y, int M,
+                                  int N, int K, int bits, int group_size, int x_dtype,
+                                  int scale_dtype, long long x_stride, int epilogue, void* stream) {
+  return cacheir_b200_qgemv_ex(x, packed, scales, zero_points, residual, y, M, N, K, bits, group_size, x_dtype,
+                               scale_dtype, x_stride, epilogue, nullptr, 0, stream);
 }
 
 extern "C" int cacheir_b200_device_status(int reset) {
   const int gemm = qgemm_tc_device_status(reset != 0);
   const int attn = paged_attention_device_status(reset != 0);
-  return gemm != 0 ? gemm : attn;
+  const int i8 = qgemm_i8_device_status(reset != 0);
+  return gemm != 0 ? gemm : (attn != 0 ? attn : i8);
 }

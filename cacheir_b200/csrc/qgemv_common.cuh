@@ -27,6 +27,12 @@ int launch_qgemv_cuda_core(const QGemvParams& p, cudaStream_t stream);
 // Tensor-core (tcgen05) small-M GEMM: weights are the 128-row MMA operand.
 bool qgemm_tc_supported(const QGemvParams& p);
 int launch_qgemm_tc(const QGemvParams& p, cudaStream_t stream);
+// Integer tensor-core path (int8 per-row weights, fp16 activations turned into 16-bit fixed point).
+// Needs `qgemm_i8_workspace_bytes` of caller scratch for the activation bytes.
+size_t qgemm_i8_workspace_bytes(int M, int K);
+bool qgemm_i8_supported(const QGemvParams& p, const void* workspace, size_t workspace_bytes);
+int launch_qgemm_i8(const QGemvParams& p, void* workspace, cudaStream_t stream);
+int qgemm_i8_device_status(bool reset);
 // Device-side status word of the tensor-core kernel (0 = no bounded wait ever gave up).
 int qgemm_tc_device_status(bool reset);
 

@@ -100,9 +100,14 @@ def paged_attention_decode_batch(q: torch.Tensor, k_cache: torch.Tensor, v_cache
     return out
 
 
+def qgemv_workspace_bytes(m: int, k: int) -> int:
+    return int(_lib.load().cacheir_b200_qgemv_workspace_bytes(int(m), int(k)))
+
+
 def qgemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor | None, zero_points: torch.Tensor | None, *,
           bits: int, n: int, k: int, group_size: int = 0, epilogue: int = EPI_NONE,
-          residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+          residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
+          workspace: torch.Tensor | None = None) -> torch.Tensor:
     """y[M, N_out] = x[M, K] . deq(W)[N, K]^T with the reference's pack format
     (bits 8/4; bits 0 = dense weights of x's dtype). x: [..., K] with dense rows."""
     _require_cuda(x, packed, scales, zero_points, residual, out)
@@ -134,11 +139,13 @@ def qgemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor | None, ze
         raise ValueError("out must be a contiguous [M, N_out] tensor of x's dtype")
     if residual is not None and (residual.numel() != m * n_out or residual.dtype != x.dtype or not residual.is_contiguous()):
         raise ValueError("residual must be a contiguous [M, N_out] tensor of x's dtype")
-    check(_lib.load().cacheir_b200_qgemv(
+    _require_cuda(workspace)
+    ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    check(_lib.load().cacheir_b200_qgemv_ex(
         x2.data_ptr(), packed.data_ptr(), _ptr(scales), _ptr(zero_points), _ptr(residual), out.data_ptr(),
         m, n, k, bits, group_size, dtype_code(x.dtype),
         F16 if (scales is not None and scales.dtype == torch.float16) else F32,
-        x2.stride(0), epilogue, _stream()), "qgemv")
+        x2.stride(0), epilogue, _ptr(workspace), ws_bytes, _stream()), "qgemv")
     return out
 
 

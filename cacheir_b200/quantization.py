@@ -104,7 +104,9 @@ def dequantize_device(w: B200PackedWeight, dtype: torch.dtype) -> torch.Tensor:
 
 
 def quantized_matmul(x: torch.Tensor, w: B200PackedWeight, *, epilogue: int = ops.EPI_NONE,
-                     residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
-    """`_quantized_matmul` (cacheir/runtime/cuda.py:932-940) without materialising the dense weight."""
+                     residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                     workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """`_quantized_matmul` (cacheir/runtime/cuda.py:932-940) without materialising the dense weight.
+    `workspace` (ops.qgemv_workspace_bytes) enables the integer tensor-core path for int8 weights."""
     return ops.qgemv(x, w.packed_values, w.scales, w.zero_points, bits=w.bits, n=w.shape[0], k=w.shape[1],
-                     group_size=w.group_size or 0, epilogue=epilogue, residual=residual, out=out)
+                     group_size=w.group_size or 0, epilogue=epilogue, residual=residual, out=out, workspace=workspace)

@@ -243,6 +243,9 @@ class _DecodePlan:
         for name in eng.graph.outputs:
             uses[name] = uses.get(name, 0) + 1
 
+        if eng.dtype == torch.float16 and eng.quant:
+            widest = max(int(eng.config.hidden_size), int(eng.config.intermediate_size))
+            self._gemm_ws = torch.empty((ops.qgemv_workspace_bytes(self.batch, widest),), device=eng.device, dtype=torch.uint8)
         self._emit(lambda: ops.advance_positions(self.positions, self.seq_lens), "b200.advance_positions")
         skip: set[int] = set()
         for idx, node in enumerate(nodes):
@@ -347,10 +350,15 @@ class _DecodePlan:
         if isinstance(weight, B200PackedWeight):
             n, k, bits = weight.shape[0], weight.shape[1], weight.bits
             out = self._buf(n // 2 if epilogue == ops.EPI_SWIGLU else n)
+            ws = self._gemm_workspace(k) if (bits == 8 and not weight.group_size and eng.dtype == torch.float16) else None
             fn = lambda: ops.qgemv(x, weight.packed_values, weight.scales, weight.zero_points, bits=bits, n=n, k=k,
-                                   group_size=weight.group_size or 0, epilogue=epilogue, residual=residual, out=out)
+                                   group_size=weight.group_size or 0, epilogue=epilogue, residual=residual, out=out,
+                                   workspace=ws)
             key = f"b200.qgemv.int{bits}" + (".swiglu" if epilogue == ops.EPI_SWIGLU else ".residual" if residual is not None else "")
             eng.gemm_plans[f"q{bits}:{(self.batch, 1, k)}x{weight.shape}"] = key
+            if ws is not None and self.batch <= 64 and k % 128 == 0:   # activation pre-pass + integer GEMM
+                self._emit(fn, key, launches=2)
+                return out
         else:
             n, k = int(weight.shape[0]), int(weight.shape[1])
             out = self._buf(n // 2 if epilogue == ops.EPI_SWIGLU else n)
@@ -359,6 +367,17 @@ class _DecodePlan:
             eng.gemm_plans[f"{(self.batch, 1, k)}x{(n, k)}"] = key
         self._emit(fn, key)
         return out
+
+    def _gemm_workspace(self, k: int) -> torch.Tensor:
+        """Scratch for the integer tensor-core GEMM (activation bytes); one buffer per plan, sized for
+        the widest input, reused by every projection of the step (they run back to back on one stream)."""
+        need = ops.qgemv_workspace_bytes(self.batch, k)
+        ws = getattr(self, "_gemm_ws", None)
+        if ws is None or ws.numel() < need:
+            if ws is not None and self.program:
+                raise RuntimeError("GEMM workspace must be sized before the first projection is lowered")
+            self._gemm_ws = ws = torch.empty((need,), device=self.engine.device, dtype=torch.uint8)
+        return ws
 
     def _attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attrs: dict[str, Any]) -> torch.Tensor:
         eng = self.engine

@@ -154,6 +154,22 @@ int cacheir_b200_qgemv(const void* x, const void* packed, const void* scales,
                        int x_dtype, int scale_dtype, long long x_stride,
                        int epilogue, void* stream);
 
+/* Same operation with caller-provided scratch. With at least
+ * cacheir_b200_qgemv_workspace_bytes(M, K) bytes of 128-byte aligned workspace, int8
+ * per-row weights with fp16 activations (M <= 64, K % 128 == 0) run on the integer
+ * tensor cores: the uint8 codes are fed to the MMA as they are, and x is first turned
+ * into 16-bit fixed point per row (two signed bytes, 2^-15 of the row maximum) in the
+ * workspace. Other shapes ignore the workspace. workspace may be NULL (then this is
+ * cacheir_b200_qgemv). The workspace is only used during the call's own kernels; two
+ * calls that may overlap on the GPU need separate workspaces. */
+size_t cacheir_b200_qgemv_workspace_bytes(int M, int K);
+int cacheir_b200_qgemv_ex(const void* x, const void* packed, const void* scales,
+                          const float* zero_points, const void* residual, void* y,
+                          int M, int N, int K, int bits, int group_size,
+                          int x_dtype, int scale_dtype, long long x_stride,
+                          int epilogue, void* workspace, size_t workspace_bytes,
+                          void* stream);
+
 /* Status word of the kernels that wait on hardware barriers (the tensor-core GEMM):
  * 0, or a non-zero code recorded by the first wait that ran out of its poll budget
  * (the kernel then drains and returns instead of hanging; its output is undefined).

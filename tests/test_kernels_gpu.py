@@ -386,3 +386,55 @@ def test_qgemm_tensor_core_epilogues_and_odd_zero_points():
     assert _rel(y2, base) <= TOL[torch.float16]
     torch.cuda.synchronize()
     _device_status_ok()
+
+
+# ---- integer tensor-core path: int8 codes straight into tcgen05.mma kind::i8 -------------
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("n,k", [(512, 1024), (200, 256), (128, 4096), (4096, 2048)])
+def test_qgemm_int8_tensor_core_with_workspace(m, n, k):
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(m * 31 + n + k)
+    x, packed = _qgemv_case(rng, m, n, k, 8, torch.float16)
+    ws = torch.empty(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
+    y = quantized_matmul(x.cuda(), _device_pack(packed), workspace=ws)
+    torch.cuda.synchronize()
+    _device_status_ok()
+    want = oracle.quantized_matmul(x.float().numpy(), packed)
+    assert _rel(y, want) <= TOL[torch.float16]
+    # and it agrees with the fp16 tensor-core path to well inside the gate
+    y2 = quantized_matmul(x.cuda(), _device_pack(packed))
+    assert _rel(y, y2.float().cpu().numpy()) <= TOL[torch.float16]
+
+
+def test_qgemm_int8_tensor_core_epilogues_offsets_and_determinism():
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(91)
+    m, n, k = 32, 512, 2048
+    x, packed = _qgemv_case(rng, m, n, k, 8, torch.float16)
+    x = (x.float() * 3.0 + 2.5).half()          # activations with a large mean: the zero-point term must cancel exactly
+    x[5] = 0                                    # an all-zero row
+    x[7, 3] = 60000.0                           # a row dominated by one huge value
+    dev = _device_pack(packed)
+    dev.zero_points[3] = 2500.0                 # an unclipped zero point of the reference packer
+    dev.zero_points[9] = 100.5
+    host = oracle.PackedQuantizedTensor(packed.packed_values, packed.scales, dev.zero_points.cpu().numpy(), 8, (n, k))
+    base = oracle.quantized_matmul(x.float().numpy(), host)
+    ws = torch.empty(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
+    y = quantized_matmul(x.cuda(), dev, workspace=ws)
+    rows = [i for i in range(m) if i != 7]      # row 7 overflows fp16 in the oracle too
+    assert _rel(y[rows], base[rows]) <= TOL[torch.float16]
+    assert float(y[5].abs().max()) == 0.0
+    y_again = quantized_matmul(x.cuda(), dev, workspace=ws)
+    assert torch.equal(y, y_again)
+    res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).half()
+    y = quantized_matmul(x.cuda(), dev, epilogue=ops.EPI_RESIDUAL, residual=res.cuda(), workspace=ws)
+    assert _rel(y[rows], (base + res.float().numpy())[rows]) <= TOL[torch.float16]
+    x2, packed2 = _qgemv_case(rng, m, n, k, 8, torch.float16)
+    base2 = oracle.quantized_matmul(x2.float().numpy(), packed2)
+    y = quantized_matmul(x2.cuda(), _device_pack(packed2), epilogue=ops.EPI_SWIGLU, workspace=ws)
+    assert y.shape == (m, n // 2)
+    assert _rel(y, oracle.silu_mul(base2[:, : n // 2], base2[:, n // 2:])) <= TOL[torch.float16] * 2
+    torch.cuda.synchronize()
+    _device_status_ok()
