@@ -440,13 +440,15 @@ def run_micro(args) -> None:
         epi = {"none": ops.EPI_NONE, "swiglu": ops.EPI_SWIGLU}[args.epilogue]
         out = torch.empty((m, n // 2 if epi == ops.EPI_SWIGLU else n), device=dev, dtype=torch.float16)
 
+        if args.tiled:
+            packed = [ops.pack_relayout(w, n=n, k=k, bits=bits) for w in packed]
         ws = None
         if args.workspace:
             ws = torch.empty(ops.qgemv_workspace_bytes(m, k), device=dev, dtype=torch.uint8)
 
         def launch(i: int) -> None:
             ops.qgemv(x, packed[i % copies], scales, zeros, bits=bits, n=n, k=k, group_size=args.group, epilogue=epi,
-                      out=out, workspace=ws)
+                      out=out, workspace=ws, tiled=args.tiled)
 
         algo = n * row_bytes + scales.numel() * scales.element_size() + (n * 4 if zeros is not None else 0) + m * k * 2 + out.numel() * 2
         name = f"qgemv_int{bits}" + (f"_g{args.group}" if args.group else "")
@@ -519,6 +521,7 @@ def main() -> None:
     parser.add_argument("--epilogue", default="none", choices=["none", "swiglu"])
     parser.add_argument("--copies", type=int, default=4)
     parser.add_argument("--workspace", action="store_true", help="give qgemv its scratch (integer tensor-core path)")
+    parser.add_argument("--tiled", action="store_true", help="weights in the tile order of pack_relayout")
     parser.add_argument("--batch", type=int, default=64)
     parser.add_argument("--ctx-min", type=int, default=512)
     parser.add_argument("--ctx-max", type=int, default=8192)

@@ -92,10 +92,65 @@ __global__ void dequantize_rows_kernel(const uint8_t* __restrict__ packed, const
   }
 }
 
+// Tile-major device layout of the packed codes: the matrix is cut into tiles of 128 rows x 128
+// k elements (128 bytes per row for int8, 64 for int4) and each tile is stored contiguously,
+// tiles of one 128-row band following each other along K:
+//   tiled[((band * KB + kb) * 128 + r) * TB + j] = packed[(band*128 + r) * row_bytes + kb*TB + j]
+// A pure permutation of bytes (rows past N are zero), so it is exactly invertible.
+template <bool INVERSE>
+__global__ void __launch_bounds__(256)
+relayout_tiles_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int N, int row_bytes, int tile_bytes_per_row) {
+  const int kb = blockIdx.x;
+  const int band = blockIdx.y;
+  const int kblocks = row_bytes / tile_bytes_per_row;
+  const int chunks_per_row = tile_bytes_per_row / 16;
+  for (int idx = threadIdx.x; idx < 128 * chunks_per_row; idx += 256) {
+    const int r = idx / chunks_per_row;
+    const int c = idx % chunks_per_row;
+    const int n = band * 128 + r;
+    const size_t tiled_off = ((static_cast<size_t>(band) * kblocks + kb) * 128 + r) * tile_bytes_per_row + c * 16;
+    const size_t rows_off = static_cast<size_t>(n) * row_bytes + static_cast<size_t>(kb) * tile_bytes_per_row + c * 16;
+    if (INVERSE) {
+      if (n < N) *reinterpret_cast<uint4*>(dst + rows_off) = *reinterpret_cast<const uint4*>(src + tiled_off);
+    } else {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (n < N) v = *reinterpret_cast<const uint4*>(src + rows_off);
+      *reinterpret_cast<uint4*>(dst + tiled_off) = v;
+    }
+  }
+}
+
 }  // namespace
 }  // namespace cb200
 
 using namespace cb200;
+
+extern "C" size_t cacheir_b200_pack_tiled_bytes(int N, int K, int bits) {
+  if (N <= 0 || K <= 0 || (bits != 4 && bits != 8) || K % 128 != 0) return 0;
+  const size_t row_bytes = bits == 8 ? static_cast<size_t>(K) : static_cast<size_t>(K / 2);
+  return static_cast<size_t>((N + 127) / 128) * 128 * row_bytes;
+}
+
+static int relayout_impl(const uint8_t* src, uint8_t* dst, int N, int K, int bits, bool inverse, void* stream) {
+  if (N <= 0 || K <= 0) return 0;
+  if (!src || !dst || (bits != 4 && bits != 8) || K % 128 != 0) return CACHEIR_B200_EINVAL;
+  if (!aligned_to(src, 16) || !aligned_to(dst, 16)) return CACHEIR_B200_EALIGN;
+  const int row_bytes = bits == 8 ? K : K / 2;
+  const int tile_bytes_per_row = bits == 8 ? 128 : 64;
+  const dim3 grid(row_bytes / tile_bytes_per_row, (N + 127) / 128);
+  if (grid.y > 65535) return CACHEIR_B200_ELIMIT;
+  if (inverse) relayout_tiles_kernel<true><<<grid, 256, 0, as_stream(stream)>>>(src, dst, N, row_bytes, tile_bytes_per_row);
+  else relayout_tiles_kernel<false><<<grid, 256, 0, as_stream(stream)>>>(src, dst, N, row_bytes, tile_bytes_per_row);
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_pack_relayout(const uint8_t* packed, uint8_t* tiled, int N, int K, int bits, void* stream) {
+  return relayout_impl(packed, tiled, N, K, bits, false, stream);
+}
+
+extern "C" int cacheir_b200_pack_unrelayout(const uint8_t* tiled, uint8_t* packed, int N, int K, int bits, void* stream) {
+  return relayout_impl(tiled, packed, N, K, bits, true, stream);
+}
 
 extern "C" int cacheir_b200_pack_rows(const float* weight, uint8_t* packed, float* scales,
                                       int32_t* zero_points_i32, float* zero_points_f32, int N,

@@ -124,6 +124,7 @@ struct I8Params {
   int scale_dtype;
   int epilogue;
   int split_k;
+  int tiled;        // weights in 128x128 tile order: tile (band, kb) starts at row (band*KB + kb)*128 of a 128-byte-wide tensor
 };
 
 template <int MP>
@@ -149,6 +150,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 64) CB200_TRACE(3, 0, 0);
   const bool swiglu = p.epilogue == CACHEIR_B200_EPI_SWIGLU;
   const int passes = swiglu ? 2 : 1;
   const int split = p.split_k;
@@ -174,6 +176,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 64) CB200_TRACE(3, 0, 1);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -187,7 +190,12 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         const int kb = kb_begin + i % kblocks;
         const uint32_t bar = smem_u32(&full[s]);
         mbar_expect_tx(bar, kWBytes + kXBytes);
-        tma_load_2d(smem_u32(s_w + s * kWBytes), &tmap_w, bar, kb * kBlockK, n0 + pass * (p.N / 2));
+        if (p.tiled) {
+          const int band = blockIdx.x + pass * (p.N / 2 / kBlockN);
+          tma_load_2d(smem_u32(s_w + s * kWBytes), &tmap_w, bar, 0, (band * kblocks_all + kb) * kBlockN);
+        } else {
+          tma_load_2d(smem_u32(s_w + s * kWBytes), &tmap_w, bar, kb * kBlockK, n0 + pass * (p.N / 2));
+        }
         tma_load_2d(smem_u32(s_x + s * kXBytes), &tmap_x, bar, kb * kBlockK, 0);
         CB200_TRACE(0, i, 2);
       }
@@ -225,6 +233,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     bool ok = mbar_wait(smem_u32(acc_full), 0, &g_i8_status, (3 << 8) | 3);
     tc_fence_after();
+    if (threadIdx.x == 64) CB200_TRACE(3, 0, 2);
     const int n_out_idx = n0 + r;
     const bool store = ok && n_out_idx < p.n_out;
     double scale[2] = {0.0, 0.0}, zero[2] = {128.0, 128.0};
@@ -244,6 +253,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       // s_partial[sender][2*MS columns][128 weight rows].
       const int MS = MP / split;
       cluster_sync_all();                        // #1: every ring of the cluster has drained
+      if (threadIdx.x == 64) CB200_TRACE(3, 0, 3);
 #pragma unroll 1
       for (int c0 = 0; c0 < kAccCols; c0 += 8) {
         uint32_t v[8];
@@ -263,7 +273,9 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           st_cluster_u32(smem_u32(s_partial + (static_cast<size_t>(krank) * 2 * MS + lc) * kBlockN + r), dest, v[j]);
         }
       }
+      if (threadIdx.x == 64) CB200_TRACE(3, 1, 0);
       cluster_sync_all();                        // #2: all partials have arrived
+      if (threadIdx.x == 64) CB200_TRACE(3, 1, 1);
       for (int ml = 0; ml < MS; ++ml) {
         const int m = krank * MS + ml;
         int32_t hi = 0, lo = 0;
@@ -322,6 +334,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     cluster_sync_all();
     cluster_sync_all();
   }
+  if (threadIdx.x == 64) CB200_TRACE(3, 1, 2);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -329,6 +342,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     tc_fence_after();
     tc_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 64) CB200_TRACE(3, 1, 3);
 }
 
 // CTAs per cluster along K: enough to put about two CTAs on every SM; a power of two that
@@ -350,8 +364,11 @@ int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
   if (rc != 0) return rc;
 
   CUtensorMap tmap_w, tmap_x;
-  if (!encode_u8_rows_sw128(&tmap_w, q.packed, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.N), static_cast<uint64_t>(q.K), kBlockN))
-    return CACHEIR_B200_EUNSUPPORTED;
+  const uint64_t bands = static_cast<uint64_t>((q.N + kBlockN - 1) / kBlockN);
+  const bool w_ok = q.tiled
+      ? encode_u8_rows_sw128(&tmap_w, q.packed, kBlockK, bands * (q.K / kBlockK) * kBlockN, kBlockK, kBlockN)
+      : encode_u8_rows_sw128(&tmap_w, q.packed, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.N), static_cast<uint64_t>(q.K), kBlockN);
+  if (!w_ok) return CACHEIR_B200_EUNSUPPORTED;
   if (!encode_u8_rows_sw128(&tmap_x, planes, static_cast<uint64_t>(q.K), static_cast<uint64_t>(2 * MP), static_cast<uint64_t>(q.K), 2 * MP))
     return CACHEIR_B200_EUNSUPPORTED;
   I8Params p{};
@@ -359,7 +376,7 @@ int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
   p.sx = sx; p.qsum = qsum;
   p.M = q.M; p.N = q.N; p.K = q.K;
   p.n_out = q.epilogue == CACHEIR_B200_EPI_SWIGLU ? q.N / 2 : q.N;
-  p.scale_dtype = q.scale_dtype; p.epilogue = q.epilogue;
+  p.scale_dtype = q.scale_dtype; p.epilogue = q.epilogue; p.tiled = q.tiled ? 1 : 0;
   const int n_tiles = (p.n_out + kBlockN - 1) / kBlockN;
   p.split_k = choose_split_k(n_tiles, q.K / kBlockK, q.epilogue, MP);
   constexpr size_t kSmem = 1024 + static_cast<size_t>(num_stages(MP)) * stage_bytes(MP) + 1024;

@@ -163,6 +163,7 @@ struct TcParams {
   int scale_dtype;
   int epilogue;
   int split_k;      // CTAs per cluster along K (1 = no split)
+  int tiled;        // weights in 128x128 tile order (see cacheir_b200_pack_relayout)
 };
 
 __device__ __forceinline__ float load_scale(const void* scales, int scale_dtype, size_t idx) {
@@ -277,7 +278,12 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         const int row0 = n0 + pass * (p.N / 2);
         const uint32_t bar = smem_u32(&full[s]);
         mbar_expect_tx(bar, kRawBytes + kXBytes);
-        tma_load_2d(smem_u32(s_raw + s * kRawBytes), &tmap_w, bar, kb * kRawRow, row0);
+        if (p.tiled) {
+          const int band = blockIdx.x + pass * (p.N / 2 / kBlockN);
+          tma_load_2d(smem_u32(s_raw + s * kRawBytes), &tmap_w, bar, 0, (band * kblocks_all + kb) * kBlockN);
+        } else {
+          tma_load_2d(smem_u32(s_raw + s * kRawBytes), &tmap_w, bar, kb * kRawRow, row0);
+        }
         // x viewed as [K/64 spans][M rows][64 elements]: both 64-element halves of the k block in one copy
         tma_load_3d(smem_u32(s_x + s * kXBytes), &tmap_x, bar, 0, 0, kb * 2);
         CB200_TRACE(0, i, 2);
@@ -546,9 +552,14 @@ int launch_tc(const QGemvParams& q, cudaStream_t stream) {
                 "split-K partials must fit in the pipeline ring");
   CUtensorMap tmap_w, tmap_x;
   const uint64_t row_bytes = BITS == 8 ? static_cast<uint64_t>(q.K) : static_cast<uint64_t>(q.K / 2);
-  if (!encode_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, q.packed, row_bytes, static_cast<uint64_t>(q.N), row_bytes,
-                 BITS == 8 ? 128 : 64, kBlockN, BITS == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
-    return CACHEIR_B200_EUNSUPPORTED;
+  constexpr uint32_t kTileRowBytes = BITS == 8 ? 128 : 64;
+  const uint64_t tiled_rows = static_cast<uint64_t>((q.N + kBlockN - 1) / kBlockN) * (q.K / kBlockK) * kBlockN;
+  const bool w_ok = q.tiled
+      ? encode_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, q.packed, kTileRowBytes, tiled_rows, kTileRowBytes, kTileRowBytes, kBlockN,
+                  BITS == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)
+      : encode_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, q.packed, row_bytes, static_cast<uint64_t>(q.N), row_bytes, kTileRowBytes,
+                  kBlockN, BITS == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+  if (!w_ok) return CACHEIR_B200_EUNSUPPORTED;
   if (!encode_x_3d(&tmap_x, q.x, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.M),
                    static_cast<uint64_t>(q.x_stride) * 2, MP))
     return CACHEIR_B200_EUNSUPPORTED;
@@ -556,7 +567,7 @@ int launch_tc(const QGemvParams& q, cudaStream_t stream) {
   p.scales = q.scales; p.zero_points = q.zero_points; p.residual = q.residual; p.y = q.y;
   p.M = q.M; p.N = q.N; p.K = q.K;
   p.n_out = q.epilogue == CACHEIR_B200_EPI_SWIGLU ? q.N / 2 : q.N;
-  p.group_size = q.group_size; p.scale_dtype = q.scale_dtype; p.epilogue = q.epilogue;
+  p.group_size = q.group_size; p.scale_dtype = q.scale_dtype; p.epilogue = q.epilogue; p.tiled = q.tiled ? 1 : 0;
   const int n_tiles = (p.n_out + kBlockN - 1) / kBlockN;
   p.split_k = choose_split_k(n_tiles, q.K / kBlockK, q.epilogue);
   auto kern = qgemm_tc_kernel<BITS, MP>;

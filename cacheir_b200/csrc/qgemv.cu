@@ -195,7 +195,7 @@ extern "C" size_t cacheir_b200_qgemv_workspace_bytes(int M, int K) { return qgem
 extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const void* scales,
                                      const float* zero_points, const void* residual, void* y, int M,
                                      int N, int K, int bits, int group_size, int x_dtype,
-                                     int scale_dtype, long long x_stride, int epilogue,
+                                     int scale_dtype, long long x_stride, int epilogue, int weight_layout,
                                      void* workspace, size_t workspace_bytes, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (!x || !packed || !y) return CACHEIR_B200_EINVAL;
@@ -221,6 +221,8 @@ extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const vo
   p.x_dtype = x_dtype; p.scale_dtype = scale_dtype;
   p.x_stride = x_stride > 0 ? x_stride : K;
   p.epilogue = epilogue;
+  p.tiled = weight_layout == CACHEIR_B200_LAYOUT_TILED;
+  if (weight_layout != CACHEIR_B200_LAYOUT_ROWS && weight_layout != CACHEIR_B200_LAYOUT_TILED) return CACHEIR_B200_EINVAL;
   const size_t row_bytes = bits == 8 ? static_cast<size_t>(K)
                          : bits == 4 ? static_cast<size_t>((K + 1) / 2)
                                      : static_cast<size_t>(K) * esize;
@@ -229,6 +231,7 @@ extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const vo
   cudaStream_t st = as_stream(stream);
   if (qgemm_i8_supported(p, workspace, workspace_bytes)) return launch_qgemm_i8(p, workspace, st);
   if (qgemm_tc_supported(p)) return launch_qgemm_tc(p, st);
+  if (p.tiled) return CACHEIR_B200_EUNSUPPORTED;   // the tile order only exists for the tensor-core kernels
   return launch_qgemv_cuda_core(p, st);
 }
 
@@ -237,7 +240,7 @@ extern "C" int cacheir_b200_qgemv(const void* x, const void* packed, const void*
                                   int N, int K, int bits, int group_size, int x_dtype,
                                   int scale_dtype, long long x_stride, int epilogue, void* stream) {
   return cacheir_b200_qgemv_ex(x, packed, scales, zero_points, residual, y, M, N, K, bits, group_size, x_dtype,
-                               scale_dtype, x_stride, epilogue, nullptr, 0, stream);
+                               scale_dtype, x_stride, epilogue, CACHEIR_B200_LAYOUT_ROWS, nullptr, 0, stream);
 }
 
 extern "C" int cacheir_b200_device_status(int reset) {

@@ -20,6 +20,7 @@ struct QGemvParams {
   long long x_stride;
   int epilogue;
   bool vector_ok;  // rows of x and of the packed weight can be read in 16-byte units
+  bool tiled;      // codes are in the 128x128 tile order of cacheir_b200_pack_relayout
 };
 
 int launch_qgemv_cuda_core(const QGemvParams& p, cudaStream_t stream);

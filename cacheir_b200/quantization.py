@@ -41,6 +41,7 @@ class B200PackedWeight:
     axis: int = 1
     group_size: int | None = None
     zero_points_i32: torch.Tensor | None = None   # the reference's int32 form, kept for parity checks
+    tiled: bool = False                           # packed_values is in the 128x128 tile order (ops.pack_relayout)
 
     @property
     def nbytes(self) -> int:
@@ -96,6 +97,24 @@ def concat_rows(weights: list[B200PackedWeight]) -> B200PackedWeight:
     )
 
 
+def to_tiled(w: B200PackedWeight) -> B200PackedWeight:
+    """The same weight with its codes in the tile order of the tensor-core kernels (K % 128 == 0)."""
+    if w.tiled:
+        return w
+    n, k = w.shape
+    return B200PackedWeight(ops.pack_relayout(w.packed_values, n=n, k=k, bits=w.bits), w.scales, w.zero_points, w.bits,
+                            w.shape, group_size=w.group_size, zero_points_i32=w.zero_points_i32, tiled=True)
+
+
+def to_rows(w: B200PackedWeight) -> B200PackedWeight:
+    """Back to the reference's row-major `packed_values` (bit-exact)."""
+    if not w.tiled:
+        return w
+    n, k = w.shape
+    return B200PackedWeight(ops.pack_unrelayout(w.packed_values, n=n, k=k, bits=w.bits), w.scales, w.zero_points, w.bits,
+                            w.shape, group_size=w.group_size, zero_points_i32=w.zero_points_i32, tiled=False)
+
+
 def dequantize_device(w: B200PackedWeight, dtype: torch.dtype) -> torch.Tensor:
     """`dequantize_packed_weight` (cacheir/quantization.py:74-84) on the GPU, per-row affine weights only."""
     if w.group_size:
@@ -109,4 +128,5 @@ def quantized_matmul(x: torch.Tensor, w: B200PackedWeight, *, epilogue: int = op
     """`_quantized_matmul` (cacheir/runtime/cuda.py:932-940) without materialising the dense weight.
     `workspace` (ops.qgemv_workspace_bytes) enables the integer tensor-core path for int8 weights."""
     return ops.qgemv(x, w.packed_values, w.scales, w.zero_points, bits=w.bits, n=w.shape[0], k=w.shape[1],
-                     group_size=w.group_size or 0, epilogue=epilogue, residual=residual, out=out, workspace=workspace)
+                     group_size=w.group_size or 0, epilogue=epilogue, residual=residual, out=out, workspace=workspace,
+                     tiled=w.tiled)

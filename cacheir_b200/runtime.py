@@ -32,7 +32,7 @@ import torch
 from . import ops
 from .artifact import CompileArtifact
 from .kv_cache import B200KVPageAllocator, B200PagedKVCache
-from .quantization import B200PackedWeight, concat_rows, quant_bits
+from .quantization import B200PackedWeight, concat_rows, quant_bits, to_tiled
 from .weights import B200WeightStore, TensorSource
 
 
@@ -143,6 +143,7 @@ class _Engine:
                                  kv_heads=int(self.config.num_key_value_heads), head_dim=int(self.config.head_dim))
         self.max_seq_len = int(max_seq_len or self.config.max_position_embeddings)
         self.use_cuda_graph = use_cuda_graph
+        self.tile_weights = True
         self.attention_splits = int(attention_splits)
         self.max_plans = max(1, int(max_plans))
         self.plans: OrderedDict[tuple[str, ...], "_DecodePlan"] = OrderedDict()
@@ -168,6 +169,14 @@ class _Engine:
             if len(parts) > 1:   # the concatenation replaces the parts: keep one copy of the codes in HBM
                 for n in names:
                     self.weights.release(n)
+            # device pack layout: tile order for the tensor-core kernels (fp16 activations, K a multiple of 128;
+            # the gate|up pair additionally needs each half to be whole 128-row bands)
+            halves_ok = len(names) != 2 or (fused.shape[0] // 2) % 128 == 0
+            if self.dtype == torch.float16 and fused.shape[1] % 128 == 0 and halves_ok and self.tile_weights:
+                tiled = to_tiled(fused)
+                if len(parts) == 1:
+                    self.weights.release(names[0])
+                fused = tiled
         else:
             dense = [self.weights.get(n) for n in names]
             fused = dense[0] if len(dense) == 1 else torch.cat(dense, dim=0).contiguous()
@@ -353,7 +362,7 @@ class _DecodePlan:
             ws = self._gemm_workspace(k) if (bits == 8 and not weight.group_size and eng.dtype == torch.float16) else None
             fn = lambda: ops.qgemv(x, weight.packed_values, weight.scales, weight.zero_points, bits=bits, n=n, k=k,
                                    group_size=weight.group_size or 0, epilogue=epilogue, residual=residual, out=out,
-                                   workspace=ws)
+                                   workspace=ws, tiled=weight.tiled)
             key = f"b200.qgemv.int{bits}" + (".swiglu" if epilogue == ops.EPI_SWIGLU else ".residual" if residual is not None else "")
             eng.gemm_plans[f"q{bits}:{(self.batch, 1, k)}x{weight.shape}"] = key
             if ws is not None and self.batch <= 64 and k % 128 == 0:   # activation pre-pass + integer GEMM

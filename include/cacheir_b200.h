@@ -39,6 +39,10 @@ extern "C" {
 #define CACHEIR_B200_EUNSUPPORTED (-4)/* shape outside what the kernels cover */
 #define CACHEIR_B200_ELIMIT (-5)      /* beyond a documented fixed maximum    */
 
+/* weight layouts accepted by cacheir_b200_qgemv_ex */
+#define CACHEIR_B200_LAYOUT_ROWS 0     /* the reference's row-major packed_values   */
+#define CACHEIR_B200_LAYOUT_TILED 1    /* cacheir_b200_pack_relayout's tile order   */
+
 /* qgemv epilogues */
 #define CACHEIR_B200_EPI_NONE 0       /* y = x W^T                            */
 #define CACHEIR_B200_EPI_RESIDUAL 1   /* y = residual + x W^T                 */
@@ -167,8 +171,23 @@ int cacheir_b200_qgemv_ex(const void* x, const void* packed, const void* scales,
                           const float* zero_points, const void* residual, void* y,
                           int M, int N, int K, int bits, int group_size,
                           int x_dtype, int scale_dtype, long long x_stride,
-                          int epilogue, void* workspace, size_t workspace_bytes,
-                          void* stream);
+                          int epilogue, int weight_layout, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
+/* Device pack layout of the quantization loader. The codes of the reference format
+ * (`packed_values`, cacheir/quantization.py:107-120; uploaded row-major by
+ * CudaWeightStore.get_quantized, cacheir/runtime/cuda.py:77-94) are permuted into
+ * tiles of 128 rows x 128 k elements stored contiguously (16 KB for int8, 8 KB for int4),
+ * the tiles of one 128-row band following each other along K, so that a tensor-core CTA
+ * streams one contiguous span of HBM instead of 128 strided 128-byte pieces per step.
+ * Pure byte permutation (rows past N are zero padding): `unrelayout` restores the
+ * reference bytes exactly. K must be a multiple of 128; `tiled` holds
+ * cacheir_b200_pack_tiled_bytes(N, K, bits) bytes. Scales and zero points are not
+ * touched. Pass CACHEIR_B200_LAYOUT_TILED to cacheir_b200_qgemv_ex for such weights
+ * (tensor-core shapes only: fp16 x, M <= 64). */
+size_t cacheir_b200_pack_tiled_bytes(int N, int K, int bits);
+int cacheir_b200_pack_relayout(const uint8_t* packed, uint8_t* tiled, int N, int K, int bits, void* stream);
+int cacheir_b200_pack_unrelayout(const uint8_t* tiled, uint8_t* packed, int N, int K, int bits, void* stream);
 
 /* Status word of the kernels that wait on hardware barriers (the tensor-core GEMM):
  * 0, or a non-zero code recorded by the first wait that ran out of its poll budget

@@ -438,3 +438,38 @@ def test_qgemm_int8_tensor_core_epilogues_offsets_and_determinism():
     assert _rel(y, oracle.silu_mul(base2[:, : n // 2], base2[:, n // 2:])) <= TOL[torch.float16] * 2
     torch.cuda.synchronize()
     _device_status_ok()
+
+
+# ---- device pack layout: tile order is an exact permutation and changes no result ---------
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("n,k", [(512, 1024), (200, 256), (128, 4096)])
+def test_pack_relayout_roundtrip_and_gemm_equivalence(bits, n, k):
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul, to_rows, to_tiled
+    rng = np.random.default_rng(bits + n + k)
+    x, packed = _qgemv_case(rng, 32, n, k, bits, torch.float16)
+    rows = _device_pack(packed)
+    tiled = to_tiled(rows)
+    assert tiled.tiled and tiled.packed_values.numel() == ops.pack_tiled_bytes(n, k, bits)
+    back = to_rows(tiled)
+    assert torch.equal(back.packed_values, rows.packed_values)            # bit-exact inverse
+    # spot-check the permutation itself: tile (band, kb) holds rows band*128.. and bytes kb*TB..
+    tb = 128 if bits == 8 else 64
+    kblocks = (k if bits == 8 else k // 2) // tb
+    t = tiled.packed_values.cpu().numpy().reshape(-1, kblocks, 128, tb)
+    ref = packed.packed_values
+    band, kb, r = (n - 1) // 128, kblocks - 1, (n - 1) % 128
+    np.testing.assert_array_equal(t[band, kb, r], ref[n - 1, kb * tb:(kb + 1) * tb])
+    assert not t[band, :, r + 1:].any()                                  # rows past N are zero padding
+    y_rows = quantized_matmul(x.cuda(), rows)
+    y_tiled = quantized_matmul(x.cuda(), tiled)
+    assert torch.equal(y_rows, y_tiled)
+    if bits == 8:
+        ws = torch.empty(ops.qgemv_workspace_bytes(32, k), dtype=torch.uint8, device="cuda")
+        assert torch.equal(quantized_matmul(x.cuda(), rows, workspace=ws), quantized_matmul(x.cuda(), tiled, workspace=ws))
+    if n % 256 == 0:
+        a = quantized_matmul(x.cuda(), rows, epilogue=ops.EPI_SWIGLU)
+        b = quantized_matmul(x.cuda(), tiled, epilogue=ops.EPI_SWIGLU)
+        assert torch.equal(a, b)
+    torch.cuda.synchronize()
+    _device_status_ok()
