@@ -112,6 +112,158 @@ quantize_rows_kernel(const __half* __restrict__ x, long long x_stride, int M, in
   }
 }
 
+// Block-wide reductions for the single-pass kernels below (up to 32 warps).
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) t += scratch[w];
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  v = warp_max(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) t = fmaxf(t, scratch[w]);
+  return t;
+}
+
+// One row of activations held in registers -> byte planes, scale and sum. Shared by the
+// stand-alone pre-pass and the RMSNorm-fused form; `vals` are the fp16-rounded activations.
+template <int PT>
+__device__ __forceinline__ void quantize_row_from_registers(const float (&vals)[PT][8], int nvec, int8_t* hi_row, int8_t* lo_row,
+                                                            float* sx_out, int* qsum_out, float* scratch) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < PT; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(vals[i][j]));
+  amax = block_max(amax, scratch);
+  const float inv = amax > 0.f ? kQMax / amax : 0.f;
+  int sum = 0;
+#pragma unroll
+  for (int i = 0; i < PT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < nvec) {
+      uint32_t hi_w[2] = {0u, 0u}, lo_w[2] = {0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        int q = __float2int_rn(vals[i][j] * inv);
+        q = max(-32639, min(32639, q));
+        const int hi = (q + 128) >> 8;
+        const int lo = q - (hi << 8);
+        sum += q;
+        hi_w[j >> 2] |= static_cast<uint32_t>(hi & 0xFF) << (8 * (j & 3));
+        lo_w[j >> 2] |= static_cast<uint32_t>(lo & 0xFF) << (8 * (j & 3));
+      }
+      *reinterpret_cast<uint2*>(hi_row + c * 8) = make_uint2(hi_w[0], hi_w[1]);
+      *reinterpret_cast<uint2*>(lo_row + c * 8) = make_uint2(lo_w[0], lo_w[1]);
+    }
+  }
+  __shared__ int s_isum[32];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  if ((threadIdx.x & 31) == 0) s_isum[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tot = 0;
+    for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) tot += s_isum[w];
+    *qsum_out = tot;
+    *sx_out = amax > 0.f ? amax / kQMax : 0.f;
+  }
+}
+
+__device__ __forceinline__ void zero_plane_rows(int8_t* hi_row, int8_t* lo_row, int nvec) {
+  for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+    *reinterpret_cast<uint2*>(hi_row + c * 8) = make_uint2(0u, 0u);
+    *reinterpret_cast<uint2*>(lo_row + c * 8) = make_uint2(0u, 0u);
+  }
+}
+
+// Stand-alone pre-pass, single pass: the row stays in registers between the max and the rounding.
+template <int PT>
+__global__ void __launch_bounds__(1024)
+quantize_rows_fast_kernel(const __half* __restrict__ x, long long x_stride, int M, int K, int mp,
+                          int8_t* __restrict__ planes, float* __restrict__ sx, int* __restrict__ qsum) {
+  __shared__ float scratch[32];
+  const int m = blockIdx.x;
+  int8_t* hi_row = planes + static_cast<size_t>(m) * K;
+  int8_t* lo_row = planes + static_cast<size_t>(mp + m) * K;
+  const int nvec = K / 8;
+  if (m >= M) {
+    zero_plane_rows(hi_row, lo_row, nvec);
+    if (threadIdx.x == 0) { sx[m] = 0.f; qsum[m] = 0; }
+    return;
+  }
+  float vals[PT][8];
+#pragma unroll
+  for (int i = 0; i < PT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) vals[i][j] = 0.f;
+    if (c < nvec) VecIO<__half, 8>::ld(x + static_cast<size_t>(m) * x_stride + c * 8, vals[i]);
+  }
+  quantize_row_from_registers<PT>(vals, nvec, hi_row, lo_row, sx + m, qsum + m, scratch);
+}
+
+// RMSNorm (optionally of x + residual, the rounded sum going to sum_out) fused with the pre-pass:
+// the normalised row is rounded to fp16 exactly as the stand-alone RMSNorm stores it, optionally
+// written to `out`, and quantised from registers.
+template <int PT>
+__global__ void __launch_bounds__(512)
+rms_norm_quantize_kernel(const __half* __restrict__ x, const __half* __restrict__ residual, const __half* __restrict__ weight,
+                         __half* __restrict__ sum_out, __half* __restrict__ out, int M, int hidden, float eps, int mp,
+                         int8_t* __restrict__ planes, float* __restrict__ sx, int* __restrict__ qsum) {
+  __shared__ float scratch[32];
+  const int m = blockIdx.x;
+  int8_t* hi_row = planes + static_cast<size_t>(m) * hidden;
+  int8_t* lo_row = planes + static_cast<size_t>(mp + m) * hidden;
+  const int nvec = hidden / 8;
+  if (m >= M) {
+    zero_plane_rows(hi_row, lo_row, nvec);
+    if (threadIdx.x == 0) { sx[m] = 0.f; qsum[m] = 0; }
+    return;
+  }
+  const size_t row = static_cast<size_t>(m) * hidden;
+  float vals[PT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < PT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) vals[i][j] = 0.f;
+    if (c < nvec) {
+      VecIO<__half, 8>::ld(x + row + c * 8, vals[i]);
+      if (residual) {
+        float r[8];
+        VecIO<__half, 8>::ld(residual + row + c * 8, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[i][j] = __half2float(__float2half_rn(vals[i][j] + r[j]));
+        VecIO<__half, 8>::st(sum_out + row + c * 8, vals[i]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(vals[i][j], vals[i][j], ss);
+    }
+  }
+  const float inv = rsqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps);
+#pragma unroll
+  for (int i = 0; i < PT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < nvec) {
+      float w[8];
+      VecIO<__half, 8>::ld(weight + c * 8, w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) vals[i][j] = __half2float(__float2half_rn(vals[i][j] * inv * w[j]));
+      if (out) VecIO<__half, 8>::st(out + row + c * 8, vals[i]);
+    }
+  }
+  quantize_row_from_registers<PT>(vals, nvec, hi_row, lo_row, sx + m, qsum + m, scratch);
+}
+
 struct I8Params {
   const void* scales;
   const float* zero_points;
@@ -127,7 +279,17 @@ struct I8Params {
   int tiled;        // weights in 128x128 tile order: tile (band, kb) starts at row (band*KB + kb)*128 of a 128-byte-wide tensor
 };
 
-template <int MP>
+// y value from the exact integer sums: (256*hi + lo - zero*qsum) as float. Integer zero points (what the
+// reference packer produces) are handled in 64-bit integers, anything else in double precision.
+__device__ __forceinline__ float recombine(int32_t hi, int32_t lo, float zero, int qsum) {
+  if (zero == rintf(zero) && fabsf(zero) < 1.0e9f) {
+    const long long v = 256LL * hi + lo - static_cast<long long>(zero) * qsum;
+    return static_cast<float>(v);
+  }
+  return static_cast<float>(256.0 * hi + static_cast<double>(lo) - static_cast<double>(zero) * qsum);
+}
+
+template <int MP, int SPLIT>
 __global__ void __launch_bounds__(kThreads, 2)
 qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const I8Params p) {
   constexpr int kStages = num_stages(MP);
@@ -153,7 +315,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   if (threadIdx.x == 64) CB200_TRACE(3, 0, 0);
   const bool swiglu = p.epilogue == CACHEIR_B200_EPI_SWIGLU;
   const int passes = swiglu ? 2 : 1;
-  const int split = p.split_k;
+  constexpr int split = SPLIT;
   const int krank = split > 1 ? static_cast<int>(cluster_ctarank()) : 0;
   const int kblocks_all = p.K / kBlockK;
   const int kb_begin = (kblocks_all * krank) / split;
@@ -236,59 +398,95 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     if (threadIdx.x == 64) CB200_TRACE(3, 0, 2);
     const int n_out_idx = n0 + r;
     const bool store = ok && n_out_idx < p.n_out;
-    double scale[2] = {0.0, 0.0}, zero[2] = {128.0, 128.0};
+    float scale[2] = {0.f, 0.f}, zero[2] = {128.f, 128.f};
     for (int pass = 0; pass < passes; ++pass) {
       const int n = n0 + pass * (p.N / 2) + r;
       if (n < p.N) {
-        scale[pass] = p.scale_dtype == CACHEIR_B200_F16 ? static_cast<double>(__half2float(static_cast<const __half*>(p.scales)[n]))
-                                                        : static_cast<double>(static_cast<const float*>(p.scales)[n]);
-        if (p.zero_points) zero[pass] = static_cast<double>(p.zero_points[n]);
+        scale[pass] = p.scale_dtype == CACHEIR_B200_F16 ? __half2float(static_cast<const __half*>(p.scales)[n])
+                                                        : static_cast<const float*>(p.scales)[n];
+        if (p.zero_points) zero[pass] = p.zero_points[n];
       }
     }
     __half* y = static_cast<__half*>(p.y);
     const __half* res = static_cast<const __half*>(p.residual);
     if (split > 1) {
-      // All-to-all over the cluster: rank j finishes batch rows [j*MS, (j+1)*MS). Every rank
-      // sends, for each of those rows, its high and low partial sums to rank j's buffer
-      // s_partial[sender][2*MS columns][128 weight rows].
-      const int MS = MP / split;
-      cluster_sync_all();                        // #1: every ring of the cluster has drained
+      // All-to-all over the cluster: rank j finishes batch rows [j*MS, (j+1)*MS). Every rank sends its
+      // partial sums for those rows to rank j's buffer, stored per (sender, weight row, accumulator) as
+      // [MS high words | MS low words], so both directions move 16 bytes at a time.
+      constexpr int MS = MP / SPLIT;
+      constexpr int W = 2 * MS;
+      const int row_words = passes * W;
+      cluster_sync_all();                            // #1: every ring of the cluster has drained
       if (threadIdx.x == 64) CB200_TRACE(3, 0, 3);
-#pragma unroll 1
-      for (int c0 = 0; c0 < kAccCols; c0 += 8) {
-        uint32_t v[8];
+      for (int ah = 0; ah < passes * 2; ++ah) {      // accumulator a = ah / 2, half h = ah % 2 (0 high, 1 low)
+        uint32_t acc[MP];
         if (total > 0) {
-          tc_ld_x8(tmem_base + lane_addr + c0, v);
+#pragma unroll
+          for (int c0 = 0; c0 < MP; c0 += 8) tc_ld_x8(tmem_base + lane_addr + (ah >> 1) * kAccCols + (ah & 1) * MP + c0,
+                                                      reinterpret_cast<uint32_t(&)[8]>(acc[c0]));
           tc_wait_ld();
         } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = 0u;
+          for (int c = 0; c < MP; ++c) acc[c] = 0u;
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int c = c0 + j;
-          const int m = c % MP;                  // batch row; c / MP selects high (0) or low (1) bytes
-          const int dest = m / MS;
-          const int lc = (c / MP) * MS + (m % MS);
-          st_cluster_u32(smem_u32(s_partial + (static_cast<size_t>(krank) * 2 * MS + lc) * kBlockN + r), dest, v[j]);
+        for (int dest = 0; dest < SPLIT; ++dest) {
+          const uint32_t dst = smem_u32(s_partial + (static_cast<size_t>(krank) * kBlockN + r) * row_words + (ah >> 1) * W + (ah & 1) * MS);
+          if constexpr (MS >= 4) {
+#pragma unroll
+            for (int u = 0; u < MS; u += 4) {
+              const uint32_t v[4] = {acc[dest * MS + u], acc[dest * MS + u + 1], acc[dest * MS + u + 2], acc[dest * MS + u + 3]};
+              st_cluster_v4(dst + u * 4, dest, v);
+            }
+          } else {
+            const uint32_t v[4] = {acc[dest * MS], acc[dest * MS + 1], 0u, 0u};
+            st_cluster_v2(dst, dest, v);
+          }
         }
       }
       if (threadIdx.x == 64) CB200_TRACE(3, 1, 0);
-      cluster_sync_all();                        // #2: all partials have arrived
+      cluster_sync_all();                            // #2: all partials have arrived
       if (threadIdx.x == 64) CB200_TRACE(3, 1, 1);
-      for (int ml = 0; ml < MS; ++ml) {
-        const int m = krank * MS + ml;
-        int32_t hi = 0, lo = 0;
-        for (int k = 0; k < split; ++k) {
-          hi += s_partial[(static_cast<size_t>(k) * 2 * MS + ml) * kBlockN + r];
-          lo += s_partial[(static_cast<size_t>(k) * 2 * MS + MS + ml) * kBlockN + r];
+      constexpr int G = MS >= 4 ? 4 : 2;
+#pragma unroll 1
+      for (int u0 = 0; u0 < MS; u0 += G) {
+        int32_t sum[4][4];                           // [accumulator*2 + half][word]
+#pragma unroll
+        for (int ah = 0; ah < 4; ++ah)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) sum[ah][j] = 0;
+#pragma unroll
+        for (int k = 0; k < SPLIT; ++k) {            // integer sums: exact, order-free
+          const int32_t* src = s_partial + (static_cast<size_t>(k) * kBlockN + r) * row_words + u0;
+#pragma unroll
+          for (int ah = 0; ah < 4; ++ah) {
+            if (ah < passes * 2) {
+              if constexpr (G == 4) {
+                const int4 t = *reinterpret_cast<const int4*>(src + (ah >> 1) * W + (ah & 1) * MS);
+                sum[ah][0] += t.x; sum[ah][1] += t.y; sum[ah][2] += t.z; sum[ah][3] += t.w;
+              } else {
+                const int2 t = *reinterpret_cast<const int2*>(src + (ah >> 1) * W + (ah & 1) * MS);
+                sum[ah][0] += t.x; sum[ah][1] += t.y;
+              }
+            }
+          }
         }
-        if (m < p.M && store) {
-          const double v = 256.0 * static_cast<double>(hi) + static_cast<double>(lo) - zero[0] * static_cast<double>(s_qsum[m]);
-          float out = static_cast<float>(v * scale[0] * static_cast<double>(s_sx[m]));
-          const size_t o = static_cast<size_t>(m) * p.n_out + n_out_idx;
-          if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) out += __half2float(res[o]);
-          y[o] = __float2half_rn(out);
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+          const int m = krank * MS + u0 + j;
+          if (m < p.M && store) {
+            const float sxm = s_sx[m];
+            const int qs = s_qsum[m];
+            float out = recombine(sum[0][j], sum[1][j], zero[0], qs) * (scale[0] * sxm);
+            const size_t o = static_cast<size_t>(m) * p.n_out + n_out_idx;
+            if (swiglu) {
+              const float u = recombine(sum[2][j], sum[3][j], zero[1], qs) * (scale[1] * sxm);
+              out = (out / (1.f + __expf(-out))) * u;
+            } else if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
+              out += __half2float(res[o]);
+            }
+            y[o] = __float2half_rn(out);
+          }
         }
       }
     } else {
@@ -310,16 +508,13 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         for (int j = 0; j < 8; ++j) {
           const int m = c0 + j;
           if (m < p.M && store) {
-            const double sxm = static_cast<double>(s_sx[m]);
-            const double qs = static_cast<double>(s_qsum[m]);
-            const double v = 256.0 * static_cast<double>(static_cast<int32_t>(hi[0][j])) +
-                             static_cast<double>(static_cast<int32_t>(lo[0][j])) - zero[0] * qs;
-            float out = static_cast<float>(v * scale[0] * sxm);
+            const float sxm = s_sx[m];
+            const int qs = s_qsum[m];
+            float out = recombine(static_cast<int32_t>(hi[0][j]), static_cast<int32_t>(lo[0][j]), zero[0], qs) * (scale[0] * sxm);
             const size_t o = static_cast<size_t>(m) * p.n_out + n_out_idx;
             if (swiglu) {
-              const double u = 256.0 * static_cast<double>(static_cast<int32_t>(hi[1][j])) +
-                               static_cast<double>(static_cast<int32_t>(lo[1][j])) - zero[1] * qs;
-              out = (out / (1.f + __expf(-out))) * static_cast<float>(u * scale[1] * sxm);
+              const float u = recombine(static_cast<int32_t>(hi[1][j]), static_cast<int32_t>(lo[1][j]), zero[1], qs) * (scale[1] * sxm);
+              out = (out / (1.f + __expf(-out))) * u;
             } else if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
               out += __half2float(res[o]);
             }
@@ -345,13 +540,46 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   if (threadIdx.x == 64) CB200_TRACE(3, 1, 3);
 }
 
-// CTAs per cluster along K: enough to put about two CTAs on every SM; a power of two that
-// divides the padded batch (each rank finishes MP/split batch rows). Never for SwiGLU.
+// CTAs per cluster along K. Every doubling adds cluster-barrier and exchange time to the epilogue, so the
+// split only grows while the grid stays within two CTAs per SM; a power of two that leaves each rank at
+// least two batch rows to finish and four k blocks to stream. The SwiGLU form (two accumulators, many row
+// tiles) is not split.
 int choose_split_k(int n_tiles, int kblocks, int epilogue, int mp) {
   if (epilogue == CACHEIR_B200_EPI_SWIGLU) return 1;
   int s = 1;
-  while (s * 2 <= kMaxSplitK && n_tiles * s * 2 <= 2 * kNumSMs && kblocks / (s * 2) >= 4 && mp % (s * 2) == 0) s *= 2;
+  while (s * 2 <= kMaxSplitK && n_tiles * s * 2 <= 2 * kNumSMs && kblocks / (s * 2) >= 4 && mp / (s * 2) >= 2) s *= 2;
   return s;
+}
+
+int launch_quantize(const __half* x, long long x_stride, int M, int K, int mp, void* workspace, cudaStream_t stream) {
+  int8_t* planes = static_cast<int8_t*>(workspace);
+  float* sx = reinterpret_cast<float*>(planes + static_cast<size_t>(2 * mp) * K);
+  int* qsum = reinterpret_cast<int*>(sx + 64);
+  if (K <= 8192) quantize_rows_fast_kernel<1><<<mp, 1024, 0, stream>>>(x, x_stride, M, K, mp, planes, sx, qsum);
+  else if (K <= 16384) quantize_rows_fast_kernel<2><<<mp, 1024, 0, stream>>>(x, x_stride, M, K, mp, planes, sx, qsum);
+  else quantize_rows_kernel<<<mp, 256, 0, stream>>>(x, x_stride, M, K, mp, planes, sx, qsum);
+  return launch_status();
+}
+
+template <int MP, int SPLIT>
+cudaError_t launch_i8_split(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x, const I8Params& p, int n_tiles, cudaStream_t stream) {
+  constexpr size_t kSmem = 1024 + static_cast<size_t>(num_stages(MP)) * stage_bytes(MP) + 1024;
+  auto kern = qgemm_i8_kernel<MP, SPLIT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(n_tiles, SPLIT, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = SPLIT;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmap_w, tmap_x, p);
 }
 
 template <int MP>
@@ -359,9 +587,10 @@ int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
   int8_t* planes = static_cast<int8_t*>(workspace);
   float* sx = reinterpret_cast<float*>(planes + static_cast<size_t>(2 * MP) * q.K);
   int* qsum = reinterpret_cast<int*>(sx + 64);
-  quantize_rows_kernel<<<MP, 256, 0, stream>>>(static_cast<const __half*>(q.x), q.x_stride, q.M, q.K, MP, planes, sx, qsum);
-  int rc = launch_status();
-  if (rc != 0) return rc;
+  if (!q.x_prequantized) {
+    const int rc = launch_quantize(static_cast<const __half*>(q.x), q.x_stride, q.M, q.K, MP, workspace, stream);
+    if (rc != 0) return rc;
+  }
 
   CUtensorMap tmap_w, tmap_x;
   const uint64_t bands = static_cast<uint64_t>((q.N + kBlockN - 1) / kBlockN);
@@ -379,23 +608,13 @@ int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
   p.scale_dtype = q.scale_dtype; p.epilogue = q.epilogue; p.tiled = q.tiled ? 1 : 0;
   const int n_tiles = (p.n_out + kBlockN - 1) / kBlockN;
   p.split_k = choose_split_k(n_tiles, q.K / kBlockK, q.epilogue, MP);
-  constexpr size_t kSmem = 1024 + static_cast<size_t>(num_stages(MP)) * stage_bytes(MP) + 1024;
-  auto kern = qgemm_i8_kernel<MP>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
-  if (e != cudaSuccess) return static_cast<int>(e);
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(n_tiles, p.split_k, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = kSmem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = p.split_k;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kern, tmap_w, tmap_x, p);
+  cudaError_t e;
+  switch (p.split_k) {
+    case 8: e = launch_i8_split<MP, 8>(tmap_w, tmap_x, p, n_tiles, stream); break;
+    case 4: e = launch_i8_split<MP, 4>(tmap_w, tmap_x, p, n_tiles, stream); break;
+    case 2: e = launch_i8_split<MP, 2>(tmap_w, tmap_x, p, n_tiles, stream); break;
+    default: e = launch_i8_split<MP, 1>(tmap_w, tmap_x, p, n_tiles, stream); break;
+  }
   if (e != cudaSuccess) return static_cast<int>(e);
   return launch_status();
 }
@@ -428,6 +647,29 @@ extern "C" int cacheir_b200_debug_trace_i8(long long* out) {
   return static_cast<int>(cudaMemcpyFromSymbol(out, g_i8_trace, sizeof(long long) * 4 * 256 * 4));
 }
 #endif
+
+int i8_plane_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
+
+int qgemm_i8_quantize_activations(const void* x, long long x_stride, int M, int K, void* workspace, cudaStream_t stream) {
+  return launch_quantize(static_cast<const __half*>(x), x_stride, M, K, i8_plane_rows(M), workspace, stream);
+}
+
+int qgemm_i8_rms_norm_quantize(const void* x, const void* residual, const void* weight, void* sum_out, void* out, int M,
+                               int hidden, float eps, void* workspace, cudaStream_t stream) {
+  const int mp = i8_plane_rows(M);
+  int8_t* planes = static_cast<int8_t*>(workspace);
+  float* sx = reinterpret_cast<float*>(planes + static_cast<size_t>(2 * mp) * hidden);
+  int* qsum = reinterpret_cast<int*>(sx + 64);
+  const __half* xp = static_cast<const __half*>(x);
+  const __half* rp = static_cast<const __half*>(residual);
+  const __half* wp = static_cast<const __half*>(weight);
+  __half* sp = static_cast<__half*>(sum_out);
+  __half* op = static_cast<__half*>(out);
+  if (hidden <= 4096) rms_norm_quantize_kernel<1><<<mp, 512, 0, stream>>>(xp, rp, wp, sp, op, M, hidden, eps, mp, planes, sx, qsum);
+  else if (hidden <= 8192) rms_norm_quantize_kernel<2><<<mp, 512, 0, stream>>>(xp, rp, wp, sp, op, M, hidden, eps, mp, planes, sx, qsum);
+  else return CACHEIR_B200_EUNSUPPORTED;
+  return launch_status();
+}
 
 int qgemm_i8_device_status(bool reset) {
   int status = 0;

@@ -221,8 +221,9 @@ extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const vo
   p.x_dtype = x_dtype; p.scale_dtype = scale_dtype;
   p.x_stride = x_stride > 0 ? x_stride : K;
   p.epilogue = epilogue;
-  p.tiled = weight_layout == CACHEIR_B200_LAYOUT_TILED;
-  if (weight_layout != CACHEIR_B200_LAYOUT_ROWS && weight_layout != CACHEIR_B200_LAYOUT_TILED) return CACHEIR_B200_EINVAL;
+  if (weight_layout < 0 || weight_layout > (CACHEIR_B200_LAYOUT_TILED | CACHEIR_B200_X_PREQUANTIZED)) return CACHEIR_B200_EINVAL;
+  p.tiled = (weight_layout & CACHEIR_B200_LAYOUT_TILED) != 0;
+  p.x_prequantized = (weight_layout & CACHEIR_B200_X_PREQUANTIZED) != 0;
   const size_t row_bytes = bits == 8 ? static_cast<size_t>(K)
                          : bits == 4 ? static_cast<size_t>((K + 1) / 2)
                                      : static_cast<size_t>(K) * esize;
@@ -230,6 +231,7 @@ extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const vo
                 (p.x_stride * esize) % 16 == 0;
   cudaStream_t st = as_stream(stream);
   if (qgemm_i8_supported(p, workspace, workspace_bytes)) return launch_qgemm_i8(p, workspace, st);
+  if (p.x_prequantized) return CACHEIR_B200_EINVAL;   // only the integer path can consume a quantized workspace
   if (qgemm_tc_supported(p)) return launch_qgemm_tc(p, st);
   if (p.tiled) return CACHEIR_B200_EUNSUPPORTED;   // the tile order only exists for the tensor-core kernels
   return launch_qgemv_cuda_core(p, st);
@@ -248,4 +250,27 @@ extern "C" int cacheir_b200_device_status(int reset) {
   const int attn = paged_attention_device_status(reset != 0);
   const int i8 = qgemm_i8_device_status(reset != 0);
   return gemm != 0 ? gemm : (attn != 0 ? attn : i8);
+}
+
+extern "C" int cacheir_b200_quantize_activations(const void* x, int M, int K, long long x_stride, int x_dtype,
+                                                 void* workspace, size_t workspace_bytes, void* stream) {
+  if (M <= 0 || K <= 0) return 0;
+  if (!x || x_dtype != CACHEIR_B200_F16 || M > 64 || K % 128 != 0) return CACHEIR_B200_EUNSUPPORTED;
+  if (!workspace || workspace_bytes < qgemm_i8_workspace_bytes(M, K) || !aligned_to(workspace, 128)) return CACHEIR_B200_EWORKSPACE;
+  const long long stride = x_stride > 0 ? x_stride : K;
+  if (!aligned_to(x, 16) || (stride * 2) % 16 != 0) return CACHEIR_B200_EALIGN;
+  return qgemm_i8_quantize_activations(x, stride, M, K, workspace, as_stream(stream));
+}
+
+extern "C" int cacheir_b200_rms_norm_quantize(const void* x, const void* residual, const void* weight, void* sum_out,
+                                              void* out, int rows, int hidden, float eps, int dtype, void* workspace,
+                                              size_t workspace_bytes, void* stream) {
+  if (rows <= 0 || hidden <= 0) return 0;
+  if (!x || !weight || (residual && !sum_out)) return CACHEIR_B200_EINVAL;
+  if (dtype != CACHEIR_B200_F16 || rows > 64 || hidden % 128 != 0 || hidden > 8192) return CACHEIR_B200_EUNSUPPORTED;
+  if (!workspace || workspace_bytes < qgemm_i8_workspace_bytes(rows, hidden) || !aligned_to(workspace, 128)) return CACHEIR_B200_EWORKSPACE;
+  if (!aligned_to(x, 16) || !aligned_to(weight, 16) || (residual && (!aligned_to(residual, 16) || !aligned_to(sum_out, 16))) ||
+      (out && !aligned_to(out, 16)))
+    return CACHEIR_B200_EALIGN;
+  return qgemm_i8_rms_norm_quantize(x, residual, weight, sum_out, out, rows, hidden, eps, workspace, as_stream(stream));
 }

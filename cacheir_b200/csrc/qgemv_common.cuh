@@ -21,6 +21,7 @@ struct QGemvParams {
   int epilogue;
   bool vector_ok;  // rows of x and of the packed weight can be read in 16-byte units
   bool tiled;      // codes are in the 128x128 tile order of cacheir_b200_pack_relayout
+  bool x_prequantized;  // the workspace already holds the integer form of x (see cacheir_b200_quantize_activations)
 };
 
 int launch_qgemv_cuda_core(const QGemvParams& p, cudaStream_t stream);
@@ -34,6 +35,9 @@ size_t qgemm_i8_workspace_bytes(int M, int K);
 bool qgemm_i8_supported(const QGemvParams& p, const void* workspace, size_t workspace_bytes);
 int launch_qgemm_i8(const QGemvParams& p, void* workspace, cudaStream_t stream);
 int qgemm_i8_device_status(bool reset);
+int qgemm_i8_quantize_activations(const void* x, long long x_stride, int M, int K, void* workspace, cudaStream_t stream);
+int qgemm_i8_rms_norm_quantize(const void* x, const void* residual, const void* weight, void* sum_out, void* out, int M,
+                               int hidden, float eps, void* workspace, cudaStream_t stream);
 // Device-side status word of the tensor-core kernel (0 = no bounded wait ever gave up).
 int qgemm_tc_device_status(bool reset);
 

@@ -107,7 +107,7 @@ def qgemv_workspace_bytes(m: int, k: int) -> int:
 def qgemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor | None, zero_points: torch.Tensor | None, *,
           bits: int, n: int, k: int, group_size: int = 0, epilogue: int = EPI_NONE,
           residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
-          workspace: torch.Tensor | None = None, tiled: bool = False) -> torch.Tensor:
+          workspace: torch.Tensor | None = None, tiled: bool = False, prequantized: bool = False) -> torch.Tensor:
     """y[M, N_out] = x[M, K] . deq(W)[N, K]^T with the reference's pack format
     (bits 8/4; bits 0 = dense weights of x's dtype). x: [..., K] with dense rows."""
     _require_cuda(x, packed, scales, zero_points, residual, out)
@@ -148,7 +148,7 @@ def qgemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor | None, ze
         x2.data_ptr(), packed.data_ptr(), _ptr(scales), _ptr(zero_points), _ptr(residual), out.data_ptr(),
         m, n, k, bits, group_size, dtype_code(x.dtype),
         F16 if (scales is not None and scales.dtype == torch.float16) else F32,
-        x2.stride(0), epilogue, 1 if tiled else 0, _ptr(workspace), ws_bytes, _stream()), "qgemv")
+        x2.stride(0), epilogue, (1 if tiled else 0) | (2 if prequantized else 0), _ptr(workspace), ws_bytes, _stream()), "qgemv")
     return out
 
 
@@ -222,6 +222,33 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, residual: tor
                                             out.data_ptr(), rows, hidden, float(eps), dtype_code(x.dtype), _stream()),
           "rms_norm")
     return out
+
+
+def quantize_activations(x: torch.Tensor, workspace: torch.Tensor) -> None:
+    """x [M, K] fp16 -> 16-bit fixed point per row in `workspace` (the integer GEMM's pre-pass)."""
+    _require_cuda(x, workspace)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("quantize_activations expects x [M, K] with dense rows")
+    check(_lib.load().cacheir_b200_quantize_activations(x.data_ptr(), int(x.shape[0]), int(x.shape[1]), x.stride(0),
+                                                        dtype_code(x.dtype), workspace.data_ptr(),
+                                                        workspace.numel() * workspace.element_size(), _stream()),
+          "quantize_activations")
+
+
+def rms_norm_quantize(x: torch.Tensor, weight: torch.Tensor, eps: float, workspace: torch.Tensor, *,
+                      residual: torch.Tensor | None = None, sum_out: torch.Tensor | None = None,
+                      out: torch.Tensor | None = None) -> None:
+    """RMSNorm fused with the integer GEMM's activation pre-pass; the fp16 result is stored only if `out` is given."""
+    _require_cuda(x, weight, residual, sum_out, out, workspace)
+    hidden = int(x.shape[-1])
+    if not x.is_contiguous() or weight.numel() != hidden or weight.dtype != x.dtype:
+        raise ValueError("rms_norm_quantize expects contiguous x and a weight of x's dtype and width")
+    if residual is not None and sum_out is None:
+        raise ValueError("a residual needs sum_out")
+    check(_lib.load().cacheir_b200_rms_norm_quantize(x.data_ptr(), _ptr(residual), weight.data_ptr(), _ptr(sum_out), _ptr(out),
+                                                     x.numel() // hidden, hidden, float(eps), dtype_code(x.dtype),
+                                                     workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+                                                     _stream()), "rms_norm_quantize")
 
 
 def rope_inplace(x: torch.Tensor, positions: torch.Tensor, *, num_heads: int, head_dim: int, theta: float) -> torch.Tensor:

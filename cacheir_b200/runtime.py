@@ -245,6 +245,7 @@ class _DecodePlan:
         nodes = list(eng.graph.nodes)
         env: dict[str, Any] = {}
         self._count_keys: list[tuple[str, int]] = []
+        self._prequantized: set[str] = set()
         uses: dict[str, int] = {}
         for node in nodes:
             for name in node.inputs:
@@ -269,10 +270,22 @@ class _DecodePlan:
                 env[node.outputs[0]] = out
             elif op == "rms_norm":
                 x, w = env[node.inputs[0]], eng.weights.get(node.inputs[1])
-                out = self._buf(int(x.shape[1]))
                 eps = float(attrs.get("eps", 1e-6))
-                self._emit(lambda x=x, w=w, out=out, eps=eps: ops.rms_norm(x, w, eps, out=out), "b200.rms_norm")
-                env[node.outputs[0]] = out
+                nxt = nodes[idx + 1] if idx + 1 < len(nodes) else None
+                fused = False
+                if (nxt is not None and nxt.op in {"quantized_matmul", "quantized_fused_swiglu"}
+                        and nxt.inputs[0] == node.outputs[0] and uses.get(node.outputs[0], 0) == 1):
+                    names = (nxt.inputs[1],) if nxt.op == "quantized_matmul" else tuple(nxt.inputs[1:3])
+                    if self._i8_eligible(eng.matmul_weight(names, True), int(x.shape[1]), swiglu=len(names) == 2):
+                        ws = self._gemm_workspace(int(x.shape[1]))
+                        self._emit(lambda x=x, w=w, eps=eps, ws=ws: ops.rms_norm_quantize(x, w, eps, ws), "b200.rms_norm_quantize")
+                        env[node.outputs[0]] = x            # placeholder: the consumer reads the workspace, not this tensor
+                        self._prequantized.add(node.outputs[0])
+                        fused = True
+                if not fused:
+                    out = self._buf(int(x.shape[1]))
+                    self._emit(lambda x=x, w=w, out=out, eps=eps: ops.rms_norm(x, w, eps, out=out), "b200.rms_norm")
+                    env[node.outputs[0]] = out
             elif op in {"matmul", "quantized_matmul"}:
                 x = env[node.inputs[0]]
                 weight = eng.matmul_weight((node.inputs[1],), op == "quantized_matmul")
@@ -285,15 +298,20 @@ class _DecodePlan:
                     residual = env[other]
                     skip.add(idx + 1)
                     out_name = nxt.outputs[0]
-                out = self._matmul(x, weight, residual=residual)
+                out = self._matmul(x, weight, residual=residual, prequantized=node.inputs[0] in self._prequantized)
                 env[out_name] = out
             elif op in {"fused_rmsnorm_qkv_rope", "quantized_fused_rmsnorm_qkv_rope"}:
                 x, norm_w = env[node.inputs[0]], eng.weights.get(node.inputs[1])
                 weight = eng.matmul_weight(tuple(node.inputs[2:5]), op.startswith("quantized_"))
                 eps = float(attrs.get("eps", 1e-6))
-                normed = self._buf(int(x.shape[1]))
-                self._emit(lambda x=x, w=norm_w, out=normed, eps=eps: ops.rms_norm(x, w, eps, out=out), "b200.rms_norm")
-                qkv = self._matmul(normed, weight)
+                if self._i8_eligible(weight, int(x.shape[1])):
+                    ws = self._gemm_workspace(int(x.shape[1]))
+                    self._emit(lambda x=x, w=norm_w, eps=eps, ws=ws: ops.rms_norm_quantize(x, w, eps, ws), "b200.rms_norm_quantize")
+                    qkv = self._matmul(x, weight, prequantized=True)
+                else:
+                    normed = self._buf(int(x.shape[1]))
+                    self._emit(lambda x=x, w=norm_w, out=normed, eps=eps: ops.rms_norm(x, w, eps, out=out), "b200.rms_norm")
+                    qkv = self._matmul(normed, weight)
                 q_dim = self._rows_of(node.inputs[2])
                 k_dim = self._rows_of(node.inputs[3])
                 head_dim = int(attrs["head_dim"])
@@ -327,7 +345,8 @@ class _DecodePlan:
             elif op in {"fused_swiglu", "quantized_fused_swiglu"}:
                 x = env[node.inputs[0]]
                 weight = eng.matmul_weight(tuple(node.inputs[1:3]), op.startswith("quantized_"))
-                env[node.outputs[0]] = self._matmul(x, weight, epilogue=ops.EPI_SWIGLU)
+                env[node.outputs[0]] = self._matmul(x, weight, epilogue=ops.EPI_SWIGLU,
+                                                    prequantized=node.inputs[0] in self._prequantized)
             elif op == "elementwise_mul" and idx > 0 and nodes[idx - 1].op == "silu" and nodes[idx - 1].outputs[0] in node.inputs:
                 gate = env["__silu_in__" + nodes[idx - 1].outputs[0]]
                 up = env[node.inputs[1] if node.inputs[0] == nodes[idx - 1].outputs[0] else node.inputs[0]]
@@ -351,8 +370,16 @@ class _DecodePlan:
         shape = getattr(spec, "shape", None) or spec.tensor_type.shape
         return int(shape[0])
 
+    def _i8_eligible(self, weight: Any, k: int, swiglu: bool = False) -> bool:
+        """Will this projection run on the integer tensor cores (and so accept pre-quantized activations)?"""
+        if swiglu and isinstance(weight, B200PackedWeight) and (weight.shape[0] // 2) % 128 != 0:
+            return False
+        return (isinstance(weight, B200PackedWeight) and weight.bits == 8 and not weight.group_size
+                and self.engine.dtype == torch.float16 and self.batch <= 64 and k % 128 == 0 and k <= 8192
+                and hasattr(self, "_gemm_ws"))
+
     def _matmul(self, x: torch.Tensor, weight: B200PackedWeight | torch.Tensor, *, epilogue: int = ops.EPI_NONE,
-                residual: torch.Tensor | None = None) -> torch.Tensor:
+                residual: torch.Tensor | None = None, prequantized: bool = False) -> torch.Tensor:
         eng = self.engine
         if residual is not None:
             epilogue = ops.EPI_RESIDUAL
@@ -362,10 +389,10 @@ class _DecodePlan:
             ws = self._gemm_workspace(k) if (bits == 8 and not weight.group_size and eng.dtype == torch.float16) else None
             fn = lambda: ops.qgemv(x, weight.packed_values, weight.scales, weight.zero_points, bits=bits, n=n, k=k,
                                    group_size=weight.group_size or 0, epilogue=epilogue, residual=residual, out=out,
-                                   workspace=ws, tiled=weight.tiled)
+                                   workspace=ws, tiled=weight.tiled, prequantized=prequantized)
             key = f"b200.qgemv.int{bits}" + (".swiglu" if epilogue == ops.EPI_SWIGLU else ".residual" if residual is not None else "")
             eng.gemm_plans[f"q{bits}:{(self.batch, 1, k)}x{weight.shape}"] = key
-            if ws is not None and self.batch <= 64 and k % 128 == 0:   # activation pre-pass + integer GEMM
+            if ws is not None and self.batch <= 64 and k % 128 == 0 and not prequantized:   # activation pre-pass + integer GEMM
                 self._emit(fn, key, launches=2)
                 return out
         else:

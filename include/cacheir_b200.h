@@ -39,9 +39,10 @@ extern "C" {
 #define CACHEIR_B200_EUNSUPPORTED (-4)/* shape outside what the kernels cover */
 #define CACHEIR_B200_ELIMIT (-5)      /* beyond a documented fixed maximum    */
 
-/* weight layouts accepted by cacheir_b200_qgemv_ex */
+/* `weight_layout` flags of cacheir_b200_qgemv_ex (may be OR-ed) */
 #define CACHEIR_B200_LAYOUT_ROWS 0     /* the reference's row-major packed_values   */
 #define CACHEIR_B200_LAYOUT_TILED 1    /* cacheir_b200_pack_relayout's tile order   */
+#define CACHEIR_B200_X_PREQUANTIZED 2  /* workspace already holds x in integer form */
 
 /* qgemv epilogues */
 #define CACHEIR_B200_EPI_NONE 0       /* y = x W^T                            */
@@ -173,6 +174,20 @@ int cacheir_b200_qgemv_ex(const void* x, const void* packed, const void* scales,
                           int x_dtype, int scale_dtype, long long x_stride,
                           int epilogue, int weight_layout, void* workspace,
                           size_t workspace_bytes, void* stream);
+
+/* The activation pre-pass of the integer tensor-core path on its own, and fused with RMSNorm
+ * (`_rms_norm`, cacheir/runtime/cuda.py:889-895, followed by `_quantized_matmul`, :932-940):
+ * both leave x as 16-bit fixed point per row in `workspace` (>= cacheir_b200_qgemv_workspace_bytes
+ * bytes, 128-byte aligned, fp16 only, rows <= 64, width a multiple of 128). A following
+ * cacheir_b200_qgemv_ex with the same M, K and workspace and CACHEIR_B200_X_PREQUANTIZED set skips
+ * its own pre-pass (x is then not read). rms_norm_quantize normalises x (+ residual, the rounded
+ * sum going to sum_out) exactly like cacheir_b200_rms_norm, rounds to fp16, optionally stores the
+ * fp16 row to `out` (may be NULL) and quantises it; width <= 8192. */
+int cacheir_b200_quantize_activations(const void* x, int M, int K, long long x_stride, int x_dtype,
+                                      void* workspace, size_t workspace_bytes, void* stream);
+int cacheir_b200_rms_norm_quantize(const void* x, const void* residual, const void* weight,
+                                   void* sum_out, void* out, int rows, int hidden, float eps,
+                                   int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Device pack layout of the quantization loader. The codes of the reference format
  * (`packed_values`, cacheir/quantization.py:107-120; uploaded row-major by

@@ -473,3 +473,36 @@ def test_pack_relayout_roundtrip_and_gemm_equivalence(bits, n, k):
         assert torch.equal(a, b)
     torch.cuda.synchronize()
     _device_status_ok()
+
+
+def test_rms_norm_quantize_and_prequantized_gemm_match_the_two_step_path():
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(123)
+    for m, n, k in [(32, 512, 4096), (5, 256, 1024), (64, 384, 8192)]:
+        x, packed = _qgemv_case(rng, m, n, k, 8, torch.float16)
+        res = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).half().cuda()
+        w = torch.from_numpy(rng.standard_normal((k,)).astype(np.float32)).half().cuda()
+        dev = _device_pack(packed)
+        ws = torch.empty(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
+        # two-step: rms_norm (+residual) to fp16, then the GEMM with its own pre-pass
+        summed = torch.empty_like(res)
+        normed = ops.rms_norm(x.cuda(), w, 1e-5, residual=res, sum_out=summed)
+        want = quantized_matmul(normed, dev, workspace=ws)
+        # fused: one kernel normalises and quantises, the GEMM consumes the workspace
+        summed2 = torch.empty_like(res)
+        out2 = torch.empty_like(res)
+        ops.rms_norm_quantize(x.cuda(), w, 1e-5, ws, residual=res, sum_out=summed2, out=out2)
+        got = ops.qgemv(x.cuda(), dev.packed_values, dev.scales, dev.zero_points, bits=8, n=n, k=k, workspace=ws, prequantized=True)
+        assert torch.equal(summed, summed2)
+        # the two kernels reduce the sum of squares with different block shapes: the fp16 rows may differ by one ulp
+        assert _rel(out2, normed.float().cpu().numpy()) <= 5e-4
+        assert _rel(got, want.float().cpu().numpy()) <= TOL[torch.float16]
+        # stand-alone pre-pass entry point
+        ops.quantize_activations(normed, ws)
+        got2 = ops.qgemv(x.cuda(), dev.packed_values, dev.scales, dev.zero_points, bits=8, n=n, k=k, workspace=ws, prequantized=True)
+        assert torch.equal(got2, want)          # same pre-pass arithmetic, same integers
+        base = oracle.quantized_matmul(normed.float().cpu().numpy(), packed)
+        assert _rel(got, base) <= TOL[torch.float16]
+    torch.cuda.synchronize()
+    _device_status_ok()
