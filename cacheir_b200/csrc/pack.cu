@@ -95,8 +95,12 @@ __global__ void dequantize_rows_kernel(const uint8_t* __restrict__ packed, const
 // Tile-major device layout of the packed codes: the matrix is cut into tiles of 128 rows x 128
 // k elements (128 bytes per row for int8, 64 for int4) and each tile is stored contiguously,
 // tiles of one 128-row band following each other along K:
-//   tiled[((band * KB + kb) * 128 + r) * TB + j] = packed[(band*128 + r) * row_bytes + kb*TB + j]
-// A pure permutation of bytes (rows past N are zero), so it is exactly invertible.
+//   tiled[((band * KB + kb) * 128 + r) * TB + swz(r, j)] = packed[(band*128 + r) * row_bytes + kb*TB + j]
+// Inside a tile the 16-byte chunks of row r are stored in the XOR order that a 128-byte (int8) or
+// 64-byte (int4) swizzled TMA copy would produce in shared memory -- chunk c of row r sits at
+// c ^ (r & 7), respectively c ^ ((r >> 1) & 3) -- so a plain contiguous bulk copy of the tile lands
+// in the bank-conflict-free layout the kernels read. A pure permutation of bytes (rows past N are
+// zero), so it is exactly invertible.
 template <bool INVERSE>
 __global__ void __launch_bounds__(256)
 relayout_tiles_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int N, int row_bytes, int tile_bytes_per_row) {
@@ -108,7 +112,8 @@ relayout_tiles_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst
     const int r = idx / chunks_per_row;
     const int c = idx % chunks_per_row;
     const int n = band * 128 + r;
-    const size_t tiled_off = ((static_cast<size_t>(band) * kblocks + kb) * 128 + r) * tile_bytes_per_row + c * 16;
+    const int cs = chunks_per_row == 8 ? (c ^ (r & 7)) : (c ^ ((r >> 1) & 3));
+    const size_t tiled_off = ((static_cast<size_t>(band) * kblocks + kb) * 128 + r) * tile_bytes_per_row + cs * 16;
     const size_t rows_off = static_cast<size_t>(n) * row_bytes + static_cast<size_t>(kb) * tile_bytes_per_row + c * 16;
     if (INVERSE) {
       if (n < N) *reinterpret_cast<uint4*>(dst + rows_off) = *reinterpret_cast<const uint4*>(src + tiled_off);

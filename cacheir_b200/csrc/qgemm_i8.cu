@@ -13,8 +13,11 @@
 // exactly (int32). The epilogue recombines in double precision:
 //   y[m,n] = scale[n] * sx[m] * (256*D[n,m] + D[n,MP+m] - zero[n] * sum_k q[m,k]).
 //
-// One CTA owns 128 weight rows and a K range: warp 0 issues the TMA copies, warp 1 the
-// MMAs (K = 32 per instruction, 4 per 128-column stage), warps 2-5 run the epilogue.
+// One CTA owns 128 weight rows and a K range: warp 0 issues the TMA copies, warps 1 and 6 the
+// MMAs (K = 32 per instruction, 4 per 128-column stage; the two issuers take alternate stages
+// and own separate accumulators, so one can wait on a barrier while the other feeds the tensor
+// core -- integer sums, so adding the two accumulators afterwards is exact), warps 2-5 run the
+// epilogue.
 // K ranges of one row tile form a thread-block cluster. Their partial sums are integers, so
 // the order of addition cannot matter; they are exchanged all-to-all through distributed
 // shared memory, each CTA of the cluster finishing the outputs of its own slice of the batch.
@@ -29,7 +32,7 @@ using namespace ptx;
 
 constexpr int kBlockN = 128;          // weight rows per CTA (UMMA M)
 constexpr int kBlockK = 128;          // bytes of a weight row per stage
-constexpr int kThreads = 192;         // producer, MMA, four epilogue warps
+constexpr int kThreads = 224;         // producer, MMA, four epilogue warps, second MMA issuer
 constexpr int kTmemCols = 256;
 constexpr int kRingBudget = 96 * 1024;   // two CTAs per SM: one issues MMAs while the other waits on a barrier
 constexpr int kMaxSplitK = 8;
@@ -48,20 +51,25 @@ __host__ __device__ constexpr int stage_bytes(int mp) { return kBlockN * kBlockK
 __host__ __device__ constexpr int num_stages(int mp) { return kRingBudget / stage_bytes(mp) > 8 ? 8 : kRingBudget / stage_bytes(mp); }
 
 // ---- pre-pass: rows of x -> two planes of signed bytes + scale + sum ------------------
-// planes: [2*mp rows][K] int8 (rows [0,mp): high bytes, [mp,2mp): low bytes; rows >= M are zero)
+// The planes are stored the way the GEMM consumes them: per 128-column k block one contiguous
+// tile [2*mp rows][128 bytes] (rows [0,mp): high bytes, [mp,2mp): low bytes; rows >= M are zero),
+// with the 16-byte chunks of row R in the XOR order of a 128-byte swizzle (chunk c at c ^ (R & 7)),
+// so that one contiguous bulk copy per stage lands it ready for the tensor core.
+__device__ __forceinline__ size_t plane_offset(int mp, int R, int k) {
+  const int kb = k >> 7, j = k & 127;
+  return (static_cast<size_t>(kb) * 2 * mp + R) * 128 + ((((j >> 4) ^ (R & 7)) << 4) | (j & 15));
+}
 __global__ void __launch_bounds__(256)
 quantize_rows_kernel(const __half* __restrict__ x, long long x_stride, int M, int K, int mp,
                      int8_t* __restrict__ planes, float* __restrict__ sx, int* __restrict__ qsum) {
   __shared__ float s_red[8];
   __shared__ int s_sum[8];
   const int m = blockIdx.x;
-  int8_t* hi_row = planes + static_cast<size_t>(m) * K;
-  int8_t* lo_row = planes + static_cast<size_t>(mp + m) * K;
   const int nvec = K / 8;
   if (m >= M) {
     for (int c = threadIdx.x; c < nvec; c += 256) {
-      *reinterpret_cast<uint2*>(hi_row + c * 8) = make_uint2(0u, 0u);
-      *reinterpret_cast<uint2*>(lo_row + c * 8) = make_uint2(0u, 0u);
+      *reinterpret_cast<uint2*>(planes + plane_offset(mp, m, c * 8)) = make_uint2(0u, 0u);
+      *reinterpret_cast<uint2*>(planes + plane_offset(mp, mp + m, c * 8)) = make_uint2(0u, 0u);
     }
     if (threadIdx.x == 0) { sx[m] = 0.f; qsum[m] = 0; }
     return;
@@ -96,8 +104,8 @@ quantize_rows_kernel(const __half* __restrict__ x, long long x_stride, int M, in
       hi_w[i >> 2] |= static_cast<uint32_t>(hi & 0xFF) << (8 * (i & 3));
       lo_w[i >> 2] |= static_cast<uint32_t>(lo & 0xFF) << (8 * (i & 3));
     }
-    *reinterpret_cast<uint2*>(hi_row + c * 8) = make_uint2(hi_w[0], hi_w[1]);
-    *reinterpret_cast<uint2*>(lo_row + c * 8) = make_uint2(lo_w[0], lo_w[1]);
+    *reinterpret_cast<uint2*>(planes + plane_offset(mp, m, c * 8)) = make_uint2(hi_w[0], hi_w[1]);
+    *reinterpret_cast<uint2*>(planes + plane_offset(mp, mp + m, c * 8)) = make_uint2(lo_w[0], lo_w[1]);
   }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
@@ -135,7 +143,7 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // One row of activations held in registers -> byte planes, scale and sum. Shared by the
 // stand-alone pre-pass and the RMSNorm-fused form; `vals` are the fp16-rounded activations.
 template <int PT>
-__device__ __forceinline__ void quantize_row_from_registers(const float (&vals)[PT][8], int nvec, int8_t* hi_row, int8_t* lo_row,
+__device__ __forceinline__ void quantize_row_from_registers(const float (&vals)[PT][8], int nvec, int8_t* planes, int mp, int m,
                                                             float* sx_out, int* qsum_out, float* scratch) {
   float amax = 0.f;
 #pragma unroll
@@ -160,8 +168,8 @@ __device__ __forceinline__ void quantize_row_from_registers(const float (&vals)[
         hi_w[j >> 2] |= static_cast<uint32_t>(hi & 0xFF) << (8 * (j & 3));
         lo_w[j >> 2] |= static_cast<uint32_t>(lo & 0xFF) << (8 * (j & 3));
       }
-      *reinterpret_cast<uint2*>(hi_row + c * 8) = make_uint2(hi_w[0], hi_w[1]);
-      *reinterpret_cast<uint2*>(lo_row + c * 8) = make_uint2(lo_w[0], lo_w[1]);
+      *reinterpret_cast<uint2*>(planes + plane_offset(mp, m, c * 8)) = make_uint2(hi_w[0], hi_w[1]);
+      *reinterpret_cast<uint2*>(planes + plane_offset(mp, mp + m, c * 8)) = make_uint2(lo_w[0], lo_w[1]);
     }
   }
   __shared__ int s_isum[32];
@@ -177,10 +185,10 @@ __device__ __forceinline__ void quantize_row_from_registers(const float (&vals)[
   }
 }
 
-__device__ __forceinline__ void zero_plane_rows(int8_t* hi_row, int8_t* lo_row, int nvec) {
+__device__ __forceinline__ void zero_plane_rows(int8_t* planes, int mp, int m, int nvec) {
   for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
-    *reinterpret_cast<uint2*>(hi_row + c * 8) = make_uint2(0u, 0u);
-    *reinterpret_cast<uint2*>(lo_row + c * 8) = make_uint2(0u, 0u);
+    *reinterpret_cast<uint2*>(planes + plane_offset(mp, m, c * 8)) = make_uint2(0u, 0u);
+    *reinterpret_cast<uint2*>(planes + plane_offset(mp, mp + m, c * 8)) = make_uint2(0u, 0u);
   }
 }
 
@@ -191,11 +199,9 @@ quantize_rows_fast_kernel(const __half* __restrict__ x, long long x_stride, int 
                           int8_t* __restrict__ planes, float* __restrict__ sx, int* __restrict__ qsum) {
   __shared__ float scratch[32];
   const int m = blockIdx.x;
-  int8_t* hi_row = planes + static_cast<size_t>(m) * K;
-  int8_t* lo_row = planes + static_cast<size_t>(mp + m) * K;
   const int nvec = K / 8;
   if (m >= M) {
-    zero_plane_rows(hi_row, lo_row, nvec);
+    zero_plane_rows(planes, mp, m, nvec);
     if (threadIdx.x == 0) { sx[m] = 0.f; qsum[m] = 0; }
     return;
   }
@@ -207,7 +213,7 @@ quantize_rows_fast_kernel(const __half* __restrict__ x, long long x_stride, int 
     for (int j = 0; j < 8; ++j) vals[i][j] = 0.f;
     if (c < nvec) VecIO<__half, 8>::ld(x + static_cast<size_t>(m) * x_stride + c * 8, vals[i]);
   }
-  quantize_row_from_registers<PT>(vals, nvec, hi_row, lo_row, sx + m, qsum + m, scratch);
+  quantize_row_from_registers<PT>(vals, nvec, planes, mp, m, sx + m, qsum + m, scratch);
 }
 
 // RMSNorm (optionally of x + residual, the rounded sum going to sum_out) fused with the pre-pass:
@@ -220,11 +226,9 @@ rms_norm_quantize_kernel(const __half* __restrict__ x, const __half* __restrict_
                          int8_t* __restrict__ planes, float* __restrict__ sx, int* __restrict__ qsum) {
   __shared__ float scratch[32];
   const int m = blockIdx.x;
-  int8_t* hi_row = planes + static_cast<size_t>(m) * hidden;
-  int8_t* lo_row = planes + static_cast<size_t>(mp + m) * hidden;
   const int nvec = hidden / 8;
   if (m >= M) {
-    zero_plane_rows(hi_row, lo_row, nvec);
+    zero_plane_rows(planes, mp, m, nvec);
     if (threadIdx.x == 0) { sx[m] = 0.f; qsum[m] = 0; }
     return;
   }
@@ -261,7 +265,7 @@ rms_norm_quantize_kernel(const __half* __restrict__ x, const __half* __restrict_
       if (out) VecIO<__half, 8>::st(out + row + c * 8, vals[i]);
     }
   }
-  quantize_row_from_registers<PT>(vals, nvec, hi_row, lo_row, sx + m, qsum + m, scratch);
+  quantize_row_from_registers<PT>(vals, nvec, planes, mp, m, sx + m, qsum + m, scratch);
 }
 
 struct I8Params {
@@ -271,6 +275,8 @@ struct I8Params {
   void* y;
   const float* sx;
   const int* qsum;
+  const uint8_t* w_tiled;     // tile-ordered codes (tiled != 0)
+  const int8_t* x_planes;     // activation byte tiles written by the pre-pass
   int M, N, K;
   int n_out;
   int scale_dtype;
@@ -291,7 +297,7 @@ __device__ __forceinline__ float recombine(int32_t hi, int32_t lo, float zero, i
 
 template <int MP, int SPLIT>
 __global__ void __launch_bounds__(kThreads, 2)
-qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const I8Params p) {
+qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
   constexpr int kStages = num_stages(MP);
   constexpr int kWBytes = kBlockN * kBlockK;          // 16 KB of codes per stage
   constexpr int kXBytes = 2 * MP * kBlockK;           // [hi; lo] rows per stage
@@ -323,10 +329,13 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   const int kblocks = kb_end - kb_begin;
   const int total = kblocks * passes;
   const int n0 = blockIdx.x * kBlockN;
+  // two MMA streams when both sets of accumulators fit in the allocated tensor memory
+  const int streams = (kblocks >= 2 && 2 * passes * kAccCols <= kTmemCols) ? 2 : 1;
+  const int stream_cols = passes * kAccCols;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
-    mbar_init(smem_u32(acc_full), 1);
+    mbar_init(smem_u32(acc_full), 2);
     mbar_fence_init();
   }
   if (threadIdx.x >= 64 && threadIdx.x < 64 + MP) {
@@ -352,23 +361,24 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         const int kb = kb_begin + i % kblocks;
         const uint32_t bar = smem_u32(&full[s]);
         mbar_expect_tx(bar, kWBytes + kXBytes);
-        if (p.tiled) {
-          const int band = blockIdx.x + pass * (p.N / 2 / kBlockN);
-          tma_load_2d(smem_u32(s_w + s * kWBytes), &tmap_w, bar, 0, (band * kblocks_all + kb) * kBlockN);
+        if (p.tiled) {   // one contiguous, pre-swizzled 16 KB tile
+          const size_t band = blockIdx.x + pass * (p.N / 2 / kBlockN);
+          bulk_load(smem_u32(s_w + s * kWBytes), p.w_tiled + (band * kblocks_all + kb) * kWBytes, kWBytes, bar);
         } else {
           tma_load_2d(smem_u32(s_w + s * kWBytes), &tmap_w, bar, kb * kBlockK, n0 + pass * (p.N / 2));
         }
-        tma_load_2d(smem_u32(s_x + s * kXBytes), &tmap_x, bar, kb * kBlockK, 0);
+        bulk_load(smem_u32(s_x + s * kXBytes), p.x_planes + static_cast<size_t>(kb) * kXBytes, kXBytes, bar);
         CB200_TRACE(0, i, 2);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 6) {
     if (lane == 0) {
-      // ---------------- MMA issuer ----------------
+      // ---------------- MMA issuers: stream 0 (warp 1) and stream 1 (warp 6) take alternate stages ----------------
       // D = s32, A (codes) unsigned 8 bit, B (activation bytes) signed 8 bit, both K-major, N = 2*MP, M = 128
+      const int st = warp == 1 ? 0 : 1;
       const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(kAccCols >> 3) << 17) |
                              (static_cast<uint32_t>(kBlockN >> 4) << 24);
-      for (int i = 0; i < total; ++i) {
+      for (int i = st; i < total && st < streams; i += streams) {
         const int s = i % kStages;
         CB200_TRACE(1, i, 0);
         if (!mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, &g_i8_status, (3 << 8) | 2)) break;
@@ -376,12 +386,14 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         tc_fence_after();
         const int pass = i / kblocks;
         const int kb = i % kblocks;
-        const uint32_t d = tmem_base + pass * kAccCols;
+        // the first block this stream sees in a pass overwrites its accumulator
+        const int kb_first = ((st - pass * kblocks) % streams + streams) % streams;
+        const uint32_t d = tmem_base + st * stream_cols + pass * kAccCols;
         const uint32_t w_base = smem_u32(s_w + s * kWBytes);
         const uint32_t x_base = smem_u32(s_x + s * kXBytes);
 #pragma unroll
         for (int j = 0; j < kBlockK / 32; ++j)   // 32 bytes of k per instruction inside the 128-byte swizzle span
-          tc_mma_i8_ss(d, smem_desc_sw128(w_base + j * 32), smem_desc_sw128(x_base + j * 32), idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          tc_mma_i8_ss(d, smem_desc_sw128(w_base + j * 32), smem_desc_sw128(x_base + j * 32), idesc, (kb != kb_first || j > 0) ? 1u : 0u);
         CB200_TRACE(1, i, 2);
         tc_commit(smem_u32(&empty[s]));
         CB200_TRACE(1, i, 3);
@@ -425,6 +437,16 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           for (int c0 = 0; c0 < MP; c0 += 8) tc_ld_x8(tmem_base + lane_addr + (ah >> 1) * kAccCols + (ah & 1) * MP + c0,
                                                       reinterpret_cast<uint32_t(&)[8]>(acc[c0]));
           tc_wait_ld();
+          if (streams == 2) {
+#pragma unroll
+            for (int c0 = 0; c0 < MP; c0 += 8) {
+              uint32_t other[8];
+              tc_ld_x8(tmem_base + lane_addr + stream_cols + (ah >> 1) * kAccCols + (ah & 1) * MP + c0, other);
+              tc_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[c0 + j] += other[j];
+            }
+          }
         } else {
 #pragma unroll
           for (int c = 0; c < MP; ++c) acc[c] = 0u;
@@ -499,6 +521,14 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             tc_ld_x8(tmem_base + lane_addr + pass * kAccCols + c0, hi[pass]);
             tc_ld_x8(tmem_base + lane_addr + pass * kAccCols + MP + c0, lo[pass]);
             tc_wait_ld();
+            if (streams == 2) {
+              uint32_t h2[8], l2[8];
+              tc_ld_x8(tmem_base + lane_addr + stream_cols + pass * kAccCols + c0, h2);
+              tc_ld_x8(tmem_base + lane_addr + stream_cols + pass * kAccCols + MP + c0, l2);
+              tc_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { hi[pass][j] += h2[j]; lo[pass][j] += l2[j]; }
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < 8; ++j) { hi[pass][j] = 0u; lo[pass][j] = 0u; }
@@ -524,7 +554,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       }
     }
   }
-  if (warp < 2 && split > 1) {   // warps without an epilogue still take part in the two cluster barriers
+  if ((warp < 2 || warp == 6) && split > 1) {   // warps without an epilogue still take part in the two cluster barriers
     __syncwarp();
     cluster_sync_all();
     cluster_sync_all();
@@ -562,7 +592,7 @@ int launch_quantize(const __half* x, long long x_stride, int M, int K, int mp, v
 }
 
 template <int MP, int SPLIT>
-cudaError_t launch_i8_split(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x, const I8Params& p, int n_tiles, cudaStream_t stream) {
+cudaError_t launch_i8_split(const CUtensorMap& tmap_w, const I8Params& p, int n_tiles, cudaStream_t stream) {
   constexpr size_t kSmem = 1024 + static_cast<size_t>(num_stages(MP)) * stage_bytes(MP) + 1024;
   auto kern = qgemm_i8_kernel<MP, SPLIT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
@@ -579,7 +609,7 @@ cudaError_t launch_i8_split(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, tmap_w, tmap_x, p);
+  return cudaLaunchKernelEx(&cfg, kern, tmap_w, p);
 }
 
 template <int MP>
@@ -592,17 +622,16 @@ int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
     if (rc != 0) return rc;
   }
 
-  CUtensorMap tmap_w, tmap_x;
+  CUtensorMap tmap_w;
   const uint64_t bands = static_cast<uint64_t>((q.N + kBlockN - 1) / kBlockN);
   const bool w_ok = q.tiled
       ? encode_u8_rows_sw128(&tmap_w, q.packed, kBlockK, bands * (q.K / kBlockK) * kBlockN, kBlockK, kBlockN)
       : encode_u8_rows_sw128(&tmap_w, q.packed, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.N), static_cast<uint64_t>(q.K), kBlockN);
   if (!w_ok) return CACHEIR_B200_EUNSUPPORTED;
-  if (!encode_u8_rows_sw128(&tmap_x, planes, static_cast<uint64_t>(q.K), static_cast<uint64_t>(2 * MP), static_cast<uint64_t>(q.K), 2 * MP))
-    return CACHEIR_B200_EUNSUPPORTED;
   I8Params p{};
   p.scales = q.scales; p.zero_points = q.zero_points; p.residual = q.residual; p.y = q.y;
   p.sx = sx; p.qsum = qsum;
+  p.w_tiled = static_cast<const uint8_t*>(q.packed); p.x_planes = planes;
   p.M = q.M; p.N = q.N; p.K = q.K;
   p.n_out = q.epilogue == CACHEIR_B200_EPI_SWIGLU ? q.N / 2 : q.N;
   p.scale_dtype = q.scale_dtype; p.epilogue = q.epilogue; p.tiled = q.tiled ? 1 : 0;
@@ -610,10 +639,10 @@ int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
   p.split_k = choose_split_k(n_tiles, q.K / kBlockK, q.epilogue, MP);
   cudaError_t e;
   switch (p.split_k) {
-    case 8: e = launch_i8_split<MP, 8>(tmap_w, tmap_x, p, n_tiles, stream); break;
-    case 4: e = launch_i8_split<MP, 4>(tmap_w, tmap_x, p, n_tiles, stream); break;
-    case 2: e = launch_i8_split<MP, 2>(tmap_w, tmap_x, p, n_tiles, stream); break;
-    default: e = launch_i8_split<MP, 1>(tmap_w, tmap_x, p, n_tiles, stream); break;
+    case 8: e = launch_i8_split<MP, 8>(tmap_w, p, n_tiles, stream); break;
+    case 4: e = launch_i8_split<MP, 4>(tmap_w, p, n_tiles, stream); break;
+    case 2: e = launch_i8_split<MP, 2>(tmap_w, p, n_tiles, stream); break;
+    default: e = launch_i8_split<MP, 1>(tmap_w, p, n_tiles, stream); break;
   }
   if (e != cudaSuccess) return static_cast<int>(e);
   return launch_status();

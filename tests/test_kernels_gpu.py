@@ -459,7 +459,11 @@ def test_pack_relayout_roundtrip_and_gemm_equivalence(bits, n, k):
     t = tiled.packed_values.cpu().numpy().reshape(-1, kblocks, 128, tb)
     ref = packed.packed_values
     band, kb, r = (n - 1) // 128, kblocks - 1, (n - 1) % 128
-    np.testing.assert_array_equal(t[band, kb, r], ref[n - 1, kb * tb:(kb + 1) * tb])
+    # inside a tile row the 16-byte chunks sit in the shared-memory swizzle order (chunk c at c ^ key(r))
+    key = (r & 7) if bits == 8 else ((r >> 1) & 3)
+    chunks = t[band, kb, r].reshape(tb // 16, 16)
+    unswizzled = np.stack([chunks[c ^ key] for c in range(tb // 16)]).reshape(-1)
+    np.testing.assert_array_equal(unswizzled, ref[n - 1, kb * tb:(kb + 1) * tb])
     assert not t[band, :, r + 1:].any()                                  # rows past N are zero padding
     y_rows = quantized_matmul(x.cuda(), rows)
     y_tiled = quantized_matmul(x.cuda(), tiled)
