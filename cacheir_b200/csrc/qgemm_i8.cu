@@ -32,9 +32,10 @@ using namespace ptx;
 
 constexpr int kBlockN = 128;          // weight rows per CTA (UMMA M)
 constexpr int kBlockK = 128;          // bytes of a weight row per stage
-constexpr int kThreads = 224;         // producer, MMA, four epilogue warps, second MMA issuer
+constexpr int kThreads = 192;         // producer, MMA issuer, four epilogue warps
 constexpr int kTmemCols = 256;
-constexpr int kRingBudget = 96 * 1024;   // two CTAs per SM: one issues MMAs while the other waits on a barrier
+constexpr int kCtaBudget = 104 * 1024;   // ring + exchange buffer; two CTAs per SM: one issues MMAs while the other waits on a barrier
+constexpr int kCtaBudgetWide = 200 * 1024;   // split-K with more than 32 batch rows: one CTA per SM
 constexpr int kMaxSplitK = 8;
 constexpr float kQMax = 32639.f;      // 127*256 + 127: every value splits into two signed bytes
 
@@ -48,7 +49,14 @@ __device__ long long g_i8_trace[4][256][4];
 #endif
 
 __host__ __device__ constexpr int stage_bytes(int mp) { return kBlockN * kBlockK + 2 * mp * kBlockK; }
-__host__ __device__ constexpr int num_stages(int mp) { return kRingBudget / stage_bytes(mp) > 8 ? 8 : kRingBudget / stage_bytes(mp); }
+// split-K: every rank receives, from each rank, 128 rows x 2*(mp/split) words
+__host__ __device__ constexpr int exchange_bytes(int mp, int split) { return split > 1 ? kBlockN * 2 * mp * 4 : 0; }
+__host__ __device__ constexpr int ring_bytes(int mp, int split) {
+  return (split > 1 && mp > 32 ? kCtaBudgetWide : kCtaBudget) - exchange_bytes(mp, split);
+}
+__host__ __device__ constexpr int num_stages(int mp, int split) {
+  return ring_bytes(mp, split) / stage_bytes(mp) > 8 ? 8 : ring_bytes(mp, split) / stage_bytes(mp);
+}
 
 // ---- pre-pass: rows of x -> two planes of signed bytes + scale + sum ------------------
 // The planes are stored the way the GEMM consumes them: per 128-column k block one contiguous
@@ -298,23 +306,30 @@ __device__ __forceinline__ float recombine(int32_t hi, int32_t lo, float zero, i
 template <int MP, int SPLIT>
 __global__ void __launch_bounds__(kThreads, 2)
 qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
-  constexpr int kStages = num_stages(MP);
+  constexpr int kStages = num_stages(MP, SPLIT);
   constexpr int kWBytes = kBlockN * kBlockK;          // 16 KB of codes per stage
   constexpr int kXBytes = 2 * MP * kBlockK;           // [hi; lo] rows per stage
   constexpr int kAccCols = 2 * MP;                    // one accumulator: MP high + MP low columns
+  // split-K exchange: rank j finishes batch rows [j*MS, (j+1)*MS); a partial row for one destination is
+  // W words: [MS high | MS low]
+  constexpr int MS = MP / SPLIT;
+  constexpr int W = 2 * MS;
+  constexpr int kSlotBytes = kBlockN * W * 4;         // what one rank sends to one other rank
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* s_w = smem;
   uint8_t* s_x = s_w + kStages * kWBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_x + kStages * kXBytes);
+  int32_t* s_xch = reinterpret_cast<int32_t*>(s_x + kStages * kXBytes);   // [SPLIT senders][128 rows][W], written by the peers
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_xch) + exchange_bytes(MP, SPLIT));
   uint64_t* full = bars;                  // [kStages] TMA landed
   uint64_t* empty = bars + kStages;       // [kStages] MMAs that read the stage have retired
   uint64_t* acc_full = empty + kStages;   // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* xch_bar = acc_full + 1;       // [1] all partials of the other ranks have landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xch_bar + 1);
   float* s_sx = reinterpret_cast<float*>(tmem_slot + 2);     // [MP]
   int* s_qsum = reinterpret_cast<int*>(s_sx + MP);           // [MP]
-  int32_t* s_partial = reinterpret_cast<int32_t*>(smem);     // split-K partials reuse the drained ring
+  int32_t* s_stage = reinterpret_cast<int32_t*>(smem);       // outgoing partials [SPLIT dests][128 rows][W] reuse the drained ring
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -329,19 +344,34 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
   const int kblocks = kb_end - kb_begin;
   const int total = kblocks * passes;
   const int n0 = blockIdx.x * kBlockN;
-  // two MMA streams when both sets of accumulators fit in the allocated tensor memory
-  const int streams = (kblocks >= 2 && 2 * passes * kAccCols <= kTmemCols) ? 2 : 1;
-  const int stream_cols = passes * kAccCols;
+
+  auto load_stage = [&](int i, int s) {
+    const int pass = i / kblocks;
+    const int kb = kb_begin + i % kblocks;
+    const uint32_t bar = smem_u32(&full[s]);
+    mbar_expect_tx(bar, kWBytes + kXBytes);
+    if (p.tiled) {   // one contiguous, pre-swizzled 16 KB tile
+      const size_t band = blockIdx.x + pass * (p.N / 2 / kBlockN);
+      bulk_load(smem_u32(s_w + s * kWBytes), p.w_tiled + (band * kblocks_all + kb) * kWBytes, kWBytes, bar);
+    } else {
+      tma_load_2d(smem_u32(s_w + s * kWBytes), &tmap_w, bar, kb * kBlockK, n0 + pass * (p.N / 2));
+    }
+    bulk_load(smem_u32(s_x + s * kXBytes), p.x_planes + static_cast<size_t>(kb) * kXBytes, kXBytes, bar);
+  };
+  const int pre = total < kStages ? total : kStages;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
-    mbar_init(smem_u32(acc_full), 2);
+    mbar_init(smem_u32(acc_full), 1);
+    mbar_init(smem_u32(xch_bar), 1);
     mbar_fence_init();
+    if (split > 1) mbar_expect_tx(smem_u32(xch_bar), (split - 1) * kSlotBytes);
+    // the first ring of requests leaves before the rest of the CTA has finished setting up
+    for (int i = 0; i < pre; ++i) load_stage(i, i);
+    CB200_TRACE(0, 0, 2);
   }
-  if (threadIdx.x >= 64 && threadIdx.x < 64 + MP) {
-    s_sx[threadIdx.x - 64] = p.sx[threadIdx.x - 64];
-    s_qsum[threadIdx.x - 64] = p.qsum[threadIdx.x - 64];
-  }
+  __syncwarp();
+  if (split > 1) cluster_arrive();          // phase A: this CTA runs and its exchange barrier is armed
   if (warp == 1) tc_alloc(smem_u32(tmem_slot), kTmemCols);
   tc_fence_before();
   __syncthreads();
@@ -351,34 +381,23 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
 
   if (warp == 0) {
     if (lane == 0) {
-      // ---------------- TMA producer ----------------
-      for (int i = 0; i < total; ++i) {
+      // ---------------- TMA producer (stages beyond the first ring) ----------------
+      for (int i = pre; i < total; ++i) {
         const int s = i % kStages;
         CB200_TRACE(0, i, 0);
         if (!mbar_wait(smem_u32(&empty[s]), ((i / kStages) & 1) ^ 1, &g_i8_status, (3 << 8) | 1)) break;
         CB200_TRACE(0, i, 1);
-        const int pass = i / kblocks;
-        const int kb = kb_begin + i % kblocks;
-        const uint32_t bar = smem_u32(&full[s]);
-        mbar_expect_tx(bar, kWBytes + kXBytes);
-        if (p.tiled) {   // one contiguous, pre-swizzled 16 KB tile
-          const size_t band = blockIdx.x + pass * (p.N / 2 / kBlockN);
-          bulk_load(smem_u32(s_w + s * kWBytes), p.w_tiled + (band * kblocks_all + kb) * kWBytes, kWBytes, bar);
-        } else {
-          tma_load_2d(smem_u32(s_w + s * kWBytes), &tmap_w, bar, kb * kBlockK, n0 + pass * (p.N / 2));
-        }
-        bulk_load(smem_u32(s_x + s * kXBytes), p.x_planes + static_cast<size_t>(kb) * kXBytes, kXBytes, bar);
+        load_stage(i, s);
         CB200_TRACE(0, i, 2);
       }
     }
-  } else if (warp == 1 || warp == 6) {
+  } else if (warp == 1) {
     if (lane == 0) {
-      // ---------------- MMA issuers: stream 0 (warp 1) and stream 1 (warp 6) take alternate stages ----------------
+      // ---------------- MMA issuer ----------------
       // D = s32, A (codes) unsigned 8 bit, B (activation bytes) signed 8 bit, both K-major, N = 2*MP, M = 128
-      const int st = warp == 1 ? 0 : 1;
       const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(kAccCols >> 3) << 17) |
                              (static_cast<uint32_t>(kBlockN >> 4) << 24);
-      for (int i = st; i < total && st < streams; i += streams) {
+      for (int i = 0; i < total; ++i) {
         const int s = i % kStages;
         CB200_TRACE(1, i, 0);
         if (!mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, &g_i8_status, (3 << 8) | 2)) break;
@@ -386,14 +405,12 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
         tc_fence_after();
         const int pass = i / kblocks;
         const int kb = i % kblocks;
-        // the first block this stream sees in a pass overwrites its accumulator
-        const int kb_first = ((st - pass * kblocks) % streams + streams) % streams;
-        const uint32_t d = tmem_base + st * stream_cols + pass * kAccCols;
+        const uint32_t d = tmem_base + pass * kAccCols;
         const uint32_t w_base = smem_u32(s_w + s * kWBytes);
         const uint32_t x_base = smem_u32(s_x + s * kXBytes);
 #pragma unroll
         for (int j = 0; j < kBlockK / 32; ++j)   // 32 bytes of k per instruction inside the 128-byte swizzle span
-          tc_mma_i8_ss(d, smem_desc_sw128(w_base + j * 32), smem_desc_sw128(x_base + j * 32), idesc, (kb != kb_first || j > 0) ? 1u : 0u);
+          tc_mma_i8_ss(d, smem_desc_sw128(w_base + j * 32), smem_desc_sw128(x_base + j * 32), idesc, (kb > 0 || j > 0) ? 1u : 0u);
         CB200_TRACE(1, i, 2);
         tc_commit(smem_u32(&empty[s]));
         CB200_TRACE(1, i, 3);
@@ -405,11 +422,14 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
     const int q = warp & 3;
     const int r = q * 32 + lane;                 // weight row of the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    bool ok = mbar_wait(smem_u32(acc_full), 0, &g_i8_status, (3 << 8) | 3);
-    tc_fence_after();
-    if (threadIdx.x == 64) CB200_TRACE(3, 0, 2);
     const int n_out_idx = n0 + r;
-    const bool store = ok && n_out_idx < p.n_out;
+    __half* y = static_cast<__half*>(p.y);
+    const __half* res = static_cast<const __half*>(p.residual);
+    // everything the epilogue needs from global memory is fetched while the main loop runs
+    if (threadIdx.x - 64 < MP) {
+      s_sx[threadIdx.x - 64] = p.sx[threadIdx.x - 64];
+      s_qsum[threadIdx.x - 64] = p.qsum[threadIdx.x - 64];
+    }
     float scale[2] = {0.f, 0.f}, zero[2] = {128.f, 128.f};
     for (int pass = 0; pass < passes; ++pass) {
       const int n = n0 + pass * (p.N / 2) + r;
@@ -419,98 +439,101 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
         if (p.zero_points) zero[pass] = p.zero_points[n];
       }
     }
-    __half* y = static_cast<__half*>(p.y);
-    const __half* res = static_cast<const __half*>(p.residual);
-    if (split > 1) {
-      // All-to-all over the cluster: rank j finishes batch rows [j*MS, (j+1)*MS). Every rank sends its
-      // partial sums for those rows to rank j's buffer, stored per (sender, weight row, accumulator) as
-      // [MS high words | MS low words], so both directions move 16 bytes at a time.
-      constexpr int MS = MP / SPLIT;
-      constexpr int W = 2 * MS;
-      const int row_words = passes * W;
-      cluster_sync_all();                            // #1: every ring of the cluster has drained
-      if (threadIdx.x == 64) CB200_TRACE(3, 0, 3);
-      for (int ah = 0; ah < passes * 2; ++ah) {      // accumulator a = ah / 2, half h = ah % 2 (0 high, 1 low)
-        uint32_t acc[MP];
+    float res_v[MS];
+#pragma unroll
+    for (int j = 0; j < MS; ++j) {
+      const int m = krank * MS + j;
+      res_v[j] = (split > 1 && p.epilogue == CACHEIR_B200_EPI_RESIDUAL && m < p.M && n_out_idx < p.n_out)
+                     ? __half2float(res[static_cast<size_t>(m) * p.n_out + n_out_idx]) : 0.f;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps: s_sx / s_qsum are in place
+    bool ok = mbar_wait(smem_u32(acc_full), 0, &g_i8_status, (3 << 8) | 3);
+    tc_fence_after();
+    if (threadIdx.x == 64) CB200_TRACE(3, 0, 2);
+    const bool store = ok && n_out_idx < p.n_out;
+    if constexpr (SPLIT > 1) {
+      // All-to-all over the cluster. Each rank lays its partial sums out per destination in its own
+      // drained ring, one bulk copy per destination moves a slot into that rank's exchange buffer and
+      // signals its barrier; the sums are integers, so the order of addition cannot matter.
+      constexpr int G = MS >= 4 ? 4 : 2;
+      {
+        uint32_t acc[2 * MP];
         if (total > 0) {
 #pragma unroll
-          for (int c0 = 0; c0 < MP; c0 += 8) tc_ld_x8(tmem_base + lane_addr + (ah >> 1) * kAccCols + (ah & 1) * MP + c0,
-                                                      reinterpret_cast<uint32_t(&)[8]>(acc[c0]));
+          for (int c0 = 0; c0 < 2 * MP; c0 += 8) tc_ld_x8(tmem_base + lane_addr + c0, reinterpret_cast<uint32_t(&)[8]>(acc[c0]));
           tc_wait_ld();
-          if (streams == 2) {
-#pragma unroll
-            for (int c0 = 0; c0 < MP; c0 += 8) {
-              uint32_t other[8];
-              tc_ld_x8(tmem_base + lane_addr + stream_cols + (ah >> 1) * kAccCols + (ah & 1) * MP + c0, other);
-              tc_wait_ld();
-#pragma unroll
-              for (int j = 0; j < 8; ++j) acc[c0 + j] += other[j];
-            }
-          }
         } else {
 #pragma unroll
-          for (int c = 0; c < MP; ++c) acc[c] = 0u;
+          for (int c = 0; c < 2 * MP; ++c) acc[c] = 0u;
         }
 #pragma unroll
         for (int dest = 0; dest < SPLIT; ++dest) {
-          const uint32_t dst = smem_u32(s_partial + (static_cast<size_t>(krank) * kBlockN + r) * row_words + (ah >> 1) * W + (ah & 1) * MS);
-          if constexpr (MS >= 4) {
+          int32_t* row = s_stage + (static_cast<size_t>(dest) * kBlockN + r) * W;
 #pragma unroll
-            for (int u = 0; u < MS; u += 4) {
-              const uint32_t v[4] = {acc[dest * MS + u], acc[dest * MS + u + 1], acc[dest * MS + u + 2], acc[dest * MS + u + 3]};
-              st_cluster_v4(dst + u * 4, dest, v);
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int u = 0; u < MS; u += G) {
+              const int c = h * MP + dest * MS + u;
+              if constexpr (G == 4) *reinterpret_cast<uint4*>(row + h * MS + u) = make_uint4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
+              else *reinterpret_cast<uint2*>(row + h * MS + u) = make_uint2(acc[c], acc[c + 1]);
             }
-          } else {
-            const uint32_t v[4] = {acc[dest * MS], acc[dest * MS + 1], 0u, 0u};
-            st_cluster_v2(dst, dest, v);
           }
         }
       }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the bulk copies below read what was just stored
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) CB200_TRACE(3, 0, 3);
+      cluster_wait();                                // phase A: every rank of the cluster runs and has armed its barrier
+      if (threadIdx.x == 64 && ok) {
+#pragma unroll 1
+        for (int dd = 1; dd < SPLIT; ++dd) {
+          const int dest = (krank + dd) % SPLIT;
+          bulk_copy_to_rank(smem_u32(reinterpret_cast<uint8_t*>(s_xch) + krank * kSlotBytes),
+                            smem_u32(reinterpret_cast<uint8_t*>(s_stage) + dest * kSlotBytes), kSlotBytes,
+                            smem_u32(xch_bar), dest);
+        }
+      }
       if (threadIdx.x == 64) CB200_TRACE(3, 1, 0);
-      cluster_sync_all();                            // #2: all partials have arrived
+      ok = mbar_wait(smem_u32(xch_bar), 0, &g_i8_status, (3 << 8) | 4) && ok;
       if (threadIdx.x == 64) CB200_TRACE(3, 1, 1);
-      constexpr int G = MS >= 4 ? 4 : 2;
+      cluster_arrive();                              // phase B: nothing more will be written into this CTA
 #pragma unroll 1
       for (int u0 = 0; u0 < MS; u0 += G) {
-        int32_t sum[4][4];                           // [accumulator*2 + half][word]
+        int32_t sum[2][4];                           // [half][word]
 #pragma unroll
-        for (int ah = 0; ah < 4; ++ah)
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) sum[ah][j] = 0;
+          for (int j = 0; j < 4; ++j) sum[h][j] = 0;
 #pragma unroll
         for (int k = 0; k < SPLIT; ++k) {            // integer sums: exact, order-free
-          const int32_t* src = s_partial + (static_cast<size_t>(k) * kBlockN + r) * row_words + u0;
+          const int32_t* src = (k == krank ? s_stage : s_xch) + (static_cast<size_t>(k) * kBlockN + r) * W + u0;
 #pragma unroll
-          for (int ah = 0; ah < 4; ++ah) {
-            if (ah < passes * 2) {
-              if constexpr (G == 4) {
-                const int4 t = *reinterpret_cast<const int4*>(src + (ah >> 1) * W + (ah & 1) * MS);
-                sum[ah][0] += t.x; sum[ah][1] += t.y; sum[ah][2] += t.z; sum[ah][3] += t.w;
-              } else {
-                const int2 t = *reinterpret_cast<const int2*>(src + (ah >> 1) * W + (ah & 1) * MS);
-                sum[ah][0] += t.x; sum[ah][1] += t.y;
-              }
+          for (int h = 0; h < 2; ++h) {
+            if constexpr (G == 4) {
+              const int4 t = *reinterpret_cast<const int4*>(src + h * MS);
+              sum[h][0] += t.x; sum[h][1] += t.y; sum[h][2] += t.z; sum[h][3] += t.w;
+            } else {
+              const int2 t = *reinterpret_cast<const int2*>(src + h * MS);
+              sum[h][0] += t.x; sum[h][1] += t.y;
             }
           }
         }
 #pragma unroll
         for (int j = 0; j < G; ++j) {
           const int m = krank * MS + u0 + j;
-          if (m < p.M && store) {
-            const float sxm = s_sx[m];
-            const int qs = s_qsum[m];
-            float out = recombine(sum[0][j], sum[1][j], zero[0], qs) * (scale[0] * sxm);
-            const size_t o = static_cast<size_t>(m) * p.n_out + n_out_idx;
-            if (swiglu) {
-              const float u = recombine(sum[2][j], sum[3][j], zero[1], qs) * (scale[1] * sxm);
-              out = (out / (1.f + __expf(-out))) * u;
-            } else if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
-              out += __half2float(res[o]);
+          if (m < p.M && store && ok) {
+            float out = recombine(sum[0][j], sum[1][j], zero[0], s_qsum[m]) * (scale[0] * s_sx[m]);
+            if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
+              float rv = 0.f;
+#pragma unroll
+              for (int jj = 0; jj < MS; ++jj) rv = (jj == u0 + j) ? res_v[jj] : rv;   // register select, no local array
+              out += rv;
             }
-            y[o] = __float2half_rn(out);
+            y[static_cast<size_t>(m) * p.n_out + n_out_idx] = __float2half_rn(out);
           }
         }
       }
+      cluster_wait();                                // phase B: every rank has received everything, this CTA's copies included
     } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < MP; c0 += 8) {
@@ -520,20 +543,12 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
           if (pass < passes && total > 0) {
             tc_ld_x8(tmem_base + lane_addr + pass * kAccCols + c0, hi[pass]);
             tc_ld_x8(tmem_base + lane_addr + pass * kAccCols + MP + c0, lo[pass]);
-            tc_wait_ld();
-            if (streams == 2) {
-              uint32_t h2[8], l2[8];
-              tc_ld_x8(tmem_base + lane_addr + stream_cols + pass * kAccCols + c0, h2);
-              tc_ld_x8(tmem_base + lane_addr + stream_cols + pass * kAccCols + MP + c0, l2);
-              tc_wait_ld();
-#pragma unroll
-              for (int j = 0; j < 8; ++j) { hi[pass][j] += h2[j]; lo[pass][j] += l2[j]; }
-            }
           } else {
 #pragma unroll
             for (int j = 0; j < 8; ++j) { hi[pass][j] = 0u; lo[pass][j] = 0u; }
           }
         }
+        tc_wait_ld();
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int m = c0 + j;
@@ -554,10 +569,11 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
       }
     }
   }
-  if ((warp < 2 || warp == 6) && split > 1) {   // warps without an epilogue still take part in the two cluster barriers
+  if (warp < 2 && split > 1) {   // warps without an epilogue still take part in both phases of the cluster barrier
     __syncwarp();
-    cluster_sync_all();
-    cluster_sync_all();
+    cluster_wait();
+    cluster_arrive();
+    cluster_wait();
   }
   if (threadIdx.x == 64) CB200_TRACE(3, 1, 2);
   tc_fence_before();
@@ -593,7 +609,9 @@ int launch_quantize(const __half* x, long long x_stride, int M, int K, int mp, v
 
 template <int MP, int SPLIT>
 cudaError_t launch_i8_split(const CUtensorMap& tmap_w, const I8Params& p, int n_tiles, cudaStream_t stream) {
-  constexpr size_t kSmem = 1024 + static_cast<size_t>(num_stages(MP)) * stage_bytes(MP) + 1024;
+  constexpr size_t kSmem = 1024 + static_cast<size_t>(num_stages(MP, SPLIT)) * stage_bytes(MP) + exchange_bytes(MP, SPLIT) + 1024;
+  static_assert(num_stages(MP, SPLIT) >= 2, "the pipeline needs at least two stages");
+  static_assert(num_stages(MP, SPLIT) * stage_bytes(MP) >= exchange_bytes(MP, SPLIT), "outgoing partials are staged in the drained ring");
   auto kern = qgemm_i8_kernel<MP, SPLIT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
   if (e != cudaSuccess) return e;
