@@ -360,23 +360,31 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
   };
   const int pre = total < kStages ? total : kStages;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
-    mbar_init(smem_u32(acc_full), 1);
-    mbar_init(smem_u32(xch_bar), 1);
-    mbar_fence_init();
-    if (split > 1) mbar_expect_tx(smem_u32(xch_bar), (split - 1) * kSlotBytes);
-    // the first ring of requests leaves before the rest of the CTA has finished setting up
-    for (int i = 0; i < pre; ++i) load_stage(i, i);
-    CB200_TRACE(0, 0, 2);
+  // Set-up: thread 0 initialises the barriers and goes straight on to request the first ring of
+  // tiles; warp 0 only arrives at the CTA-wide barrier below, the other warps wait on it.
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
+      mbar_init(smem_u32(acc_full), 1);
+      mbar_init(smem_u32(xch_bar), 1);
+      mbar_fence_init();                       // visible to the copy engine and to the other CTAs of the cluster
+      if (split > 1) mbar_expect_tx(smem_u32(xch_bar), (split - 1) * kSlotBytes);
+    }
+    __syncwarp();
+    asm volatile("bar.arrive 2, %0;" ::"n"(kThreads) : "memory");
+    if (split > 1) cluster_arrive_relaxed();   // phase A: this CTA runs and its exchange barrier exists
+    if (lane == 0) {
+      for (int i = 0; i < pre; ++i) load_stage(i, i);
+      CB200_TRACE(0, 0, 2);
+    }
+  } else {
+    if (warp == 1) tc_alloc(smem_u32(tmem_slot), kTmemCols);
+    if (split > 1) cluster_arrive_relaxed();
+    tc_fence_before();
+    asm volatile("bar.sync 2, %0;" ::"n"(kThreads) : "memory");
+    tc_fence_after();
   }
-  __syncwarp();
-  if (split > 1) cluster_arrive();          // phase A: this CTA runs and its exchange barrier is armed
-  if (warp == 1) tc_alloc(smem_u32(tmem_slot), kTmemCols);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = warp == 0 ? 0u : *tmem_slot;
   if (threadIdx.x == 64) CB200_TRACE(3, 0, 1);
 
   if (warp == 0) {
@@ -484,19 +492,17 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 64) CB200_TRACE(3, 0, 3);
       cluster_wait();                                // phase A: every rank of the cluster runs and has armed its barrier
-      if (threadIdx.x == 64 && ok) {
-#pragma unroll 1
-        for (int dd = 1; dd < SPLIT; ++dd) {
-          const int dest = (krank + dd) % SPLIT;
-          bulk_copy_to_rank(smem_u32(reinterpret_cast<uint8_t*>(s_xch) + krank * kSlotBytes),
-                            smem_u32(reinterpret_cast<uint8_t*>(s_stage) + dest * kSlotBytes), kSlotBytes,
-                            smem_u32(xch_bar), dest);
-        }
+      if (warp == 2 && lane < SPLIT - 1 && ok) {     // one lane per destination
+        const int dest = (krank + 1 + lane) % SPLIT;
+        bulk_copy_to_rank(smem_u32(reinterpret_cast<uint8_t*>(s_xch) + krank * kSlotBytes),
+                          smem_u32(reinterpret_cast<uint8_t*>(s_stage) + dest * kSlotBytes), kSlotBytes,
+                          smem_u32(xch_bar), dest);
       }
+      __syncwarp();
       if (threadIdx.x == 64) CB200_TRACE(3, 1, 0);
       ok = mbar_wait(smem_u32(xch_bar), 0, &g_i8_status, (3 << 8) | 4) && ok;
       if (threadIdx.x == 64) CB200_TRACE(3, 1, 1);
-      cluster_arrive();                              // phase B: nothing more will be written into this CTA
+      cluster_arrive_relaxed();                      // phase B: nothing more will be written into this CTA
 #pragma unroll 1
       for (int u0 = 0; u0 < MS; u0 += G) {
         int32_t sum[2][4];                           // [half][word]
@@ -572,7 +578,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
   if (warp < 2 && split > 1) {   // warps without an epilogue still take part in both phases of the cluster barrier
     __syncwarp();
     cluster_wait();
-    cluster_arrive();
+    cluster_arrive_relaxed();
     cluster_wait();
   }
   if (threadIdx.x == 64) CB200_TRACE(3, 1, 2);

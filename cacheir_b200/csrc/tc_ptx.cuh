@@ -90,6 +90,8 @@ __device__ __forceinline__ void cluster_sync_all() {
 // The two halves of the cluster barrier, for work placed between arrival and wait. Every thread of
 // the cluster executes arrive, wait, arrive, wait ... in that order, warp-converged.
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+// Arrival that orders no memory: for phases that only say "this CTA has reached this point".
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // Bulk copy from this CTA's shared memory into the same offsets of CTA `rank` of the cluster;
 // completion is counted in bytes on that CTA's barrier at offset `bar`.
