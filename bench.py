@@ -550,6 +550,8 @@ def main() -> None:
         import torch.distributed as dist  # type: ignore[no-redef]
         dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
 
+    from cacheir_b200.sharding import max_over_ranks
+
     e2e_steps = max(4, args.e2e_steps)
     extra = warmup + args.steps + e2e_steps + 3 + 48
     rt, _ = build_runtime(cfg, local_rank, extra)
@@ -579,10 +581,7 @@ def main() -> None:
     clocks = sampler.stop()
     last = [int(t) for t in toks[-1].tolist()]
     ctx_mid = cfg["ctx"] + warmup + args.steps // 2
-    if dist is not None:
-        t = torch.tensor([elapsed_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_s = float(t.item())
+    elapsed_s = max_over_ranks(elapsed_s, torch.device("cuda", local_rank))
     tokens_total = world * cfg["batch"] * args.steps
     value = tokens_total / elapsed_s
 
@@ -605,10 +604,7 @@ def main() -> None:
         d2h += cfg["batch"] * 8
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
-    if dist is not None:
-        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    e2e_s = max_over_ranks(e2e_s, torch.device("cuda", local_rank))
     e2e_value = world * cfg["batch"] * e2e_steps / e2e_s
 
     # ---- per-kernel roofline (rank 0 reports) -------------------------------------------
