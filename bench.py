@@ -36,6 +36,10 @@ import threading
 import time
 from pathlib import Path
 
+if "reference" in sys.argv and "TORCHELASTIC_RUN_ID" in os.environ and os.environ.get("OMP_NUM_THREADS") == "1":
+    # torchrun defaults every rank to one OpenMP thread; the CPU arm runs on rank 0 alone with all host cores
+    del os.environ["OMP_NUM_THREADS"]
+
 import numpy as np
 
 ROOT = Path(__file__).resolve().parent

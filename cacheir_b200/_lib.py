@@ -45,8 +45,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "cacheir_b200_rms_norm_quantize": (
         c_int, [c_void_p] * 5 + [c_int, c_int, c_float, c_int, c_void_p, c_size_t, c_void_p]),
     "cacheir_b200_pack_tiled_bytes": (c_size_t, [c_int, c_int, c_int]),
-    "cacheir_b200_pack_relayout": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
-    "cacheir_b200_pack_unrelayout": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "cacheir_b200_pack_relayout": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "cacheir_b200_pack_unrelayout": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "cacheir_b200_device_status": (c_int, [c_int]),
     "cacheir_b200_pack_rows": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_void_p]),
     "cacheir_b200_dequantize_rows": (c_int, [c_void_p] * 4 + [c_int, c_int, c_int, c_int, c_void_p]),

@@ -103,7 +103,8 @@ __global__ void dequantize_rows_kernel(const uint8_t* __restrict__ packed, const
 // zero), so it is exactly invertible.
 template <bool INVERSE>
 __global__ void __launch_bounds__(256)
-relayout_tiles_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int N, int row_bytes, int tile_bytes_per_row) {
+relayout_tiles_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int N, int row_bytes, int tile_bytes_per_row,
+                      int paired) {
   const int kb = blockIdx.x;
   const int band = blockIdx.y;
   const int kblocks = row_bytes / tile_bytes_per_row;
@@ -111,7 +112,8 @@ relayout_tiles_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst
   for (int idx = threadIdx.x; idx < 128 * chunks_per_row; idx += 256) {
     const int r = idx / chunks_per_row;
     const int c = idx % chunks_per_row;
-    const int n = band * 128 + r;
+    // paired: tile rows 0..63 are rows 64*band.. of the first half of W, rows 64..127 the same rows of the second half
+    const int n = paired ? (r < 64 ? band * 64 + r : N / 2 + band * 64 + (r - 64)) : band * 128 + r;
     const int cs = chunks_per_row == 8 ? (c ^ (r & 7)) : (c ^ ((r >> 1) & 3));
     const size_t tiled_off = ((static_cast<size_t>(band) * kblocks + kb) * 128 + r) * tile_bytes_per_row + cs * 16;
     const size_t rows_off = static_cast<size_t>(n) * row_bytes + static_cast<size_t>(kb) * tile_bytes_per_row + c * 16;
@@ -136,25 +138,26 @@ extern "C" size_t cacheir_b200_pack_tiled_bytes(int N, int K, int bits) {
   return static_cast<size_t>((N + 127) / 128) * 128 * row_bytes;
 }
 
-static int relayout_impl(const uint8_t* src, uint8_t* dst, int N, int K, int bits, bool inverse, void* stream) {
+static int relayout_impl(const uint8_t* src, uint8_t* dst, int N, int K, int bits, int paired, bool inverse, void* stream) {
   if (N <= 0 || K <= 0) return 0;
   if (!src || !dst || (bits != 4 && bits != 8) || K % 128 != 0) return CACHEIR_B200_EINVAL;
+  if (paired && N % 128 != 0) return CACHEIR_B200_EINVAL;   // both halves must be whole 64-row groups
   if (!aligned_to(src, 16) || !aligned_to(dst, 16)) return CACHEIR_B200_EALIGN;
   const int row_bytes = bits == 8 ? K : K / 2;
   const int tile_bytes_per_row = bits == 8 ? 128 : 64;
   const dim3 grid(row_bytes / tile_bytes_per_row, (N + 127) / 128);
   if (grid.y > 65535) return CACHEIR_B200_ELIMIT;
-  if (inverse) relayout_tiles_kernel<true><<<grid, 256, 0, as_stream(stream)>>>(src, dst, N, row_bytes, tile_bytes_per_row);
-  else relayout_tiles_kernel<false><<<grid, 256, 0, as_stream(stream)>>>(src, dst, N, row_bytes, tile_bytes_per_row);
+  if (inverse) relayout_tiles_kernel<true><<<grid, 256, 0, as_stream(stream)>>>(src, dst, N, row_bytes, tile_bytes_per_row, paired);
+  else relayout_tiles_kernel<false><<<grid, 256, 0, as_stream(stream)>>>(src, dst, N, row_bytes, tile_bytes_per_row, paired);
   return launch_status();
 }
 
-extern "C" int cacheir_b200_pack_relayout(const uint8_t* packed, uint8_t* tiled, int N, int K, int bits, void* stream) {
-  return relayout_impl(packed, tiled, N, K, bits, false, stream);
+extern "C" int cacheir_b200_pack_relayout(const uint8_t* packed, uint8_t* tiled, int N, int K, int bits, int paired, void* stream) {
+  return relayout_impl(packed, tiled, N, K, bits, paired != 0, false, stream);
 }
 
-extern "C" int cacheir_b200_pack_unrelayout(const uint8_t* tiled, uint8_t* packed, int N, int K, int bits, void* stream) {
-  return relayout_impl(tiled, packed, N, K, bits, true, stream);
+extern "C" int cacheir_b200_pack_unrelayout(const uint8_t* tiled, uint8_t* packed, int N, int K, int bits, int paired, void* stream) {
+  return relayout_impl(tiled, packed, N, K, bits, paired != 0, true, stream);
 }
 
 extern "C" int cacheir_b200_pack_rows(const float* weight, uint8_t* packed, float* scales,

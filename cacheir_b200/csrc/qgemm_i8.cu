@@ -33,7 +33,6 @@ using namespace ptx;
 constexpr int kBlockN = 128;          // weight rows per CTA (UMMA M)
 constexpr int kBlockK = 128;          // bytes of a weight row per stage
 constexpr int kThreads = 192;         // producer, MMA issuer, four epilogue warps
-constexpr int kTmemCols = 256;
 constexpr int kCtaBudget = 104 * 1024;   // ring + exchange buffer; two CTAs per SM: one issues MMAs while the other waits on a barrier
 constexpr int kCtaBudgetWide = 200 * 1024;   // split-K with more than 32 batch rows: one CTA per SM
 constexpr int kMaxSplitK = 8;
@@ -292,6 +291,10 @@ struct I8Params {
   int split_k;
   int tiled;        // weights in 128x128 tile order: tile (band, kb) starts at row (band*KB + kb)*128 of a 128-byte-wide tensor
 };
+// With the SwiGLU epilogue a tile pairs 64 gate rows (tile rows 0..63, weight rows 64t..64t+63) with the
+// 64 up rows of the same output columns (tile rows 64..127, weight rows N/2+64t..): one pass, one
+// accumulator, and twice as many CTAs as whole-half tiles would give.
+constexpr int kPairRows = 64;
 
 // y value from the exact integer sums: (256*hi + lo - zero*qsum) as float. Integer zero points (what the
 // reference packer produces) are handled in 64-bit integers, anything else in double precision.
@@ -310,6 +313,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
   constexpr int kWBytes = kBlockN * kBlockK;          // 16 KB of codes per stage
   constexpr int kXBytes = 2 * MP * kBlockK;           // [hi; lo] rows per stage
   constexpr int kAccCols = 2 * MP;                    // one accumulator: MP high + MP low columns
+  constexpr int kTmemCols = kAccCols;                 // 32, 64 or 128: a power of two, as the allocator wants
   // split-K exchange: rank j finishes batch rows [j*MS, (j+1)*MS); a partial row for one destination is
   // W words: [MS high | MS low]
   constexpr int MS = MP / SPLIT;
@@ -335,26 +339,26 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
   const int lane = threadIdx.x & 31;
   if (threadIdx.x == 64) CB200_TRACE(3, 0, 0);
   const bool swiglu = p.epilogue == CACHEIR_B200_EPI_SWIGLU;
-  const int passes = swiglu ? 2 : 1;
   constexpr int split = SPLIT;
   const int krank = split > 1 ? static_cast<int>(cluster_ctarank()) : 0;
   const int kblocks_all = p.K / kBlockK;
   const int kb_begin = (kblocks_all * krank) / split;
   const int kb_end = (kblocks_all * (krank + 1)) / split;
   const int kblocks = kb_end - kb_begin;
-  const int total = kblocks * passes;
-  const int n0 = blockIdx.x * kBlockN;
+  const int total = kblocks;
+  const int n0 = blockIdx.x * (swiglu ? kPairRows : kBlockN);   // first output column of this tile
 
   auto load_stage = [&](int i, int s) {
-    const int pass = i / kblocks;
-    const int kb = kb_begin + i % kblocks;
+    const int kb = kb_begin + i;
     const uint32_t bar = smem_u32(&full[s]);
     mbar_expect_tx(bar, kWBytes + kXBytes);
     if (p.tiled) {   // one contiguous, pre-swizzled 16 KB tile
-      const size_t band = blockIdx.x + pass * (p.N / 2 / kBlockN);
-      bulk_load(smem_u32(s_w + s * kWBytes), p.w_tiled + (band * kblocks_all + kb) * kWBytes, kWBytes, bar);
+      bulk_load(smem_u32(s_w + s * kWBytes), p.w_tiled + (static_cast<size_t>(blockIdx.x) * kblocks_all + kb) * kWBytes, kWBytes, bar);
+    } else if (swiglu) {   // the map's box is 64 rows: gate rows, then the up rows of the same columns
+      tma_load_2d(smem_u32(s_w + s * kWBytes), &tmap_w, bar, kb * kBlockK, n0);
+      tma_load_2d(smem_u32(s_w + s * kWBytes + kPairRows * kBlockK), &tmap_w, bar, kb * kBlockK, p.N / 2 + n0);
     } else {
-      tma_load_2d(smem_u32(s_w + s * kWBytes), &tmap_w, bar, kb * kBlockK, n0 + pass * (p.N / 2));
+      tma_load_2d(smem_u32(s_w + s * kWBytes), &tmap_w, bar, kb * kBlockK, n0);
     }
     bulk_load(smem_u32(s_x + s * kXBytes), p.x_planes + static_cast<size_t>(kb) * kXBytes, kXBytes, bar);
   };
@@ -411,14 +415,12 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
         if (!mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, &g_i8_status, (3 << 8) | 2)) break;
         CB200_TRACE(1, i, 1);
         tc_fence_after();
-        const int pass = i / kblocks;
-        const int kb = i % kblocks;
-        const uint32_t d = tmem_base + pass * kAccCols;
+        const uint32_t d = tmem_base;
         const uint32_t w_base = smem_u32(s_w + s * kWBytes);
         const uint32_t x_base = smem_u32(s_x + s * kXBytes);
 #pragma unroll
         for (int j = 0; j < kBlockK / 32; ++j)   // 32 bytes of k per instruction inside the 128-byte swizzle span
-          tc_mma_i8_ss(d, smem_desc_sw128(w_base + j * 32), smem_desc_sw128(x_base + j * 32), idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          tc_mma_i8_ss(d, smem_desc_sw128(w_base + j * 32), smem_desc_sw128(x_base + j * 32), idesc, (i > 0 || j > 0) ? 1u : 0u);
         CB200_TRACE(1, i, 2);
         tc_commit(smem_u32(&empty[s]));
         CB200_TRACE(1, i, 3);
@@ -430,7 +432,10 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
     const int q = warp & 3;
     const int r = q * 32 + lane;                 // weight row of the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    const int n_out_idx = n0 + r;
+    // output column and weight row of this thread's accumulator row
+    const bool is_up = swiglu && r >= kPairRows;
+    const int n_out_idx = swiglu ? n0 + (r & (kPairRows - 1)) : n0 + r;
+    const int w_row = is_up ? p.N / 2 + n_out_idx : n_out_idx;
     __half* y = static_cast<__half*>(p.y);
     const __half* res = static_cast<const __half*>(p.residual);
     // everything the epilogue needs from global memory is fetched while the main loop runs
@@ -438,14 +443,11 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
       s_sx[threadIdx.x - 64] = p.sx[threadIdx.x - 64];
       s_qsum[threadIdx.x - 64] = p.qsum[threadIdx.x - 64];
     }
-    float scale[2] = {0.f, 0.f}, zero[2] = {128.f, 128.f};
-    for (int pass = 0; pass < passes; ++pass) {
-      const int n = n0 + pass * (p.N / 2) + r;
-      if (n < p.N) {
-        scale[pass] = p.scale_dtype == CACHEIR_B200_F16 ? __half2float(static_cast<const __half*>(p.scales)[n])
-                                                        : static_cast<const float*>(p.scales)[n];
-        if (p.zero_points) zero[pass] = p.zero_points[n];
-      }
+    float scale = 0.f, zero = 128.f;
+    if (n_out_idx < p.n_out) {
+      scale = p.scale_dtype == CACHEIR_B200_F16 ? __half2float(static_cast<const __half*>(p.scales)[w_row])
+                                                : static_cast<const float*>(p.scales)[w_row];
+      if (p.zero_points) zero = p.zero_points[w_row];
     }
     float res_v[MS];
 #pragma unroll
@@ -528,7 +530,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
         for (int j = 0; j < G; ++j) {
           const int m = krank * MS + u0 + j;
           if (m < p.M && store && ok) {
-            float out = recombine(sum[0][j], sum[1][j], zero[0], s_qsum[m]) * (scale[0] * s_sx[m]);
+            float out = recombine(sum[0][j], sum[1][j], zero, s_qsum[m]) * (scale * s_sx[m]);
             if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
               float rv = 0.f;
 #pragma unroll
@@ -540,35 +542,58 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
         }
       }
       cluster_wait();                                // phase B: every rank has received everything, this CTA's copies included
+    } else if (swiglu) {
+      // gate rows keep their values in registers, up rows hand theirs over through the drained ring
+      float* s_up = reinterpret_cast<float*>(smem);          // [MP][64]
+      float g[MP];
+#pragma unroll
+      for (int c0 = 0; c0 < MP; c0 += 8) {
+        uint32_t hi[8], lo[8];
+        if (total > 0) {
+          tc_ld_x8(tmem_base + lane_addr + c0, hi);
+          tc_ld_x8(tmem_base + lane_addr + MP + c0, lo);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { hi[j] = 0u; lo[j] = 0u; }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int m = c0 + j;
+          const float v = recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, s_qsum[m]) * (scale * s_sx[m]);
+          g[m] = v;
+          if (is_up) s_up[m * kPairRows + (r - kPairRows)] = v;
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!is_up && store) {
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+          if (m < p.M) {
+            const float u = s_up[m * kPairRows + r];
+            y[static_cast<size_t>(m) * p.n_out + n_out_idx] = __float2half_rn((g[m] / (1.f + __expf(-g[m]))) * u);
+          }
+        }
+      }
     } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < MP; c0 += 8) {
-        uint32_t hi[2][8], lo[2][8];
+        uint32_t hi[8], lo[8];
+        if (total > 0) {
+          tc_ld_x8(tmem_base + lane_addr + c0, hi);
+          tc_ld_x8(tmem_base + lane_addr + MP + c0, lo);
+          tc_wait_ld();
+        } else {
 #pragma unroll
-        for (int pass = 0; pass < 2; ++pass) {
-          if (pass < passes && total > 0) {
-            tc_ld_x8(tmem_base + lane_addr + pass * kAccCols + c0, hi[pass]);
-            tc_ld_x8(tmem_base + lane_addr + pass * kAccCols + MP + c0, lo[pass]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) { hi[pass][j] = 0u; lo[pass][j] = 0u; }
-          }
+          for (int j = 0; j < 8; ++j) { hi[j] = 0u; lo[j] = 0u; }
         }
-        tc_wait_ld();
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int m = c0 + j;
           if (m < p.M && store) {
-            const float sxm = s_sx[m];
-            const int qs = s_qsum[m];
-            float out = recombine(static_cast<int32_t>(hi[0][j]), static_cast<int32_t>(lo[0][j]), zero[0], qs) * (scale[0] * sxm);
+            float out = recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, s_qsum[m]) * (scale * s_sx[m]);
             const size_t o = static_cast<size_t>(m) * p.n_out + n_out_idx;
-            if (swiglu) {
-              const float u = recombine(static_cast<int32_t>(hi[1][j]), static_cast<int32_t>(lo[1][j]), zero[1], qs) * (scale[1] * sxm);
-              out = (out / (1.f + __expf(-out))) * u;
-            } else if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
-              out += __half2float(res[o]);
-            }
+            if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) out += __half2float(res[o]);
             y[o] = __float2half_rn(out);
           }
         }
@@ -647,10 +672,13 @@ int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
   }
 
   CUtensorMap tmap_w;
+  // (the tiled layout is fetched with plain bulk copies; its map is only a valid placeholder)
+  const bool swiglu = q.epilogue == CACHEIR_B200_EPI_SWIGLU;
   const uint64_t bands = static_cast<uint64_t>((q.N + kBlockN - 1) / kBlockN);
   const bool w_ok = q.tiled
       ? encode_u8_rows_sw128(&tmap_w, q.packed, kBlockK, bands * (q.K / kBlockK) * kBlockN, kBlockK, kBlockN)
-      : encode_u8_rows_sw128(&tmap_w, q.packed, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.N), static_cast<uint64_t>(q.K), kBlockN);
+      : encode_u8_rows_sw128(&tmap_w, q.packed, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.N), static_cast<uint64_t>(q.K),
+                             swiglu ? kPairRows : kBlockN);
   if (!w_ok) return CACHEIR_B200_EUNSUPPORTED;
   I8Params p{};
   p.scales = q.scales; p.zero_points = q.zero_points; p.residual = q.residual; p.y = q.y;
@@ -659,7 +687,7 @@ int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
   p.M = q.M; p.N = q.N; p.K = q.K;
   p.n_out = q.epilogue == CACHEIR_B200_EPI_SWIGLU ? q.N / 2 : q.N;
   p.scale_dtype = q.scale_dtype; p.epilogue = q.epilogue; p.tiled = q.tiled ? 1 : 0;
-  const int n_tiles = (p.n_out + kBlockN - 1) / kBlockN;
+  const int n_tiles = swiglu ? (p.n_out + kPairRows - 1) / kPairRows : (p.n_out + kBlockN - 1) / kBlockN;
   p.split_k = choose_split_k(n_tiles, q.K / kBlockK, q.epilogue, MP);
   cudaError_t e;
   switch (p.split_k) {
@@ -683,7 +711,8 @@ bool qgemm_i8_supported(const QGemvParams& q, const void* workspace, size_t work
   if (q.x_dtype != CACHEIR_B200_F16 || q.bits != 8 || q.group_size != 0) return false;
   if (q.M < 1 || q.M > 64) return false;
   if (q.K % kBlockK != 0 || q.K < kBlockK) return false;
-  if (q.epilogue == CACHEIR_B200_EPI_SWIGLU && (q.N / 2) % kBlockN != 0) return false;
+  if (q.epilogue == CACHEIR_B200_EPI_SWIGLU && ((q.N / 2) % kPairRows != 0 || (q.tiled && !q.paired))) return false;
+  if (q.paired && !(q.tiled && q.epilogue == CACHEIR_B200_EPI_SWIGLU)) return false;
   if (!workspace || workspace_bytes < qgemm_i8_workspace_bytes(q.M, q.K) || !aligned_to(workspace, 128)) return false;
   if (!aligned_to(q.packed, 16) || !aligned_to(q.x, 16) || (q.x_stride * 2) % 16 != 0) return false;
   return tensor_map_encoder() != nullptr;

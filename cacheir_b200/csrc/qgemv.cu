@@ -221,8 +221,11 @@ extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const vo
   p.x_dtype = x_dtype; p.scale_dtype = scale_dtype;
   p.x_stride = x_stride > 0 ? x_stride : K;
   p.epilogue = epilogue;
-  if (weight_layout < 0 || weight_layout > (CACHEIR_B200_LAYOUT_TILED | CACHEIR_B200_X_PREQUANTIZED)) return CACHEIR_B200_EINVAL;
+  if (weight_layout < 0 || weight_layout > (CACHEIR_B200_LAYOUT_TILED | CACHEIR_B200_X_PREQUANTIZED | CACHEIR_B200_LAYOUT_PAIRED))
+    return CACHEIR_B200_EINVAL;
   p.tiled = (weight_layout & CACHEIR_B200_LAYOUT_TILED) != 0;
+  p.paired = (weight_layout & CACHEIR_B200_LAYOUT_PAIRED) != 0;
+  if (p.paired && !(p.tiled && epilogue == CACHEIR_B200_EPI_SWIGLU)) return CACHEIR_B200_EINVAL;
   p.x_prequantized = (weight_layout & CACHEIR_B200_X_PREQUANTIZED) != 0;
   const size_t row_bytes = bits == 8 ? static_cast<size_t>(K)
                          : bits == 4 ? static_cast<size_t>((K + 1) / 2)
@@ -232,6 +235,7 @@ extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const vo
   cudaStream_t st = as_stream(stream);
   if (qgemm_i8_supported(p, workspace, workspace_bytes)) return launch_qgemm_i8(p, workspace, st);
   if (p.x_prequantized) return CACHEIR_B200_EINVAL;   // only the integer path can consume a quantized workspace
+  if (p.paired) return CACHEIR_B200_EUNSUPPORTED;     // only the integer tensor-core kernel reads paired tiles
   if (qgemm_tc_supported(p)) return launch_qgemm_tc(p, st);
   if (p.tiled) return CACHEIR_B200_EUNSUPPORTED;   // the tile order only exists for the tensor-core kernels
   return launch_qgemv_cuda_core(p, st);

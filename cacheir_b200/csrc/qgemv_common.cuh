@@ -21,6 +21,7 @@ struct QGemvParams {
   int epilogue;
   bool vector_ok;  // rows of x and of the packed weight can be read in 16-byte units
   bool tiled;      // codes are in the 128x128 tile order of cacheir_b200_pack_relayout
+  bool paired;     // tiled, and every tile pairs 64 rows of the first half of W with the matching 64 of the second half
   bool x_prequantized;  // the workspace already holds the integer form of x (see cacheir_b200_quantize_activations)
 };
 

@@ -107,7 +107,8 @@ def qgemv_workspace_bytes(m: int, k: int) -> int:
 def qgemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor | None, zero_points: torch.Tensor | None, *,
           bits: int, n: int, k: int, group_size: int = 0, epilogue: int = EPI_NONE,
           residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
-          workspace: torch.Tensor | None = None, tiled: bool = False, prequantized: bool = False) -> torch.Tensor:
+          workspace: torch.Tensor | None = None, tiled: bool = False, prequantized: bool = False,
+          paired: bool = False) -> torch.Tensor:
     """y[M, N_out] = x[M, K] . deq(W)[N, K]^T with the reference's pack format
     (bits 8/4; bits 0 = dense weights of x's dtype). x: [..., K] with dense rows."""
     _require_cuda(x, packed, scales, zero_points, residual, out)
@@ -148,7 +149,7 @@ def qgemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor | None, ze
         x2.data_ptr(), packed.data_ptr(), _ptr(scales), _ptr(zero_points), _ptr(residual), out.data_ptr(),
         m, n, k, bits, group_size, dtype_code(x.dtype),
         F16 if (scales is not None and scales.dtype == torch.float16) else F32,
-        x2.stride(0), epilogue, (1 if tiled else 0) | (2 if prequantized else 0), _ptr(workspace), ws_bytes, _stream()), "qgemv")
+        x2.stride(0), epilogue, (1 if tiled else 0) | (2 if prequantized else 0) | (4 if paired else 0), _ptr(workspace), ws_bytes, _stream()), "qgemv")
     return out
 
 
@@ -156,22 +157,23 @@ def pack_tiled_bytes(n: int, k: int, bits: int) -> int:
     return int(_lib.load().cacheir_b200_pack_tiled_bytes(int(n), int(k), int(bits)))
 
 
-def pack_relayout(packed: torch.Tensor, *, n: int, k: int, bits: int) -> torch.Tensor:
-    """Reference row-major codes -> the 128x128 tile order the tensor-core kernels stream (exactly invertible)."""
+def pack_relayout(packed: torch.Tensor, *, n: int, k: int, bits: int, paired: bool = False) -> torch.Tensor:
+    """Reference row-major codes -> the 128x128 tile order the tensor-core kernels stream (exactly invertible).
+    `paired` builds the [gate; up] form: each tile holds 64 gate rows and the 64 up rows of the same columns."""
     _require_cuda(packed)
     size = pack_tiled_bytes(n, k, bits)
     if size == 0 or packed.dtype != torch.uint8 or not packed.is_contiguous():
         raise ValueError("pack_relayout needs contiguous uint8 codes and K % 128 == 0")
     tiled = torch.empty((size,), device=packed.device, dtype=torch.uint8)
-    check(_lib.load().cacheir_b200_pack_relayout(packed.data_ptr(), tiled.data_ptr(), n, k, bits, _stream()), "pack_relayout")
+    check(_lib.load().cacheir_b200_pack_relayout(packed.data_ptr(), tiled.data_ptr(), n, k, bits, int(paired), _stream()), "pack_relayout")
     return tiled
 
 
-def pack_unrelayout(tiled: torch.Tensor, *, n: int, k: int, bits: int) -> torch.Tensor:
+def pack_unrelayout(tiled: torch.Tensor, *, n: int, k: int, bits: int, paired: bool = False) -> torch.Tensor:
     _require_cuda(tiled)
     row_bytes = k if bits == 8 else k // 2
     packed = torch.empty((n, row_bytes), device=tiled.device, dtype=torch.uint8)
-    check(_lib.load().cacheir_b200_pack_unrelayout(tiled.data_ptr(), packed.data_ptr(), n, k, bits, _stream()), "pack_unrelayout")
+    check(_lib.load().cacheir_b200_pack_unrelayout(tiled.data_ptr(), packed.data_ptr(), n, k, bits, int(paired), _stream()), "pack_unrelayout")
     return packed
 
 

@@ -42,6 +42,7 @@ class B200PackedWeight:
     group_size: int | None = None
     zero_points_i32: torch.Tensor | None = None   # the reference's int32 form, kept for parity checks
     tiled: bool = False                           # packed_values is in the 128x128 tile order (ops.pack_relayout)
+    paired: bool = False                          # tiled as [gate; up] pairs: 64 + 64 rows per tile (SwiGLU, int8)
 
     @property
     def nbytes(self) -> int:
@@ -97,13 +98,17 @@ def concat_rows(weights: list[B200PackedWeight]) -> B200PackedWeight:
     )
 
 
-def to_tiled(w: B200PackedWeight) -> B200PackedWeight:
-    """The same weight with its codes in the tile order of the tensor-core kernels (K % 128 == 0)."""
+def to_tiled(w: B200PackedWeight, *, paired: bool = False) -> B200PackedWeight:
+    """The same weight with its codes in the tile order of the tensor-core kernels (K % 128 == 0).
+    `paired` is the [gate; up] form consumed by the SwiGLU epilogue of the integer kernel."""
     if w.tiled:
+        if w.paired != paired:
+            return to_tiled(to_rows(w), paired=paired)
         return w
     n, k = w.shape
-    return B200PackedWeight(ops.pack_relayout(w.packed_values, n=n, k=k, bits=w.bits), w.scales, w.zero_points, w.bits,
-                            w.shape, group_size=w.group_size, zero_points_i32=w.zero_points_i32, tiled=True)
+    return B200PackedWeight(ops.pack_relayout(w.packed_values, n=n, k=k, bits=w.bits, paired=paired), w.scales, w.zero_points,
+                            w.bits, w.shape, group_size=w.group_size, zero_points_i32=w.zero_points_i32, tiled=True,
+                            paired=paired)
 
 
 def to_rows(w: B200PackedWeight) -> B200PackedWeight:
@@ -111,8 +116,9 @@ def to_rows(w: B200PackedWeight) -> B200PackedWeight:
     if not w.tiled:
         return w
     n, k = w.shape
-    return B200PackedWeight(ops.pack_unrelayout(w.packed_values, n=n, k=k, bits=w.bits), w.scales, w.zero_points, w.bits,
-                            w.shape, group_size=w.group_size, zero_points_i32=w.zero_points_i32, tiled=False)
+    return B200PackedWeight(ops.pack_unrelayout(w.packed_values, n=n, k=k, bits=w.bits, paired=w.paired), w.scales,
+                            w.zero_points, w.bits, w.shape, group_size=w.group_size, zero_points_i32=w.zero_points_i32,
+                            tiled=False)
 
 
 def dequantize_device(w: B200PackedWeight, dtype: torch.dtype) -> torch.Tensor:
@@ -129,4 +135,4 @@ def quantized_matmul(x: torch.Tensor, w: B200PackedWeight, *, epilogue: int = op
     `workspace` (ops.qgemv_workspace_bytes) enables the integer tensor-core path for int8 weights."""
     return ops.qgemv(x, w.packed_values, w.scales, w.zero_points, bits=w.bits, n=w.shape[0], k=w.shape[1],
                      group_size=w.group_size or 0, epilogue=epilogue, residual=residual, out=out, workspace=workspace,
-                     tiled=w.tiled)
+                     tiled=w.tiled, paired=w.paired)

@@ -32,7 +32,7 @@ import torch
 from . import ops
 from .artifact import CompileArtifact
 from .kv_cache import B200KVPageAllocator, B200PagedKVCache
-from .quantization import B200PackedWeight, concat_rows, quant_bits, to_tiled
+from .quantization import B200PackedWeight, concat_rows, quant_bits, to_rows, to_tiled
 from .weights import B200WeightStore, TensorSource
 
 
@@ -157,23 +157,33 @@ class _Engine:
         self.kernel_counts[name] = self.kernel_counts.get(name, 0) + n
 
     # -- weights as the kernels want them -------------------------------------------
-    def matmul_weight(self, names: tuple[str, ...], quantized: bool) -> B200PackedWeight | torch.Tensor:
+    def matmul_weight(self, names: tuple[str, ...], quantized: bool, batch: int = 1) -> B200PackedWeight | torch.Tensor:
         """One (row-concatenated) weight for a matmul-family node: packed when the
         node is a quantized op, dense [N, K] otherwise (cuda.py:1017-1023 caches the
-        same concatenation for its unquantized fused ops)."""
+        same concatenation for its unquantized fused ops). Batches beyond the tensor-core
+        kernels' 64 rows run on the CUDA-core kernel, which reads the reference's row
+        order: the first such batch moves the weight back to rows for good."""
         if names in self.fused_weights:
-            return self.fused_weights[names]
+            fused = self.fused_weights[names]
+            if batch > 64 and isinstance(fused, B200PackedWeight) and fused.tiled:
+                self.tile_weights = False
+                fused = self.fused_weights[names] = to_rows(fused)
+            return fused
         if quantized:
             parts = [self.weights.get_quantized(n) for n in names]
             fused = parts[0] if len(parts) == 1 else concat_rows(parts)
             if len(parts) > 1:   # the concatenation replaces the parts: keep one copy of the codes in HBM
                 for n in names:
                     self.weights.release(n)
-            # device pack layout: tile order for the tensor-core kernels (fp16 activations, K a multiple of 128;
-            # the gate|up pair additionally needs each half to be whole 128-row bands)
-            halves_ok = len(names) != 2 or (fused.shape[0] // 2) % 128 == 0
-            if self.dtype == torch.float16 and fused.shape[1] % 128 == 0 and halves_ok and self.tile_weights:
-                tiled = to_tiled(fused)
+            # device pack layout: tile order for the tensor-core kernels (fp16 activations, K a multiple of 128).
+            # A gate|up pair of per-row int8 weights takes the paired form (64 gate + 64 up rows per tile) that the
+            # integer kernel's SwiGLU epilogue reads; any other pair needs each half to be whole 128-row bands.
+            pair = len(names) == 2
+            half = fused.shape[0] // 2
+            paired = pair and fused.bits == 8 and not fused.group_size and half % 64 == 0
+            halves_ok = not pair or paired or half % 128 == 0
+            if self.dtype == torch.float16 and fused.shape[1] % 128 == 0 and halves_ok and self.tile_weights and batch <= 64:
+                tiled = to_tiled(fused, paired=paired)
                 if len(parts) == 1:
                     self.weights.release(names[0])
                 fused = tiled
@@ -276,7 +286,7 @@ class _DecodePlan:
                 if (nxt is not None and nxt.op in {"quantized_matmul", "quantized_fused_swiglu"}
                         and nxt.inputs[0] == node.outputs[0] and uses.get(node.outputs[0], 0) == 1):
                     names = (nxt.inputs[1],) if nxt.op == "quantized_matmul" else tuple(nxt.inputs[1:3])
-                    if self._i8_eligible(eng.matmul_weight(names, True), int(x.shape[1]), swiglu=len(names) == 2):
+                    if self._i8_eligible(eng.matmul_weight(names, True, self.batch), int(x.shape[1]), swiglu=len(names) == 2):
                         ws = self._gemm_workspace(int(x.shape[1]))
                         self._emit(lambda x=x, w=w, eps=eps, ws=ws: ops.rms_norm_quantize(x, w, eps, ws), "b200.rms_norm_quantize")
                         env[node.outputs[0]] = x            # placeholder: the consumer reads the workspace, not this tensor
@@ -288,7 +298,7 @@ class _DecodePlan:
                     env[node.outputs[0]] = out
             elif op in {"matmul", "quantized_matmul"}:
                 x = env[node.inputs[0]]
-                weight = eng.matmul_weight((node.inputs[1],), op == "quantized_matmul")
+                weight = eng.matmul_weight((node.inputs[1],), op == "quantized_matmul", self.batch)
                 out_name = node.outputs[0]
                 nxt = nodes[idx + 1] if idx + 1 < len(nodes) else None
                 residual = None
@@ -302,7 +312,7 @@ class _DecodePlan:
                 env[out_name] = out
             elif op in {"fused_rmsnorm_qkv_rope", "quantized_fused_rmsnorm_qkv_rope"}:
                 x, norm_w = env[node.inputs[0]], eng.weights.get(node.inputs[1])
-                weight = eng.matmul_weight(tuple(node.inputs[2:5]), op.startswith("quantized_"))
+                weight = eng.matmul_weight(tuple(node.inputs[2:5]), op.startswith("quantized_"), self.batch)
                 eps = float(attrs.get("eps", 1e-6))
                 if self._i8_eligible(weight, int(x.shape[1])):
                     ws = self._gemm_workspace(int(x.shape[1]))
@@ -344,7 +354,7 @@ class _DecodePlan:
                 env[node.outputs[0]] = out
             elif op in {"fused_swiglu", "quantized_fused_swiglu"}:
                 x = env[node.inputs[0]]
-                weight = eng.matmul_weight(tuple(node.inputs[1:3]), op.startswith("quantized_"))
+                weight = eng.matmul_weight(tuple(node.inputs[1:3]), op.startswith("quantized_"), self.batch)
                 env[node.outputs[0]] = self._matmul(x, weight, epilogue=ops.EPI_SWIGLU,
                                                     prequantized=node.inputs[0] in self._prequantized)
             elif op == "elementwise_mul" and idx > 0 and nodes[idx - 1].op == "silu" and nodes[idx - 1].outputs[0] in node.inputs:
@@ -372,7 +382,7 @@ class _DecodePlan:
 
     def _i8_eligible(self, weight: Any, k: int, swiglu: bool = False) -> bool:
         """Will this projection run on the integer tensor cores (and so accept pre-quantized activations)?"""
-        if swiglu and isinstance(weight, B200PackedWeight) and (weight.shape[0] // 2) % 128 != 0:
+        if swiglu and isinstance(weight, B200PackedWeight) and ((weight.shape[0] // 2) % 64 != 0 or (weight.tiled and not weight.paired)):
             return False
         return (isinstance(weight, B200PackedWeight) and weight.bits == 8 and not weight.group_size
                 and self.engine.dtype == torch.float16 and self.batch <= 64 and k % 128 == 0 and k <= 8192
@@ -389,7 +399,7 @@ class _DecodePlan:
             ws = self._gemm_workspace(k) if (bits == 8 and not weight.group_size and eng.dtype == torch.float16) else None
             fn = lambda: ops.qgemv(x, weight.packed_values, weight.scales, weight.zero_points, bits=bits, n=n, k=k,
                                    group_size=weight.group_size or 0, epilogue=epilogue, residual=residual, out=out,
-                                   workspace=ws, tiled=weight.tiled, prequantized=prequantized)
+                                   workspace=ws, tiled=weight.tiled, prequantized=prequantized, paired=weight.paired)
             key = f"b200.qgemv.int{bits}" + (".swiglu" if epilogue == ops.EPI_SWIGLU else ".residual" if residual is not None else "")
             eng.gemm_plans[f"q{bits}:{(self.batch, 1, k)}x{weight.shape}"] = key
             if ws is not None and self.batch <= 64 and k % 128 == 0 and not prequantized:   # activation pre-pass + integer GEMM

@@ -43,6 +43,7 @@ extern "C" {
 #define CACHEIR_B200_LAYOUT_ROWS 0     /* the reference's row-major packed_values   */
 #define CACHEIR_B200_LAYOUT_TILED 1    /* cacheir_b200_pack_relayout's tile order   */
 #define CACHEIR_B200_X_PREQUANTIZED 2  /* workspace already holds x in integer form */
+#define CACHEIR_B200_LAYOUT_PAIRED 4   /* tiled with `paired` != 0 (SwiGLU weights only)  */
 
 /* qgemv epilogues */
 #define CACHEIR_B200_EPI_NONE 0       /* y = x W^T                            */
@@ -199,10 +200,14 @@ int cacheir_b200_rms_norm_quantize(const void* x, const void* residual, const vo
  * reference bytes exactly. K must be a multiple of 128; `tiled` holds
  * cacheir_b200_pack_tiled_bytes(N, K, bits) bytes. Scales and zero points are not
  * touched. Pass CACHEIR_B200_LAYOUT_TILED to cacheir_b200_qgemv_ex for such weights
- * (tensor-core shapes only: fp16 x, M <= 64). */
+ * (tensor-core shapes only: fp16 x, M <= 64).
+ * `paired` != 0 (N a multiple of 128) is the form for W = [gate; up] used with
+ * CACHEIR_B200_EPI_SWIGLU on int8 weights: tile t holds gate rows 64t..64t+63 followed by
+ * up rows N/2+64t..N/2+64t+63, so one CTA owns both factors of 64 output columns. Pass
+ * CACHEIR_B200_LAYOUT_TILED | CACHEIR_B200_LAYOUT_PAIRED for such weights. */
 size_t cacheir_b200_pack_tiled_bytes(int N, int K, int bits);
-int cacheir_b200_pack_relayout(const uint8_t* packed, uint8_t* tiled, int N, int K, int bits, void* stream);
-int cacheir_b200_pack_unrelayout(const uint8_t* tiled, uint8_t* packed, int N, int K, int bits, void* stream);
+int cacheir_b200_pack_relayout(const uint8_t* packed, uint8_t* tiled, int N, int K, int bits, int paired, void* stream);
+int cacheir_b200_pack_unrelayout(const uint8_t* tiled, uint8_t* packed, int N, int K, int bits, int paired, void* stream);
 
 /* Status word of the kernels that wait on hardware barriers (the tensor-core GEMM):
  * 0, or a non-zero code recorded by the first wait that ran out of its poll budget

@@ -475,6 +475,26 @@ def test_pack_relayout_roundtrip_and_gemm_equivalence(bits, n, k):
         a = quantized_matmul(x.cuda(), rows, epilogue=ops.EPI_SWIGLU)
         b = quantized_matmul(x.cuda(), tiled, epilogue=ops.EPI_SWIGLU)
         assert torch.equal(a, b)
+    if n % 128 == 0:
+        # [gate; up] pairing: tile t = gate rows 64t.. followed by up rows n/2+64t..; exact inverse, same SwiGLU result
+        paired = to_tiled(rows, paired=True)
+        assert paired.paired and torch.equal(to_rows(paired).packed_values, rows.packed_values)
+        tp = paired.packed_values.cpu().numpy().reshape(-1, kblocks, 128, tb)
+        for r, src in ((5, 64 + 5), (64 + 9, n // 2 + 64 + 9)):            # tile 1: a gate row and an up row
+            if n >= 256:
+                key = (r & 7) if bits == 8 else ((r >> 1) & 3)
+                chunks = tp[1, 0, r].reshape(tb // 16, 16)
+                np.testing.assert_array_equal(np.stack([chunks[c ^ key] for c in range(tb // 16)]).reshape(-1), ref[src, :tb])
+        if bits == 8:
+            ws = torch.empty(ops.qgemv_workspace_bytes(32, k), dtype=torch.uint8, device="cuda")
+            a = quantized_matmul(x.cuda(), rows, epilogue=ops.EPI_SWIGLU, workspace=ws)
+            b = quantized_matmul(x.cuda(), paired, epilogue=ops.EPI_SWIGLU, workspace=ws)
+            assert torch.equal(a, b)
+            base = oracle.quantized_matmul(x.float().numpy(), packed)
+            assert _rel(a, oracle.silu_mul(base[:, : n // 2], base[:, n // 2:])) <= TOL[torch.float16] * 2
+        else:
+            with pytest.raises(Exception):                                  # only the integer kernel reads paired tiles
+                quantized_matmul(x.cuda(), paired, epilogue=ops.EPI_SWIGLU)
     torch.cuda.synchronize()
     _device_status_ok()
 
