@@ -444,15 +444,16 @@ def run_micro(args) -> None:
         epi = {"none": ops.EPI_NONE, "swiglu": ops.EPI_SWIGLU}[args.epilogue]
         out = torch.empty((m, n // 2 if epi == ops.EPI_SWIGLU else n), device=dev, dtype=torch.float16)
 
+        paired = args.tiled and epi == ops.EPI_SWIGLU and bits == 8 and not args.group
         if args.tiled:
-            packed = [ops.pack_relayout(w, n=n, k=k, bits=bits) for w in packed]
+            packed = [ops.pack_relayout(w, n=n, k=k, bits=bits, paired=paired) for w in packed]
         ws = None
         if args.workspace:
             ws = torch.empty(ops.qgemv_workspace_bytes(m, k), device=dev, dtype=torch.uint8)
 
         def launch(i: int) -> None:
             ops.qgemv(x, packed[i % copies], scales, zeros, bits=bits, n=n, k=k, group_size=args.group, epilogue=epi,
-                      out=out, workspace=ws, tiled=args.tiled)
+                      out=out, workspace=ws, tiled=args.tiled, paired=paired)
 
         algo = n * row_bytes + scales.numel() * scales.element_size() + (n * 4 if zeros is not None else 0) + m * k * 2 + out.numel() * 2
         name = f"qgemv_int{bits}" + (f"_g{args.group}" if args.group else "")
@@ -624,13 +625,15 @@ def main() -> None:
     step_gbs = sb["total"] / (elapsed_s / args.steps) / 1e9
 
     if rank == 0:
+        # DRAM traffic of the attention kernel: the ratio measured by ncu on a small case (the profile
+        # summary states the capture) times this workload's algorithmic bytes per launch
         traffic = None
-        prof = ROOT / "profiles" / "attention_traffic.json"
+        prof = ROOT / "profiles" / "paged_decode_mma_b16_ctx2048-4096.md"
         if prof.exists():
-            try:
-                traffic = json.loads(prof.read_text()).get("dram_bytes_per_launch_scaled")
-            except Exception:
-                traffic = None
+            import re
+            found = re.search(r"dram_traffic_over_algorithmic_bytes\s*=\s*([0-9.]+)", prof.read_text())
+            if found:
+                traffic = int(float(found.group(1)) * attn["bytes"])
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": elapsed_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
