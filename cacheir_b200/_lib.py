@@ -41,6 +41,12 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
          c_int, c_int, c_int, c_int, c_int, c_int, c_int,
          c_longlong, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "cacheir_b200_qkv_rope_append": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_int,  # x..qkv M N K scale_dtype stride layout
+         c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,             # q_dim k_dim hd theta table n pos table maxp page
+         c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),                                             # k v ws bytes stream
+    "cacheir_b200_rope_table": (c_int, [c_void_p, c_int, c_int, c_float, c_void_p]),
     "cacheir_b200_quantize_activations": (c_int, [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_size_t, c_void_p]),
     "cacheir_b200_rms_norm_quantize": (
         c_int, [c_void_p] * 5 + [c_int, c_int, c_float, c_int, c_void_p, c_size_t, c_void_p]),

@@ -101,6 +101,19 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---- RoPE arithmetic shared by the stand-alone kernel, the table builder and the fused epilogue
+// (one definition, so the three produce the same bits). Interleaved pairs (2i, 2i+1);
+// angle = pos * theta^(-2i/D), evaluated in fp32 like the reference (cacheir/runtime/cuda.py:1072-1102).
+__device__ __forceinline__ void rope_cos_sin(int pos, int i, int head_dim, float theta, float* c, float* s) {
+  const float freq = 1.0f / powf(theta, static_cast<float>(i) * 2.0f / static_cast<float>(head_dim));
+  const float angle = static_cast<float>(pos) * freq;
+  sincosf(angle, s, c);
+}
+__device__ __forceinline__ void rope_rotate(float e, float o, float c, float s, float* re, float* ro) {
+  *re = __fmaf_rn(e, c, -__fmul_rn(o, s));
+  *ro = __fmaf_rn(e, s, __fmul_rn(o, c));
+}
+
 // ---- host side ----------------------------------------------------------------
 inline int dtype_size(int dtype) {
   switch (dtype) {

@@ -125,15 +125,23 @@ __global__ void rope_inplace_kernel(T* __restrict__ x, const int32_t* __restrict
   if (idx >= num_heads * half) return;
   const int h = idx / half;
   const int i = idx % half;
-  const float freq = 1.0f / powf(theta, static_cast<float>(i) * 2.0f / static_cast<float>(head_dim));
-  const float angle = static_cast<float>(positions[b]) * freq;
   float s, c;
-  sincosf(angle, &s, &c);
+  rope_cos_sin(positions[b], i, head_dim, theta, &c, &s);
   T* p = x + static_cast<size_t>(b) * stride + static_cast<size_t>(h) * head_dim + 2 * i;
-  const float e = Elem<T>::ld(p);
-  const float o = Elem<T>::ld(p + 1);
-  Elem<T>::st(p, e * c - o * s);
-  Elem<T>::st(p + 1, e * s + o * c);
+  float re, ro;
+  rope_rotate(Elem<T>::ld(p), Elem<T>::ld(p + 1), c, s, &re, &ro);
+  Elem<T>::st(p, re);
+  Elem<T>::st(p + 1, ro);
+}
+
+// (cos, sin) of every (position, pair) for the fused QKV epilogue: table[pos][i] = float2(cos, sin)
+__global__ void rope_table_kernel(float2* __restrict__ table, int positions, int head_dim, float theta) {
+  const int half = head_dim / 2;
+  const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<size_t>(positions) * half) return;
+  float s, c;
+  rope_cos_sin(static_cast<int>(idx / half), static_cast<int>(idx % half), head_dim, theta, &c, &s);
+  table[idx] = make_float2(c, s);
 }
 
 // ---- KV append: one new row per (request, kv head) into its page ------------------
@@ -259,6 +267,16 @@ extern "C" int cacheir_b200_rope_inplace(void* x, const int32_t* positions, int 
   const dim3 grid((pairs + 127) / 128, batch_size);
   CB200_DISPATCH_DTYPE(dtype, (rope_inplace_kernel<T><<<grid, 128, 0, as_stream(stream)>>>(
                                   static_cast<T*>(x), positions, num_heads, head_dim, theta, stride)));
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_rope_table(float* table, int positions, int head_dim, float theta, void* stream) {
+  if (positions <= 0 || head_dim <= 0) return 0;
+  if (!table || (head_dim % 2) != 0) return CACHEIR_B200_EINVAL;
+  if (!aligned_to(table, 8)) return CACHEIR_B200_EALIGN;
+  const size_t total = static_cast<size_t>(positions) * (head_dim / 2);
+  rope_table_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(
+      reinterpret_cast<float2*>(table), positions, head_dim, theta);
   return launch_status();
 }
 

@@ -290,6 +290,7 @@ struct I8Params {
   int epilogue;
   int split_k;
   int tiled;        // weights in 128x128 tile order: tile (band, kb) starts at row (band*KB + kb)*128 of a 128-byte-wide tensor
+  RopeAppendParams rope;   // epilogue == kEpiQkvRopeAppend
 };
 // With the SwiGLU epilogue a tile pairs 64 gate rows (tile rows 0..63, weight rows 64t..64t+63) with the
 // 64 up rows of the same output columns (tile rows 64..127, weight rows N/2+64t..): one pass, one
@@ -306,7 +307,7 @@ __device__ __forceinline__ float recombine(int32_t hi, int32_t lo, float zero, i
   return static_cast<float>(256.0 * hi + static_cast<double>(lo) - static_cast<double>(zero) * qsum);
 }
 
-template <int MP, int SPLIT>
+template <int MP, int SPLIT, bool ROPE>
 __global__ void __launch_bounds__(kThreads, 2)
 qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
   constexpr int kStages = num_stages(MP, SPLIT);
@@ -456,6 +457,54 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
       res_v[j] = (split > 1 && p.epilogue == CACHEIR_B200_EPI_RESIDUAL && m < p.M && n_out_idx < p.n_out)
                      ? __half2float(res[static_cast<size_t>(m) * p.n_out + n_out_idx]) : 0.f;
     }
+    // Fused QKV epilogue: per batch row, the (cos, sin) of this thread's pair and where its k/v element goes in the pool.
+    constexpr bool rope_epi = ROPE;   // a template parameter: the other projections do not carry this code
+    const RopeAppendParams& ra = p.rope;
+    auto rope_row = [&](int m, float2* cs, long long* off) {
+      *cs = make_float2(1.f, 0.f);
+      *off = -1;
+      if (m >= p.M || n_out_idx >= p.n_out) return;
+      const int pos = ra.positions[m];
+      if (n_out_idx < ra.q_dim + ra.k_dim) {
+        const int i = (n_out_idx % ra.head_dim) >> 1;
+        if (pos >= 0 && pos < ra.table_positions)
+          *cs = reinterpret_cast<const float2*>(ra.table)[static_cast<size_t>(pos) * (ra.head_dim / 2) + i];
+        else
+          atomicCAS(&g_i8_status, 0, (3 << 8) | 5);   // position outside the cos/sin table: flagged, value left unrotated
+      }
+      if (n_out_idx >= ra.q_dim) {
+        const int col = (n_out_idx - ra.q_dim) % ra.k_dim;      // v follows k and has the same width
+        const int page_idx = pos / ra.page_size;
+        if (pos >= 0 && page_idx < ra.max_pages) {               // no page reserved: drop rather than write out of range
+          const int page = ra.page_table[static_cast<size_t>(m) * ra.max_pages + page_idx];
+          *off = static_cast<long long>(((static_cast<size_t>(page) * ra.kv_heads + col / ra.head_dim) * ra.page_size +
+                                         pos % ra.page_size) * ra.head_dim + col % ra.head_dim);
+        }
+      }
+    };
+    // all 32 lanes call this together (pairs are adjacent lanes); only `do_store` lanes write
+    auto rope_finish = [&](float out, float2 cs, long long off, int m, bool do_store) {
+      float v = __half2float(__float2half_rn(out));             // what the plain epilogue would have stored
+      const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+      const bool is_qk = n_out_idx < ra.q_dim + ra.k_dim;
+      if (is_qk) {
+        const bool odd = (n_out_idx & 1) != 0;
+        float re, ro;
+        rope_rotate(odd ? partner : v, odd ? v : partner, cs.x, cs.y, &re, &ro);
+        v = odd ? ro : re;
+      }
+      const __half h = __float2half_rn(v);
+      if (do_store) {
+        y[static_cast<size_t>(m) * p.n_out + n_out_idx] = h;
+        if (off >= 0) static_cast<__half*>(is_qk ? ra.k_cache : ra.v_cache)[off] = h;
+      }
+    };
+    float2 cs_v[MS];
+    long long off_v[MS];
+    if constexpr (SPLIT > 1 && ROPE) {
+#pragma unroll
+      for (int j = 0; j < MS; ++j) rope_row(krank * MS + j, &cs_v[j], &off_v[j]);
+    }
     asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps: s_sx / s_qsum are in place
     bool ok = mbar_wait(smem_u32(acc_full), 0, &g_i8_status, (3 << 8) | 3);
     tc_fence_after();
@@ -529,7 +578,14 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
 #pragma unroll
         for (int j = 0; j < G; ++j) {
           const int m = krank * MS + u0 + j;
-          if (m < p.M && store && ok) {
+          if constexpr (ROPE) {
+            float2 cs = make_float2(1.f, 0.f);
+            long long off = -1;
+#pragma unroll
+            for (int jj = 0; jj < MS; ++jj)
+              if (jj == u0 + j) { cs = cs_v[jj]; off = off_v[jj]; }
+            rope_finish(recombine(sum[0][j], sum[1][j], zero, s_qsum[m]) * (scale * s_sx[m]), cs, off, m, m < p.M && store && ok);
+          } else if (m < p.M && store && ok) {
             float out = recombine(sum[0][j], sum[1][j], zero, s_qsum[m]) * (scale * s_sx[m]);
             if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
               float rv = 0.f;
@@ -590,7 +646,13 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int m = c0 + j;
-          if (m < p.M && store) {
+          if constexpr (ROPE) {
+            float2 cs;
+            long long off;
+            rope_row(m, &cs, &off);
+            rope_finish(recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, s_qsum[m]) * (scale * s_sx[m]),
+                        cs, off, m, m < p.M && store);
+          } else if (m < p.M && store) {
             float out = recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, s_qsum[m]) * (scale * s_sx[m]);
             const size_t o = static_cast<size_t>(m) * p.n_out + n_out_idx;
             if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) out += __half2float(res[o]);
@@ -638,12 +700,12 @@ int launch_quantize(const __half* x, long long x_stride, int M, int K, int mp, v
   return launch_status();
 }
 
-template <int MP, int SPLIT>
+template <int MP, int SPLIT, bool ROPE>
 cudaError_t launch_i8_split(const CUtensorMap& tmap_w, const I8Params& p, int n_tiles, cudaStream_t stream) {
   constexpr size_t kSmem = 1024 + static_cast<size_t>(num_stages(MP, SPLIT)) * stage_bytes(MP) + exchange_bytes(MP, SPLIT) + 1024;
   static_assert(num_stages(MP, SPLIT) >= 2, "the pipeline needs at least two stages");
   static_assert(num_stages(MP, SPLIT) * stage_bytes(MP) >= exchange_bytes(MP, SPLIT), "outgoing partials are staged in the drained ring");
-  auto kern = qgemm_i8_kernel<MP, SPLIT>;
+  auto kern = qgemm_i8_kernel<MP, SPLIT, ROPE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg{};
@@ -687,14 +749,24 @@ int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
   p.M = q.M; p.N = q.N; p.K = q.K;
   p.n_out = q.epilogue == CACHEIR_B200_EPI_SWIGLU ? q.N / 2 : q.N;
   p.scale_dtype = q.scale_dtype; p.epilogue = q.epilogue; p.tiled = q.tiled ? 1 : 0;
+  p.rope = q.rope;
   const int n_tiles = swiglu ? (p.n_out + kPairRows - 1) / kPairRows : (p.n_out + kBlockN - 1) / kBlockN;
   p.split_k = choose_split_k(n_tiles, q.K / kBlockK, q.epilogue, MP);
   cudaError_t e;
-  switch (p.split_k) {
-    case 8: e = launch_i8_split<MP, 8>(tmap_w, p, n_tiles, stream); break;
-    case 4: e = launch_i8_split<MP, 4>(tmap_w, p, n_tiles, stream); break;
-    case 2: e = launch_i8_split<MP, 2>(tmap_w, p, n_tiles, stream); break;
-    default: e = launch_i8_split<MP, 1>(tmap_w, p, n_tiles, stream); break;
+  if (q.epilogue == kEpiQkvRopeAppend) {
+    switch (p.split_k) {
+      case 8: e = launch_i8_split<MP, 8, true>(tmap_w, p, n_tiles, stream); break;
+      case 4: e = launch_i8_split<MP, 4, true>(tmap_w, p, n_tiles, stream); break;
+      case 2: e = launch_i8_split<MP, 2, true>(tmap_w, p, n_tiles, stream); break;
+      default: e = launch_i8_split<MP, 1, true>(tmap_w, p, n_tiles, stream); break;
+    }
+  } else {
+    switch (p.split_k) {
+      case 8: e = launch_i8_split<MP, 8, false>(tmap_w, p, n_tiles, stream); break;
+      case 4: e = launch_i8_split<MP, 4, false>(tmap_w, p, n_tiles, stream); break;
+      case 2: e = launch_i8_split<MP, 2, false>(tmap_w, p, n_tiles, stream); break;
+      default: e = launch_i8_split<MP, 1, false>(tmap_w, p, n_tiles, stream); break;
+    }
   }
   if (e != cudaSuccess) return static_cast<int>(e);
   return launch_status();

@@ -278,3 +278,36 @@ extern "C" int cacheir_b200_rms_norm_quantize(const void* x, const void* residua
     return CACHEIR_B200_EALIGN;
   return qgemm_i8_rms_norm_quantize(x, residual, weight, sum_out, out, rows, hidden, eps, workspace, as_stream(stream));
 }
+
+extern "C" int cacheir_b200_qkv_rope_append(const void* x, const void* packed, const void* scales, const float* zero_points,
+                                            void* qkv, int M, int N, int K, int scale_dtype, long long x_stride,
+                                            int weight_layout, int q_dim, int k_dim, int head_dim, float theta,
+                                            const float* rope_table, int rope_table_positions, const int32_t* positions,
+                                            const int32_t* page_table, int max_pages_per_seq, int page_size, void* k_cache,
+                                            void* v_cache, void* workspace, size_t workspace_bytes, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (!packed || !scales || !qkv || !positions || !page_table || !k_cache || !v_cache) return CACHEIR_B200_EINVAL;
+  if (head_dim <= 0 || (head_dim % 2) != 0 || q_dim <= 0 || k_dim <= 0 || q_dim % head_dim != 0 || k_dim % head_dim != 0 ||
+      N != q_dim + 2 * k_dim || max_pages_per_seq <= 0 || page_size <= 0)
+    return CACHEIR_B200_EINVAL;
+  if (scale_dtype != CACHEIR_B200_F32 && scale_dtype != CACHEIR_B200_F16) return CACHEIR_B200_EINVAL;
+  if (weight_layout < 0 || (weight_layout & ~(CACHEIR_B200_LAYOUT_TILED | CACHEIR_B200_X_PREQUANTIZED)) != 0) return CACHEIR_B200_EINVAL;
+  if (!rope_table || rope_table_positions <= 0 || !aligned_to(rope_table, 8)) return CACHEIR_B200_EINVAL;
+  QGemvParams p{};
+  p.x = x; p.packed = packed; p.scales = scales; p.zero_points = zero_points; p.residual = nullptr; p.y = qkv;
+  p.M = M; p.N = N; p.K = K; p.bits = 8; p.group_size = 0;
+  p.x_dtype = CACHEIR_B200_F16; p.scale_dtype = scale_dtype;
+  p.x_stride = x_stride > 0 ? x_stride : K;
+  p.epilogue = kEpiQkvRopeAppend;
+  p.tiled = (weight_layout & CACHEIR_B200_LAYOUT_TILED) != 0;
+  p.x_prequantized = (weight_layout & CACHEIR_B200_X_PREQUANTIZED) != 0;
+  if (!p.x_prequantized && !x) return CACHEIR_B200_EINVAL;
+  p.vector_ok = true;
+  p.rope.table = rope_table; p.rope.table_positions = rope_table_positions;
+  p.rope.positions = positions; p.rope.page_table = page_table; p.rope.k_cache = k_cache; p.rope.v_cache = v_cache;
+  p.rope.q_dim = q_dim; p.rope.k_dim = k_dim; p.rope.head_dim = head_dim; p.rope.kv_heads = k_dim / head_dim;
+  p.rope.max_pages = max_pages_per_seq; p.rope.page_size = page_size; p.rope.theta = theta;
+  // only the integer tensor-core kernel carries this epilogue; other shapes use the separate kernels
+  if (!qgemm_i8_supported(p, workspace, workspace_bytes)) return CACHEIR_B200_EUNSUPPORTED;
+  return launch_qgemm_i8(p, workspace, as_stream(stream));
+}

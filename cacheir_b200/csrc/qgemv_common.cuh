@@ -6,6 +6,19 @@
 
 namespace cb200 {
 
+// Fused QKV epilogue: RoPE on the q and k heads, new k/v rows written into the page pool.
+struct RopeAppendParams {
+  const float* table;          // [table_positions][head_dim/2] (cos, sin) pairs, or null: evaluate on the fly
+  int table_positions;
+  const int32_t* positions;    // [M] position of the token of each batch row
+  const int32_t* page_table;   // [M][max_pages]
+  void* k_cache;               // [slots][kv_heads][page_size][head_dim], fp16
+  void* v_cache;
+  int q_dim, k_dim, head_dim, kv_heads, max_pages, page_size;
+  float theta;
+};
+constexpr int kEpiQkvRopeAppend = 3;   // internal epilogue code (cacheir_b200_qkv_rope_append)
+
 struct QGemvParams {
   const void* x;
   const void* packed;
@@ -23,6 +36,7 @@ struct QGemvParams {
   bool tiled;      // codes are in the 128x128 tile order of cacheir_b200_pack_relayout
   bool paired;     // tiled, and every tile pairs 64 rows of the first half of W with the matching 64 of the second half
   bool x_prequantized;  // the workspace already holds the integer form of x (see cacheir_b200_quantize_activations)
+  RopeAppendParams rope;  // epilogue == kEpiQkvRopeAppend only
 };
 
 int launch_qgemv_cuda_core(const QGemvParams& p, cudaStream_t stream);

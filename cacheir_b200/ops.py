@@ -332,3 +332,42 @@ def advance_positions(positions: torch.Tensor, seq_lens: torch.Tensor) -> None:
 
 def default_softmax_scale(head_dim: int) -> float:
     return 1.0 / math.sqrt(float(head_dim))
+
+
+def rope_table(positions: int, head_dim: int, theta: float, device: torch.device) -> torch.Tensor:
+    """(cos, sin) of every (position, pair): float32 [positions, head_dim/2, 2], the values rope_inplace evaluates."""
+    table = torch.empty((int(positions), head_dim // 2, 2), device=device, dtype=torch.float32)
+    check(_lib.load().cacheir_b200_rope_table(table.data_ptr(), int(positions), int(head_dim), float(theta), _stream()), "rope_table")
+    return table
+
+
+def qkv_rope_append(x: torch.Tensor | None, packed: torch.Tensor, scales: torch.Tensor, zero_points: torch.Tensor | None,
+                    out: torch.Tensor, *, n: int, k: int, q_dim: int, k_dim: int, head_dim: int, theta: float,
+                    table: torch.Tensor, positions: torch.Tensor, page_table: torch.Tensor, k_cache: torch.Tensor,
+                    v_cache: torch.Tensor, workspace: torch.Tensor, tiled: bool = False, prequantized: bool = False) -> torch.Tensor:
+    """Fused QKV projection (int8 weights) + RoPE on q and k + append of the new k/v rows to the page pool.
+    `out` [M, N] fp16 receives q (roped), k (roped), v. Raises CacheIRB200Error (unsupported) outside the
+    integer tensor-core shapes; the caller then uses qgemv + rope_inplace + kv_append."""
+    _require_cuda(x, packed, scales, zero_points, out, table, positions, page_table, k_cache, v_cache, workspace)
+    m = int(out.shape[0])
+    if out.dtype != torch.float16 or tuple(out.shape) != (m, n) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous fp16 [M, N] tensor")
+    if k_cache.dtype != torch.float16 or v_cache.dtype != torch.float16 or k_cache.shape != v_cache.shape:
+        raise ValueError("the page pool must be fp16")
+    if positions.dtype != torch.int32 or page_table.dtype != torch.int32 or positions.numel() != m or page_table.shape[0] != m:
+        raise ValueError("positions [M] and page_table [M, max_pages] must be int32")
+    if x is not None and (x.dtype != torch.float16 or x.dim() != 2 or x.stride(1) != 1 or tuple(x.shape) != (m, k)):
+        raise ValueError("x must be fp16 [M, K] with dense rows")
+    _, kv_heads, page_size, hd = (int(v) for v in k_cache.shape)
+    if hd != head_dim or kv_heads * head_dim != k_dim:
+        raise ValueError("pool geometry does not match k_dim / head_dim")
+    if table.dtype != torch.float32 or not table.is_contiguous() or table.shape[1:] != (head_dim // 2, 2):
+        raise ValueError("rope table must be float32 [positions, head_dim/2, 2]")
+    check(_lib.load().cacheir_b200_qkv_rope_append(
+        _ptr(x), packed.data_ptr(), scales.data_ptr(), _ptr(zero_points), out.data_ptr(), m, n, k,
+        F16 if scales.dtype == torch.float16 else F32, 0 if x is None else x.stride(0),
+        (1 if tiled else 0) | (2 if prequantized else 0), q_dim, k_dim, head_dim, float(theta),
+        table.data_ptr(), int(table.shape[0]), positions.data_ptr(), page_table.data_ptr(),
+        int(page_table.shape[1]), page_size, k_cache.data_ptr(), v_cache.data_ptr(), workspace.data_ptr(),
+        workspace.numel() * workspace.element_size(), _stream()), "qkv_rope_append")
+    return out

@@ -22,6 +22,8 @@ cacheir/runtime/scheduler.py:508-577): `run`, `fork`, `run_decode_batch`,
 """
 from __future__ import annotations
 
+import os
+
 from collections import OrderedDict
 from pathlib import Path
 from typing import Any, Callable, Iterable
@@ -144,6 +146,7 @@ class _Engine:
         self.max_seq_len = int(max_seq_len or self.config.max_position_embeddings)
         self.use_cuda_graph = use_cuda_graph
         self.tile_weights = True
+        self._rope_tables: dict[tuple[int, float], torch.Tensor] = {}
         self.attention_splits = int(attention_splits)
         self.max_plans = max(1, int(max_plans))
         self.plans: OrderedDict[tuple[str, ...], "_DecodePlan"] = OrderedDict()
@@ -195,6 +198,13 @@ class _Engine:
                     self.weights.release(n)
         self.fused_weights[names] = fused
         return fused
+
+    def rope_table(self, head_dim: int, theta: float) -> torch.Tensor:
+        """(cos, sin) for every position up to max_seq_len, shared by all plans and layers."""
+        key = (int(head_dim), float(theta))
+        if key not in self._rope_tables:
+            self._rope_tables[key] = ops.rope_table(self.max_seq_len, head_dim, theta, self.device)
+        return self._rope_tables[key]
 
     def plan_for(self, sessions: list["B200DecodeRuntime"]) -> "_DecodePlan":
         key = tuple(s.kv_cache.owner_id for s in sessions)
@@ -256,6 +266,7 @@ class _DecodePlan:
         env: dict[str, Any] = {}
         self._count_keys: list[tuple[str, int]] = []
         self._prequantized: set[str] = set()
+        self._kv_appended: set[str] = set()
         uses: dict[str, int] = {}
         for node in nodes:
             for name in node.inputs:
@@ -314,18 +325,39 @@ class _DecodePlan:
                 x, norm_w = env[node.inputs[0]], eng.weights.get(node.inputs[1])
                 weight = eng.matmul_weight(tuple(node.inputs[2:5]), op.startswith("quantized_"), self.batch)
                 eps = float(attrs.get("eps", 1e-6))
+                q_dim = self._rows_of(node.inputs[2])
+                k_dim = self._rows_of(node.inputs[3])
+                head_dim = int(attrs["head_dim"])
+                theta = float(attrs.get("rope_theta", 10000.0))
+                consumer = self._attention_consumer(nodes, idx, node)
                 if self._i8_eligible(weight, int(x.shape[1])):
                     ws = self._gemm_workspace(int(x.shape[1]))
                     self._emit(lambda x=x, w=norm_w, eps=eps, ws=ws: ops.rms_norm_quantize(x, w, eps, ws), "b200.rms_norm_quantize")
+                    pool = eng.allocator.pool_for_layer(int(consumer.attrs.get("layer", 0))) if consumer is not None else None
+                    if (pool is not None and self._rows_of(node.inputs[4]) == k_dim and pool["keys"].dtype == torch.float16
+                            and int(pool["keys"].shape[3]) == head_dim and int(pool["keys"].shape[1]) * head_dim == k_dim):
+                        # projection + RoPE + append of the new k/v rows in one kernel
+                        n, k = weight.shape
+                        qkv = self._buf(n)
+                        table = eng.rope_table(head_dim, theta)
+                        k_pool, v_pool = pool["keys"], pool["values"]
+                        self._emit(lambda qkv=qkv, weight=weight, n=n, k=k, ws=ws, table=table, k_pool=k_pool, v_pool=v_pool:
+                                   ops.qkv_rope_append(None, weight.packed_values, weight.scales, weight.zero_points, qkv, n=n, k=k,
+                                                       q_dim=q_dim, k_dim=k_dim, head_dim=head_dim, theta=theta, table=table,
+                                                       positions=self.positions, page_table=self.page_table, k_cache=k_pool,
+                                                       v_cache=v_pool, workspace=ws, tiled=weight.tiled, prequantized=True),
+                                   "b200.qkv_rope_append")
+                        eng.gemm_plans[f"q8:{(self.batch, 1, k)}x{weight.shape}"] = "b200.qkv_rope_append"
+                        self._kv_appended.add(node.outputs[1])
+                        env[node.outputs[0]] = qkv[:, :q_dim]
+                        env[node.outputs[1]] = qkv[:, q_dim:q_dim + k_dim]
+                        env[node.outputs[2]] = qkv[:, q_dim + k_dim:]
+                        continue
                     qkv = self._matmul(x, weight, prequantized=True)
                 else:
                     normed = self._buf(int(x.shape[1]))
                     self._emit(lambda x=x, w=norm_w, out=normed, eps=eps: ops.rms_norm(x, w, eps, out=out), "b200.rms_norm")
                     qkv = self._matmul(normed, weight)
-                q_dim = self._rows_of(node.inputs[2])
-                k_dim = self._rows_of(node.inputs[3])
-                head_dim = int(attrs["head_dim"])
-                theta = float(attrs.get("rope_theta", 10000.0))
                 qk = qkv[:, : q_dim + k_dim]   # q and k heads are adjacent: one RoPE launch covers both
                 self._emit(lambda qk=qk, hd=head_dim, theta=theta, nh=(q_dim + k_dim) // head_dim:
                            ops.rope_inplace(qk, self.positions, num_heads=nh, head_dim=hd, theta=theta), "b200.rope")
@@ -346,7 +378,8 @@ class _DecodePlan:
                                "b200.rope")
                     env[out_name] = t
             elif op in {"paged_attention_decode", "grouped_query_attention"}:
-                env[node.outputs[0]] = self._attention(env[node.inputs[0]], env[node.inputs[1]], env[node.inputs[2]], attrs)
+                env[node.outputs[0]] = self._attention(env[node.inputs[0]], env[node.inputs[1]], env[node.inputs[2]], attrs,
+                                                       appended=node.inputs[1] in self._kv_appended)
             elif op == "add":
                 a, b = env[node.inputs[0]], env[node.inputs[1]]
                 out = self._buf(int(a.shape[1]))
@@ -425,7 +458,16 @@ class _DecodePlan:
             self._gemm_ws = ws = torch.empty((need,), device=self.engine.device, dtype=torch.uint8)
         return ws
 
-    def _attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attrs: dict[str, Any]) -> torch.Tensor:
+    @staticmethod
+    def _attention_consumer(nodes: list[Any], idx: int, node: Any) -> Any | None:
+        """The decode-attention node that takes this node's q, k, v outputs (and so owns the cache append)."""
+        for later in nodes[idx + 1:]:
+            if later.op in {"paged_attention_decode", "grouped_query_attention"} and list(later.inputs[:3]) == list(node.outputs[:3]):
+                return later
+        return None
+
+    def _attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attrs: dict[str, Any], *,
+                   appended: bool = False) -> torch.Tensor:
         eng = self.engine
         layer = int(attrs.get("layer", 0))
         heads, kv_heads, head_dim = int(attrs["num_heads"]), int(attrs["num_kv_heads"]), int(attrs["head_dim"])
@@ -442,7 +484,8 @@ class _DecodePlan:
         if not hasattr(self, "_attn_ws") or self._attn_ws.numel() * 4 < ws_bytes:
             self._attn_ws = torch.empty((max(1, (ws_bytes + 3) // 4),), device=eng.device, dtype=torch.float32)
         ws = self._attn_ws if ws_bytes else None
-        self._emit(lambda: ops.kv_append(k, v, k_pool, v_pool, self.page_table, self.positions), "b200.kv_append")
+        if not appended:   # (the fused QKV kernel has already written the new rows)
+            self._emit(lambda: ops.kv_append(k, v, k_pool, v_pool, self.page_table, self.positions), "b200.kv_append")
         self._emit(lambda: ops.paged_attention_decode_batch(q3, k_pool, v_pool, self.page_table, self.seq_lens, out=out3,
                                                             num_splits=splits, workspace=ws),
                    "b200.paged_attention_decode_batch.persistent_shared", launches=2 if splits > 1 else 1)

@@ -176,6 +176,34 @@ int cacheir_b200_qgemv_ex(const void* x, const void* packed, const void* scales,
                           int epilogue, int weight_layout, void* workspace,
                           size_t workspace_bytes, void* stream);
 
+/* The fused QKV projection of a decode step on int8 weights (fp16 activations, M <= 64):
+ * qkv[M, N] = x W^T with W = [Wq; Wk; Wv] (N = q_dim + 2*k_dim), then, in the same kernel,
+ * interleaved-pair RoPE on the q and k heads at positions[m] and the new k / v rows written
+ * into the page pool at (page_table[m][pos / page_size], kv head, pos % page_size).
+ *
+ * Replaces: the matmul of `fused_rmsnorm_qkv_rope` / `quantized_matmul`
+ *   (cacheir/runtime/cuda.py:932-954), `_rope_with_offsets` (:1072-1102) and the cache
+ *   append that opens `_try_triton_decode_attention_batch` (:1183-1229) for the batched
+ *   decode step; results are bit-identical to cacheir_b200_qgemv_ex followed by
+ *   cacheir_b200_rope_inplace and cacheir_b200_kv_append.
+ * `rope_table` holds (cos, sin) float pairs [rope_table_positions][head_dim/2] written by
+ * cacheir_b200_rope_table and must cover every position in use: a position outside it is
+ * left unrotated and recorded in cacheir_b200_device_status.
+ * `weight_layout`: CACHEIR_B200_LAYOUT_TILED and/or CACHEIR_B200_X_PREQUANTIZED. Needs the
+ * workspace of cacheir_b200_qgemv_workspace_bytes(M, K). Returns CACHEIR_B200_EUNSUPPORTED
+ * for shapes outside the integer tensor-core kernel (call the three separate entry points). */
+int cacheir_b200_qkv_rope_append(const void* x, const void* packed, const void* scales,
+                                 const float* zero_points, void* qkv, int M, int N, int K,
+                                 int scale_dtype, long long x_stride, int weight_layout, int q_dim,
+                                 int k_dim, int head_dim, float theta, const float* rope_table,
+                                 int rope_table_positions, const int32_t* positions,
+                                 const int32_t* page_table, int max_pages_per_seq, int page_size,
+                                 void* k_cache, void* v_cache, void* workspace,
+                                 size_t workspace_bytes, void* stream);
+/* table[pos][i] = (cos, sin)(pos * theta^(-2i/head_dim)) in fp32 for pos < positions, the
+ * values cacheir_b200_rope_inplace evaluates on the fly. 8 * positions * head_dim/2 bytes. */
+int cacheir_b200_rope_table(float* table, int positions, int head_dim, float theta, void* stream);
+
 /* The activation pre-pass of the integer tensor-core path on its own, and fused with RMSNorm
  * (`_rms_norm`, cacheir/runtime/cuda.py:889-895, followed by `_quantized_matmul`, :932-940):
  * both leave x as 16-bit fixed point per row in `workspace` (>= cacheir_b200_qgemv_workspace_bytes

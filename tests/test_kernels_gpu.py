@@ -530,3 +530,67 @@ def test_rms_norm_quantize_and_prequantized_gemm_match_the_two_step_path():
         assert _rel(got, base) <= TOL[torch.float16]
     torch.cuda.synchronize()
     _device_status_ok()
+
+
+# ---- fused QKV projection + RoPE + cache append == the three separate kernels, bit for bit ----
+@pytest.mark.parametrize("k,tiled", [(1024, True), (1024, False), (256, True)])   # K=1024: cluster split-K; K=256: one CTA per tile
+def test_qkv_rope_append_equals_separate_kernels(k, tiled):
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul, to_tiled
+    rng = np.random.default_rng(k + int(tiled))
+    m, head_dim, heads, kv_heads, page, max_pages, theta = 13, 128, 4, 2, 16, 6, 10000.0
+    q_dim, k_dim = heads * head_dim, kv_heads * head_dim
+    n = q_dim + 2 * k_dim
+    x, packed = _qgemv_case(rng, m, n, k, 8, torch.float16)
+    rows = _device_pack(packed)
+    weight = to_tiled(rows) if tiled else rows
+    slots = m * max_pages + 3
+    table_np = rng.permutation(slots)[: m * max_pages].astype(np.int32).reshape(m, max_pages)
+    # positions inside the table of cos/sin, one of them without a reserved page
+    pos_np = rng.integers(0, 60, m).astype(np.int32)
+    pos_np[5] = page * max_pages + 2
+    positions = torch.from_numpy(pos_np).cuda()
+    page_table = torch.from_numpy(table_np).cuda()
+    pools = [torch.from_numpy(rng.standard_normal((slots, kv_heads, page, head_dim)).astype(np.float32)).half().cuda() for _ in range(4)]
+    k_ref, v_ref, k_fused, v_fused = pools[0], pools[1], pools[0].clone(), pools[1].clone()
+    ws = torch.empty(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
+    xd = x.cuda()
+    # separate kernels
+    qkv_ref = quantized_matmul(xd, weight, workspace=ws)
+    ops.rope_inplace(qkv_ref[:, : q_dim + k_dim], positions, num_heads=heads + kv_heads, head_dim=head_dim, theta=theta)
+    ops.kv_append(qkv_ref[:, q_dim:q_dim + k_dim], qkv_ref[:, q_dim + k_dim:], k_ref, v_ref, page_table, positions)
+    # fused kernel
+    rope = ops.rope_table(page * max_pages + 3, head_dim, theta, xd.device)
+    qkv = torch.empty_like(qkv_ref)
+    ops.qkv_rope_append(xd, weight.packed_values, weight.scales, weight.zero_points, qkv, n=n, k=k, q_dim=q_dim, k_dim=k_dim,
+                        head_dim=head_dim, theta=theta, table=rope, positions=positions, page_table=page_table,
+                        k_cache=k_fused, v_cache=v_fused, workspace=ws, tiled=weight.tiled)
+    torch.cuda.synchronize()
+    assert torch.equal(qkv, qkv_ref)
+    assert torch.equal(k_fused, k_ref) and torch.equal(v_fused, v_ref)
+    # the append really happened for a row with a page, and not for the row without one
+    b = 0
+    slot, off = int(table_np[b, pos_np[b] // page]), int(pos_np[b] % page)
+    assert torch.equal(k_fused[slot, :, off].reshape(-1), qkv[b, q_dim:q_dim + k_dim])
+    assert torch.equal(v_fused[slot, :, off].reshape(-1), qkv[b, q_dim + k_dim:])
+    # pre-quantized activations give the same result without reading x
+    ops.quantize_activations(xd, ws)
+    qkv2 = torch.empty_like(qkv)
+    ops.qkv_rope_append(None, weight.packed_values, weight.scales, weight.zero_points, qkv2, n=n, k=k, q_dim=q_dim, k_dim=k_dim,
+                        head_dim=head_dim, theta=theta, table=rope, positions=positions, page_table=page_table,
+                        k_cache=k_fused, v_cache=v_fused, workspace=ws, tiled=weight.tiled, prequantized=True)
+    assert torch.equal(qkv2, qkv_ref)
+    _device_status_ok()
+    # a position outside the table is reported through the device status word, not computed silently
+    ops.qkv_rope_append(None, weight.packed_values, weight.scales, weight.zero_points, qkv2, n=n, k=k, q_dim=q_dim, k_dim=k_dim,
+                        head_dim=head_dim, theta=theta, table=rope[:8].contiguous(), positions=positions, page_table=page_table,
+                        k_cache=k_fused, v_cache=v_fused, workspace=ws, tiled=weight.tiled, prequantized=True)
+    torch.cuda.synchronize()
+    from cacheir_b200 import _lib
+    assert _lib.load().cacheir_b200_device_status(1) != 0
+    assert _lib.load().cacheir_b200_device_status(1) == 0        # cleared by the read above
+    # the cos/sin table holds what rope_inplace evaluates
+    want = oracle.rope_one(np.ones((1, 1, head_dim), dtype=np.float32), head_dim, theta, np.array([37]))
+    got = rope[37].cpu().numpy()
+    np.testing.assert_allclose(got[:, 0] - got[:, 1], want.reshape(-1)[0::2], rtol=0, atol=1e-5)
+    _device_status_ok()
