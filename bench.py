@@ -263,7 +263,7 @@ def time_gemv_kernels(rt, cfg: dict, iters: int = 3) -> list[dict]:
         epi = ops.EPI_SWIGLU if name == "gate_up" else ops.EPI_NONE
         x = torch.randn((B, k), device=rt.device, dtype=torch.float16)
         out = torch.empty((B, n // 2 if epi == ops.EPI_SWIGLU else n), device=rt.device, dtype=torch.float16)
-        scratch = torch.empty(ops.qgemv_workspace_bytes(B, k), device=rt.device, dtype=torch.uint8)
+        scratch = torch.zeros(ops.qgemv_workspace_bytes(B, k), device=rt.device, dtype=torch.uint8)
 
         def sweep(ws=ws, x=x, out=out, epi=epi, scratch=scratch) -> None:
             for w in ws:
@@ -449,7 +449,7 @@ def run_micro(args) -> None:
             packed = [ops.pack_relayout(w, n=n, k=k, bits=bits, paired=paired) for w in packed]
         ws = None
         if args.workspace:
-            ws = torch.empty(ops.qgemv_workspace_bytes(m, k), device=dev, dtype=torch.uint8)
+            ws = torch.zeros(ops.qgemv_workspace_bytes(m, k), device=dev, dtype=torch.uint8)
 
         def launch(i: int) -> None:
             ops.qgemv(x, packed[i % copies], scales, zeros, bits=bits, n=n, k=k, group_size=args.group, epilogue=epi,

@@ -101,6 +101,11 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// silu(g) = g / (1 + e^-g) for the fused epilogues. The quotient uses the reciprocal unit directly:
+// when e^-g overflows (g below about -88) the denominator is infinite and a full IEEE division would
+// detour through its slow path on every such element; here the reciprocal is 0 and the result -0.
+__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+
 // ---- RoPE arithmetic shared by the stand-alone kernel, the table builder and the fused epilogue
 // (one definition, so the three produce the same bits). Interleaved pairs (2i, 2i+1);
 // angle = pos * theta^(-2i/D), evaluated in fp32 like the reference (cacheir/runtime/cuda.py:1072-1102).

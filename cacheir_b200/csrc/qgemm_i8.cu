@@ -41,10 +41,18 @@ constexpr float kQMax = 32639.f;      // 127*256 + 127: every value splits into 
 __device__ int g_i8_status = 0;
 
 #ifdef CB200_QGEMM_TRACE
+__device__ unsigned long long g_i8_cta_trace[2048][4];   // per CTA: global timer at entry, first data, accumulator complete, exit
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define CB200_CTA_TRACE(slot) do { const int c_ = blockIdx.y * gridDim.x + blockIdx.x; if (c_ < 2048) g_i8_cta_trace[c_][slot] = global_ns(); } while (0)
 __device__ long long g_i8_trace[4][256][4];
 #define CB200_TRACE(role, i, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 256) g_i8_trace[role][i][slot] = clock64(); } while (0)
 #else
 #define CB200_TRACE(role, i, slot) do { } while (0)
+#define CB200_CTA_TRACE(slot) do { } while (0)
 #endif
 
 __host__ __device__ constexpr int stage_bytes(int mp) { return kBlockN * kBlockK + 2 * mp * kBlockK; }
@@ -299,12 +307,16 @@ constexpr int kPairRows = 64;
 
 // y value from the exact integer sums: (256*hi + lo - zero*qsum) as float. Integer zero points (what the
 // reference packer produces) are handled in 64-bit integers, anything else in double precision.
+// (The double-precision form is rare and kept out of line so that the epilogues stay short.)
+__device__ __noinline__ float recombine_fractional(int32_t hi, int32_t lo, float zero, int qsum) {
+  return static_cast<float>(256.0 * hi + static_cast<double>(lo) - static_cast<double>(zero) * qsum);
+}
 __device__ __forceinline__ float recombine(int32_t hi, int32_t lo, float zero, int qsum) {
   if (zero == rintf(zero) && fabsf(zero) < 1.0e9f) {
-    const long long v = 256LL * hi + lo - static_cast<long long>(zero) * qsum;
+    const long long v = 256LL * hi + lo - static_cast<long long>(__float2int_rn(zero)) * qsum;
     return static_cast<float>(v);
   }
-  return static_cast<float>(256.0 * hi + static_cast<double>(lo) - static_cast<double>(zero) * qsum);
+  return recombine_fractional(hi, lo, zero, qsum);
 }
 
 template <int MP, int SPLIT, bool ROPE>
@@ -339,6 +351,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   if (threadIdx.x == 64) CB200_TRACE(3, 0, 0);
+  if (threadIdx.x == 64) CB200_CTA_TRACE(0);
   const bool swiglu = p.epilogue == CACHEIR_B200_EPI_SWIGLU;
   constexpr int split = SPLIT;
   const int krank = split > 1 ? static_cast<int>(cluster_ctarank()) : 0;
@@ -415,6 +428,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
         CB200_TRACE(1, i, 0);
         if (!mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, &g_i8_status, (3 << 8) | 2)) break;
         CB200_TRACE(1, i, 1);
+        if (i == 0) CB200_CTA_TRACE(1);
         tc_fence_after();
         const uint32_t d = tmem_base;
         const uint32_t w_base = smem_u32(s_w + s * kWBytes);
@@ -509,6 +523,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
     bool ok = mbar_wait(smem_u32(acc_full), 0, &g_i8_status, (3 << 8) | 3);
     tc_fence_after();
     if (threadIdx.x == 64) CB200_TRACE(3, 0, 2);
+    if (threadIdx.x == 64) CB200_CTA_TRACE(2);
     const bool store = ok && n_out_idx < p.n_out;
     if constexpr (SPLIT > 1) {
       // All-to-all over the cluster. Each rank lays its partial sums out per destination in its own
@@ -599,10 +614,9 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
       }
       cluster_wait();                                // phase B: every rank has received everything, this CTA's copies included
     } else if (swiglu) {
-      // gate rows keep their values in registers, up rows hand theirs over through the drained ring
+      // eight batch rows at a time: up rows hand their values over through the drained ring, gate rows finish
       float* s_up = reinterpret_cast<float*>(smem);          // [MP][64]
-      float g[MP];
-#pragma unroll
+#pragma unroll 1
       for (int c0 = 0; c0 < MP; c0 += 8) {
         uint32_t hi[8], lo[8];
         if (total > 0) {
@@ -613,23 +627,28 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) { hi[j] = 0u; lo[j] = 0u; }
         }
+        if (threadIdx.x == 64) CB200_TRACE(2, c0 / 8, 0);
+        float g[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int m = c0 + j;
-          const float v = recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, s_qsum[m]) * (scale * s_sx[m]);
-          g[m] = v;
-          if (is_up) s_up[m * kPairRows + (r - kPairRows)] = v;
+          g[j] = recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, s_qsum[m]) * (scale * s_sx[m]);
+          if (is_up) s_up[m * kPairRows + (r - kPairRows)] = g[j];
         }
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!is_up && store) {
+        if (threadIdx.x == 64) CB200_TRACE(2, c0 / 8, 1);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) CB200_TRACE(2, c0 / 8, 2);
+        if (!is_up && store) {
 #pragma unroll
-        for (int m = 0; m < MP; ++m) {
-          if (m < p.M) {
-            const float u = s_up[m * kPairRows + r];
-            y[static_cast<size_t>(m) * p.n_out + n_out_idx] = __float2half_rn((g[m] / (1.f + __expf(-g[m]))) * u);
+          for (int j = 0; j < 8; ++j) {
+            const int m = c0 + j;
+            if (m < p.M) {
+              const float u = s_up[m * kPairRows + r];
+              y[static_cast<size_t>(m) * p.n_out + n_out_idx] = __float2half_rn(silu_fast(g[j]) * u);
+            }
           }
         }
+        if (threadIdx.x == 64) CB200_TRACE(2, c0 / 8, 3);
       }
     } else {
 #pragma unroll 1
@@ -677,6 +696,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
     tc_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 64) CB200_TRACE(3, 1, 3);
+  if (threadIdx.x == 64) CB200_CTA_TRACE(3);
 }
 
 // CTAs per cluster along K. Every doubling adds cluster-barrier and exchange time to the epilogue, so the
@@ -797,6 +817,9 @@ int launch_qgemm_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) 
 }
 
 #ifdef CB200_QGEMM_TRACE
+extern "C" int cacheir_b200_debug_cta_trace_i8(unsigned long long* out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_i8_cta_trace, sizeof(unsigned long long) * 2048 * 4));
+}
 extern "C" int cacheir_b200_debug_trace_i8(long long* out) {
   return static_cast<int>(cudaMemcpyFromSymbol(out, g_i8_trace, sizeof(long long) * 4 * 256 * 4));
 }

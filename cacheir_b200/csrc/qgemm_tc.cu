@@ -468,7 +468,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           const size_t o = static_cast<size_t>(m) * p.n_out + n_out_idx;
           if (swiglu) {
             const float u = acc[1][j] * row_scale[1];
-            v = (v / (1.f + __expf(-v))) * u;
+            v = silu_fast(v) * u;
           } else if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
             v += __half2float(res[o]);
           }

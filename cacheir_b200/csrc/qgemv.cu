@@ -143,7 +143,7 @@ qgemv_cuda_core_kernel(const QGemvParams p) {
       const size_t o = static_cast<size_t>(m0 + m) * n_out_total + n_out;
       float v = result[0][m];
       if (p.epilogue == CACHEIR_B200_EPI_SWIGLU) {
-        v = (v / (1.f + __expf(-v))) * result[1][m];
+        v = silu_fast(v) * result[1][m];
       } else if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
         v += Elem<XT>::ld(static_cast<const XT*>(p.residual) + o);
       }

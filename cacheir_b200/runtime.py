@@ -276,7 +276,7 @@ class _DecodePlan:
 
         if eng.dtype == torch.float16 and eng.quant:
             widest = max(int(eng.config.hidden_size), int(eng.config.intermediate_size))
-            self._gemm_ws = torch.empty((ops.qgemv_workspace_bytes(self.batch, widest),), device=eng.device, dtype=torch.uint8)
+            self._gemm_ws = torch.zeros((ops.qgemv_workspace_bytes(self.batch, widest),), device=eng.device, dtype=torch.uint8)
         self._emit(lambda: ops.advance_positions(self.positions, self.seq_lens), "b200.advance_positions")
         skip: set[int] = set()
         for idx, node in enumerate(nodes):
@@ -455,7 +455,7 @@ class _DecodePlan:
         if ws is None or ws.numel() < need:
             if ws is not None and self.program:
                 raise RuntimeError("GEMM workspace must be sized before the first projection is lowered")
-            self._gemm_ws = ws = torch.empty((need,), device=self.engine.device, dtype=torch.uint8)
+            self._gemm_ws = ws = torch.zeros((need,), device=self.engine.device, dtype=torch.uint8)
         return ws
 
     @staticmethod

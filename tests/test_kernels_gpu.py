@@ -396,7 +396,7 @@ def test_qgemm_int8_tensor_core_with_workspace(m, n, k):
     from cacheir_b200.quantization import quantized_matmul
     rng = np.random.default_rng(m * 31 + n + k)
     x, packed = _qgemv_case(rng, m, n, k, 8, torch.float16)
-    ws = torch.empty(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
     y = quantized_matmul(x.cuda(), _device_pack(packed), workspace=ws)
     torch.cuda.synchronize()
     _device_status_ok()
@@ -421,7 +421,7 @@ def test_qgemm_int8_tensor_core_epilogues_offsets_and_determinism():
     dev.zero_points[9] = 100.5
     host = oracle.PackedQuantizedTensor(packed.packed_values, packed.scales, dev.zero_points.cpu().numpy(), 8, (n, k))
     base = oracle.quantized_matmul(x.float().numpy(), host)
-    ws = torch.empty(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
     y = quantized_matmul(x.cuda(), dev, workspace=ws)
     rows = [i for i in range(m) if i != 7]      # row 7 overflows fp16 in the oracle too
     assert _rel(y[rows], base[rows]) <= TOL[torch.float16]
@@ -469,7 +469,7 @@ def test_pack_relayout_roundtrip_and_gemm_equivalence(bits, n, k):
     y_tiled = quantized_matmul(x.cuda(), tiled)
     assert torch.equal(y_rows, y_tiled)
     if bits == 8:
-        ws = torch.empty(ops.qgemv_workspace_bytes(32, k), dtype=torch.uint8, device="cuda")
+        ws = torch.zeros(ops.qgemv_workspace_bytes(32, k), dtype=torch.uint8, device="cuda")
         assert torch.equal(quantized_matmul(x.cuda(), rows, workspace=ws), quantized_matmul(x.cuda(), tiled, workspace=ws))
     if n % 256 == 0:
         a = quantized_matmul(x.cuda(), rows, epilogue=ops.EPI_SWIGLU)
@@ -486,7 +486,7 @@ def test_pack_relayout_roundtrip_and_gemm_equivalence(bits, n, k):
                 chunks = tp[1, 0, r].reshape(tb // 16, 16)
                 np.testing.assert_array_equal(np.stack([chunks[c ^ key] for c in range(tb // 16)]).reshape(-1), ref[src, :tb])
         if bits == 8:
-            ws = torch.empty(ops.qgemv_workspace_bytes(32, k), dtype=torch.uint8, device="cuda")
+            ws = torch.zeros(ops.qgemv_workspace_bytes(32, k), dtype=torch.uint8, device="cuda")
             a = quantized_matmul(x.cuda(), rows, epilogue=ops.EPI_SWIGLU, workspace=ws)
             b = quantized_matmul(x.cuda(), paired, epilogue=ops.EPI_SWIGLU, workspace=ws)
             assert torch.equal(a, b)
@@ -508,7 +508,7 @@ def test_rms_norm_quantize_and_prequantized_gemm_match_the_two_step_path():
         res = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).half().cuda()
         w = torch.from_numpy(rng.standard_normal((k,)).astype(np.float32)).half().cuda()
         dev = _device_pack(packed)
-        ws = torch.empty(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
+        ws = torch.zeros(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
         # two-step: rms_norm (+residual) to fp16, then the GEMM with its own pre-pass
         summed = torch.empty_like(res)
         normed = ops.rms_norm(x.cuda(), w, 1e-5, residual=res, sum_out=summed)
@@ -553,7 +553,7 @@ def test_qkv_rope_append_equals_separate_kernels(k, tiled):
     page_table = torch.from_numpy(table_np).cuda()
     pools = [torch.from_numpy(rng.standard_normal((slots, kv_heads, page, head_dim)).astype(np.float32)).half().cuda() for _ in range(4)]
     k_ref, v_ref, k_fused, v_fused = pools[0], pools[1], pools[0].clone(), pools[1].clone()
-    ws = torch.empty(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
     xd = x.cuda()
     # separate kernels
     qkv_ref = quantized_matmul(xd, weight, workspace=ws)
