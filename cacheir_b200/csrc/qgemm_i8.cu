@@ -305,16 +305,23 @@ struct I8Params {
 // accumulator, and twice as many CTAs as whole-half tiles would give.
 constexpr int kPairRows = 64;
 
-// y value from the exact integer sums: (256*hi + lo - zero*qsum) as float. Integer zero points (what the
-// reference packer produces) are handled in 64-bit integers, anything else in double precision.
+// y value from the exact integer sums: (256*hi + lo - zero*qsum) as float. Integer zero points in
+// [-255, 255] (what the reference packer produces) are handled in integers, anything else in double precision.
 // (The double-precision form is rare and kept out of line so that the epilogues stay short.)
 __device__ __noinline__ float recombine_fractional(int32_t hi, int32_t lo, float zero, int qsum) {
   return static_cast<float>(256.0 * hi + static_cast<double>(lo) - static_cast<double>(zero) * qsum);
 }
-__device__ __forceinline__ float recombine(int32_t hi, int32_t lo, float zero, int qsum) {
-  if (zero == rintf(zero) && fabsf(zero) < 1.0e9f) {
-    const long long v = 256LL * hi + lo - static_cast<long long>(__float2int_rn(zero)) * qsum;
-    return static_cast<float>(v);
+// `zero_int` is the zero point as an integer and `zero_is_int` says whether that is exact; both are
+// per-thread constants worked out once, outside the loops over the batch rows.
+__device__ __forceinline__ float recombine(int32_t hi, int32_t lo, float zero, int zero_int, bool zero_is_int, int qsum) {
+  if (zero_is_int) {
+    // 32-bit arithmetic only (64-bit integer math and its conversion cost several times more issue
+    // slots): with qsum = 256*qh + ql, v = 256*(hi - z*qh) + (lo - z*ql); both brackets fit in 32 bits
+    // for |z| <= 255. The float of v is exact-rounded while the first bracket is below 2^24
+    // (|v| < 2^32, far above what cancelled sums reach), and within 1.5 units in the last place beyond.
+    const int a = hi - zero_int * (qsum >> 8);
+    const int b = lo - zero_int * (qsum & 255);
+    return fmaf(static_cast<float>(a), 256.f, static_cast<float>(b));
   }
   return recombine_fractional(hi, lo, zero, qsum);
 }
@@ -464,6 +471,8 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
                                                 : static_cast<const float*>(p.scales)[w_row];
       if (p.zero_points) zero = p.zero_points[w_row];
     }
+    const bool zero_is_int = zero == rintf(zero) && fabsf(zero) <= 255.f;
+    const int zero_int = zero_is_int ? __float2int_rn(zero) : 0;
     float res_v[MS];
 #pragma unroll
     for (int j = 0; j < MS; ++j) {
@@ -599,9 +608,9 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
 #pragma unroll
             for (int jj = 0; jj < MS; ++jj)
               if (jj == u0 + j) { cs = cs_v[jj]; off = off_v[jj]; }
-            rope_finish(recombine(sum[0][j], sum[1][j], zero, s_qsum[m]) * (scale * s_sx[m]), cs, off, m, m < p.M && store && ok);
+            rope_finish(recombine(sum[0][j], sum[1][j], zero, zero_int, zero_is_int, s_qsum[m]) * (scale * s_sx[m]), cs, off, m, m < p.M && store && ok);
           } else if (m < p.M && store && ok) {
-            float out = recombine(sum[0][j], sum[1][j], zero, s_qsum[m]) * (scale * s_sx[m]);
+            float out = recombine(sum[0][j], sum[1][j], zero, zero_int, zero_is_int, s_qsum[m]) * (scale * s_sx[m]);
             if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
               float rv = 0.f;
 #pragma unroll
@@ -632,7 +641,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int m = c0 + j;
-          g[j] = recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, s_qsum[m]) * (scale * s_sx[m]);
+          g[j] = recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, zero_int, zero_is_int, s_qsum[m]) * (scale * s_sx[m]);
           if (is_up) s_up[m * kPairRows + (r - kPairRows)] = g[j];
         }
         if (threadIdx.x == 64) CB200_TRACE(2, c0 / 8, 1);
@@ -669,10 +678,10 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
             float2 cs;
             long long off;
             rope_row(m, &cs, &off);
-            rope_finish(recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, s_qsum[m]) * (scale * s_sx[m]),
+            rope_finish(recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, zero_int, zero_is_int, s_qsum[m]) * (scale * s_sx[m]),
                         cs, off, m, m < p.M && store);
           } else if (m < p.M && store) {
-            float out = recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, s_qsum[m]) * (scale * s_sx[m]);
+            float out = recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, zero_int, zero_is_int, s_qsum[m]) * (scale * s_sx[m]);
             const size_t o = static_cast<size_t>(m) * p.n_out + n_out_idx;
             if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) out += __half2float(res[o]);
             y[o] = __float2half_rn(out);
@@ -802,7 +811,7 @@ size_t qgemm_i8_workspace_bytes(int M, int K) {
 bool qgemm_i8_supported(const QGemvParams& q, const void* workspace, size_t workspace_bytes) {
   if (q.x_dtype != CACHEIR_B200_F16 || q.bits != 8 || q.group_size != 0) return false;
   if (q.M < 1 || q.M > 64) return false;
-  if (q.K % kBlockK != 0 || q.K < kBlockK) return false;
+  if (q.K % kBlockK != 0 || q.K < kBlockK || q.K > 32768) return false;   // 32-bit accumulators and epilogue arithmetic
   if (q.epilogue == CACHEIR_B200_EPI_SWIGLU && ((q.N / 2) % kPairRows != 0 || (q.tiled && !q.paired))) return false;
   if (q.paired && !(q.tiled && q.epilogue == CACHEIR_B200_EPI_SWIGLU)) return false;
   if (!workspace || workspace_bytes < qgemm_i8_workspace_bytes(q.M, q.K) || !aligned_to(workspace, 128)) return false;
