@@ -194,7 +194,19 @@ argmax_rows_kernel(const T* __restrict__ logits, int64_t* __restrict__ out_ids, 
   const T* row = logits + static_cast<size_t>(blockIdx.x) * vocab;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int c = threadIdx.x; c < vocab; c += blockDim.x) {
+  constexpr int VEC = sizeof(T) == 2 ? 8 : 4;     // 16-byte loads when the row allows it
+  int done = 0;
+  if (vocab % VEC == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    for (int c = threadIdx.x * VEC; c < vocab; c += blockDim.x * VEC) {
+      float v[VEC];
+      VecIO<T, VEC>::ld(row + c, v);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i)      // ascending index inside the vector: the first maximum wins
+        if (v[i] > best || (v[i] == best && c + i < best_i)) { best = v[i]; best_i = c + i; }
+    }
+    done = vocab;
+  }
+  for (int c = done + threadIdx.x; c < vocab; c += blockDim.x) {
     const float v = Elem<T>::ld(row + c);
     if (v > best || (v == best && c < best_i)) { best = v; best_i = c; }
   }

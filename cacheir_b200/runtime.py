@@ -35,6 +35,7 @@ from . import ops
 from .artifact import CompileArtifact
 from .kv_cache import B200KVPageAllocator, B200PagedKVCache
 from .quantization import B200PackedWeight, concat_rows, quant_bits, to_rows, to_tiled
+from .tensor_parallel import TensorParallel, shard_columns, shard_rows
 from .weights import B200WeightStore, TensorSource
 
 
@@ -124,8 +125,9 @@ class _Engine:
 
     def __init__(self, artifact: Any, *, device: torch.device, dtype: torch.dtype, weights: B200WeightStore | None,
                  tensor_source: Any, kv_allocator: B200KVPageAllocator | None, max_seq_len: int | None,
-                 use_cuda_graph: bool, attention_splits: int, max_plans: int):
+                 use_cuda_graph: bool, attention_splits: int, max_plans: int, tensor_parallel: TensorParallel | None = None):
         self.artifact = artifact
+        self.tp = tensor_parallel or TensorParallel(0, 1)
         self.device = device
         self.dtype = dtype
         self.graph = artifact.graph("decode")
@@ -141,10 +143,15 @@ class _Engine:
         self.allocator = kv_allocator or B200KVPageAllocator(page_size=self.page_size)
         if self.allocator.page_size != self.page_size:
             raise ValueError("kv_allocator page_size differs from the artifact's decode page size")
+        self.tp.check_model(heads=int(self.config.num_attention_heads), kv_heads=int(self.config.num_key_value_heads),
+                            intermediate=int(self.config.intermediate_size), vocab=int(self.config.vocab_size))
+        # under tensor parallelism a rank's pool holds only its own KV heads
         self.allocator.configure(torch=torch, device=device, dtype=dtype, num_layers=int(self.config.num_layers),
-                                 kv_heads=int(self.config.num_key_value_heads), head_dim=int(self.config.head_dim))
+                                 kv_heads=int(self.config.num_key_value_heads) // self.tp.world,
+                                 head_dim=int(self.config.head_dim))
         self.max_seq_len = int(max_seq_len or self.config.max_position_embeddings)
-        self.use_cuda_graph = use_cuda_graph
+        # Collectives are launched eagerly for now: a tensor-parallel step is not captured into a CUDA graph
+        self.use_cuda_graph = use_cuda_graph and not self.tp.enabled
         self.tile_weights = True
         self._rope_tables: dict[tuple[int, float], torch.Tensor] = {}
         self.attention_splits = int(attention_splits)
@@ -160,22 +167,31 @@ class _Engine:
         self.kernel_counts[name] = self.kernel_counts.get(name, 0) + n
 
     # -- weights as the kernels want them -------------------------------------------
-    def matmul_weight(self, names: tuple[str, ...], quantized: bool, batch: int = 1) -> B200PackedWeight | torch.Tensor:
+    def matmul_weight(self, names: tuple[str, ...], quantized: bool, batch: int = 1,
+                      role: str = "column") -> B200PackedWeight | torch.Tensor:
         """One (row-concatenated) weight for a matmul-family node: packed when the
         node is a quantized op, dense [N, K] otherwise (cuda.py:1017-1023 caches the
         same concatenation for its unquantized fused ops). Batches beyond the tensor-core
         kernels' 64 rows run on the CUDA-core kernel, which reads the reference's row
-        order: the first such batch moves the weight back to rows for good."""
+        order: the first such batch moves the weight back to rows for good.
+        `role` says how tensor parallelism slices it: "column" (output rows, each fused
+        part separately so a rank keeps whole heads / matching gate and up rows), "row"
+        (the input dimension) or "replicated"."""
         if names in self.fused_weights:
             fused = self.fused_weights[names]
             if batch > 64 and isinstance(fused, B200PackedWeight) and fused.tiled:
                 self.tile_weights = False
                 fused = self.fused_weights[names] = to_rows(fused)
             return fused
+        def shard(w):
+            if not self.tp.enabled or role == "replicated":
+                return w
+            return shard_rows(w, self.tp) if role == "column" else shard_columns(w, self.tp)
+
         if quantized:
-            parts = [self.weights.get_quantized(n) for n in names]
+            parts = [shard(self.weights.get_quantized(n)) for n in names]
             fused = parts[0] if len(parts) == 1 else concat_rows(parts)
-            if len(parts) > 1:   # the concatenation replaces the parts: keep one copy of the codes in HBM
+            if len(parts) > 1 or self.tp.enabled:   # the concatenation / shard replaces the parts: keep one copy of the codes in HBM
                 for n in names:
                     self.weights.release(n)
             # device pack layout: tile order for the tensor-core kernels (fp16 activations, K a multiple of 128).
@@ -191,7 +207,7 @@ class _Engine:
                     self.weights.release(names[0])
                 fused = tiled
         else:
-            dense = [self.weights.get(n) for n in names]
+            dense = [shard(self.weights.get(n)) for n in names]
             fused = dense[0] if len(dense) == 1 else torch.cat(dense, dim=0).contiguous()
             if len(dense) > 1:
                 for n in names:
@@ -309,24 +325,38 @@ class _DecodePlan:
                     env[node.outputs[0]] = out
             elif op in {"matmul", "quantized_matmul"}:
                 x = env[node.inputs[0]]
-                weight = eng.matmul_weight((node.inputs[1],), op == "quantized_matmul", self.batch)
+                tp = eng.tp
+                projection = attrs.get("projection")
+                role = "replicated"
+                if tp.enabled:   # o / down consume a rank-local activation slice; lm_head produces a vocabulary slice
+                    role = {"o": "row", "down": "row", "lm_head": "column"}.get(projection, "replicated")
+                weight = eng.matmul_weight((node.inputs[1],), op == "quantized_matmul", self.batch, role)
                 out_name = node.outputs[0]
                 nxt = nodes[idx + 1] if idx + 1 < len(nodes) else None
                 residual = None
                 if (nxt is not None and nxt.op == "add" and out_name in nxt.inputs and uses.get(out_name, 0) == 1
                         and nxt.inputs[0] != nxt.inputs[1]):
                     other = nxt.inputs[0] if nxt.inputs[1] == out_name else nxt.inputs[1]
-                    residual = env[other]
+                    # a row-parallel projection yields partial sums: the residual joins on rank 0 only
+                    residual = env[other] if (role != "row" or tp.rank == 0) else None
                     skip.add(idx + 1)
                     out_name = nxt.outputs[0]
                 out = self._matmul(x, weight, residual=residual, prequantized=node.inputs[0] in self._prequantized)
+                if role == "row":
+                    self._emit(lambda out=out: tp.all_reduce_sum(out), "b200.tp.all_reduce", launches=0)
+                elif role == "column":
+                    local = out
+                    out = self._buf(int(local.shape[1]) * tp.world)
+                    gathered = torch.empty((tp.world * self.batch, int(local.shape[1])), device=eng.device, dtype=eng.dtype)
+                    self._emit(lambda local=local, gathered=gathered, out=out: tp.all_gather_columns(local, gathered, out),
+                               "b200.tp.all_gather", launches=0)
                 env[out_name] = out
             elif op in {"fused_rmsnorm_qkv_rope", "quantized_fused_rmsnorm_qkv_rope"}:
                 x, norm_w = env[node.inputs[0]], eng.weights.get(node.inputs[1])
                 weight = eng.matmul_weight(tuple(node.inputs[2:5]), op.startswith("quantized_"), self.batch)
                 eps = float(attrs.get("eps", 1e-6))
-                q_dim = self._rows_of(node.inputs[2])
-                k_dim = self._rows_of(node.inputs[3])
+                q_dim = self._rows_of(node.inputs[2]) // eng.tp.world      # whole heads per rank
+                k_dim = self._rows_of(node.inputs[3]) // eng.tp.world
                 head_dim = int(attrs["head_dim"])
                 theta = float(attrs.get("rope_theta", 10000.0))
                 consumer = self._attention_consumer(nodes, idx, node)
@@ -334,7 +364,7 @@ class _DecodePlan:
                     ws = self._gemm_workspace(int(x.shape[1]))
                     self._emit(lambda x=x, w=norm_w, eps=eps, ws=ws: ops.rms_norm_quantize(x, w, eps, ws), "b200.rms_norm_quantize")
                     pool = eng.allocator.pool_for_layer(int(consumer.attrs.get("layer", 0))) if consumer is not None else None
-                    if (pool is not None and self._rows_of(node.inputs[4]) == k_dim and pool["keys"].dtype == torch.float16
+                    if (pool is not None and self._rows_of(node.inputs[4]) // eng.tp.world == k_dim and pool["keys"].dtype == torch.float16
                             and int(pool["keys"].shape[3]) == head_dim and int(pool["keys"].shape[1]) * head_dim == k_dim):
                         # projection + RoPE + append of the new k/v rows in one kernel
                         n, k = weight.shape
@@ -471,6 +501,7 @@ class _DecodePlan:
         eng = self.engine
         layer = int(attrs.get("layer", 0))
         heads, kv_heads, head_dim = int(attrs["num_heads"]), int(attrs["num_kv_heads"]), int(attrs["head_dim"])
+        heads, kv_heads = heads // eng.tp.world, kv_heads // eng.tp.world      # this rank's heads
         pool = eng.allocator.pool_for_layer(layer)
         if pool is None:
             raise RuntimeError(f"no KV page pool for layer {layer}")
@@ -567,6 +598,7 @@ class B200DecodeRuntime:
         attention_splits: int = 0,
         max_plans: int = 8,
         clone_outputs: bool = True,
+        tensor_parallel: TensorParallel | None = None,
         _engine: _Engine | None = None,
     ):
         if isinstance(artifact, (str, Path)):
@@ -585,7 +617,7 @@ class B200DecodeRuntime:
             with torch.cuda.device(dev):
                 _engine = _Engine(artifact, device=dev, dtype=selected, weights=weights, tensor_source=tensor_source,
                                   kv_allocator=kv_allocator, max_seq_len=max_seq_len, use_cuda_graph=use_cuda_graph,
-                                  attention_splits=attention_splits, max_plans=max_plans)
+                                  attention_splits=attention_splits, max_plans=max_plans, tensor_parallel=tensor_parallel)
         self._engine = _engine
         self.artifact = _engine.artifact
         self.device = _engine.device

@@ -1,0 +1,115 @@
+"""Tensor parallelism for the decode step (the 70B-shaped configuration on 8 GPUs).
+
+Megatron-style split of one decoder layer over `world` ranks, applied to the
+reference's packed weights after quantization, so every rank holds a slice of the
+*same* integer codes the single-GPU model has:
+
+* column-parallel (rows of W sliced): Q, K, V (whole heads per rank), gate, up, lm_head.
+  Per-row scales and zero points are sliced with their rows.
+* row-parallel (the K dimension sliced): O and down. A row keeps its scale and zero
+  point; group-wise scales are sliced with their groups. Each rank produces a partial
+  sum over its K slice; the residual is added on rank 0 only and one all-reduce (sum)
+  completes the output on every rank.
+* each rank owns `kv_heads / world` KV heads, so its page pool holds only those heads
+  and attention needs no exchange; the page table is the same on every rank.
+* lm_head logits are all-gathered so every rank sees `[B, vocab]` and picks the same
+  greedy token.
+
+The reference has no multi-device execution (its CUDA runtime is one process on one
+device, cacheir/runtime/cuda.py:430-506); this module extends its per-layer graph
+(cacheir/importers/hf.py:171-268) without changing op names or weight formats.
+Collectives go through `torch.distributed` (NCCL on GPUs; gloo in the CPU tests).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from .quantization import B200PackedWeight
+
+
+@dataclass(frozen=True)
+class TensorParallel:
+    rank: int
+    world: int
+    group: Any = None          # a torch.distributed process group (None = the default group)
+
+    def __post_init__(self) -> None:
+        if self.world < 1 or not (0 <= self.rank < self.world):
+            raise ValueError(f"bad tensor-parallel rank {self.rank} of {self.world}")
+
+    @property
+    def enabled(self) -> bool:
+        return self.world > 1
+
+    def check_model(self, *, heads: int, kv_heads: int, intermediate: int, vocab: int) -> None:
+        for name, value in (("attention heads", heads), ("KV heads", kv_heads), ("intermediate size", intermediate),
+                            ("vocabulary", vocab)):
+            if value % self.world != 0:
+                raise ValueError(f"{name} ({value}) is not divisible by the tensor-parallel size {self.world}")
+
+    # -- collectives (enqueued on the current stream; NCCL captures into CUDA graphs) -------------
+    def all_reduce_sum(self, t: torch.Tensor) -> None:
+        if self.enabled:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+
+    def all_gather_columns(self, local: torch.Tensor, gathered: torch.Tensor, out: torch.Tensor) -> None:
+        """local [B, n] on every rank -> out [B, world*n] (rank r's columns at [r*n, (r+1)*n)).
+        `gathered` is a [world*B, n] staging buffer (rank-major)."""
+        if not self.enabled:
+            out.copy_(local)
+            return
+        dist.all_gather_into_tensor(gathered, local, group=self.group)
+        b, n = int(local.shape[0]), int(local.shape[1])
+        out.view(b, self.world, n).copy_(gathered.view(self.world, b, n).permute(1, 0, 2))
+
+
+def _rows(w: B200PackedWeight | torch.Tensor, start: int, stop: int) -> B200PackedWeight | torch.Tensor:
+    if isinstance(w, torch.Tensor):
+        return w[start:stop].contiguous()
+    if w.tiled:
+        raise ValueError("shard the reference row layout, then tile the shard")
+    zp = None if w.zero_points is None else w.zero_points[start:stop].contiguous()
+    zpi = None if w.zero_points_i32 is None else w.zero_points_i32[start:stop].contiguous()
+    scales = w.scales[start:stop].contiguous()
+    return B200PackedWeight(w.packed_values[start:stop].contiguous(), scales, zp, w.bits, (stop - start, w.shape[1]),
+                            group_size=w.group_size, zero_points_i32=zpi)
+
+
+def shard_rows(w: B200PackedWeight | torch.Tensor, tp: TensorParallel) -> B200PackedWeight | torch.Tensor:
+    """Column-parallel shard: rank r keeps output rows [r*N/world, (r+1)*N/world)."""
+    n = int(w.shape[0])
+    if n % tp.world != 0:
+        raise ValueError(f"{n} output rows do not split over {tp.world} ranks")
+    per = n // tp.world
+    return _rows(w, tp.rank * per, (tp.rank + 1) * per)
+
+
+def shard_columns(w: B200PackedWeight | torch.Tensor, tp: TensorParallel) -> B200PackedWeight | torch.Tensor:
+    """Row-parallel shard: rank r keeps input columns [r*K/world, (r+1)*K/world) of every row.
+    Rows keep their scale and zero point; group-wise scales are sliced with their groups."""
+    k = int(w.shape[1])
+    if k % tp.world != 0:
+        raise ValueError(f"{k} input columns do not split over {tp.world} ranks")
+    per = k // tp.world
+    lo, hi = tp.rank * per, (tp.rank + 1) * per
+    if isinstance(w, torch.Tensor):
+        return w[:, lo:hi].contiguous()
+    if w.tiled:
+        raise ValueError("shard the reference row layout, then tile the shard")
+    if w.bits == 4:
+        if per % 2 != 0:
+            raise ValueError("an int4 K slice must start on a byte boundary")
+        codes = w.packed_values[:, lo // 2:hi // 2].contiguous()
+    else:
+        codes = w.packed_values[:, lo:hi].contiguous()
+    scales = w.scales
+    if w.group_size:
+        if per % w.group_size != 0:
+            raise ValueError("a K slice must hold whole quantization groups")
+        scales = w.scales.reshape(int(w.shape[0]), -1)[:, lo // w.group_size:hi // w.group_size].contiguous()
+    return B200PackedWeight(codes, scales, w.zero_points, w.bits, (int(w.shape[0]), per), group_size=w.group_size,
+                            zero_points_i32=w.zero_points_i32)

@@ -84,12 +84,15 @@ def test_two_ranks_partition_gather_and_reduce():
     manager = ctx.Manager()
     results = manager.dict()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, results)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, results), daemon=True) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
         p.join(100)
-        assert p.exitcode == 0
+    stuck = [p for p in procs if p.is_alive()]
+    for p in stuck:
+        p.kill()
+    assert not stuck and all(p.exitcode == 0 for p in procs)
     reqs = [(f"req-{i}", [i, 2 * i + 1, 5]) for i in range(7)]
     expected = _fake_decode(reqs)
     r0, r1 = results[0], results[1]

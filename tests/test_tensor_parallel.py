@@ -1,0 +1,198 @@
+"""Tensor-parallel sharding of packed weights.
+
+CPU part (gloo, two ranks): the shards are slices of the same integer codes, so the partial
+products of a row-parallel projection all-reduce to the full product and the column-parallel
+shards concatenate to it -- checked with the oracle's dequantisation on the host.
+GPU part (two B200s, skipped with fewer): a two-layer int8 model decoded with TP=2 produces the
+logits and greedy tokens of the single-GPU runtime.
+"""
+from __future__ import annotations
+
+import os
+import socket
+import zlib
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import oracle
+from cacheir_b200.quantization import B200PackedWeight
+from cacheir_b200.tensor_parallel import TensorParallel, shard_columns, shard_rows
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _host_packed(rng, n, k, bits, group=0):
+    """A packed weight on the host in the runtime's container type."""
+    w = rng.standard_normal((n, k)).astype(np.float32) * 0.05
+    if group:
+        codes = rng.integers(0, 16, (n, k)).astype(np.uint8)
+        packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
+        scales = rng.uniform(0.005, 0.02, (n, k // group)).astype(np.float16)
+        return B200PackedWeight(torch.from_numpy(packed), torch.from_numpy(scales), None, 4, (n, k), group_size=group)
+    ref = oracle.pack_quantized_weight(w, f"int{bits}")
+    return B200PackedWeight(torch.from_numpy(ref.packed_values), torch.from_numpy(ref.scales.astype(np.float32)),
+                            torch.from_numpy(ref.zero_points.astype(np.float32)), bits, (n, k),
+                            zero_points_i32=torch.from_numpy(ref.zero_points.astype(np.int32)))
+
+
+def _dequant(w: B200PackedWeight) -> np.ndarray:
+    n, k = w.shape
+    codes = w.packed_values.numpy()
+    if w.bits == 4:
+        q = np.empty((n, codes.shape[1] * 2), dtype=np.float32)
+        q[:, 0::2] = codes & 0xF
+        q[:, 1::2] = codes >> 4
+        q = q[:, :k]
+    else:
+        q = codes.astype(np.float32)
+    if w.group_size:
+        s = np.repeat(w.scales.numpy().astype(np.float32).reshape(n, -1), w.group_size, axis=1)
+        return (q - 8.0) * s
+    return (q - w.zero_points.numpy()[:, None]) * w.scales.numpy()[:, None]
+
+
+def test_shards_partition_the_codes():
+    rng = np.random.default_rng(0)
+    for bits, group in ((8, 0), (4, 0), (4, 128)):
+        w = _host_packed(rng, 64, 512, bits, group)
+        full = _dequant(w)
+        for world in (2, 4):
+            rows = [_dequant(shard_rows(w, TensorParallel(r, world))) for r in range(world)]
+            cols = [_dequant(shard_columns(w, TensorParallel(r, world))) for r in range(world)]
+            np.testing.assert_array_equal(np.concatenate(rows, axis=0), full)
+            np.testing.assert_array_equal(np.concatenate(cols, axis=1), full)
+    with pytest.raises(ValueError):
+        shard_rows(_host_packed(rng, 10, 128, 8), TensorParallel(0, 4))
+    with pytest.raises(ValueError):
+        shard_columns(_host_packed(rng, 8, 384, 4, 128), TensorParallel(0, 2))      # 192 columns: not whole groups
+    with pytest.raises(ValueError):
+        TensorParallel(2, 2)
+    with pytest.raises(ValueError):
+        TensorParallel(0, 4).check_model(heads=8, kv_heads=2, intermediate=64, vocab=64)
+
+
+def _cpu_worker(rank: int, world: int, port: int, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        tp = TensorParallel(rank, world)
+        rng = np.random.default_rng(3)                     # same weights and activations on every rank
+        x = rng.standard_normal((5, 256)).astype(np.float32)
+        w_row = _host_packed(rng, 48, 256, 8)              # row-parallel (o / down): slice K
+        w_col = _host_packed(rng, 64, 256, 4, 128)         # column-parallel (lm_head): slice N
+        k0, k1 = rank * 128, (rank + 1) * 128
+        partial = torch.from_numpy(x[:, k0:k1] @ _dequant(shard_columns(w_row, tp)).T)
+        tp.all_reduce_sum(partial)
+        local = torch.from_numpy(x @ _dequant(shard_rows(w_col, tp)).T)
+        gathered = torch.empty((world * local.shape[0], local.shape[1]))
+        out = torch.empty((5, 64))
+        tp.all_gather_columns(local, gathered, out)
+        results[rank] = {"row": partial.numpy(), "col": out.numpy(),
+                         "row_full": x @ _dequant(w_row).T, "col_full": x @ _dequant(w_col).T}
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_two_ranks_reduce_and_gather_to_the_unsharded_product():
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_cpu_worker, args=(r, 2, port, results), daemon=True) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(100)
+    stuck = [p for p in procs if p.is_alive()]
+    for p in stuck:
+        p.kill()
+    assert not stuck and all(p.exitcode == 0 for p in procs)
+    for r in range(2):
+        np.testing.assert_allclose(results[r]["row"], results[r]["row_full"], rtol=1e-5, atol=1e-5)
+        np.testing.assert_allclose(results[r]["col"], results[r]["col_full"], rtol=1e-5, atol=1e-5)
+    np.testing.assert_array_equal(results[0]["row"], results[1]["row"])      # every rank ends with the same sum
+
+
+# ---- GPU: TP=2 against the single-GPU runtime ------------------------------------------------
+def _gpu_worker(rank: int, world: int, port: int, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from cacheir_b200 import B200DecodeRuntime
+        from cacheir_b200.artifact import ModelConfig, build_decoder_artifact
+
+        cfg = ModelConfig(architecture="LlamaForCausalLM", hidden_size=512, intermediate_size=1024, num_layers=2,
+                          num_attention_heads=4, num_key_value_heads=2, vocab_size=512, max_position_embeddings=256,
+                          rope_theta=10000.0, rms_norm_eps=1e-5, dtype="float16")
+        artifact = build_decoder_artifact(cfg, quant="int8")
+
+        def source(key, shape):                           # identical synthetic weights on every rank
+            g = torch.Generator(device="cpu")
+            g.manual_seed(zlib.crc32(key.encode()))
+            if len(shape) == 1:
+                return torch.ones(shape)
+            return torch.randn(shape, generator=g) * 0.05
+
+        prompts = [[3, 17, 200, 45, 9, 310, 77, 5], [8, 1, 499, 23, 64, 2, 11, 90]]
+        outs = {}
+        for name, tp in (("tp", TensorParallel(rank, world)), ("single", None)):
+            if name == "single" and rank != 0:
+                continue
+            rt = B200DecodeRuntime(artifact, device=f"cuda:{rank}", dtype="float16", tensor_source=source,
+                                   max_seq_len=256, tensor_parallel=tp)
+            sessions = [rt.fork() for _ in prompts]
+            logits = rt.run_prefill_batch(sessions, prompts)
+            trace = [logits[:, -1].float().cpu().numpy()]
+            generated = [[int(t) for t in logits[:, -1].argmax(dim=-1).tolist()]]
+            forced = [[41, 7], [300, 12], [5, 5], [128, 64], [2, 509], [77, 30]]      # the same next tokens for both runs
+            for tokens in forced:
+                logits = rt.run_decode_batch(sessions, tokens)
+                generated.append([int(t) for t in logits[:, -1].argmax(dim=-1).tolist()])
+                trace.append(logits[:, -1].float().cpu().numpy())
+            outs[name] = {"tokens": generated, "logits": np.stack(trace)}
+            if name == "tp":
+                dist.barrier()
+        results[rank] = outs
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.timeout(400)
+def test_tp2_matches_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_gpu_worker, args=(r, 2, port, results), daemon=True) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+    stuck = [p for p in procs if p.is_alive()]
+    for p in stuck:                       # never leave a rank behind: a stuck collective would outlive the test
+        p.kill()
+    assert not stuck, "a tensor-parallel rank did not finish in time"
+    assert all(p.exitcode == 0 for p in procs)
+    single, tp0, tp1 = results[0]["single"], results[0]["tp"], results[1]["tp"]
+    np.testing.assert_array_equal(tp0["logits"], tp1["logits"])          # both ranks hold the same gathered logits
+    # fp16 partial sums and per-rank activation scales: a little looser than the single-kernel gates
+    assert oracle.rel_l2(tp0["logits"], single["logits"]) <= 1e-2
+    assert tp0["tokens"] == tp1["tokens"]
+    agree = np.mean(np.array(tp0["tokens"]) == np.array(single["tokens"]))
+    assert agree >= 0.7                                                     # near-flat random logits may flip a tie
