@@ -1,0 +1,221 @@
+// One-shot collectives over NVLink peer memory for the tensor-parallel decode step.
+//
+// Every rank (one process per GPU) owns a data buffer and a small flag array allocated here
+// and opened by its peers through CUDA IPC. A collective is one kernel per rank:
+//   1. announce: write this call's epoch into slot [my rank] of every peer's flag array
+//      (system-scope release: the producer kernel's writes to my buffer are visible first);
+//   2. wait, bounded, until every peer's slot in my own flag array shows the epoch;
+//   3. read all ranks' buffers with plain peer loads and combine them in rank order, so every
+//      rank computes bit-identical results (all-reduce), or copy the peers' slices (all-gather).
+// Callers alternate between two data buffers from call to call: a rank may refill buffer A
+// only after the call that used buffer B, whose wait proves every peer has left buffer A.
+// The epoch lives on the device and advances with every call, so a captured CUDA graph can be
+// replayed. No multicast, no TMA, no library collective: plain loads and stores. A wait that
+// runs out of polls records a code in the status word and the kernel returns (output undefined).
+#include <string.h>
+
+#include "common.cuh"
+
+namespace cb200 {
+namespace {
+
+constexpr int kMaxRanks = 8;
+constexpr uint32_t kPeerPollLimit = 30u * 1000u * 1000u;  // with the sleep below: about a minute, then give up
+
+__device__ int g_peer_status = 0;
+
+struct PeerParams {
+  const void* data[kMaxRanks];    // every rank's data buffer (index = rank), mapped into this process
+  int* flags[kMaxRanks];          // every rank's flag array [kMaxRanks]
+  void* out;
+  size_t count;                   // all-reduce: elements; all-gather: elements of one rank's slice row
+  int rows;                       // all-gather only: rows of the [rows, count] slices
+  int rank, world;
+  int* state;                     // local: {epoch, CTAs finished}
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Steps 1 and 2 for one CTA. Returns false when a peer never showed up.
+__device__ __forceinline__ bool announce_and_wait(const PeerParams& p, int epoch) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < p.world && threadIdx.x != p.rank) {
+    __threadfence_system();
+    st_release_sys(p.flags[threadIdx.x] + p.rank, epoch);
+  }
+  if (threadIdx.x < p.world && threadIdx.x != p.rank) {
+    const int* slot = p.flags[p.rank] + threadIdx.x;
+    bool seen = false;
+    for (uint32_t i = 0; i < kPeerPollLimit; ++i) {
+      if (ld_acquire_sys(slot) - epoch >= 0) { seen = true; break; }   // (difference: survives wrap-around)
+      if (i > 64) __nanosleep(i > 4096 ? 2000 : 100);
+    }
+    if (!seen) {
+      s_ok = 0;
+      atomicCAS(&g_peer_status, 0, (4 << 8) | 1);
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+__device__ __forceinline__ void finish(const PeerParams& p, int epoch) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(p.state + 1, 1) == static_cast<int>(gridDim.x) - 1) {   // last CTA: publish the epoch for the next call
+      p.state[1] = 0;
+      p.state[0] = epoch;
+      __threadfence();
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) all_reduce_kernel(const PeerParams p) {
+  const int epoch = p.state[0] + 1;
+  if (announce_and_wait(p, epoch)) {
+    constexpr int VEC = 16 / sizeof(T);
+    const size_t nvec = p.count / VEC;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+      float acc[VEC];
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+      for (int r = 0; r < p.world; ++r) {        // rank order: the same sum, bit for bit, on every rank
+        float v[VEC];
+        VecIO<T, VEC>::ld(static_cast<const T*>(p.data[r]) + i * VEC, v);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[j] += v[j];
+      }
+      VecIO<T, VEC>::st(static_cast<T*>(p.out) + i * VEC, acc);
+    }
+  }
+  finish(p, epoch);
+}
+
+// out[rows, world*count]: rank r's [rows, count] slice lands in columns [r*count, (r+1)*count)
+template <typename T>
+__global__ void __launch_bounds__(256) all_gather_kernel(const PeerParams p) {
+  const int epoch = p.state[0] + 1;
+  if (announce_and_wait(p, epoch)) {
+    constexpr int VEC = 16 / sizeof(T);
+    const size_t vec_per_row = p.count / VEC;
+    const size_t total = static_cast<size_t>(p.world) * p.rows * vec_per_row;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+      const size_t c = i % vec_per_row;
+      const size_t row = (i / vec_per_row) % p.rows;
+      const int r = static_cast<int>(i / (vec_per_row * p.rows));
+      const uint4 v = reinterpret_cast<const uint4*>(p.data[r])[row * vec_per_row + c];
+      reinterpret_cast<uint4*>(p.out)[(row * p.world + r) * vec_per_row + c] = v;
+    }
+  }
+  finish(p, epoch);
+}
+
+int fill(PeerParams& p, void* const* data, void* const* flags, void* out, int rank, int world, int* state) {
+  if (!data || !flags || !out || !state || world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return CACHEIR_B200_EINVAL;
+  for (int r = 0; r < world; ++r) {
+    if (!data[r] || !flags[r] || !aligned_to(data[r], 16)) return CACHEIR_B200_EINVAL;
+    p.data[r] = data[r];
+    p.flags[r] = static_cast<int*>(flags[r]);
+  }
+  if (!aligned_to(out, 16)) return CACHEIR_B200_EALIGN;
+  p.out = out; p.rank = rank; p.world = world; p.state = state;
+  return 0;
+}
+
+}  // namespace
+}  // namespace cb200
+
+using namespace cb200;
+
+extern "C" int cacheir_b200_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64) {
+  if (!ptr || !handle64 || bytes == 0) return CACHEIR_B200_EINVAL;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are exchanged as 64-byte blobs");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) { cudaFree(p); return static_cast<int>(e); }
+  memcpy(handle64, &h, 64);
+  *ptr = p;
+  return 0;
+}
+
+extern "C" int cacheir_b200_peer_open(const unsigned char* handle64, void** ptr) {
+  if (!handle64 || !ptr) return CACHEIR_B200_EINVAL;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  return static_cast<int>(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+
+extern "C" int cacheir_b200_peer_close(void* ptr) { return ptr ? static_cast<int>(cudaIpcCloseMemHandle(ptr)) : 0; }
+extern "C" int cacheir_b200_peer_free(void* ptr) { return ptr ? static_cast<int>(cudaFree(ptr)) : 0; }
+
+extern "C" int cacheir_b200_peer_all_reduce(void* const* data, void* const* flags, void* out, size_t count, int dtype,
+                                            int rank, int world, int* state, void* stream) {
+  if (count == 0) return 0;
+  PeerParams p{};
+  const int rc = fill(p, data, flags, out, rank, world, state);
+  if (rc != 0) return rc;
+  const int esize = dtype_size(dtype);
+  if (esize == 0) return CACHEIR_B200_EINVAL;
+  if ((count * esize) % 16 != 0) return CACHEIR_B200_EALIGN;
+  p.count = count;
+  const size_t nvec = count * esize / 16;
+  const unsigned grid = static_cast<unsigned>(nvec / 256 < 1 ? 1 : (nvec / 256 > kNumSMs ? kNumSMs : nvec / 256));
+  cudaStream_t st = as_stream(stream);
+  switch (dtype) {
+    case CACHEIR_B200_F32: all_reduce_kernel<float><<<grid, 256, 0, st>>>(p); break;
+    case CACHEIR_B200_F16: all_reduce_kernel<__half><<<grid, 256, 0, st>>>(p); break;
+    default: all_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p); break;
+  }
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_peer_all_gather(void* const* data, void* const* flags, void* out, int rows, size_t cols, int dtype,
+                                            int rank, int world, int* state, void* stream) {
+  if (rows <= 0 || cols == 0) return 0;
+  PeerParams p{};
+  const int rc = fill(p, data, flags, out, rank, world, state);
+  if (rc != 0) return rc;
+  const int esize = dtype_size(dtype);
+  if (esize == 0) return CACHEIR_B200_EINVAL;
+  if ((cols * esize) % 16 != 0) return CACHEIR_B200_EALIGN;
+  p.count = cols; p.rows = rows;
+  const size_t nvec = static_cast<size_t>(world) * rows * cols * esize / 16;
+  const unsigned grid = static_cast<unsigned>(nvec / 256 < 1 ? 1 : (nvec / 256 > kNumSMs ? kNumSMs : nvec / 256));
+  cudaStream_t st = as_stream(stream);
+  switch (dtype) {
+    case CACHEIR_B200_F32: all_gather_kernel<float><<<grid, 256, 0, st>>>(p); break;
+    case CACHEIR_B200_F16: all_gather_kernel<__half><<<grid, 256, 0, st>>>(p); break;
+    default: all_gather_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p); break;
+  }
+  return launch_status();
+}
+
+namespace cb200 {
+int peer_collectives_device_status(bool reset);
+}
+int cb200::peer_collectives_device_status(bool reset) {
+  int status = 0;
+  if (cudaMemcpyFromSymbol(&status, g_peer_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && status != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_peer_status, &zero, sizeof(int));
+  }
+  return status;
+}

@@ -249,11 +249,16 @@ extern "C" int cacheir_b200_qgemv(const void* x, const void* packed, const void*
                                scale_dtype, x_stride, epilogue, CACHEIR_B200_LAYOUT_ROWS, nullptr, 0, stream);
 }
 
+namespace cb200 {
+int peer_collectives_device_status(bool reset);
+}
+
 extern "C" int cacheir_b200_device_status(int reset) {
   const int gemm = qgemm_tc_device_status(reset != 0);
   const int attn = paged_attention_device_status(reset != 0);
   const int i8 = qgemm_i8_device_status(reset != 0);
-  return gemm != 0 ? gemm : (attn != 0 ? attn : i8);
+  const int peer = peer_collectives_device_status(reset != 0);
+  return gemm != 0 ? gemm : (attn != 0 ? attn : (i8 != 0 ? i8 : peer));
 }
 
 extern "C" int cacheir_b200_quantize_activations(const void* x, int M, int K, long long x_stride, int x_dtype,

@@ -35,7 +35,7 @@ from . import ops
 from .artifact import CompileArtifact
 from .kv_cache import B200KVPageAllocator, B200PagedKVCache
 from .quantization import B200PackedWeight, concat_rows, quant_bits, to_rows, to_tiled
-from .tensor_parallel import TensorParallel, shard_columns, shard_rows
+from .tensor_parallel import PeerCollectives, TensorParallel, shard_columns, shard_rows
 from .weights import B200WeightStore, TensorSource
 
 
@@ -150,8 +150,11 @@ class _Engine:
                                  kv_heads=int(self.config.num_key_value_heads) // self.tp.world,
                                  head_dim=int(self.config.head_dim))
         self.max_seq_len = int(max_seq_len or self.config.max_position_embeddings)
-        # Collectives are launched eagerly for now: a tensor-parallel step is not captured into a CUDA graph
-        self.use_cuda_graph = use_cuda_graph and not self.tp.enabled
+        # Tensor-parallel collectives: this package's own kernels over peer memory (graph-capturable), or the
+        # process group's library collectives launched eagerly (CB200_TP_COLLECTIVES=nccl; never captured).
+        self.peer_mode = self.tp.enabled and os.environ.get("CB200_TP_COLLECTIVES", "peer") != "nccl"
+        self.peer: PeerCollectives | None = None
+        self.use_cuda_graph = use_cuda_graph and (not self.tp.enabled or self.peer_mode)
         self.tile_weights = True
         self._rope_tables: dict[tuple[int, float], torch.Tensor] = {}
         self.attention_splits = int(attention_splits)
@@ -214,6 +217,14 @@ class _Engine:
                     self.weights.release(n)
         self.fused_weights[names] = fused
         return fused
+
+    def peer_collectives(self, rows: int) -> PeerCollectives:
+        """The peer-memory buffers, sized on first use for up to max(rows, 256) batch rows."""
+        if self.peer is None:
+            widest = max(int(self.config.hidden_size), int(self.config.vocab_size) // self.tp.world)
+            elem = torch.empty((), dtype=self.dtype).element_size()
+            self.peer = PeerCollectives(self.tp, self.device, max(rows, 256) * widest * elem)
+        return self.peer
 
     def rope_table(self, head_dim: int, theta: float) -> torch.Tensor:
         """(cos, sin) for every position up to max_seq_len, shared by all plans and layers."""
@@ -283,6 +294,8 @@ class _DecodePlan:
         self._count_keys: list[tuple[str, int]] = []
         self._prequantized: set[str] = set()
         self._kv_appended: set[str] = set()
+        self._peer_calls = 0
+        self._peer_gathers = 0
         uses: dict[str, int] = {}
         for node in nodes:
             for name in node.inputs:
@@ -341,15 +354,32 @@ class _DecodePlan:
                     residual = env[other] if (role != "row" or tp.rank == 0) else None
                     skip.add(idx + 1)
                     out_name = nxt.outputs[0]
-                out = self._matmul(x, weight, residual=residual, prequantized=node.inputs[0] in self._prequantized)
-                if role == "row":
-                    self._emit(lambda out=out: tp.all_reduce_sum(out), "b200.tp.all_reduce", launches=0)
-                elif role == "column":
-                    local = out
-                    out = self._buf(int(local.shape[1]) * tp.world)
-                    gathered = torch.empty((tp.world * self.batch, int(local.shape[1])), device=eng.device, dtype=eng.dtype)
-                    self._emit(lambda local=local, gathered=gathered, out=out: tp.all_gather_columns(local, gathered, out),
-                               "b200.tp.all_gather", launches=0)
+                peer = eng.peer_collectives(self.batch) if (role != "replicated" and eng.peer_mode) else None
+                n_local = int(weight.shape[0])
+                if peer is not None and role == "row":
+                    # partial sums go straight into a peer-visible buffer (A and B alternate), one kernel sums all ranks
+                    which = self._peer_calls % 2
+                    self._peer_calls += 1
+                    partial = peer.buffer(which, self.batch, n_local, eng.dtype)
+                    self._matmul(x, weight, residual=residual, prequantized=node.inputs[0] in self._prequantized, out=partial)
+                    out = self._buf(n_local)
+                    self._emit(lambda out=out, which=which: peer.all_reduce(which, out), "b200.peer_all_reduce")
+                elif peer is not None and role == "column":
+                    local = peer.buffer(2, self.batch, n_local, eng.dtype)
+                    self._matmul(x, weight, residual=residual, prequantized=node.inputs[0] in self._prequantized, out=local)
+                    out = self._buf(n_local * tp.world)
+                    self._emit(lambda out=out: peer.all_gather_columns(2, out), "b200.peer_all_gather")
+                    self._peer_gathers += 1
+                else:
+                    out = self._matmul(x, weight, residual=residual, prequantized=node.inputs[0] in self._prequantized)
+                    if role == "row":
+                        self._emit(lambda out=out: tp.all_reduce_sum(out), "b200.tp.all_reduce", launches=0)
+                    elif role == "column":
+                        local = out
+                        out = self._buf(n_local * tp.world)
+                        gathered = torch.empty((tp.world * self.batch, n_local), device=eng.device, dtype=eng.dtype)
+                        self._emit(lambda local=local, gathered=gathered, out=out: tp.all_gather_columns(local, gathered, out),
+                                   "b200.tp.all_gather", launches=0)
                 env[out_name] = out
             elif op in {"fused_rmsnorm_qkv_rope", "quantized_fused_rmsnorm_qkv_rope"}:
                 x, norm_w = env[node.inputs[0]], eng.weights.get(node.inputs[1])
@@ -432,6 +462,9 @@ class _DecodePlan:
                 raise NotImplementedError("the B200 runtime executes the decode graph; prefill runs as decode steps")
             else:
                 raise NotImplementedError(f"B200 decode runtime does not implement op {op}")
+        if self._peer_calls % 2 == 1 and self._peer_gathers == 0:
+            # consecutive steps would refill the same peer buffer with no other call in between
+            raise NotImplementedError("an odd number of row-parallel projections per step needs a gather (or a third buffer) between steps")
         logits = env[eng.graph.outputs[0]]
         self.logits = logits
         # Greedy feedback variant: the row argmax overwrites `ids` (already consumed by the
@@ -452,13 +485,13 @@ class _DecodePlan:
                 and hasattr(self, "_gemm_ws"))
 
     def _matmul(self, x: torch.Tensor, weight: B200PackedWeight | torch.Tensor, *, epilogue: int = ops.EPI_NONE,
-                residual: torch.Tensor | None = None, prequantized: bool = False) -> torch.Tensor:
+                residual: torch.Tensor | None = None, prequantized: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
         eng = self.engine
         if residual is not None:
             epilogue = ops.EPI_RESIDUAL
         if isinstance(weight, B200PackedWeight):
             n, k, bits = weight.shape[0], weight.shape[1], weight.bits
-            out = self._buf(n // 2 if epilogue == ops.EPI_SWIGLU else n)
+            out = out if out is not None else self._buf(n // 2 if epilogue == ops.EPI_SWIGLU else n)
             ws = self._gemm_workspace(k) if (bits == 8 and not weight.group_size and eng.dtype == torch.float16) else None
             fn = lambda: ops.qgemv(x, weight.packed_values, weight.scales, weight.zero_points, bits=bits, n=n, k=k,
                                    group_size=weight.group_size or 0, epilogue=epilogue, residual=residual, out=out,
@@ -470,7 +503,7 @@ class _DecodePlan:
                 return out
         else:
             n, k = int(weight.shape[0]), int(weight.shape[1])
-            out = self._buf(n // 2 if epilogue == ops.EPI_SWIGLU else n)
+            out = out if out is not None else self._buf(n // 2 if epilogue == ops.EPI_SWIGLU else n)
             fn = lambda: ops.qgemv(x, weight, None, None, bits=0, n=n, k=k, epilogue=epilogue, residual=residual, out=out)
             key = "b200.gemv.dense" + (".swiglu" if epilogue == ops.EPI_SWIGLU else ".residual" if residual is not None else "")
             eng.gemm_plans[f"{(self.batch, 1, k)}x{(n, k)}"] = key

@@ -113,3 +113,98 @@ def shard_columns(w: B200PackedWeight | torch.Tensor, tp: TensorParallel) -> B20
         scales = w.scales.reshape(int(w.shape[0]), -1)[:, lo // w.group_size:hi // w.group_size].contiguous()
     return B200PackedWeight(codes, scales, w.zero_points, w.bits, (int(w.shape[0]), per), group_size=w.group_size,
                             zero_points_i32=w.zero_points_i32)
+
+
+class _RawCudaBuffer:
+    """Lets torch wrap device memory that this library allocated (CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerCollectives:
+    """The library's own all-reduce / all-gather over NVLink peer memory (include/cacheir_b200.h,
+    `cacheir_b200_peer_*`): three data buffers per rank (A and B alternate between consecutive
+    all-reduces, C carries the logits slice), one flag array, all mapped into every peer through
+    CUDA IPC. Unlike a library collective these are plain kernels of this package, so a whole
+    tensor-parallel step can be captured into one CUDA graph. All ranks must construct it, and
+    issue its calls, in the same order."""
+
+    def __init__(self, tp: TensorParallel, device: torch.device, data_bytes: int):
+        import ctypes
+
+        from . import _lib
+        from ._lib import check
+
+        if not tp.enabled:
+            raise ValueError("peer collectives need more than one rank")
+        self.tp = tp
+        self.device = device
+        self.data_bytes = (int(data_bytes) + 255) // 256 * 256
+        self._lib = _lib.load()
+        self._ctypes = ctypes
+        self._local: list[int] = []
+        self._opened: list[int] = []
+        handles: list[bytes] = []
+        with torch.cuda.device(device):
+            for nbytes in (self.data_bytes, self.data_bytes, self.data_bytes, 256):      # A, B, C, flags
+                ptr = ctypes.c_void_p()
+                handle = (ctypes.c_ubyte * 64)()
+                check(self._lib.cacheir_b200_peer_alloc(nbytes, ctypes.byref(ptr), handle), "peer_alloc")
+                self._local.append(int(ptr.value))
+                handles.append(bytes(handle))
+            everyone: list[Any] = [None] * tp.world
+            dist.all_gather_object(everyone, handles, group=tp.group)
+            # pointer tables [buffer][rank]
+            self._ptrs: list[list[int]] = [[0] * tp.world for _ in range(4)]
+            for r in range(tp.world):
+                for b in range(4):
+                    if r == tp.rank:
+                        self._ptrs[b][r] = self._local[b]
+                    else:
+                        ptr = ctypes.c_void_p()
+                        blob = (ctypes.c_ubyte * 64).from_buffer_copy(everyone[r][b])
+                        check(self._lib.cacheir_b200_peer_open(blob, ctypes.byref(ptr)), "peer_open")
+                        self._ptrs[b][r] = int(ptr.value)
+                        self._opened.append(int(ptr.value))
+            self._tables = [(ctypes.c_void_p * tp.world)(*self._ptrs[b]) for b in range(4)]
+            self.state = torch.zeros((2,), device=device, dtype=torch.int32)
+            self._views = [torch.as_tensor(_RawCudaBuffer(self._local[b], self.data_bytes), device=device) for b in range(3)]
+        dist.barrier(group=tp.group)
+
+    def buffer(self, index: int, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        """A [rows, cols] view of local data buffer `index` (0 = A, 1 = B, 2 = C) for a producer kernel to fill."""
+        nbytes = rows * cols * torch.empty((), dtype=dtype).element_size()
+        if nbytes > self.data_bytes:
+            raise ValueError(f"a peer buffer holds {self.data_bytes} bytes, {nbytes} requested")
+        return self._views[index][:nbytes].view(dtype).view(rows, cols)
+
+    def all_reduce(self, index: int, out: torch.Tensor) -> None:
+        """out = sum over ranks of their buffer `index` (same shape and dtype as `out`), identical bits on every rank."""
+        from . import ops
+        from ._lib import check
+
+        check(self._lib.cacheir_b200_peer_all_reduce(self._tables[index], self._tables[3], out.data_ptr(), out.numel(),
+                                                     ops.dtype_code(out.dtype), self.tp.rank, self.tp.world,
+                                                     self.state.data_ptr(), ops._stream()), "peer_all_reduce")
+
+    def all_gather_columns(self, index: int, out: torch.Tensor) -> None:
+        """out [rows, world*cols] from every rank's [rows, cols] slice in its buffer `index`."""
+        from . import ops
+        from ._lib import check
+
+        rows, cols = int(out.shape[0]), int(out.shape[1]) // self.tp.world
+        check(self._lib.cacheir_b200_peer_all_gather(self._tables[index], self._tables[3], out.data_ptr(), rows, cols,
+                                                     ops.dtype_code(out.dtype), self.tp.rank, self.tp.world,
+                                                     self.state.data_ptr(), ops._stream()), "peer_all_gather")
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free the local ones (call on every rank, after a barrier)."""
+        torch.cuda.synchronize(self.device)
+        for ptr in self._opened:
+            self._lib.cacheir_b200_peer_close(self._ctypes.c_void_p(ptr))
+        self._opened = []
+        self._views = []
+        for ptr in self._local:
+            self._lib.cacheir_b200_peer_free(self._ctypes.c_void_p(ptr))
+        self._local = []

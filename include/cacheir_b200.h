@@ -237,6 +237,34 @@ size_t cacheir_b200_pack_tiled_bytes(int N, int K, int bits);
 int cacheir_b200_pack_relayout(const uint8_t* packed, uint8_t* tiled, int N, int K, int bits, int paired, void* stream);
 int cacheir_b200_pack_unrelayout(const uint8_t* tiled, uint8_t* packed, int N, int K, int bits, int paired, void* stream);
 
+/* ------------------------------------------------------------------------
+ * Collectives of the tensor-parallel decode step over NVLink peer memory (one process per
+ * GPU, up to 8 ranks). No reference counterpart: the reference runs on one device.
+ *
+ * peer_alloc: device memory (zero-filled) that other processes can map; `handle64` receives
+ * the 64-byte CUDA IPC handle to send them. peer_open maps a peer's allocation from its
+ * handle; peer_close / peer_free undo the two. Each rank needs data buffers and one flag
+ * array of 8 ints, all from peer_alloc, and a local `state` of 2 zero ints.
+ *
+ * peer_all_reduce: out[i] = sum over ranks r = 0..world-1 (in that order, fp32 accumulation,
+ * so every rank gets the same bits) of data[r][i]. peer_all_gather: out[rows, world*cols]
+ * with rank r's [rows, cols] slice in columns [r*cols, (r+1)*cols). `data` and `flags` are
+ * host arrays of `world` device pointers (entry [rank] = the local buffers). One kernel per
+ * rank; it announces itself to the peers, waits (bounded; a peer that never arrives is
+ * recorded in cacheir_b200_device_status and the output is then undefined) and reads the
+ * peers' buffers with plain loads. All ranks must issue the same sequence of calls, and a
+ * data buffer may be refilled only after a later call that used a different buffer (alternate
+ * between two). Safe to capture in a CUDA graph: the call counter lives in `state`. */
+int cacheir_b200_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+int cacheir_b200_peer_open(const unsigned char* handle64, void** ptr);
+int cacheir_b200_peer_close(void* ptr);
+int cacheir_b200_peer_free(void* ptr);
+int cacheir_b200_peer_all_reduce(void* const* data, void* const* flags, void* out, size_t count,
+                                 int dtype, int rank, int world, int* state, void* stream);
+int cacheir_b200_peer_all_gather(void* const* data, void* const* flags, void* out, int rows,
+                                 size_t cols, int dtype, int rank, int world, int* state,
+                                 void* stream);
+
 /* Status word of the kernels that wait on hardware barriers (the tensor-core GEMM):
  * 0, or a non-zero code recorded by the first wait that ran out of its poll budget
  * (the kernel then drains and returns instead of hanging; its output is undefined).

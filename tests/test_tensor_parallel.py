@@ -124,12 +124,58 @@ def test_two_ranks_reduce_and_gather_to_the_unsharded_product():
 
 
 # ---- GPU: TP=2 against the single-GPU runtime ------------------------------------------------
-def _gpu_worker(rank: int, world: int, port: int, results):
+def _peer_collectives_check(rank: int, world: int) -> dict:
+    """The library's own all-reduce / all-gather: eager calls alternating buffers, then a captured graph replayed."""
+    from cacheir_b200.tensor_parallel import PeerCollectives
+
+    dev = torch.device("cuda", rank)
+    peer = PeerCollectives(TensorParallel(rank, world), dev, 64 * 1024)
+    rows, cols = 8, 512
+    gens = [torch.Generator(device="cpu") for _ in range(world)]
+    report = {"reduce_ok": True, "gather_ok": True, "graph_ok": True}
+    out = torch.empty((rows, cols), device=dev, dtype=torch.float16)
+    wide = torch.empty((rows, cols * world), device=dev, dtype=torch.float16)
+    for call in range(6):                                   # every rank can regenerate every rank's data
+        parts = []
+        for r in range(world):
+            gens[r].manual_seed(1000 * call + r)
+            parts.append(torch.randn((rows, cols), generator=gens[r]).half())
+        which = call % 2
+        peer.buffer(which, rows, cols, torch.float16).copy_(parts[rank].to(dev))
+        peer.all_reduce(which, out)
+        want = sum(p.float() for p in parts).half()          # rank order, fp32 accumulation, one rounding
+        report["reduce_ok"] &= bool(torch.equal(out.cpu(), want))
+    peer.buffer(2, rows, cols, torch.float16).copy_(parts[rank].to(dev))
+    peer.all_gather_columns(2, wide)
+    report["gather_ok"] = bool(torch.equal(wide.cpu(), torch.cat(parts, dim=1)))
+    # captured: the producer copy and the collective replay together; the call counter lives on the device
+    src = parts[rank].to(dev)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for which in (0, 1):
+            peer.buffer(which, rows, cols, torch.float16).copy_(src)
+            peer.all_reduce(which, out)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    report["graph_ok"] = bool(torch.equal(out.cpu(), want))
+    from cacheir_b200 import _lib
+    report["status"] = int(_lib.load().cacheir_b200_device_status(1))
+    dist.barrier()
+    peer.close()
+    return report
+
+
+def _gpu_worker(rank: int, world: int, port: int, results, collectives: str = "peer"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    os.environ["CB200_TP_COLLECTIVES"] = collectives
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))     # a lost rank ends the others' collectives quickly
     try:
         from cacheir_b200 import B200DecodeRuntime
         from cacheir_b200.artifact import ModelConfig, build_decoder_artifact
@@ -148,6 +194,8 @@ def _gpu_worker(rank: int, world: int, port: int, results):
 
         prompts = [[3, 17, 200, 45, 9, 310, 77, 5], [8, 1, 499, 23, 64, 2, 11, 90]]
         outs = {}
+        if collectives == "peer":
+            outs["collectives"] = _peer_collectives_check(rank, world)
         for name, tp in (("tp", TensorParallel(rank, world)), ("single", None)):
             if name == "single" and rank != 0:
                 continue
@@ -173,13 +221,14 @@ def _gpu_worker(rank: int, world: int, port: int, results):
 
 @pytest.mark.gpu
 @pytest.mark.timeout(400)
-def test_tp2_matches_single_gpu():
+@pytest.mark.parametrize("collectives", ["peer", "nccl"])
+def test_tp2_matches_single_gpu(collectives):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     ctx = mp.get_context("spawn")
     results = ctx.Manager().dict()
     port = _free_port()
-    procs = [ctx.Process(target=_gpu_worker, args=(r, 2, port, results), daemon=True) for r in range(2)]
+    procs = [ctx.Process(target=_gpu_worker, args=(r, 2, port, results, collectives), daemon=True) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
@@ -189,6 +238,9 @@ def test_tp2_matches_single_gpu():
         p.kill()
     assert not stuck, "a tensor-parallel rank did not finish in time"
     assert all(p.exitcode == 0 for p in procs)
+    if collectives == "peer":
+        for r in range(2):
+            assert results[r]["collectives"] == {"reduce_ok": True, "gather_ok": True, "graph_ok": True, "status": 0}
     single, tp0, tp1 = results[0]["single"], results[0]["tp"], results[1]["tp"]
     np.testing.assert_array_equal(tp0["logits"], tp1["logits"])          # both ranks hold the same gathered logits
     # fp16 partial sums and per-rank activation scales: a little looser than the single-kernel gates
