@@ -126,7 +126,9 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------
-def build_runtime(cfg: dict, device_index: int, extra_tokens: int):
+def build_runtime(cfg: dict, device_index: int, extra_tokens: int, tensor_parallel=None):
+    import zlib
+
     import torch
 
     from cacheir_b200 import B200DecodeRuntime, B200KVPageAllocator, ModelConfig, build_decoder_artifact
@@ -144,14 +146,15 @@ def build_runtime(cfg: dict, device_index: int, extra_tokens: int):
         # random-init weights of the reference's tiny-model recipe at full shape: N(0, 0.02), norms = 1
         if len(shape) == 1:
             return torch.ones(shape, device=dev, dtype=torch.float32)
-        gen.manual_seed(abs(hash(key)) % (2 ** 31))
+        gen.manual_seed(zlib.crc32(key.encode()))          # the same weights in every process
         return torch.randn(shape, device=dev, dtype=torch.float32, generator=gen) * 0.02
 
     page = 16
     pages_per_seq = (cfg["ctx"] + extra_tokens + page - 1) // page + 1
     alloc = B200KVPageAllocator(page_size=page, initial_slots=cfg["batch"] * pages_per_seq + 8)
     rt = B200DecodeRuntime(art, device=f"cuda:{device_index}", dtype="float16", tensor_source=synth,
-                           kv_allocator=alloc, max_seq_len=cfg["ctx"] + extra_tokens, clone_outputs=False)
+                           kv_allocator=alloc, max_seq_len=cfg["ctx"] + extra_tokens, clone_outputs=False,
+                           tensor_parallel=tensor_parallel)
     del head_dim
     return rt, art
 
@@ -214,8 +217,9 @@ def time_attention_kernel(rt, sessions, cfg: dict, iters: int = 3) -> dict:
 
     from cacheir_b200 import ops
 
-    B, H, KVH = cfg["batch"], cfg["heads"], cfg["kv_heads"]
-    hd = cfg["hidden"] // H
+    hd = cfg["hidden"] // cfg["heads"]
+    tp_world = rt._engine.tp.world                      # tensor parallel: this rank's heads only
+    B, H, KVH = cfg["batch"], cfg["heads"] // tp_world, cfg["kv_heads"] // tp_world
     plan = rt._engine.plan_for(sessions)
     lens = torch.tensor([s.kv_cache.tokens for s in sessions], dtype=torch.int32, device=rt.device)
     q = torch.randn((B, H, hd), device=rt.device, dtype=torch.float16)
@@ -516,6 +520,8 @@ def main() -> None:
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--workload", default="llama3-8b-int8-b32-ctx2048", choices=sorted(WORKLOADS))
     parser.add_argument("--e2e-steps", type=int, default=32)
+    parser.add_argument("--tp", action="store_true",
+                        help="all ranks form one tensor-parallel group decoding one batch (default: data parallel by sequence)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--micro", choices=["qgemv", "attention"], help="time one kernel alone (profiling aid)")
     parser.add_argument("--m", type=int, default=32)
@@ -559,9 +565,14 @@ def main() -> None:
 
     e2e_steps = max(4, args.e2e_steps)
     extra = warmup + args.steps + e2e_steps + 3 + 48
-    rt, _ = build_runtime(cfg, local_rank, extra)
+    tp = None
+    if args.tp and world > 1:
+        from cacheir_b200.tensor_parallel import TensorParallel
+        tp = TensorParallel(rank, world)
+    rt, _ = build_runtime(cfg, local_rank, extra, tp)
     sessions = prefill_synthetic_context(rt, cfg)
-    first_tokens = [int(t) for t in np.random.default_rng(rank).integers(0, cfg["vocab"], cfg["batch"])]
+    first_tokens = [int(t) for t in np.random.default_rng(0 if tp else rank).integers(0, cfg["vocab"], cfg["batch"])]
+    replicas = 1 if tp else world                          # independent batches in flight
 
     def barrier() -> None:
         torch.cuda.synchronize()
@@ -587,7 +598,7 @@ def main() -> None:
     last = [int(t) for t in toks[-1].tolist()]
     ctx_mid = cfg["ctx"] + warmup + args.steps // 2
     elapsed_s = max_over_ranks(elapsed_s, torch.device("cuda", local_rank))
-    tokens_total = world * cfg["batch"] * args.steps
+    tokens_total = replicas * cfg["batch"] * args.steps
     value = tokens_total / elapsed_s
 
     # ---- host-facing loop: `e2e` ------------------------------------------------------
@@ -610,7 +621,7 @@ def main() -> None:
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     e2e_s = max_over_ranks(e2e_s, torch.device("cuda", local_rank))
-    e2e_value = world * cfg["batch"] * e2e_steps / e2e_s
+    e2e_value = replicas * cfg["batch"] * e2e_steps / e2e_s
 
     # ---- per-kernel roofline (rank 0 reports) -------------------------------------------
     peak, peak_kind = measured_peaks()
@@ -622,7 +633,8 @@ def main() -> None:
         kernels.append({"kernel": k["kernel"], "us": round(k["seconds"] * 1e6, 2), "algorithmic_bytes": int(k["bytes"]),
                         "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4), **({"shape": k["shape"]} if "shape" in k else {})})
     sb = step_bytes(cfg, ctx_mid)
-    step_gbs = sb["total"] / (elapsed_s / args.steps) / 1e9
+    shards = world if tp else 1                              # tensor parallel: each rank streams its share of the step
+    step_gbs = sb["total"] / shards / (elapsed_s / args.steps) / 1e9
 
     if rank == 0:
         # DRAM traffic of the attention kernel: the ratio measured by ncu on a small case (the profile
@@ -636,11 +648,12 @@ def main() -> None:
                 traffic = int(float(found.group(1)) * attn["bytes"])
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
-            "ms_per_step": elapsed_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": elapsed_s / args.steps * 1e3, "higher_is_better": True, "scaling": "strong" if tp else "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": args.workload, "batch_per_gpu": cfg["batch"], "context": cfg["ctx"],
                        "layers": cfg["layers"], "weights": "int8 per-row affine (fp32 scale+zero)", "kv": "fp16 pages of 16",
-                       "parallelism": f"dp{world} by sequence, no collective", "l2_policy": "inputs larger than L2 (16 GB/step)"},
+                       "parallelism": (f"tp{world}: heads and FFN split, own all-reduce kernels over NVLink peer memory" if tp
+                                       else f"dp{world} by sequence, no collective"), "l2_policy": "inputs larger than L2 (16 GB/step)"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d // e2e_steps, "d2h_bytes_per_step": d2h // e2e_steps,
                     "steps": e2e_steps, "api": "B200DecodeRuntime.run_decode_batch + argmax_tokens"},
             "gpu_launches": launches_per_step * args.steps,
@@ -651,7 +664,7 @@ def main() -> None:
             "kernels": kernels,
             "step": {"algorithmic_bytes": int(sb["total"]), "weight_bytes": int(sb["weights"]), "kv_bytes": int(sb["kv"]),
                      "achieved_gbs": round(step_gbs, 1), "frac_of_hbm_roofline": round(step_gbs / peak, 4),
-                     "roofline_tokens_per_s": round(cfg["batch"] * peak * 1e9 / sb["total"], 1),
+                     "roofline_tokens_per_s": round(cfg["batch"] * peak * 1e9 * shards / sb["total"], 1),
                      "launches_per_step": launches_per_step},
         }
         if world == 1 and not args.no_cpu_baseline:
