@@ -233,6 +233,26 @@ extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const vo
   p.vector_ok = aligned_to(packed, 16) && row_bytes % 16 == 0 && aligned_to(x, 16) &&
                 (p.x_stride * esize) % 16 == 0;
   cudaStream_t st = as_stream(stream);
+  if (M > 64 && !p.x_prequantized) {
+    // The tensor-core kernels take up to 64 batch rows per launch. A taller batch runs as chunks of 64 rows
+    // (the weights stream once per chunk, still far cheaper than the CUDA-core kernel at these heights) when
+    // a 64-row problem of the same shape is tensor-core eligible.
+    QGemvParams c = p;
+    c.M = 64;
+    const bool i8_ok = qgemm_i8_supported(c, workspace, workspace_bytes);
+    if (i8_ok || (!c.paired && qgemm_tc_supported(c))) {
+      const size_t n_out = epilogue == CACHEIR_B200_EPI_SWIGLU ? static_cast<size_t>(N) / 2 : static_cast<size_t>(N);
+      for (int m0 = 0; m0 < M; m0 += 64) {
+        c.M = M - m0 < 64 ? M - m0 : 64;
+        c.x = static_cast<const char*>(x) + static_cast<size_t>(m0) * p.x_stride * esize;
+        c.y = static_cast<char*>(y) + static_cast<size_t>(m0) * n_out * esize;
+        c.residual = residual ? static_cast<const char*>(residual) + static_cast<size_t>(m0) * n_out * esize : nullptr;
+        const int rc = i8_ok ? launch_qgemm_i8(c, workspace, st) : launch_qgemm_tc(c, st);
+        if (rc != 0) return rc;
+      }
+      return 0;
+    }
+  }
   if (qgemm_i8_supported(p, workspace, workspace_bytes)) return launch_qgemm_i8(p, workspace, st);
   if (p.x_prequantized) return CACHEIR_B200_EINVAL;   // only the integer path can consume a quantized workspace
   if (p.paired) return CACHEIR_B200_EUNSUPPORTED;     // only the integer tensor-core kernel reads paired tiles

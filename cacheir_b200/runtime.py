@@ -34,7 +34,7 @@ import torch
 from . import ops
 from .artifact import CompileArtifact
 from .kv_cache import B200KVPageAllocator, B200PagedKVCache
-from .quantization import B200PackedWeight, concat_rows, quant_bits, to_rows, to_tiled
+from .quantization import B200PackedWeight, concat_rows, quant_bits, to_tiled
 from .tensor_parallel import PeerCollectives, TensorParallel, shard_columns, shard_rows
 from .weights import B200WeightStore, TensorSource
 
@@ -174,18 +174,14 @@ class _Engine:
                       role: str = "column") -> B200PackedWeight | torch.Tensor:
         """One (row-concatenated) weight for a matmul-family node: packed when the
         node is a quantized op, dense [N, K] otherwise (cuda.py:1017-1023 caches the
-        same concatenation for its unquantized fused ops). Batches beyond the tensor-core
-        kernels' 64 rows run on the CUDA-core kernel, which reads the reference's row
-        order: the first such batch moves the weight back to rows for good.
+        same concatenation for its unquantized fused ops). (Batches beyond the tensor-core
+        kernels' 64 rows are run by the library as 64-row chunks, so the tile order serves them too.)
         `role` says how tensor parallelism slices it: "column" (output rows, each fused
         part separately so a rank keeps whole heads / matching gate and up rows), "row"
         (the input dimension) or "replicated"."""
         if names in self.fused_weights:
-            fused = self.fused_weights[names]
-            if batch > 64 and isinstance(fused, B200PackedWeight) and fused.tiled:
-                self.tile_weights = False
-                fused = self.fused_weights[names] = to_rows(fused)
-            return fused
+            return self.fused_weights[names]
+
         def shard(w):
             if not self.tp.enabled or role == "replicated":
                 return w
@@ -204,7 +200,7 @@ class _Engine:
             half = fused.shape[0] // 2
             paired = pair and fused.bits == 8 and not fused.group_size and half % 64 == 0
             halves_ok = not pair or paired or half % 128 == 0
-            if self.dtype == torch.float16 and fused.shape[1] % 128 == 0 and halves_ok and self.tile_weights and batch <= 64:
+            if self.dtype == torch.float16 and fused.shape[1] % 128 == 0 and halves_ok and self.tile_weights:
                 tiled = to_tiled(fused, paired=paired)
                 if len(parts) == 1:
                     self.weights.release(names[0])
@@ -498,8 +494,8 @@ class _DecodePlan:
                                    workspace=ws, tiled=weight.tiled, prequantized=prequantized, paired=weight.paired)
             key = f"b200.qgemv.int{bits}" + (".swiglu" if epilogue == ops.EPI_SWIGLU else ".residual" if residual is not None else "")
             eng.gemm_plans[f"q{bits}:{(self.batch, 1, k)}x{weight.shape}"] = key
-            if ws is not None and self.batch <= 64 and k % 128 == 0 and not prequantized:   # activation pre-pass + integer GEMM
-                self._emit(fn, key, launches=2)
+            if ws is not None and k % 128 == 0 and k <= 32768 and not prequantized:   # activation pre-pass + integer GEMM per 64-row chunk
+                self._emit(fn, key, launches=2 * ((self.batch + 63) // 64))
                 return out
         else:
             n, k = int(weight.shape[0]), int(weight.shape[1])

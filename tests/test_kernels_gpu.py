@@ -594,3 +594,30 @@ def test_qkv_rope_append_equals_separate_kernels(k, tiled):
     got = rope[37].cpu().numpy()
     np.testing.assert_allclose(got[:, 0] - got[:, 1], want.reshape(-1)[0::2], rtol=0, atol=1e-5)
     _device_status_ok()
+
+
+# ---- batches taller than one tensor-core launch run as 64-row chunks --------------------------
+@pytest.mark.parametrize("bits,group,tiled", [(8, 0, True), (8, 0, False), (4, 128, True), (4, 0, False)])
+def test_qgemv_tall_batch_runs_in_chunks(bits, group, tiled):
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul, to_tiled
+    rng = np.random.default_rng(7 + bits + group)
+    m, n, k = 150, 384, 512
+    x, packed = _qgemv_case(rng, m, n, k, bits, torch.float16, group=group, reference_pack=not group)
+    dev = _device_pack(packed)
+    if group:
+        dev.scales = torch.from_numpy(packed.scales).cuda()
+    weight = to_tiled(dev) if tiled else dev
+    ws = torch.zeros(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda") if bits == 8 else None
+    base = oracle.quantized_matmul(x.float().numpy(), packed)
+    y = quantized_matmul(x.cuda(), weight, workspace=ws)
+    assert y.shape == (m, n)
+    assert _rel(y, base) <= TOL[torch.float16]
+    # each chunk equals the same rows computed on their own
+    y_tail = quantized_matmul(x[128:].cuda().contiguous(), weight, workspace=ws)
+    assert torch.equal(y[128:], y_tail)
+    res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).half()
+    y = quantized_matmul(x.cuda(), weight, epilogue=ops.EPI_RESIDUAL, residual=res.cuda(), workspace=ws)
+    assert _rel(y, base + res.float().numpy()) <= TOL[torch.float16]
+    torch.cuda.synchronize()
+    _device_status_ok()
