@@ -54,7 +54,25 @@ WORKLOADS = {
     "llama3-8b-int8-b32-ctx2048": dict(layers=32, hidden=4096, heads=32, kv_heads=8, ffn=14336, vocab=128256,
                                        batch=32, ctx=2048, quant="int8"),
     "small": dict(layers=2, hidden=1024, heads=8, kv_heads=2, ffn=2816, vocab=4096, batch=8, ctx=256, quant="int8"),
+    # the 70B-shaped tensor-parallel configuration: group-128 int4 weights, 128 sequences with log-uniform
+    # contexts, 8 groups of 16 requests sharing a 512-token prefix (run with --tp on 8 GPUs)
+    "llama3-70b-int4g128-b128-tp8": dict(layers=80, hidden=8192, heads=64, kv_heads=8, ffn=28672, vocab=128256,
+                                         batch=128, ctx_range=(1024, 32768), shared_prefix=(16, 512), quant="int4_g128"),
+    # the same code path at a size two GPUs handle in seconds
+    "small-tp": dict(layers=4, hidden=1024, heads=8, kv_heads=8, ffn=3072, vocab=4096, batch=72,
+                     ctx_range=(64, 1024), shared_prefix=(8, 32), quant="int4_g128"),
 }
+
+
+def context_lengths(cfg: dict) -> list[int]:
+    """Per-sequence context: the fixed `ctx`, or log-uniform in `ctx_range` (seed 0) for the ragged workloads."""
+    if "ctx_range" not in cfg:
+        return [int(cfg["ctx"])] * cfg["batch"]
+    lo, hi = cfg["ctx_range"]
+    u = np.random.default_rng(0).uniform(np.log(lo), np.log(hi), cfg["batch"])
+    lens = np.exp(u).astype(np.int64)
+    group, shared = cfg.get("shared_prefix", (1, 0))
+    return [int(max(v, shared + 1 if group > 1 else 1)) for v in lens]
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -150,8 +168,8 @@ def build_runtime(cfg: dict, device_index: int, extra_tokens: int, tensor_parall
         return torch.randn(shape, device=dev, dtype=torch.float32, generator=gen) * 0.02
 
     page = 16
-    pages_per_seq = (cfg["ctx"] + extra_tokens + page - 1) // page + 1
-    alloc = B200KVPageAllocator(page_size=page, initial_slots=cfg["batch"] * pages_per_seq + 8)
+    total_pages = sum((c + extra_tokens + page - 1) // page + 1 for c in context_lengths(cfg))
+    alloc = B200KVPageAllocator(page_size=page, initial_slots=total_pages + 8)
     rt = B200DecodeRuntime(art, device=f"cuda:{device_index}", dtype="float16", tensor_source=synth,
                            kv_allocator=alloc, max_seq_len=cfg["ctx"] + extra_tokens, clone_outputs=False,
                            tensor_parallel=tensor_parallel)
@@ -165,8 +183,11 @@ def prefill_synthetic_context(rt, cfg: dict):
     import torch
 
     sessions = [rt.fork() for _ in range(cfg["batch"])]
-    for s in sessions:
-        s.kv_cache.extend(cfg["ctx"])
+    group, shared = cfg.get("shared_prefix", (1, 0))
+    for i, (s, ctx) in enumerate(zip(sessions, context_lengths(cfg))):
+        if group > 1 and i % group != 0:                  # alias the full pages of the group leader's prefix
+            s.kv_cache.share_prefix(sessions[i - i % group].kv_cache, shared)
+        s.kv_cache.extend(ctx - s.kv_cache.tokens)
     gen = torch.Generator(device=rt.device)
     gen.manual_seed(1234)
     for layer in range(cfg["layers"]):
@@ -176,16 +197,28 @@ def prefill_synthetic_context(rt, cfg: dict):
     return sessions
 
 
-def step_bytes(cfg: dict, ctx: int) -> dict:
-    """Algorithmic HBM bytes of one decode step: every weight byte once, every cached K/V row once."""
+def unique_kv_tokens(cfg: dict, generated: int) -> int:
+    """Cached tokens that occupy distinct physical pages: pages of a shared prefix count once."""
+    lens = context_lengths(cfg)
+    group, shared = cfg.get("shared_prefix", (1, 0))
+    aliased = (shared // 16) * 16 * (cfg["batch"] - (cfg["batch"] + group - 1) // group) if group > 1 else 0
+    return sum(lens) - aliased + cfg["batch"] * generated
+
+
+def step_bytes(cfg: dict, kv_tokens: int) -> dict:
+    """Algorithmic HBM bytes of one decode step: every weight byte once, every cached K/V row once
+    (`kv_tokens` = unique cached tokens over the whole batch)."""
     h, f, v, L = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["layers"]
     hd = h // cfg["heads"]
     kvd = cfg["kv_heads"] * hd
     bits = 8 if cfg["quant"] == "int8" else 4
     rows = (h + 2 * kvd) + h + 2 * f + h          # q,k,v | o | gate,up | down
-    layer_w = ((h + 2 * kvd) * h + h * h + 2 * f * h + h * f) * bits // 8 + rows * 8
-    weights = L * layer_w + v * h * bits // 8 + v * 8
-    kv = L * cfg["batch"] * ctx * kvd * 2 * 2
+    elems = (h + 2 * kvd) * h + h * h + 2 * f * h + h * f
+    group = 128 if "g128" in cfg["quant"] else 0
+    meta = elems // group * 2 if group else rows * 8            # fp16 group scales | fp32 scale + zero per row
+    layer_w = elems * bits // 8 + meta
+    weights = L * layer_w + v * h * bits // 8 + (v * h // group * 2 if group else v * 8)
+    kv = L * kv_tokens * kvd * 2 * 2
     return {"weights": weights, "kv": kv, "total": weights + kv}
 
 
@@ -234,7 +267,9 @@ def time_attention_kernel(rt, sessions, cfg: dict, iters: int = 3) -> dict:
                                              num_splits=splits, workspace=ws)
 
     per_launch_s = time_graph(sweep, iters) / len(pools)
-    total_ctx = int(lens.sum().item())
+    group, shared = cfg.get("shared_prefix", (1, 0))      # physical pages of a shared prefix are read (and count) once
+    aliased = (shared // 16) * 16 * (B - (B + group - 1) // group) if group > 1 else 0
+    total_ctx = int(lens.sum().item()) - aliased
     algo = total_ctx * KVH * hd * 2 * 2 + 2 * B * H * hd * 2 + B * plan.width * 4 + B * 4
     return {"kernel": "paged_attention_decode_batch", "seconds": per_launch_s, "bytes": algo, "splits": splits}
 
@@ -542,10 +577,14 @@ def main() -> None:
         run_micro(args)
         return
     cfg = dict(WORKLOADS[args.workload])
+    if "ctx_range" in cfg:
+        lens_all = context_lengths(cfg)
+        cfg["ctx"] = max(lens_all)                      # sizing (positions, page-table width)
+        cfg["ctx_mean"] = int(np.mean(lens_all))
     warmup = max(3, args.warmup)
 
     if args.impl == "reference":
-        run_reference_arm(args, cfg, args.workload)
+        run_reference_arm(args, dict(cfg, ctx=cfg.get("ctx_mean", cfg["ctx"])), args.workload)   # ragged: the mean context
         return
 
     import torch
@@ -596,7 +635,7 @@ def main() -> None:
     elapsed_s = start.elapsed_time(end) * 1e-3
     clocks = sampler.stop()
     last = [int(t) for t in toks[-1].tolist()]
-    ctx_mid = cfg["ctx"] + warmup + args.steps // 2
+    kv_tokens_mid = unique_kv_tokens(cfg, warmup + args.steps // 2)
     elapsed_s = max_over_ranks(elapsed_s, torch.device("cuda", local_rank))
     tokens_total = replicas * cfg["batch"] * args.steps
     value = tokens_total / elapsed_s
@@ -632,7 +671,7 @@ def main() -> None:
         gbs = k["bytes"] / k["seconds"] / 1e9
         kernels.append({"kernel": k["kernel"], "us": round(k["seconds"] * 1e6, 2), "algorithmic_bytes": int(k["bytes"]),
                         "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4), **({"shape": k["shape"]} if "shape" in k else {})})
-    sb = step_bytes(cfg, ctx_mid)
+    sb = step_bytes(cfg, kv_tokens_mid)
     shards = world if tp else 1                              # tensor parallel: each rank streams its share of the step
     step_gbs = sb["total"] / shards / (elapsed_s / args.steps) / 1e9
 
@@ -650,8 +689,13 @@ def main() -> None:
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": elapsed_s / args.steps * 1e3, "higher_is_better": True, "scaling": "strong" if tp else "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": args.workload, "batch_per_gpu": cfg["batch"], "context": cfg["ctx"],
-                       "layers": cfg["layers"], "weights": "int8 per-row affine (fp32 scale+zero)", "kv": "fp16 pages of 16",
+            "config": {"workload": args.workload, "batch_per_gpu": cfg["batch"],
+                       "context": (f"log-uniform {cfg['ctx_range'][0]}..{cfg['ctx_range'][1]} (mean {cfg['ctx_mean']}), "
+                                   f"{cfg['shared_prefix'][0]}-way shared {cfg['shared_prefix'][1]}-token prefixes"
+                                   if "ctx_range" in cfg else cfg["ctx"]),
+                       "layers": cfg["layers"],
+                       "weights": ("int4 group-128 symmetric (fp16 scales)" if "g128" in cfg["quant"]
+                                   else "int8 per-row affine (fp32 scale+zero)"), "kv": "fp16 pages of 16",
                        "parallelism": (f"tp{world}: heads and FFN split, own all-reduce kernels over NVLink peer memory" if tp
                                        else f"dp{world} by sequence, no collective"), "l2_policy": "inputs larger than L2 (16 GB/step)"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d // e2e_steps, "d2h_bytes_per_step": d2h // e2e_steps,
@@ -668,7 +712,7 @@ def main() -> None:
                      "launches_per_step": launches_per_step},
         }
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = run_cpu_baseline(cfg)
+            line["cpu_baseline"] = run_cpu_baseline(dict(cfg, ctx=cfg.get("ctx_mean", cfg["ctx"])))
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

@@ -52,14 +52,47 @@ class B200PackedWeight:
         return int(total)
 
 
+def quant_group_size(quant: str | None) -> int:
+    """Group size named by a quant string such as "int4_g128" (0: the reference's per-row affine format)."""
+    if not quant:
+        return 0
+    for part in quant.lower().replace("-", "_").split("_"):
+        if part.startswith("g") and part[1:].isdigit():
+            return int(part[1:])
+    return 0
+
+
+def pack_group_int4(weight: torch.Tensor, group_size: int = 128) -> B200PackedWeight:
+    """Group-wise symmetric int4: w[n, k] ~ (code - 8) * scale[n, k // group], fp16 scales, the nibble order
+    of the reference's int4 pack (even column in the low nibble, cacheir/quantization.py:123-130). The
+    reference has the `group_size` field (cacheir/quantization.py:25) but no packer for it; its nearest
+    relative is the GGUF Q4_0 block format, `(nibble - 8) * d` (cacheir/importers/gguf.py:297-310).
+    scale = max|w| / 7 per group (rounded to fp16), code = clip(rint(w / scale) + 8, 0, 15)."""
+    w = weight.to(dtype=torch.float32).contiguous()
+    n, k = int(w.shape[0]), int(w.shape[1])
+    if w.dim() != 2 or k % group_size != 0 or group_size % 2 != 0:
+        raise ValueError("group-wise int4 needs a 2D weight whose width is a multiple of the (even) group size")
+    groups = w.view(n, k // group_size, group_size)
+    scales = (groups.abs().amax(dim=2) / 7.0).clamp_min(1e-8).to(torch.float16)
+    q = torch.clamp(torch.round(groups / scales.float().unsqueeze(2)) + 8.0, 0.0, 15.0).to(torch.uint8).view(n, k)
+    packed = (q[:, 0::2] | (q[:, 1::2] << 4)).contiguous()
+    return B200PackedWeight(packed, scales.contiguous(), None, 4, (n, k), group_size=group_size)
+
+
 def pack_weight_device(weight: torch.Tensor, quant: str | None) -> B200PackedWeight | None:
-    """`pack_quantized_weight` (cacheir/quantization.py:63-71) on the GPU; None when `quant` names no packed format."""
+    """`pack_quantized_weight` (cacheir/quantization.py:63-71) on the GPU; None when `quant` names no packed format.
+    A group size in the name ("int4_g128") selects the group-wise symmetric int4 extension."""
     bits = quant_bits(quant)
     if bits is None:
         return None
     w = weight.to(dtype=torch.float32).contiguous()
     if w.dim() != 2:
         raise ValueError("packed quantization expects a 2D out_features x in_features weight")
+    group = quant_group_size(quant)
+    if group:
+        if bits != 4:
+            raise ValueError("group-wise quantization is defined for int4 only")
+        return pack_group_int4(w, group)
     packed, scales, zp_i, zp_f = ops.pack_rows(w, bits)
     return B200PackedWeight(packed, scales, zp_f, bits, (int(w.shape[0]), int(w.shape[1])), zero_points_i32=zp_i)
 
@@ -122,9 +155,15 @@ def to_rows(w: B200PackedWeight) -> B200PackedWeight:
 
 
 def dequantize_device(w: B200PackedWeight, dtype: torch.dtype) -> torch.Tensor:
-    """`dequantize_packed_weight` (cacheir/quantization.py:74-84) on the GPU, per-row affine weights only."""
-    if w.group_size:
-        raise NotImplementedError("dequantize_device covers the per-row affine format")
+    """`dequantize_packed_weight` (cacheir/quantization.py:74-84) on the GPU (load time)."""
+    if w.group_size:      # group-wise symmetric int4: (code - 8) * scale[n, k // group]
+        n, k = w.shape
+        codes = to_rows(w).packed_values if w.tiled else w.packed_values
+        q = torch.empty((n, k), device=codes.device, dtype=torch.float32)
+        q[:, 0::2] = (codes & 0xF).float()
+        q[:, 1::2] = (codes >> 4).float()
+        scale = w.scales.float().reshape(n, -1).repeat_interleave(w.group_size, dim=1)
+        return ((q - 8.0) * scale).to(dtype)
     return ops.dequantize_rows(w.packed_values, w.scales, w.zero_points, bits=w.bits, k=w.shape[1], dtype=dtype)
 
 

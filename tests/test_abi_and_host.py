@@ -197,3 +197,30 @@ def test_batched_launcher_equals_sequential():
     assert batched.metrics.batched_decode_rounds == 3
     assert batched.metrics.batched_decode_tokens == 6
     assert batched.metrics.completed_requests == 2
+
+
+def test_group_int4_packer_matches_oracle_dequantisation():
+    """Group-wise symmetric int4 (the extension the 70B-shaped configuration uses): codes and fp16 scales
+    made by the host-side packer dequantise, through the oracle's formula, to within half a step of the weight."""
+    import numpy as np
+    import torch
+
+    from cacheir_b200.quantization import pack_group_int4, quant_bits, quant_group_size
+    from oracle import oracle
+
+    assert quant_group_size("int4_g128") == 128 and quant_bits("int4_g128") == 4 and quant_group_size("int8") == 0
+    rng = np.random.default_rng(0)
+    w = rng.standard_normal((6, 384)).astype(np.float32) * 0.02
+    w[2, :128] = 0.0                                             # an all-zero group keeps a tiny positive scale
+    p = pack_group_int4(torch.from_numpy(w), 128)
+    assert p.packed_values.shape == (6, 192) and p.scales.shape == (6, 3) and p.scales.dtype == torch.float16
+    codes = p.packed_values.numpy()
+    q = np.empty((6, 384), dtype=np.uint8)
+    q[:, 0::2] = codes & 15                                      # even column in the low nibble
+    q[:, 1::2] = codes >> 4
+    deq = oracle.dequantize_packed_weight(oracle.symmetric_group_pack_from_codes(q, p.scales.numpy(), 4, 128))
+    step = np.repeat(p.scales.numpy().astype(np.float32), 128, axis=1)
+    assert np.all(np.abs(deq - w) <= step / 2 * 1.01 + 1e-7)
+    assert np.all(deq[2, :128] == 0.0)
+    with pytest.raises(ValueError):
+        pack_group_int4(torch.zeros(4, 100), 128)
