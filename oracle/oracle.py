@@ -117,6 +117,25 @@ def dequantize_packed_weight(q: PackedQuantizedTensor) -> np.ndarray:
     return (codes - zero) * scale
 
 
+def decode_q4_0_blocks(raw: bytes, count: int) -> np.ndarray:
+    """llama.cpp Q4_0: per 32 elements an fp16 scale d and 16 bytes; low nibbles are elements
+    0..15, high nibbles 16..31; value = (nibble - 8) * d. cacheir/importers/gguf.py:297-310."""
+    data = np.frombuffer(raw, dtype=np.uint8).reshape(count // 32, 18)
+    d = data[:, :2].copy().view(np.float16).astype(np.float32)            # [blocks, 1]
+    out = np.empty((count // 32, 32), dtype=np.float32)
+    out[:, :16] = (data[:, 2:] & 0x0F).astype(np.float32) - 8.0
+    out[:, 16:] = (data[:, 2:] >> 4).astype(np.float32) - 8.0
+    return (out * d).reshape(-1)
+
+
+def decode_q8_0_blocks(raw: bytes, count: int) -> np.ndarray:
+    """llama.cpp Q8_0: per 32 elements an fp16 scale d and 32 signed bytes; value = int8 * d.
+    cacheir/importers/gguf.py:273-283."""
+    data = np.frombuffer(raw, dtype=np.uint8).reshape(count // 32, 34)
+    d = data[:, :2].copy().view(np.float16).astype(np.float32)
+    return (data[:, 2:].view(np.int8).astype(np.float32) * d).reshape(-1)
+
+
 def quantize_dequantize(weight: np.ndarray, quant: str | None) -> np.ndarray:
     """cacheir/quantization.py:52-60 (packed branch): what a non-matmul 2-D weight becomes under quant."""
     packed = pack_quantized_weight(weight, quant)

@@ -621,3 +621,27 @@ def test_qgemv_tall_batch_runs_in_chunks(bits, group, tiled):
     assert _rel(y, base + res.float().numpy()) <= TOL[torch.float16]
     torch.cuda.synchronize()
     _device_status_ok()
+
+
+# ---- llama.cpp block formats streamed as group-32 packs (no fp32 dequantisation at load) ---------
+@pytest.mark.parametrize("fmt", ["q4_0", "q8_0"])
+def test_gguf_block_weights_run_in_place(fmt):
+    from cacheir_b200.gguf_blocks import q4_0_to_packed, q8_0_to_packed
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(11)
+    m, n, k = 5, 96, 256
+    blocks = n * k // 32
+    if fmt == "q4_0":
+        raw = b"".join(np.float16(rng.uniform(0.005, 0.02)).tobytes() + rng.integers(0, 256, 16, dtype=np.uint8).tobytes()
+                       for _ in range(blocks))
+        dense = oracle.decode_q4_0_blocks(raw, n * k).reshape(n, k)
+        packed = q4_0_to_packed(raw, n, k, "cuda")
+    else:
+        raw = b"".join(np.float16(rng.uniform(0.0005, 0.002)).tobytes() + rng.integers(-128, 128, 32).astype(np.int8).tobytes()
+                       for _ in range(blocks))
+        dense = oracle.decode_q8_0_blocks(raw, n * k).reshape(n, k)
+        packed = q8_0_to_packed(raw, n, k, "cuda")
+    for dtype in (torch.float32, torch.float16):
+        x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(dtype)
+        want = x.float().numpy() @ dense.T                       # the reference: dequantise the blocks, then matmul
+        assert _rel(quantized_matmul(x.cuda(), packed), want) <= TOL[dtype]

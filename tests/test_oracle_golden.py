@@ -4,6 +4,7 @@ import hashlib
 import json
 
 import numpy as np
+import pytest
 
 from oracle import oracle
 
@@ -143,3 +144,37 @@ def test_oracle_agrees_with_reference_native_kernels():
     xb = rng.standard_normal((2, 5, 300)).astype(np.float32)
     wb = rng.standard_normal((77, 300)).astype(np.float32)
     np.testing.assert_allclose(ref_native.matmul_out_in(xb, wb), oracle.matmul(xb, wb), rtol=1e-4, atol=1e-4)
+
+
+def test_gguf_block_formats_known_answers_and_native_repack():
+    """Q4_0 / Q8_0 (cacheir/importers/gguf.py:273-310). Known-answer blocks of the shape the reference's
+    reader test builds (tests/test_advanced_experiments.py:59-128): ascending / descending nibbles with
+    d = 0.25, and the signed ramp -16..15 with d = 0.5. The native repack is a pure permutation of the
+    codes: dequantising the repacked weight with the group-wise formula gives the block decode exactly."""
+    import torch
+
+    from cacheir_b200.gguf_blocks import q4_0_to_packed, q8_0_to_packed
+
+    low = np.arange(16, dtype=np.uint8)
+    high = (15 - np.arange(16, dtype=np.uint8)).astype(np.uint8)
+    q4_block = np.float16(0.25).tobytes() + (low | (high << 4)).astype(np.uint8).tobytes()
+    want4 = np.concatenate([(low.astype(np.float32) - 8) * 0.25, (high.astype(np.float32) - 8) * 0.25])
+    np.testing.assert_array_equal(oracle.decode_q4_0_blocks(q4_block, 32), want4)
+    q8_values = np.arange(-16, 16, dtype=np.int8)
+    q8_block = np.float16(0.5).tobytes() + q8_values.tobytes()
+    np.testing.assert_array_equal(oracle.decode_q8_0_blocks(q8_block, 32), q8_values.astype(np.float32) * 0.5)
+
+    rng = np.random.default_rng(5)
+    n, k = 6, 96
+    raw4 = b"".join(np.float16(rng.uniform(0.01, 0.5)).tobytes() + rng.integers(0, 256, 16, dtype=np.uint8).tobytes()
+                    for _ in range(n * k // 32))
+    raw8 = b"".join(np.float16(rng.uniform(0.01, 0.5)).tobytes() + rng.integers(-128, 128, 32).astype(np.int8).tobytes()
+                    for _ in range(n * k // 32))
+    for raw, decode, repack, bits in ((raw4, oracle.decode_q4_0_blocks, q4_0_to_packed, 4),
+                                      (raw8, oracle.decode_q8_0_blocks, q8_0_to_packed, 8)):
+        packed = repack(raw, n, k)
+        assert packed.bits == bits and packed.group_size == 32 and packed.scales.dtype == torch.float16
+        ref = oracle.PackedQuantizedTensor(packed.packed_values.numpy(), packed.scales.numpy(), None, bits, (n, k), group_size=32)
+        np.testing.assert_array_equal(oracle.dequantize_packed_weight(ref), decode(raw, n * k).reshape(n, k))
+    with pytest.raises(ValueError):
+        q4_0_to_packed(raw4[:-1], n, k)
