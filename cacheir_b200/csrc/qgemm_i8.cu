@@ -2,25 +2,27 @@
 //
 //   y[M, N] = x[M, K] . ((code[N, K] - zero[N]) * scale[N])^T      M <= 64, fp16 x/y
 //
-// The packed uint8 codes go from HBM through TMA into shared memory and from there
-// straight into the tensor core: nothing unpacks, converts or re-stores a weight.
+// The packed uint8 codes go from HBM through one bulk copy per 16 KB tile (tile-ordered,
+// pre-swizzled weights) or a TMA tensor copy (reference row order) into shared memory and from
+// there straight into the tensor core: nothing unpacks, converts or re-stores a weight.
 // Activations are made integer instead. A pre-pass turns every row of x into 16-bit
 // fixed point with its own scale, x[m,k] ~= sx[m] * q[m,k], |q| <= 32639 (2^-15 of the
 // row maximum: far below fp16's own resolution), and splits q into two signed bytes,
 // q = 256*hi + lo. With the weight tile as the 128-row operand and the [hi; lo] rows
 // as the other one, a single accumulator row holds, for weight row n,
 //   D[n, m] = sum_k code[n,k]*hi[m,k]      D[n, MP+m] = sum_k code[n,k]*lo[m,k]
-// exactly (int32). The epilogue recombines in double precision:
+// exactly (int32). The epilogue recombines in integers:
 //   y[m,n] = scale[n] * sx[m] * (256*D[n,m] + D[n,MP+m] - zero[n] * sum_k q[m,k]).
 //
-// One CTA owns 128 weight rows and a K range: warp 0 issues the TMA copies, warps 1 and 6 the
-// MMAs (K = 32 per instruction, 4 per 128-column stage; the two issuers take alternate stages
-// and own separate accumulators, so one can wait on a barrier while the other feeds the tensor
-// core -- integer sums, so adding the two accumulators afterwards is exact), warps 2-5 run the
-// epilogue.
+// One CTA owns 128 weight rows (with the SwiGLU epilogue: 64 gate rows and the 64 up rows of the
+// same columns) and a K range: thread 0 initialises the barriers and requests the first ring of
+// tiles while the rest of the CTA sets up, then keeps the ring full; one thread of warp 1 issues
+// the MMAs (K = 32 per instruction, 4 per 128-column stage) into an accumulator in tensor memory;
+// warps 2-5 run the epilogue (plain, residual, SwiGLU, or the fused QKV form: RoPE + cache append).
 // K ranges of one row tile form a thread-block cluster. Their partial sums are integers, so
-// the order of addition cannot matter; they are exchanged all-to-all through distributed
-// shared memory, each CTA of the cluster finishing the outputs of its own slice of the batch.
+// the order of addition cannot matter; each rank lays its partials out per destination in its
+// drained ring and one bulk shared-to-shared copy per destination signals that rank's barrier;
+// each CTA of the cluster finishes the outputs of its own slice of the batch. Two CTAs share an SM.
 #include "common.cuh"
 #include "qgemv_common.cuh"
 #include "tc_ptx.cuh"
