@@ -156,6 +156,7 @@ class _Engine:
         self.peer: PeerCollectives | None = None
         self.use_cuda_graph = use_cuda_graph and (not self.tp.enabled or self.peer_mode)
         self.tile_weights = True
+        self.prefill_chunk = 64        # prompt tokens per pass of the chunked prefill (0: one token per step)
         self._rope_tables: dict[tuple[int, float], torch.Tensor] = {}
         self.attention_splits = int(attention_splits)
         self.max_plans = max(1, int(max_plans))
@@ -228,6 +229,24 @@ class _Engine:
         if key not in self._rope_tables:
             self._rope_tables[key] = ops.rope_table(self.max_seq_len, head_dim, theta, self.device)
         return self._rope_tables[key]
+
+    def prefill_plan(self, rows: int, needed_pages: int) -> "_DecodePlan":
+        """The plan that pushes `rows` consecutive prompt tokens of ONE sequence through the decode graph at once:
+        row i is the token at position start+i, reads the sequence's page table and attends to start+i+1 tokens."""
+        key = ("prefill", rows)
+        plan = self.plans.get(key)
+        if plan is not None and (plan.pool_generation != self.allocator.generation or plan.width < needed_pages):
+            self.plans.pop(key)
+            plan = None
+        if plan is None:
+            width = max(needed_pages, (self.max_seq_len + self.page_size - 1) // self.page_size)
+            plan = _DecodePlan(self, rows, width)
+            self.plans[key] = plan
+            while len(self.plans) > self.max_plans:
+                self.plans.popitem(last=False)
+        else:
+            self.plans.move_to_end(key)
+        return plan
 
     def plan_for(self, sessions: list["B200DecodeRuntime"]) -> "_DecodePlan":
         key = tuple(s.kv_cache.owner_id for s in sessions)
@@ -572,6 +591,24 @@ class _DecodePlan:
             self.seq_lens.copy_(self.host_lens, non_blocking=True)
         self.synced_owner_state = state
 
+    def sync_prefill_chunk(self, cache: B200PagedKVCache, start: int, token_ids: list[int]) -> None:
+        """Rows 0..n-1 are the tokens at positions start..start+n-1 of one sequence whose pages already cover
+        them; rows beyond n repeat the last token (same position, same values: harmless duplicates)."""
+        n = len(token_ids)
+        self.h2d_done.synchronize()
+        ids = self.host_ids.numpy()
+        lens = self.host_lens.numpy()
+        for row in range(self.batch):
+            i = min(row, n - 1)
+            ids[row] = int(token_ids[i])
+            lens[row] = start + i            # the step turns this into position start+i and length start+i+1
+        self.host_table.numpy()[:] = cache.page_table_row(self.width)[None, :]
+        self.ids.copy_(self.host_ids, non_blocking=True)
+        self.seq_lens.copy_(self.host_lens, non_blocking=True)
+        self.page_table.copy_(self.host_table, non_blocking=True)
+        self.h2d_done.record()
+        self.synced_owner_state = None
+
     def run_program(self, *, feedback: bool = False) -> None:
         """One decode step: eager launches on the first step, CUDA-graph replay afterwards."""
         eng = self.engine
@@ -743,15 +780,42 @@ class B200DecodeRuntime:
             raise ValueError("B200DecodeRuntime.run handles one sequence; use run_decode_batch / run_prefill_batch for batches")
         if ids.shape[1] == 0:
             raise ValueError("run needs at least one token")
+        tokens = [int(t) for t in ids[0]]
+        chunk = self._engine.prefill_chunk
+        if mode == "prefill" and chunk > 1 and len(tokens) > chunk // 4:
+            return self._prefill_chunked(tokens, chunk)
         steps = []
         keep = self.clone_outputs
         self.clone_outputs = True
         try:
-            for token in ids[0]:
-                steps.append(self.run_decode_batch([self], [int(token)]))
+            for token in tokens:
+                steps.append(self.run_decode_batch([self], [token]))
         finally:
             self.clone_outputs = keep
         return torch.cat(steps, dim=1) if len(steps) > 1 else steps[0]
+
+    def _prefill_chunked(self, tokens: list[int], chunk: int) -> torch.Tensor:
+        """Prefill that fills the page pool directly, `chunk` prompt tokens per pass through the decode
+        graph (cuda.py:584-629 computes the same thing with a causal mask over contiguous copies): the
+        tokens of a chunk are the rows of one batched step -- the projections see a [chunk, hidden] matrix,
+        every row appends its K/V at its own position and attends, through the sequence's own page table,
+        to exactly the tokens up to itself. Returns logits [1, T, vocab]."""
+        eng = self._engine
+        cache = self.kv_cache
+        vocab = int(eng.config.vocab_size)
+        out = torch.empty((1, len(tokens), vocab), device=self.device, dtype=self.dtype)
+        with torch.cuda.device(self.device):
+            for c0 in range(0, len(tokens), chunk):
+                part = tokens[c0:c0 + chunk]
+                start = cache.tokens
+                cache.extend(len(part))
+                needed = (cache.tokens + eng.page_size - 1) // eng.page_size
+                plan = eng.prefill_plan(chunk, needed)
+                plan.sync_prefill_chunk(cache, start, part)
+                plan.run_program()
+                out[0, c0:c0 + len(part)] = plan.logits[: len(part)]
+        eng.count("cacheir.b200_prefill_chunk", (len(tokens) + chunk - 1) // chunk)
+        return out
 
     def run_prefill_batch(self, sessions: list["B200DecodeRuntime"], token_id_batches: list[list[int]]) -> torch.Tensor:
         """Variable-length batched prefill (cuda.py:584-629): returns zero-padded logits [N, max_len, vocab]."""
@@ -766,10 +830,16 @@ class B200DecodeRuntime:
             session.kv_cache.clear()
         vocab = int(self._engine.config.vocab_size)
         out = torch.zeros((len(sessions), max(lens), vocab), device=self.device, dtype=self.dtype)
-        for pos in range(max(lens)):
-            rows = [i for i, n in enumerate(lens) if pos < n]
-            logits = self.run_decode_batch([sessions[i] for i in rows], [token_id_batches[i][pos] for i in rows])
-            out[rows, pos] = logits[:, 0]
+        chunk = self._engine.prefill_chunk
+        if chunk > 1 and max(lens) > chunk // 4:
+            # long prompts: each sequence goes through the chunked prefill (its tokens are the rows of a step)
+            for i, (session, ids) in enumerate(zip(sessions, token_id_batches)):
+                out[i, : lens[i]] = session.run([list(ids)], mode="prefill", reset_kv=True)[0]
+        else:
+            for pos in range(max(lens)):
+                rows = [i for i, n in enumerate(lens) if pos < n]
+                logits = self.run_decode_batch([sessions[i] for i in rows], [token_id_batches[i][pos] for i in rows])
+                out[rows, pos] = logits[:, 0]
         self._engine.count("cacheir.b200_prefill_batch_graph")
         return out
 

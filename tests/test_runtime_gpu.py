@@ -130,3 +130,33 @@ def test_runtime_errors_mirror_reference(golden_dir, tmp_path):
     other, _, _ = _tiny(golden_dir, "fp32", tmp_path / "o", dtype="float32")
     with pytest.raises(ValueError):
         rt.run_decode_batch([rt, other], [1, 2])
+
+
+def test_chunked_prefill_equals_token_by_token(golden_dir, tmp_path):
+    """Prefill that pushes 64 prompt tokens per pass through the decode graph (rows = tokens of one
+    sequence, causal through per-row lengths over the shared page table) against one token per step:
+    same logits at every position, same K/V rows in the pool, same page boundaries."""
+    rng = np.random.default_rng(3)
+    rt, meta, _ = _tiny(golden_dir, "fp32", tmp_path, dtype="float32", max_seq_len=256)
+    vocab = meta["shape"]["vocab_size"]
+    prompt = [int(t) for t in rng.integers(0, vocab, 150)]          # 64 + 64 + 22 tokens, 10 pages
+    chunked, stepped = rt.fork(), rt.fork()
+    a = chunked.run([prompt], mode="prefill")
+    assert rt.cache_stats()["kernel_counts"]["cacheir.b200_prefill_chunk"] == 3
+    rt._engine.prefill_chunk = 0
+    b = stepped.run([prompt], mode="prefill")
+    rt._engine.prefill_chunk = 64
+    assert a.shape == b.shape == (1, 150, vocab)
+    np.testing.assert_allclose(a.float().cpu().numpy(), b.float().cpu().numpy(), rtol=2e-4, atol=2e-4)
+    assert [(p.start, p.length) for p in chunked.kv_cache.pages] == [(p.start, p.length) for p in stepped.kv_cache.pages]
+    for layer in range(2):
+        pool = rt.kv_allocator.pool_for_layer(layer)
+        for pa, pb in zip(chunked.kv_cache.pages, stepped.kv_cache.pages):
+            for name in ("keys", "values"):
+                ka = pool[name][pa.page_id][:, : pa.length]
+                kb = pool[name][pb.page_id][:, : pb.length]
+                np.testing.assert_allclose(ka.float().cpu().numpy(), kb.float().cpu().numpy(), rtol=2e-4, atol=2e-4)
+    # decoding continues identically from either cache
+    ta = chunked.run([[7]], mode="decode")
+    tb = stepped.run([[7]], mode="decode")
+    np.testing.assert_allclose(ta.float().cpu().numpy(), tb.float().cpu().numpy(), rtol=2e-4, atol=2e-4)
