@@ -712,12 +712,14 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
 
 // CTAs per cluster along K. Every doubling adds cluster-barrier and exchange time to the epilogue, so the
 // split only grows while the grid stays within two CTAs per SM; a power of two that leaves each rank at
-// least two batch rows to finish and four k blocks to stream. The SwiGLU form (two accumulators, many row
-// tiles) is not split.
+// least two batch rows to finish and four k blocks to stream. With more than 32 batch rows a split CTA needs
+// a whole SM (exchange buffer + ring), so the grid must then fit in one CTA per SM. The SwiGLU form (paired
+// tiles, many of them) is not split.
 int choose_split_k(int n_tiles, int kblocks, int epilogue, int mp) {
   if (epilogue == CACHEIR_B200_EPI_SWIGLU) return 1;
+  const int slots = mp > 32 ? kNumSMs : 2 * kNumSMs;
   int s = 1;
-  while (s * 2 <= kMaxSplitK && n_tiles * s * 2 <= 2 * kNumSMs && kblocks / (s * 2) >= 4 && mp / (s * 2) >= 2) s *= 2;
+  while (s * 2 <= kMaxSplitK && n_tiles * s * 2 <= slots && kblocks / (s * 2) >= 4 && mp / (s * 2) >= 2) s *= 2;
   return s;
 }
 

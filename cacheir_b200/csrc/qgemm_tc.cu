@@ -350,6 +350,14 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const __half2 mul4 = __floats2half2_rn(1.f, 0.0625f);
       const __half2 sub4 = __floats2half2_rn(-(1024.f + zero), -(64.f + zero));
       const bool scaled = p.group_size > 0;
+      // group scales are fetched one k block ahead: the load must not sit between the barrier and the unpacking
+      const int groups_per_row = scaled ? p.K / p.group_size : 1;
+      auto group_scale = [&](int kbi) {
+        return (scaled && row_valid && kbi < kblocks)
+                   ? load_scale(p.scales, p.scale_dtype, static_cast<size_t>(n) * groups_per_row + ((kb_begin + kbi) * kBlockK) / p.group_size)
+                   : 1.f;
+      };
+      float next_scale = group_scale(0);
       for (int kbi = 0; kbi < kblocks; ++kbi) {
         const int i = pass * kblocks + kbi;
         const int s = i % kStages;
@@ -363,12 +371,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         tc_fence_after();
         const uint8_t* raw_row = s_raw + s * kRawBytes + r * kRawRow;
         const uint32_t a_cols = tmem_base + lane_addr + kAColBase + t * kAStageCols;
-        __half2 gscale = __float2half2_rn(1.f);
-        if (scaled && row_valid) {
-          const int groups_per_row = p.K / p.group_size;
-          gscale = __float2half2_rn(load_scale(p.scales, p.scale_dtype,
-                                               static_cast<size_t>(n) * groups_per_row + ((kb_begin + kbi) * kBlockK) / p.group_size));
-        }
+        const __half2 gscale = __float2half2_rn(next_scale);
+        next_scale = group_scale(kbi + 1);
         uint4 raw[kChunksPerThread];
 #pragma unroll
         for (int cc = 0; cc < kChunksPerThread; ++cc) {
