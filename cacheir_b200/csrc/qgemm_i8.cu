@@ -57,14 +57,17 @@ __device__ long long g_i8_trace[4][256][4];
 #define CB200_CTA_TRACE(slot) do { } while (0)
 #endif
 
-__host__ __device__ constexpr int stage_bytes(int mp) { return kBlockN * kBlockK + 2 * mp * kBlockK; }
+// (int4 weights add the raw 8 KB nibble tile in front of the 16 KB byte tile it is unpacked into)
+__host__ __device__ constexpr int stage_bytes(int mp, int bits = 8) {
+  return kBlockN * kBlockK + (bits == 4 ? kBlockN * kBlockK / 2 : 0) + 2 * mp * kBlockK;
+}
 // split-K: every rank receives, from each rank, 128 rows x 2*(mp/split) words
 __host__ __device__ constexpr int exchange_bytes(int mp, int split) { return split > 1 ? kBlockN * 2 * mp * 4 : 0; }
 __host__ __device__ constexpr int ring_bytes(int mp, int split) {
   return (split > 1 && mp > 32 ? kCtaBudgetWide : kCtaBudget) - exchange_bytes(mp, split);
 }
-__host__ __device__ constexpr int num_stages(int mp, int split) {
-  return ring_bytes(mp, split) / stage_bytes(mp) > 8 ? 8 : ring_bytes(mp, split) / stage_bytes(mp);
+__host__ __device__ constexpr int num_stages(int mp, int split, int bits = 8) {
+  return ring_bytes(mp, split) / stage_bytes(mp, bits) > 8 ? 8 : ring_bytes(mp, split) / stage_bytes(mp, bits);
 }
 
 // ---- pre-pass: rows of x -> two planes of signed bytes + scale + sum ------------------
@@ -328,11 +331,13 @@ __device__ __forceinline__ float recombine(int32_t hi, int32_t lo, float zero, i
   return recombine_fractional(hi, lo, zero, qsum);
 }
 
-template <int MP, int SPLIT, bool ROPE>
+template <int MP, int SPLIT, bool ROPE, int BITS>
 __global__ void __launch_bounds__(kThreads, 2)
 qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
-  constexpr int kStages = num_stages(MP, SPLIT);
-  constexpr int kWBytes = kBlockN * kBlockK;          // 16 KB of codes per stage
+  constexpr int kStages = num_stages(MP, SPLIT, BITS);
+  constexpr int kWBytes = kBlockN * kBlockK;          // 16 KB of byte codes per stage (what the tensor core reads)
+  constexpr int kRawBytes = BITS == 4 ? kWBytes / 2 : 0;   // int4: the nibble tile as it comes from HBM
+  constexpr int kLoadBytes = BITS == 4 ? kRawBytes : kWBytes;
   constexpr int kXBytes = 2 * MP * kBlockK;           // [hi; lo] rows per stage
   constexpr int kAccCols = 2 * MP;                    // one accumulator: MP high + MP low columns
   constexpr int kTmemCols = kAccCols;                 // 32, 64 or 128: a power of two, as the allocator wants
@@ -346,13 +351,15 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* s_w = smem;
   uint8_t* s_x = s_w + kStages * kWBytes;
-  int32_t* s_xch = reinterpret_cast<int32_t*>(s_x + kStages * kXBytes);   // [SPLIT senders][128 rows][W], written by the peers
+  uint8_t* s_raw = s_x + kStages * kXBytes;              // int4 only
+  int32_t* s_xch = reinterpret_cast<int32_t*>(s_raw + kStages * kRawBytes);   // [SPLIT senders][128 rows][W], written by the peers
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_xch) + exchange_bytes(MP, SPLIT));
   uint64_t* full = bars;                  // [kStages] TMA landed
   uint64_t* empty = bars + kStages;       // [kStages] MMAs that read the stage have retired
   uint64_t* acc_full = empty + kStages;   // [1]
   uint64_t* xch_bar = acc_full + 1;       // [1] all partials of the other ranks have landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xch_bar + 1);
+  uint64_t* unpacked = xch_bar + 1;       // [kStages] int4: the byte tile of the stage is complete (128 unpacking threads)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(unpacked + kStages);
   float* s_sx = reinterpret_cast<float*>(tmem_slot + 2);     // [MP]
   int* s_qsum = reinterpret_cast<int*>(s_sx + MP);           // [MP]
   int32_t* s_stage = reinterpret_cast<int32_t*>(smem);       // outgoing partials [SPLIT dests][128 rows][W] reuse the drained ring
@@ -374,14 +381,16 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
   auto load_stage = [&](int i, int s) {
     const int kb = kb_begin + i;
     const uint32_t bar = smem_u32(&full[s]);
-    mbar_expect_tx(bar, kWBytes + kXBytes);
-    if (p.tiled) {   // one contiguous, pre-swizzled 16 KB tile
-      bulk_load(smem_u32(s_w + s * kWBytes), p.w_tiled + (static_cast<size_t>(blockIdx.x) * kblocks_all + kb) * kWBytes, kWBytes, bar);
+    mbar_expect_tx(bar, kLoadBytes + kXBytes);
+    constexpr int kRowBytes = BITS == 4 ? kBlockK / 2 : kBlockK;      // bytes of one tile row as stored in HBM
+    const uint32_t dst = BITS == 4 ? smem_u32(s_raw + s * kRawBytes) : smem_u32(s_w + s * kWBytes);
+    if (p.tiled) {   // one contiguous, pre-swizzled tile (16 KB of bytes or 8 KB of nibbles)
+      bulk_load(dst, p.w_tiled + (static_cast<size_t>(blockIdx.x) * kblocks_all + kb) * kLoadBytes, kLoadBytes, bar);
     } else if (swiglu) {   // the map's box is 64 rows: gate rows, then the up rows of the same columns
-      tma_load_2d(smem_u32(s_w + s * kWBytes), &tmap_w, bar, kb * kBlockK, n0);
-      tma_load_2d(smem_u32(s_w + s * kWBytes + kPairRows * kBlockK), &tmap_w, bar, kb * kBlockK, p.N / 2 + n0);
+      tma_load_2d(dst, &tmap_w, bar, kb * kRowBytes, n0);
+      tma_load_2d(dst + kPairRows * kRowBytes, &tmap_w, bar, kb * kRowBytes, p.N / 2 + n0);
     } else {
-      tma_load_2d(smem_u32(s_w + s * kWBytes), &tmap_w, bar, kb * kBlockK, n0);
+      tma_load_2d(dst, &tmap_w, bar, kb * kRowBytes, n0);
     }
     bulk_load(smem_u32(s_x + s * kXBytes), p.x_planes + static_cast<size_t>(kb) * kXBytes, kXBytes, bar);
   };
@@ -394,6 +403,8 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
       for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
       mbar_init(smem_u32(acc_full), 1);
       mbar_init(smem_u32(xch_bar), 1);
+      if (BITS == 4)
+        for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&unpacked[s]), 128);
       mbar_fence_init();                       // visible to the copy engine and to the other CTAs of the cluster
       if (split > 1) mbar_expect_tx(smem_u32(xch_bar), (split - 1) * kSlotBytes);
     }
@@ -435,7 +446,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
       for (int i = 0; i < total; ++i) {
         const int s = i % kStages;
         CB200_TRACE(1, i, 0);
-        if (!mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, &g_i8_status, (3 << 8) | 2)) break;
+        if (!mbar_wait(smem_u32(BITS == 4 ? &unpacked[s] : &full[s]), (i / kStages) & 1, &g_i8_status, (3 << 8) | 2)) break;
         CB200_TRACE(1, i, 1);
         if (i == 0) CB200_CTA_TRACE(1);
         tc_fence_after();
@@ -483,7 +494,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
                      ? __half2float(res[static_cast<size_t>(m) * p.n_out + n_out_idx]) : 0.f;
     }
     // Fused QKV epilogue: per batch row, the (cos, sin) of this thread's pair and where its k/v element goes in the pool.
-    constexpr bool rope_epi = ROPE;   // a template parameter: the other projections do not carry this code
+    [[maybe_unused]] constexpr bool rope_epi = ROPE;   // a template parameter: the other projections do not carry this code
     const RopeAppendParams& ra = p.rope;
     auto rope_row = [&](int m, float2* cs, long long* off) {
       *cs = make_float2(1.f, 0.f);
@@ -531,6 +542,37 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
       for (int j = 0; j < MS; ++j) rope_row(krank * MS + j, &cs_v[j], &off_v[j]);
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps: s_sx / s_qsum are in place
+    if constexpr (BITS == 4) {
+      // int4 weights: while the main loop runs these warps turn each landed nibble tile into the byte tile the
+      // tensor core reads. Thread r owns tile row r: 64 bytes of nibbles (four 16-byte chunks stored in the
+      // 64-byte swizzle order, chunk c at c ^ ((r >> 1) & 3)) become 128 bytes of codes in the 128-byte
+      // swizzle order (chunk c at c ^ (r & 7)); even columns sit in the low nibbles.
+      for (int i = 0; i < total; ++i) {
+        const int s = i % kStages;
+        if (!mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, &g_i8_status, (3 << 8) | 8)) break;
+        const uint8_t* raw_row = s_raw + s * kRawBytes + r * (kBlockK / 2);
+        uint8_t* out_row = s_w + s * kWBytes + r * kBlockK;
+        uint4 raw[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) raw[c] = *reinterpret_cast<const uint4*>(raw_row + ((c ^ ((r >> 1) & 3)) * 16));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t w[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+          uint32_t o[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t even = w[j] & 0x0F0F0F0Fu;
+            const uint32_t odd = (w[j] >> 4) & 0x0F0F0F0Fu;
+            o[2 * j] = __byte_perm(even, odd, 0x5140);         // columns 8j .. 8j+3
+            o[2 * j + 1] = __byte_perm(even, odd, 0x7362);     // columns 8j+4 .. 8j+7
+          }
+          *reinterpret_cast<uint4*>(out_row + (((2 * c) ^ (r & 7)) * 16)) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(out_row + (((2 * c + 1) ^ (r & 7)) * 16)) = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads these bytes through the async proxy
+        mbar_arrive(smem_u32(&unpacked[s]));
+      }
+    }
     bool ok = mbar_wait(smem_u32(acc_full), 0, &g_i8_status, (3 << 8) | 3);
     tc_fence_after();
     if (threadIdx.x == 64) CB200_TRACE(3, 0, 2);
@@ -733,12 +775,13 @@ int launch_quantize(const __half* x, long long x_stride, int M, int K, int mp, v
   return launch_status();
 }
 
-template <int MP, int SPLIT, bool ROPE>
+template <int MP, int SPLIT, bool ROPE, int BITS>
 cudaError_t launch_i8_split(const CUtensorMap& tmap_w, const I8Params& p, int n_tiles, cudaStream_t stream) {
-  constexpr size_t kSmem = 1024 + static_cast<size_t>(num_stages(MP, SPLIT)) * stage_bytes(MP) + exchange_bytes(MP, SPLIT) + 1024;
-  static_assert(num_stages(MP, SPLIT) >= 2, "the pipeline needs at least two stages");
-  static_assert(num_stages(MP, SPLIT) * stage_bytes(MP) >= exchange_bytes(MP, SPLIT), "outgoing partials are staged in the drained ring");
-  auto kern = qgemm_i8_kernel<MP, SPLIT, ROPE>;
+  constexpr size_t kSmem = 1024 + static_cast<size_t>(num_stages(MP, SPLIT, BITS)) * stage_bytes(MP, BITS) + exchange_bytes(MP, SPLIT) + 1024;
+  static_assert(num_stages(MP, SPLIT, BITS) >= 2, "the pipeline needs at least two stages");
+  static_assert(num_stages(MP, SPLIT, BITS) * (kBlockN * kBlockK + 2 * MP * kBlockK) >= exchange_bytes(MP, SPLIT) || SPLIT == 1,
+                "outgoing partials are staged in the drained byte and activation tiles at the head of the ring");
+  auto kern = qgemm_i8_kernel<MP, SPLIT, ROPE, BITS>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg{};
@@ -770,10 +813,11 @@ int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
   // (the tiled layout is fetched with plain bulk copies; its map is only a valid placeholder)
   const bool swiglu = q.epilogue == CACHEIR_B200_EPI_SWIGLU;
   const uint64_t bands = static_cast<uint64_t>((q.N + kBlockN - 1) / kBlockN);
+  const uint64_t row_bytes = q.bits == 4 ? static_cast<uint64_t>(q.K / 2) : static_cast<uint64_t>(q.K);
   const bool w_ok = q.tiled
-      ? encode_u8_rows_sw128(&tmap_w, q.packed, kBlockK, bands * (q.K / kBlockK) * kBlockN, kBlockK, kBlockN)
-      : encode_u8_rows_sw128(&tmap_w, q.packed, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.N), static_cast<uint64_t>(q.K),
-                             swiglu ? kPairRows : kBlockN);
+      ? encode_u8_rows_sw128(&tmap_w, q.packed, kBlockK, bands * (q.K / kBlockK) * (q.bits == 4 ? kBlockN / 2 : kBlockN), kBlockK, kBlockN)
+      : (q.bits == 4 ? encode_u8_rows_sw64(&tmap_w, q.packed, row_bytes, static_cast<uint64_t>(q.N), row_bytes, swiglu ? kPairRows : kBlockN)
+                     : encode_u8_rows_sw128(&tmap_w, q.packed, row_bytes, static_cast<uint64_t>(q.N), row_bytes, swiglu ? kPairRows : kBlockN));
   if (!w_ok) return CACHEIR_B200_EUNSUPPORTED;
   I8Params p{};
   p.scales = q.scales; p.zero_points = q.zero_points; p.residual = q.residual; p.y = q.y;
@@ -788,17 +832,24 @@ int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
   cudaError_t e;
   if (q.epilogue == kEpiQkvRopeAppend) {
     switch (p.split_k) {
-      case 8: e = launch_i8_split<MP, 8, true>(tmap_w, p, n_tiles, stream); break;
-      case 4: e = launch_i8_split<MP, 4, true>(tmap_w, p, n_tiles, stream); break;
-      case 2: e = launch_i8_split<MP, 2, true>(tmap_w, p, n_tiles, stream); break;
-      default: e = launch_i8_split<MP, 1, true>(tmap_w, p, n_tiles, stream); break;
+      case 8: e = launch_i8_split<MP, 8, true, 8>(tmap_w, p, n_tiles, stream); break;
+      case 4: e = launch_i8_split<MP, 4, true, 8>(tmap_w, p, n_tiles, stream); break;
+      case 2: e = launch_i8_split<MP, 2, true, 8>(tmap_w, p, n_tiles, stream); break;
+      default: e = launch_i8_split<MP, 1, true, 8>(tmap_w, p, n_tiles, stream); break;
+    }
+  } else if (q.bits == 4) {
+    switch (p.split_k) {
+      case 8: e = launch_i8_split<MP, 8, false, 4>(tmap_w, p, n_tiles, stream); break;
+      case 4: e = launch_i8_split<MP, 4, false, 4>(tmap_w, p, n_tiles, stream); break;
+      case 2: e = launch_i8_split<MP, 2, false, 4>(tmap_w, p, n_tiles, stream); break;
+      default: e = launch_i8_split<MP, 1, false, 4>(tmap_w, p, n_tiles, stream); break;
     }
   } else {
     switch (p.split_k) {
-      case 8: e = launch_i8_split<MP, 8, false>(tmap_w, p, n_tiles, stream); break;
-      case 4: e = launch_i8_split<MP, 4, false>(tmap_w, p, n_tiles, stream); break;
-      case 2: e = launch_i8_split<MP, 2, false>(tmap_w, p, n_tiles, stream); break;
-      default: e = launch_i8_split<MP, 1, false>(tmap_w, p, n_tiles, stream); break;
+      case 8: e = launch_i8_split<MP, 8, false, 8>(tmap_w, p, n_tiles, stream); break;
+      case 4: e = launch_i8_split<MP, 4, false, 8>(tmap_w, p, n_tiles, stream); break;
+      case 2: e = launch_i8_split<MP, 2, false, 8>(tmap_w, p, n_tiles, stream); break;
+      default: e = launch_i8_split<MP, 1, false, 8>(tmap_w, p, n_tiles, stream); break;
     }
   }
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -813,7 +864,8 @@ size_t qgemm_i8_workspace_bytes(int M, int K) {
 }
 
 bool qgemm_i8_supported(const QGemvParams& q, const void* workspace, size_t workspace_bytes) {
-  if (q.x_dtype != CACHEIR_B200_F16 || q.bits != 8 || q.group_size != 0) return false;
+  if (q.x_dtype != CACHEIR_B200_F16 || (q.bits != 8 && q.bits != 4) || q.group_size != 0) return false;
+  if (q.bits == 4 && q.epilogue == kEpiQkvRopeAppend) return false;      // the fused QKV form is built for int8 only
   if (q.M < 1 || q.M > 64) return false;
   if (q.K % kBlockK != 0 || q.K < kBlockK || q.K > 32768) return false;   // 32-bit accumulators and epilogue arithmetic
   if (q.epilogue == CACHEIR_B200_EPI_SWIGLU && ((q.N / 2) % kPairRows != 0 || (q.tiled && !q.paired))) return false;

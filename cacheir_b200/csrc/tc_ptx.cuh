@@ -137,5 +137,19 @@ inline bool encode_u8_rows_sw128(CUtensorMap* map, const void* base, uint64_t in
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same for 64-byte-wide boxes (int4 tiles: 128 k elements = 64 bytes per row), 64-byte swizzle.
+inline bool encode_u8_rows_sw64(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows,
+                                uint64_t row_stride_bytes, uint32_t box_rows) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {inner_bytes, rows};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace ptx
 }  // namespace cb200

@@ -199,7 +199,7 @@ class _Engine:
             # integer kernel's SwiGLU epilogue reads; any other pair needs each half to be whole 128-row bands.
             pair = len(names) == 2
             half = fused.shape[0] // 2
-            paired = pair and fused.bits == 8 and not fused.group_size and half % 64 == 0
+            paired = pair and fused.bits in (4, 8) and not fused.group_size and half % 64 == 0
             halves_ok = not pair or paired or half % 128 == 0
             if self.dtype == torch.float16 and fused.shape[1] % 128 == 0 and halves_ok and self.tile_weights:
                 tiled = to_tiled(fused, paired=paired)
@@ -409,7 +409,7 @@ class _DecodePlan:
                     ws = self._gemm_workspace(int(x.shape[1]))
                     self._emit(lambda x=x, w=norm_w, eps=eps, ws=ws: ops.rms_norm_quantize(x, w, eps, ws), "b200.rms_norm_quantize")
                     pool = eng.allocator.pool_for_layer(int(consumer.attrs.get("layer", 0))) if consumer is not None else None
-                    if (pool is not None and self._rows_of(node.inputs[4]) // eng.tp.world == k_dim and pool["keys"].dtype == torch.float16
+                    if (pool is not None and weight.bits == 8 and self._rows_of(node.inputs[4]) // eng.tp.world == k_dim and pool["keys"].dtype == torch.float16
                             and int(pool["keys"].shape[3]) == head_dim and int(pool["keys"].shape[1]) * head_dim == k_dim):
                         # projection + RoPE + append of the new k/v rows in one kernel
                         n, k = weight.shape
@@ -495,7 +495,7 @@ class _DecodePlan:
         """Will this projection run on the integer tensor cores (and so accept pre-quantized activations)?"""
         if swiglu and isinstance(weight, B200PackedWeight) and ((weight.shape[0] // 2) % 64 != 0 or (weight.tiled and not weight.paired)):
             return False
-        return (isinstance(weight, B200PackedWeight) and weight.bits == 8 and not weight.group_size
+        return (isinstance(weight, B200PackedWeight) and weight.bits in (4, 8) and not weight.group_size
                 and self.engine.dtype == torch.float16 and self.batch <= 64 and k % 128 == 0 and k <= 8192
                 and hasattr(self, "_gemm_ws"))
 
@@ -507,7 +507,7 @@ class _DecodePlan:
         if isinstance(weight, B200PackedWeight):
             n, k, bits = weight.shape[0], weight.shape[1], weight.bits
             out = out if out is not None else self._buf(n // 2 if epilogue == ops.EPI_SWIGLU else n)
-            ws = self._gemm_workspace(k) if (bits == 8 and not weight.group_size and eng.dtype == torch.float16) else None
+            ws = self._gemm_workspace(k) if (bits in (4, 8) and not weight.group_size and eng.dtype == torch.float16) else None
             fn = lambda: ops.qgemv(x, weight.packed_values, weight.scales, weight.zero_points, bits=bits, n=n, k=k,
                                    group_size=weight.group_size or 0, epilogue=epilogue, residual=residual, out=out,
                                    workspace=ws, tiled=weight.tiled, prequantized=prequantized, paired=weight.paired)

@@ -161,11 +161,12 @@ int cacheir_b200_qgemv(const void* x, const void* packed, const void* scales,
                        int epilogue, void* stream);
 
 /* Same operation with caller-provided scratch. With at least
- * cacheir_b200_qgemv_workspace_bytes(M, K) bytes of 128-byte aligned workspace, int8
- * per-row weights with fp16 activations (M <= 64, K % 128 == 0) run on the integer
- * tensor cores: the uint8 codes are fed to the MMA as they are, and x is first turned
- * into 16-bit fixed point per row (two signed bytes, 2^-15 of the row maximum) in the
- * workspace. Other shapes ignore the workspace. workspace may be NULL (then this is
+ * cacheir_b200_qgemv_workspace_bytes(M, K) bytes of 128-byte aligned workspace, int8 and
+ * int4 per-row weights with fp16 activations (K % 128 == 0, K <= 32768) run on the integer
+ * tensor cores: the uint8 codes are fed to the MMA as they are (int4 nibbles are widened to
+ * bytes in shared memory), and x is first turned into 16-bit fixed point per row (two
+ * signed bytes, 2^-15 of the row maximum) in the workspace. Batches above 64 rows run as
+ * 64-row chunks. Other shapes ignore the workspace. workspace may be NULL (then this is
  * cacheir_b200_qgemv). The workspace is only used during the call's own kernels; two
  * calls that may overlap on the GPU need separate workspaces. */
 size_t cacheir_b200_qgemv_workspace_bytes(int M, int K);

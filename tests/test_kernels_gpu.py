@@ -389,13 +389,14 @@ def test_qgemm_tensor_core_epilogues_and_odd_zero_points():
 
 
 # ---- integer tensor-core path: int8 codes straight into tcgen05.mma kind::i8 -------------
+@pytest.mark.parametrize("bits", [8, 4])       # int4 per-row codes are unpacked to bytes inside the same kernel
 @pytest.mark.parametrize("m", [1, 8, 16, 17, 32, 33, 64])
 @pytest.mark.parametrize("n,k", [(512, 1024), (200, 256), (128, 4096), (4096, 2048)])
-def test_qgemm_int8_tensor_core_with_workspace(m, n, k):
+def test_qgemm_int8_tensor_core_with_workspace(m, n, k, bits):
     from cacheir_b200 import ops
     from cacheir_b200.quantization import quantized_matmul
     rng = np.random.default_rng(m * 31 + n + k)
-    x, packed = _qgemv_case(rng, m, n, k, 8, torch.float16)
+    x, packed = _qgemv_case(rng, m, n, k, bits, torch.float16)
     ws = torch.zeros(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
     y = quantized_matmul(x.cuda(), _device_pack(packed), workspace=ws)
     torch.cuda.synchronize()
@@ -468,9 +469,8 @@ def test_pack_relayout_roundtrip_and_gemm_equivalence(bits, n, k):
     y_rows = quantized_matmul(x.cuda(), rows)
     y_tiled = quantized_matmul(x.cuda(), tiled)
     assert torch.equal(y_rows, y_tiled)
-    if bits == 8:
-        ws = torch.zeros(ops.qgemv_workspace_bytes(32, k), dtype=torch.uint8, device="cuda")
-        assert torch.equal(quantized_matmul(x.cuda(), rows, workspace=ws), quantized_matmul(x.cuda(), tiled, workspace=ws))
+    ws = torch.zeros(ops.qgemv_workspace_bytes(32, k), dtype=torch.uint8, device="cuda")
+    assert torch.equal(quantized_matmul(x.cuda(), rows, workspace=ws), quantized_matmul(x.cuda(), tiled, workspace=ws))
     if n % 256 == 0:
         a = quantized_matmul(x.cuda(), rows, epilogue=ops.EPI_SWIGLU)
         b = quantized_matmul(x.cuda(), tiled, epilogue=ops.EPI_SWIGLU)
@@ -485,16 +485,14 @@ def test_pack_relayout_roundtrip_and_gemm_equivalence(bits, n, k):
                 key = (r & 7) if bits == 8 else ((r >> 1) & 3)
                 chunks = tp[1, 0, r].reshape(tb // 16, 16)
                 np.testing.assert_array_equal(np.stack([chunks[c ^ key] for c in range(tb // 16)]).reshape(-1), ref[src, :tb])
-        if bits == 8:
-            ws = torch.zeros(ops.qgemv_workspace_bytes(32, k), dtype=torch.uint8, device="cuda")
-            a = quantized_matmul(x.cuda(), rows, epilogue=ops.EPI_SWIGLU, workspace=ws)
-            b = quantized_matmul(x.cuda(), paired, epilogue=ops.EPI_SWIGLU, workspace=ws)
-            assert torch.equal(a, b)
-            base = oracle.quantized_matmul(x.float().numpy(), packed)
-            assert _rel(a, oracle.silu_mul(base[:, : n // 2], base[:, n // 2:])) <= TOL[torch.float16] * 2
-        else:
-            with pytest.raises(Exception):                                  # only the integer kernel reads paired tiles
-                quantized_matmul(x.cuda(), paired, epilogue=ops.EPI_SWIGLU)
+        ws = torch.zeros(ops.qgemv_workspace_bytes(32, k), dtype=torch.uint8, device="cuda")
+        a = quantized_matmul(x.cuda(), rows, epilogue=ops.EPI_SWIGLU, workspace=ws)
+        b = quantized_matmul(x.cuda(), paired, epilogue=ops.EPI_SWIGLU, workspace=ws)
+        assert torch.equal(a, b)
+        base = oracle.quantized_matmul(x.float().numpy(), packed)
+        assert _rel(a, oracle.silu_mul(base[:, : n // 2], base[:, n // 2:])) <= TOL[torch.float16] * 2
+        with pytest.raises(Exception):                                      # only the integer kernel reads paired tiles
+            quantized_matmul(x.cuda(), paired, epilogue=ops.EPI_SWIGLU)
     torch.cuda.synchronize()
     _device_status_ok()
 
