@@ -273,15 +273,19 @@ rms_norm_quantize_kernel(const __half* __restrict__ x, const __half* __restrict_
       for (int j = 0; j < 8; ++j) ss = fmaf(vals[i][j], vals[i][j], ss);
     }
   }
+  float w[PT][8];      // the norm weights are requested before the reduction, not after it
+#pragma unroll
+  for (int i = 0; i < PT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < nvec) VecIO<__half, 8>::ld(weight + c * 8, w[i]);
+  }
   const float inv = rsqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps);
 #pragma unroll
   for (int i = 0; i < PT; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
     if (c < nvec) {
-      float w[8];
-      VecIO<__half, 8>::ld(weight + c * 8, w);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) vals[i][j] = __half2float(__float2half_rn(vals[i][j] * inv * w[j]));
+      for (int j = 0; j < 8; ++j) vals[i][j] = __half2float(__float2half_rn(vals[i][j] * inv * w[i][j]));
       if (out) VecIO<__half, 8>::st(out + row + c * 8, vals[i]);
     }
   }
@@ -538,8 +542,38 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
     float2 cs_v[MS];
     long long off_v[MS];
     if constexpr (SPLIT > 1 && ROPE) {
+      // Two levels of dependent loads (position, then table entry and page id): each level is issued for all of
+      // this thread's rows at once, with clamped indices instead of branches, so the latencies overlap.
+      const bool col_ok = n_out_idx < p.n_out;
+      const bool is_qk = n_out_idx < ra.q_dim + ra.k_dim;
+      const int pair = (n_out_idx % ra.head_dim) >> 1;
+      const int col = n_out_idx >= ra.q_dim ? (n_out_idx - ra.q_dim) % ra.k_dim : 0;
+      int pos_v[MS];
 #pragma unroll
-      for (int j = 0; j < MS; ++j) rope_row(krank * MS + j, &cs_v[j], &off_v[j]);
+      for (int j = 0; j < MS; ++j) {
+        const int m = krank * MS + j;
+        pos_v[j] = (m < p.M && col_ok) ? ra.positions[m] : -1;
+      }
+      int page_v[MS];
+#pragma unroll
+      for (int j = 0; j < MS; ++j) {
+        const int m = min(krank * MS + j, p.M - 1);
+        const int pos_t = min(max(pos_v[j], 0), ra.table_positions - 1);
+        const int page_idx = min(max(pos_v[j], 0) / ra.page_size, ra.max_pages - 1);
+        cs_v[j] = reinterpret_cast<const float2*>(ra.table)[static_cast<size_t>(pos_t) * (ra.head_dim / 2) + pair];
+        page_v[j] = ra.page_table[static_cast<size_t>(m) * ra.max_pages + page_idx];
+      }
+#pragma unroll
+      for (int j = 0; j < MS; ++j) {
+        const int pos = pos_v[j];
+        const bool row_ok = pos >= 0;
+        if (row_ok && is_qk && pos >= ra.table_positions) atomicCAS(&g_i8_status, 0, (3 << 8) | 5);   // outside the cos/sin table
+        if (!(row_ok && is_qk && pos < ra.table_positions)) cs_v[j] = make_float2(1.f, 0.f);
+        const bool write = row_ok && n_out_idx >= ra.q_dim && pos / ra.page_size < ra.max_pages;   // no page reserved: dropped
+        off_v[j] = write ? static_cast<long long>(((static_cast<size_t>(page_v[j]) * ra.kv_heads + col / ra.head_dim) * ra.page_size +
+                                                   pos % ra.page_size) * ra.head_dim + col % ra.head_dim)
+                         : -1;
+      }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps: s_sx / s_qsum are in place
     if constexpr (BITS == 4) {
