@@ -160,3 +160,42 @@ def test_chunked_prefill_equals_token_by_token(golden_dir, tmp_path):
     ta = chunked.run([[7]], mode="decode")
     tb = stepped.run([[7]], mode="decode")
     np.testing.assert_allclose(ta.float().cpu().numpy(), tb.float().cpu().numpy(), rtol=2e-4, atol=2e-4)
+
+
+@pytest.mark.parametrize("batch", [40, 70])
+def test_wide_batches_match_single_sequence_decoding(batch):
+    """Batches above 32 rows (64-row tiles) and above 64 rows (chunked tensor-core launches, unfused
+    RMSNorm / RoPE / append) give each sequence the logits it gets when decoded alone."""
+    import zlib
+
+    from cacheir_b200 import B200DecodeRuntime
+    from cacheir_b200.artifact import ModelConfig, build_decoder_artifact
+
+    cfg = ModelConfig(architecture="LlamaForCausalLM", hidden_size=512, intermediate_size=1024, num_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, vocab_size=512, max_position_embeddings=128,
+                      rope_theta=10000.0, rms_norm_eps=1e-5, dtype="float16")
+    art = build_decoder_artifact(cfg, quant="int8")
+
+    def source(key, shape):
+        g = torch.Generator(device="cpu")
+        g.manual_seed(zlib.crc32(key.encode()))
+        return torch.ones(shape) if len(shape) == 1 else torch.randn(shape, generator=g) * 0.05
+
+    rt = B200DecodeRuntime(art, dtype="float16", tensor_source=source, max_seq_len=128)
+    rng = np.random.default_rng(batch)
+    prompts = [[int(t) for t in rng.integers(0, 512, int(rng.integers(3, 9)))] for _ in range(batch)]
+    sessions = [rt.fork() for _ in prompts]
+    for s, p in zip(sessions, prompts):
+        s.run([p], mode="prefill")
+    tokens = [int(t) for t in rng.integers(0, 512, batch)]
+    wide = rt.run_decode_batch(sessions, tokens)[:, 0].float().cpu().numpy()
+    wide2 = rt.run_decode_batch(sessions, tokens)[:, 0].float().cpu().numpy()        # second step: the captured graph
+    for i in (0, batch // 2, batch - 1):
+        alone = rt.fork()
+        alone.run([prompts[i]], mode="prefill")
+        a1 = alone.run_decode_batch([alone], [tokens[i]])[0, 0].float().cpu().numpy()
+        a2 = alone.run_decode_batch([alone], [tokens[i]])[0, 0].float().cpu().numpy()
+        assert oracle.rel_l2(wide[i], a1) <= 4e-3
+        assert oracle.rel_l2(wide2[i], a2) <= 4e-3
+    from cacheir_b200 import _lib
+    assert _lib.load().cacheir_b200_device_status(1) == 0
