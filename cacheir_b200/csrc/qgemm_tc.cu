@@ -446,17 +446,25 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       cluster_sync_all();
       if (krank != 0) {
 #pragma unroll
-        for (int j = 0; j < kColsPerWarp; ++j) {
-          const int col = hsel * kColsPerWarp + j;
-          st_cluster_f32(smem_u32(s_partial + (static_cast<size_t>(krank - 1) * MP + col) * kBlockN + r), 0, acc[0][j]);
+        for (int a = 0; a < 2; ++a) {
+          if (a == 1 && !swiglu) break;
+#pragma unroll
+          for (int j = 0; j < kColsPerWarp; ++j) {
+            const int col = hsel * kColsPerWarp + j;
+            st_cluster_f32(smem_u32(s_partial + ((static_cast<size_t>(krank - 1) * passes + a) * MP + col) * kBlockN + r), 0, acc[a][j]);
+          }
         }
       }
       cluster_sync_all();
       if (krank == 0) {
         for (int k = 1; k < split; ++k)
 #pragma unroll
-          for (int j = 0; j < kColsPerWarp; ++j)
-            acc[0][j] += s_partial[(static_cast<size_t>(k - 1) * MP + hsel * kColsPerWarp + j) * kBlockN + r];
+          for (int a = 0; a < 2; ++a) {
+            if (a == 1 && !swiglu) break;
+#pragma unroll
+            for (int j = 0; j < kColsPerWarp; ++j)
+              acc[a][j] += s_partial[((static_cast<size_t>(k - 1) * passes + a) * MP + hsel * kColsPerWarp + j) * kBlockN + r];
+          }
       }
     }
     if (ok && krank == 0) {
@@ -541,12 +549,12 @@ bool encode_x_3d(CUtensorMap* map, const void* base, uint64_t K, uint64_t M, uin
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// CTAs per cluster along K: enough to put about one CTA on every SM, never for the SwiGLU form
-// (it has two accumulators and plenty of row tiles).
+// CTAs per cluster along K: enough to put about one CTA on every SM. The SwiGLU form exchanges two
+// accumulators per rank, so it splits at most in two (what fits in the drained ring).
 int choose_split_k(int n_tiles, int kblocks, int epilogue) {
-  if (epilogue == CACHEIR_B200_EPI_SWIGLU) return 1;
   int s = kNumSMs / n_tiles;
   if (s > kMaxSplitK) s = kMaxSplitK;
+  if (epilogue == CACHEIR_B200_EPI_SWIGLU && s > 2) s = 2;
   if (s > kblocks / 4) s = kblocks / 4;     // keep at least four k blocks per CTA
   return s < 1 ? 1 : s;
 }
@@ -555,7 +563,8 @@ template <int BITS, int MP>
 int launch_tc(const QGemvParams& q, cudaStream_t stream) {
   constexpr int kStages = num_stages(BITS, MP);
   constexpr size_t kSmem = 1024 + static_cast<size_t>(kStages) * stage_bytes(BITS, MP) + 512;
-  static_assert(static_cast<size_t>(kMaxSplitK - 1) * MP * kBlockN * 4 <= static_cast<size_t>(kStages) * stage_bytes(BITS, MP),
+  static_assert(static_cast<size_t>(kMaxSplitK - 1) * MP * kBlockN * 4 <= static_cast<size_t>(kStages) * stage_bytes(BITS, MP) &&
+                    static_cast<size_t>(2) * MP * kBlockN * 4 <= static_cast<size_t>(kStages) * stage_bytes(BITS, MP),
                 "split-K partials must fit in the pipeline ring");
   CUtensorMap tmap_w, tmap_x;
   const uint64_t row_bytes = BITS == 8 ? static_cast<uint64_t>(q.K) : static_cast<uint64_t>(q.K / 2);
