@@ -13,11 +13,13 @@
 //   warps 4-11  converters: thread (r, half) owns half of weight row r of the tile;
 //               unpacks its codes in registers (byte/nibble -> fp16 through the
 //               0x6400 mantissa trick, zero point removed exactly) and stores the
-//               fp16 operand straight into TENSOR MEMORY (tcgen05.st, row r = TMEM
-//               lane r): the dequantised weights never touch shared memory
-//   warp 1      one thread issues tcgen05.mma with A from TMEM and B (x) from shared
-//               memory (M=128, N=MP, K=16; 8 per stage) and commits to the barriers
-//               that recycle the stages
+//               fp16 operand tile into shared memory in the 128-byte swizzle order a
+//               tensor copy would leave (two tiles rotate). Tensor memory was tried
+//               as the hand-over (tcgen05.st): it sustains only ~23 B/clk per SM and
+//               made the converters, not the MMAs, the bottleneck.
+//   warp 1      one thread issues tcgen05.mma with both operands from shared memory
+//               (M=128, N=MP, K=16; 8 per stage) and commits to the barriers that
+//               recycle the stages
 //   warps 4-11  epilogue: tcgen05.ld the accumulator, split-K reduction across the
 //               CTAs of a cluster through distributed shared memory in rank order
 //               (deterministic), row scale, residual add or SiLU*mul, store y
@@ -34,14 +36,14 @@ namespace {
 
 constexpr int kBlockN = 128;      // weight rows per CTA (UMMA M)
 constexpr int kBlockK = 128;      // k elements per pipeline stage
-constexpr int kAStages = 4;       // converted fp16 operand tiles in tensor memory
-constexpr int kAStageCols = kBlockK / 2;                // 64 TMEM columns: two fp16 per 32-bit column
-constexpr int kAColBase = 256;                          // accumulators use columns [0, 256)
-constexpr int kTmemCols = 512;
-constexpr int kConvThreads = 256;                       // warps 4..11
+constexpr int kAStages = 2;       // converted fp16 operand tiles in shared memory
+constexpr int kABytes = kBlockN * kBlockK * 2;          // 32 KB: two 64-element halves of [128 rows x 128 B], 128-byte swizzled
+constexpr int kAColBase = 256;                          // accumulators use tensor-memory columns [0, 256)
+constexpr int kTmemCols = 256;
+constexpr int kConvThreads = 512;                       // warps 4..19: the unpacking is latency-bound, more warps hide it
 constexpr int kThreads = 128 + kConvThreads;
 constexpr int kMaxSplitK = 4;
-constexpr int kRingBudget = 192 * 1024;                 // shared memory for the raw/x ring
+constexpr int kRingBudget = 152 * 1024;                 // shared memory for the raw/x ring (the fp16 operand ring takes 64 KB more)
 
 __host__ __device__ constexpr int stage_bytes(int bits, int mp) {
   return (bits == 8 ? kBlockN * 128 : kBlockN * 64) + mp * kBlockK * 2;
@@ -108,18 +110,21 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void tc_mma_f16_ss(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void tc_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
-               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+// 16 fp16 (k0 .. k0+15 of tile row r) into a [2 halves][128 rows][128 B] operand tile whose 16-byte chunks sit in
+// the 128-byte swizzle order (chunk c of row r at c ^ (r & 7)): what a TMA tensor copy of an fp16 tile would leave.
+__device__ __forceinline__ void st_operand16(uint8_t* tile, int r, int k0, const uint32_t (&v)[8]) {
+  uint8_t* row = tile + (k0 >> 6) * (kBlockN * 128) + r * 128;
+  const int c = ((k0 & 63) >> 3);                      // first of the two 16-byte chunks (8 fp16 each)
+  *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) * 16)) = make_uint4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<uint4*>(row + (((c + 1) ^ (r & 7)) * 16)) = make_uint4(v[4], v[5], v[6], v[7]);
 }
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
@@ -219,13 +224,14 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   constexpr int kRawBytes = BITS == 8 ? kBlockN * 128 : kBlockN * 64;   // per stage
   constexpr int kXBytes = MP * kBlockK * 2;
   constexpr int kRawRow = BITS == 8 ? 128 : 64;                          // bytes of one row per stage
-  constexpr int kChunksPerThread = kRawRow / 16 / 2;                     // 16-byte chunks per converter thread
+  constexpr int kChunksPerThread = kRawRow / 16 / 4;                     // 16-byte chunks per converter thread (a quarter row)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* s_raw = smem;                                   // kStages x kRawBytes
   uint8_t* s_x = s_raw + kStages * kRawBytes;              // kStages x kXBytes (all sizes are multiples of 1024)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_x + kStages * kXBytes);
+  uint8_t* s_a = s_x + kStages * kXBytes;                  // kAStages x kABytes: the dequantised fp16 weight tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_a + kAStages * kABytes);
   uint64_t* full = bars;                                   // [kStages]   TMA landed
   uint64_t* empty = bars + kStages;                        // [kStages]   converters (256) + MMA commit (1)
   uint64_t* a_full = bars + 2 * kStages;                   // [kAStages]  converters (256)
@@ -309,14 +315,15 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         const int pass = i / kblocks;
         const int kb = i % kblocks;
         const uint32_t d = tmem_base + pass * nacc * MP;
-        const uint32_t a_tmem = tmem_base + kAColBase + t * kAStageCols;
+        const uint32_t a_base = smem_u32(s_a + t * kABytes);
         const uint32_t x_base = smem_u32(s_x + s * kXBytes);
 #pragma unroll
         for (int j = 0; j < kBlockK / 16; ++j) {
-          // A: tensor memory, row r in lane r, 16 fp16 of this k step in 8 columns.
-          // B: 128-byte swizzled rows (TMA), 8-row groups 1024 B apart; 32 B per k step inside a 64-element span.
+          // A (dequantised weights) and B (x): 128-byte swizzled rows, 8-row groups 1024 B apart; 32 B per k step
+          // inside a 64-element span, the second span one half tile further.
+          const uint64_t a_desc = smem_desc(a_base + (j / 4) * (kBlockN * 128) + (j % 4) * 32, 16, 1024, 2);
           const uint64_t b_desc = smem_desc(x_base + (j / 4) * (MP * 128) + (j % 4) * 32, 16, 1024, 2);
-          tc_mma_f16_ts(d + (j & (nacc - 1)) * MP, a_tmem + j * 8, b_desc, idesc, (kb > 0 || j >= nacc) ? 1u : 0u);
+          tc_mma_f16_ss(d + (j & (nacc - 1)) * MP, a_desc, b_desc, idesc, (kb > 0 || j >= nacc) ? 1u : 0u);
         }
         tc_commit(smem_u32(&a_empty[t]));   // operand columns and the x stage are free once these MMAs retire
         tc_commit(smem_u32(&empty[s]));
@@ -326,9 +333,9 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     }
   } else if (warp >= 4) {
     // ---------------- converters, then epilogue ----------------
-    const int cw = warp - 4;                      // 0..7
+    const int cw = warp - 4;                      // 0..15
     const int q = cw & 3;                         // TMEM lane quarter this warp may access (= warp % 4)
-    const int hsel = cw >> 2;                     // which half of the row's k range / of the output columns
+    const int hsel = cw >> 2;                     // converting: which quarter of the row's k range; epilogue (warps 4..11): which half of the output columns
     const int r = q * 32 + lane;                  // row of the tile owned by this thread (= TMEM lane)
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const int swz = BITS == 8 ? (r & 7) : ((r >> 1) & 3);
@@ -370,7 +377,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         if (threadIdx.x == 128) CB200_TRACE(2, i, 2);
         tc_fence_after();
         const uint8_t* raw_row = s_raw + s * kRawBytes + r * kRawRow;
-        const uint32_t a_cols = tmem_base + lane_addr + kAColBase + t * kAStageCols;
+        uint8_t* a_tile = s_a + t * kABytes;
         const __half2 gscale = __float2half2_rn(next_scale);
         next_scale = group_scale(kbi + 1);
         uint4 raw[kChunksPerThread];
@@ -392,7 +399,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
               unpack8_slow<8>(reinterpret_cast<const uint8_t*>(w), 0, zero, scale, o);
               unpack8_slow<8>(reinterpret_cast<const uint8_t*>(w), 8, zero, scale, o + 4);
             }
-            tc_st_x8(a_cols + 8 * c, reinterpret_cast<const uint32_t(&)[8]>(o));
+            st_operand16(a_tile, r, 16 * c, reinterpret_cast<const uint32_t(&)[8]>(o));
           } else {              // 32 codes -> 16 columns starting at 16c
 #pragma unroll
             for (int hw = 0; hw < 2; ++hw) {
@@ -404,17 +411,23 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 unpack8_slow<4>(reinterpret_cast<const uint8_t*>(w), 16 * hw, zero, scale, o);
                 unpack8_slow<4>(reinterpret_cast<const uint8_t*>(w), 16 * hw + 8, zero, scale, o + 4);
               }
-              tc_st_x8(a_cols + 16 * c + 8 * hw, reinterpret_cast<const uint32_t(&)[8]>(o));
+              st_operand16(a_tile, r, 32 * c + 16 * hw, reinterpret_cast<const uint32_t(&)[8]>(o));
             }
           }
         }
-        tc_wait_st();
-        tc_fence_before();                         // order the TMEM stores before the arrive the MMA thread waits on
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads the tile through the async proxy
         mbar_arrive(smem_u32(&a_full[t]));
         mbar_arrive(smem_u32(&empty[s]));
         if (threadIdx.x == 128) CB200_TRACE(2, i, 3);
       }
     }
+    if (cw >= 8) {   // the second eight converter warps have no epilogue share; they only join the cluster barriers
+      if (split > 1) {
+        __syncwarp();
+        cluster_sync_all();
+        cluster_sync_all();
+      }
+    } else {
     // ---- epilogue: this warp owns rows [32q, 32q+32) and output columns [hsel*MP/2, (hsel+1)*MP/2) ----
     constexpr int kColsPerWarp = MP / 2;
     float acc[2][kColsPerWarp];
@@ -488,6 +501,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         }
       }
     }
+    }   // cw < 8
   } 
   if (warp < 4 && split > 1) {   // warps without an epilogue still take part in the two cluster barriers
     __syncwarp();
@@ -562,7 +576,8 @@ int choose_split_k(int n_tiles, int kblocks, int epilogue) {
 template <int BITS, int MP>
 int launch_tc(const QGemvParams& q, cudaStream_t stream) {
   constexpr int kStages = num_stages(BITS, MP);
-  constexpr size_t kSmem = 1024 + static_cast<size_t>(kStages) * stage_bytes(BITS, MP) + 512;
+  constexpr size_t kSmem = 1024 + static_cast<size_t>(kStages) * stage_bytes(BITS, MP) + kAStages * kABytes + 512;
+  static_assert(kSmem <= 227 * 1024, "ring + operand tiles must fit the shared memory of one SM");
   static_assert(static_cast<size_t>(kMaxSplitK - 1) * MP * kBlockN * 4 <= static_cast<size_t>(kStages) * stage_bytes(BITS, MP) &&
                     static_cast<size_t>(2) * MP * kBlockN * 4 <= static_cast<size_t>(kStages) * stage_bytes(BITS, MP),
                 "split-K partials must fit in the pipeline ring");
