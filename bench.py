@@ -598,7 +598,8 @@ def main() -> None:
     dist = None
     if world > 1:
         import torch.distributed as dist  # type: ignore[no-redef]
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")     # keep stdout for the one JSON line
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", ""):
+            os.environ["NCCL_DEBUG"] = "WARN"                       # no version banner: stdout carries the one JSON line
         dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
 
     from cacheir_b200.sharding import max_over_ranks

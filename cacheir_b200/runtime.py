@@ -307,6 +307,7 @@ class _DecodePlan:
         nodes = list(eng.graph.nodes)
         env: dict[str, Any] = {}
         self._count_keys: list[tuple[str, int]] = []
+        self._count_totals: dict[str, int] | None = None
         self._prequantized: set[str] = set()
         self._kv_appended: set[str] = set()
         self._peer_calls = 0
@@ -630,7 +631,12 @@ class _DecodePlan:
             if feedback:
                 self.feedback_tail()
         self.steps_run += 1
-        for key, n in self._count_keys:
+        if self._count_totals is None:      # launches per kernel name of one step, summed once
+            totals: dict[str, int] = {}
+            for key, n in self._count_keys:
+                totals[key] = totals.get(key, 0) + n
+            self._count_totals = totals
+        for key, n in self._count_totals.items():
             eng.count(key, n)
         if feedback:
             eng.count("b200.argmax_rows")
