@@ -216,6 +216,15 @@ class B200PagedKVCache:
     def extend(self, length: int) -> bool:
         """Account for `length` more tokens; same walk as `_extend_pages`
         (cacheir/runtime/cuda.py:395-406). Returns True if a page was opened."""
+        if length == 1 and self.tokens % self.page_size != 0:
+            # the per-step case: one more token in the open page (the walk below does the same, slower)
+            last = self.pages[-1]
+            if self.allocator.refcount(last.page_id) > 1:
+                raise RuntimeError("cannot append into a page that other sessions alias")
+            last.length += 1
+            self.tokens += 1
+            self.allocator.pool_writes += self.num_layers
+            return False
         opened = False
         remaining = int(length)
         cursor = self.tokens

@@ -156,6 +156,8 @@ class _Engine:
         self.peer: PeerCollectives | None = None
         self.use_cuda_graph = use_cuda_graph and (not self.tp.enabled or self.peer_mode)
         self.tile_weights = True
+        self.validated_batch: tuple[int, ...] | None = None      # identity of the last decode batch that passed the checks
+        self.validated_sessions: list[Any] = []
         self.prefill_chunk = 64        # prompt tokens per pass of the chunked prefill (0: one token per step)
         self._rope_tables: dict[tuple[int, float], torch.Tensor] = {}
         self.attention_splits = int(attention_splits)
@@ -727,13 +729,17 @@ class B200DecodeRuntime:
             raise ValueError("run_decode_batch requires at least one session")
         if len(sessions) != len(token_ids):
             raise ValueError("sessions and token_ids must have the same length")
-        for session in sessions:
-            if not isinstance(session, B200DecodeRuntime):
-                raise TypeError("run_decode_batch only accepts B200DecodeRuntime sessions")
-            if session._engine is not self._engine:
-                raise ValueError("all sessions must be forks of the same runtime (same artifact, weights and device)")
-        if len({s.kv_cache.owner_id for s in sessions}) != len(sessions):
-            raise ValueError("a session may appear only once in a decode batch")
+        batch_key = tuple(map(id, sessions))
+        if batch_key != self._engine.validated_batch:      # the same sessions as last step were checked then
+            for session in sessions:
+                if not isinstance(session, B200DecodeRuntime):
+                    raise TypeError("run_decode_batch only accepts B200DecodeRuntime sessions")
+                if session._engine is not self._engine:
+                    raise ValueError("all sessions must be forks of the same runtime (same artifact, weights and device)")
+            if len({s.kv_cache.owner_id for s in sessions}) != len(sessions):
+                raise ValueError("a session may appear only once in a decode batch")
+            self._engine.validated_batch = batch_key
+            self._engine.validated_sessions = list(sessions)      # keeps the ids above from being recycled
         with torch.cuda.device(self.device):
             for session in sessions:
                 session.kv_cache.extend(1)      # opens a page when the new token starts one
