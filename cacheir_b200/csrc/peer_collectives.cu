@@ -10,7 +10,7 @@
 // Callers alternate between two data buffers from call to call: a rank may refill buffer A
 // only after the call that used buffer B, whose wait proves every peer has left buffer A.
 // The epoch lives on the device and advances with every call, so a captured CUDA graph can be
-// replayed. No multicast, no TMA, no library collective: plain loads and stores. A wait that
+// replayed. Only plain peer loads and stores, no library collective. A wait that
 // runs out of polls records a code in the status word and the kernel returns (output undefined).
 #include <string.h>
 
