@@ -451,7 +451,7 @@ def run_reference_arm(args, cfg: dict, workload: str) -> None:
                        "l2_policy": "inputs larger than L2"},
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cpu_threads(), "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # --------------------------------------------------------------------------------------
@@ -542,9 +542,28 @@ def run_micro(args) -> None:
     torch.cuda.synchronize()
     sec = start.elapsed_time(end) * 1e-3 / args.steps
     from cacheir_b200 import _lib
-    print(json.dumps({"micro": name, **shape, "us_per_launch": round(sec * 1e6, 2), "algorithmic_bytes": int(algo),
-                      "achieved_gbs": round(algo / sec / 1e9, 1), "frac": round(algo / sec / 1e9 / peak, 4),
-                      "peak": peak, "peak_source": f"of {kind}", "device_status": _lib.load().cacheir_b200_device_status(0)}), flush=True)
+    emit({"micro": name, **shape, "us_per_launch": round(sec * 1e6, 2), "algorithmic_bytes": int(algo),
+          "achieved_gbs": round(algo / sec / 1e9, 1), "frac": round(algo / sec / 1e9 / peak, 4),
+          "peak": peak, "peak_source": f"of {kind}", "device_status": _lib.load().cacheir_b200_device_status(0)})
+
+
+_RESULT_STREAM = None
+
+
+def claim_stdout() -> None:
+    """Keep the caller's stdout for the one JSON line: everything else that writes to file
+    descriptor 1 from here on (library banners from native code included) goes to stderr."""
+    global _RESULT_STREAM
+    if _RESULT_STREAM is None:
+        sys.stdout.flush()
+        _RESULT_STREAM = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    stream = _RESULT_STREAM if _RESULT_STREAM is not None else sys.stdout
+    stream.write(json.dumps(line) + "\n")
+    stream.flush()
 
 
 def main() -> None:
@@ -573,6 +592,7 @@ def main() -> None:
     parser.add_argument("--ctx-max", type=int, default=8192)
     parser.add_argument("--splits", type=int, default=0)
     args = parser.parse_args()
+    claim_stdout()
     if args.micro:
         run_micro(args)
         return
@@ -598,8 +618,6 @@ def main() -> None:
     dist = None
     if world > 1:
         import torch.distributed as dist  # type: ignore[no-redef]
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", ""):
-            os.environ["NCCL_DEBUG"] = "WARN"                       # no version banner: stdout carries the one JSON line
         dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
 
     from cacheir_b200.sharding import max_over_ranks
@@ -715,7 +733,7 @@ def main() -> None:
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = run_cpu_baseline(dict(cfg, ctx=cfg.get("ctx_mean", cfg["ctx"])))
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
