@@ -1,6 +1,6 @@
 // Small-M dequant-GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
 //
-//   y[M, N] = x[M, K] . deq(W)[N, K]^T        M <= 64, fp16 activations
+//   y[M, N] = x[M, K] . deq(W)[N, K]^T        M <= 128, fp16 activations
 //
 // The weight matrix is the 128-row MMA operand ("swap-AB"): one CTA owns 128
 // weight rows and a K range, the M activation rows are the MMA's N dimension
@@ -23,6 +23,12 @@
 //   warps 4-11  epilogue: tcgen05.ld the accumulator, split-K reduction across the
 //               CTAs of a cluster through distributed shared memory in rank order
 //               (deterministic), row scale, residual add or SiLU*mul, store y
+//
+// Batches of 65..128 rows (MP = 128) run the same pipeline with the operand roles exchanged:
+// the activation tile [128 rows x 128 k] is the 128-row MMA operand, the dequantised weight
+// tile the N = 128 operand, so the weights stream once for the whole batch. The accumulator
+// then holds batch rows on the tensor-memory lanes and weight rows along the columns; all
+// sixteen converter warps share the epilogue (32 columns each).
 //
 // Every wait is bounded: a barrier that does not complete within the poll budget
 // raises a device status flag and the CTA drains and exits instead of hanging.
@@ -225,6 +231,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   constexpr int kXBytes = MP * kBlockK * 2;
   constexpr int kRawRow = BITS == 8 ? 128 : 64;                          // bytes of one row per stage
   constexpr int kChunksPerThread = kRawRow / 16 / 4;                     // 16-byte chunks per converter thread (a quarter row)
+  constexpr bool kWide = MP == 128;                                      // activations are the 128-row operand
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -238,6 +245,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   uint64_t* a_empty = a_full + kAStages;                   // [kAStages]  MMA commit (1)
   uint64_t* acc_full = a_empty + kAStages;                 // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  float* s_rowscale = reinterpret_cast<float*>(bars + 64);   // [2 passes][128 tile rows], used when MP == 128
   float* s_partial = reinterpret_cast<float*>(smem);       // split-K partials reuse the ring once it has drained
 
   const int warp = threadIdx.x >> 5;
@@ -323,7 +331,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           // inside a 64-element span, the second span one half tile further.
           const uint64_t a_desc = smem_desc(a_base + (j / 4) * (kBlockN * 128) + (j % 4) * 32, 16, 1024, 2);
           const uint64_t b_desc = smem_desc(x_base + (j / 4) * (MP * 128) + (j % 4) * 32, 16, 1024, 2);
-          tc_mma_f16_ss(d + (j & (nacc - 1)) * MP, a_desc, b_desc, idesc, (kb > 0 || j >= nacc) ? 1u : 0u);
+          if (kWide) tc_mma_f16_ss(d + (j & (nacc - 1)) * MP, b_desc, a_desc, idesc, (kb > 0 || j >= nacc) ? 1u : 0u);
+          else tc_mma_f16_ss(d + (j & (nacc - 1)) * MP, a_desc, b_desc, idesc, (kb > 0 || j >= nacc) ? 1u : 0u);
         }
         tc_commit(smem_u32(&a_empty[t]));   // operand columns and the x stage are free once these MMAs retire
         tc_commit(smem_u32(&empty[s]));
@@ -353,6 +362,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       // exact in-register zero-point removal needs an integer zero point that fp16 can offset exactly
       const bool fast = (zero == rintf(zero)) && fabsf(zero) <= 960.f;
       row_scale[pass] = (p.group_size == 0 && fast) ? scale : 1.f;
+      if (kWide && hsel == 0) s_rowscale[pass * kBlockN + r] = row_scale[pass];
       const __half2 sub8 = __float2half2_rn(1024.f + zero);
       const __half2 mul4 = __floats2half2_rn(1.f, 0.0625f);
       const __half2 sub4 = __floats2half2_rn(-(1024.f + zero), -(64.f + zero));
@@ -421,7 +431,101 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         if (threadIdx.x == 128) CB200_TRACE(2, i, 3);
       }
     }
-    if (cw >= 8) {   // the second eight converter warps have no epilogue share; they only join the cluster barriers
+    if constexpr (kWide) {
+      // ---- epilogue, 128-row batches: this warp owns batch rows [32q, 32q+32) (its TMEM lanes) and
+      //      tile rows [32 hsel, 32 hsel + 32) (accumulator columns) ----
+      asm volatile("bar.sync 3, %0;" ::"n"(kConvThreads) : "memory");   // the row-scale table is complete
+      constexpr int kCols = 32;
+      float acc[2][kCols];
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int j = 0; j < kCols; ++j) acc[a][j] = 0.f;
+      ok = ok && mbar_wait(smem_u32(acc_full), 0, 6);
+      if (ok && total > 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int a = 0; a < 2; ++a) {
+          if (a == 1 && !swiglu) break;
+          for (int part = 0; part < nacc; ++part) {
+#pragma unroll
+            for (int c0 = 0; c0 < kCols; c0 += 8) {
+              uint32_t v[8];
+              tc_ld_x8(tmem_base + lane_addr + (a * nacc + part) * MP + hsel * kCols + c0, v);
+              tc_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[a][c0 + j] += __uint_as_float(v[j]);
+            }
+          }
+        }
+      }
+      if (split > 1) {   // two ranks at most: rank 1 hands its partial to rank 0 through the drained ring
+        cluster_sync_all();
+        if (krank != 0) {
+#pragma unroll
+          for (int a = 0; a < 2; ++a) {
+            if (a == 1 && !swiglu) break;
+#pragma unroll
+            for (int j = 0; j < kCols; ++j)
+              st_cluster_f32(smem_u32(s_partial + (a * kBlockN + hsel * kCols + j) * 128 + r), 0, acc[a][j]);
+          }
+        }
+        cluster_sync_all();
+        if (krank == 0) {
+#pragma unroll
+          for (int a = 0; a < 2; ++a) {
+            if (a == 1 && !swiglu) break;
+#pragma unroll
+            for (int j = 0; j < kCols; ++j) acc[a][j] += s_partial[(a * kBlockN + hsel * kCols + j) * 128 + r];
+          }
+        }
+      }
+      if (ok && krank == 0 && r < p.M) {
+        __half* y = static_cast<__half*>(p.y);
+        const __half* res = static_cast<const __half*>(p.residual);
+        const bool vec = (p.n_out % 8) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 && (reinterpret_cast<uintptr_t>(res) & 15) == 0;
+#pragma unroll
+        for (int j0 = 0; j0 < kCols; j0 += 8) {
+          const int col0 = hsel * kCols + j0;
+          const int n_idx = n0 + col0;
+          if (n_idx >= p.n_out) break;
+          float out[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float v = acc[0][j0 + j] * s_rowscale[col0 + j];
+            if (swiglu) v = silu_fast(v) * (acc[1][j0 + j] * s_rowscale[kBlockN + col0 + j]);
+            out[j] = v;
+          }
+          const size_t o = static_cast<size_t>(r) * p.n_out + n_idx;
+          if (vec) {
+            if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
+              const uint4 rv = *reinterpret_cast<const uint4*>(res + o);
+              const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(rh[j]);
+                out[2 * j] += f.x;
+                out[2 * j + 1] += f.y;
+              }
+            }
+            uint4 ov;
+            __half2* oh = reinterpret_cast<__half2*>(&ov);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(out[2 * j], out[2 * j + 1]);
+            *reinterpret_cast<uint4*>(y + o) = ov;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (n_idx + j < p.n_out) {
+                float v = out[j];
+                if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) v += __half2float(res[o + j]);
+                y[o + j] = __float2half_rn(v);
+              }
+            }
+          }
+        }
+      }
+    } else if (cw >= 8) {   // the second eight converter warps have no epilogue share; they only join the cluster barriers
       if (split > 1) {
         __syncwarp();
         cluster_sync_all();
@@ -576,11 +680,15 @@ int choose_split_k(int n_tiles, int kblocks, int epilogue) {
 template <int BITS, int MP>
 int launch_tc(const QGemvParams& q, cudaStream_t stream) {
   constexpr int kStages = num_stages(BITS, MP);
-  constexpr size_t kSmem = 1024 + static_cast<size_t>(kStages) * stage_bytes(BITS, MP) + kAStages * kABytes + 512;
+  constexpr size_t kSmem = 1024 + static_cast<size_t>(kStages) * stage_bytes(BITS, MP) + kAStages * kABytes + 512 + 1024;
   static_assert(kSmem <= 227 * 1024, "ring + operand tiles must fit the shared memory of one SM");
-  static_assert(static_cast<size_t>(kMaxSplitK - 1) * MP * kBlockN * 4 <= static_cast<size_t>(kStages) * stage_bytes(BITS, MP) &&
-                    static_cast<size_t>(2) * MP * kBlockN * 4 <= static_cast<size_t>(kStages) * stage_bytes(BITS, MP),
+  static_assert(MP == 128 ||
+                    (static_cast<size_t>(kMaxSplitK - 1) * MP * kBlockN * 4 <= static_cast<size_t>(kStages) * stage_bytes(BITS, MP) &&
+                     static_cast<size_t>(2) * MP * kBlockN * 4 <= static_cast<size_t>(kStages) * stage_bytes(BITS, MP)),
                 "split-K partials must fit in the pipeline ring");
+  static_assert(MP != 128 || static_cast<size_t>(2) * 128 * kBlockN * 4 <=
+                                 static_cast<size_t>(kStages) * stage_bytes(BITS, MP) + kAStages * kABytes,
+                "128-row batches: one rank's two partial accumulators must fit in the ring plus the operand tiles");
   CUtensorMap tmap_w, tmap_x;
   const uint64_t row_bytes = BITS == 8 ? static_cast<uint64_t>(q.K) : static_cast<uint64_t>(q.K / 2);
   constexpr uint32_t kTileRowBytes = BITS == 8 ? 128 : 64;
@@ -603,6 +711,7 @@ int launch_tc(const QGemvParams& q, cudaStream_t stream) {
   p.w_tiled = static_cast<const uint8_t*>(q.packed);
   const int n_tiles = (p.n_out + kBlockN - 1) / kBlockN;
   p.split_k = choose_split_k(n_tiles, q.K / kBlockK, q.epilogue);
+  if (MP == 128 && p.split_k > 2) p.split_k = 2;
   auto kern = qgemm_tc_kernel<BITS, MP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -627,7 +736,8 @@ template <int BITS>
 int launch_tc_mp(const QGemvParams& q, cudaStream_t stream) {
   if (q.M <= 16) return launch_tc<BITS, 16>(q, stream);
   if (q.M <= 32) return launch_tc<BITS, 32>(q, stream);
-  return launch_tc<BITS, 64>(q, stream);
+  if (q.M <= 64) return launch_tc<BITS, 64>(q, stream);
+  return launch_tc<BITS, 128>(q, stream);
 }
 
 }  // namespace
@@ -635,7 +745,7 @@ int launch_tc_mp(const QGemvParams& q, cudaStream_t stream) {
 bool qgemm_tc_supported(const QGemvParams& q) {
   if (q.x_dtype != CACHEIR_B200_F16) return false;
   if (q.bits != 4 && q.bits != 8) return false;
-  if (q.M < 1 || q.M > 64) return false;
+  if (q.M < 1 || q.M > 128) return false;
   if (q.K % kBlockK != 0 || q.K < kBlockK) return false;
   if (q.group_size != 0 && q.group_size % kBlockK != 0) return false;   // one scale per row and k block
   if (q.epilogue == CACHEIR_B200_EPI_SWIGLU && (q.N / 2) % kBlockN != 0) return false;

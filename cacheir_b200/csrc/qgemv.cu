@@ -234,16 +234,17 @@ extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const vo
                 (p.x_stride * esize) % 16 == 0;
   cudaStream_t st = as_stream(stream);
   if (M > 64 && !p.x_prequantized) {
-    // The tensor-core kernels take up to 64 batch rows per launch. A taller batch runs as chunks of 64 rows
-    // (the weights stream once per chunk, still far cheaper than the CUDA-core kernel at these heights) when
-    // a 64-row problem of the same shape is tensor-core eligible.
+    // The integer tensor-core kernel takes up to 64 batch rows per launch, the fp16 one up to 128. A taller
+    // batch runs as chunks of that height (the weights stream once per chunk, still far cheaper than the
+    // CUDA-core kernel at these heights) when a chunk-sized problem of the same shape is tensor-core eligible.
     QGemvParams c = p;
     c.M = 64;
     const bool i8_ok = qgemm_i8_supported(c, workspace, workspace_bytes);
     if (i8_ok || (!c.paired && qgemm_tc_supported(c))) {
+      const int rows = i8_ok ? 64 : 128;
       const size_t n_out = epilogue == CACHEIR_B200_EPI_SWIGLU ? static_cast<size_t>(N) / 2 : static_cast<size_t>(N);
-      for (int m0 = 0; m0 < M; m0 += 64) {
-        c.M = M - m0 < 64 ? M - m0 : 64;
+      for (int m0 = 0; m0 < M; m0 += rows) {
+        c.M = M - m0 < rows ? M - m0 : rows;
         c.x = static_cast<const char*>(x) + static_cast<size_t>(m0) * p.x_stride * esize;
         c.y = static_cast<char*>(y) + static_cast<size_t>(m0) * n_out * esize;
         c.residual = residual ? static_cast<const char*>(residual) + static_cast<size_t>(m0) * n_out * esize : nullptr;

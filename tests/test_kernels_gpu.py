@@ -594,7 +594,7 @@ def test_qkv_rope_append_equals_separate_kernels(k, tiled):
     _device_status_ok()
 
 
-# ---- batches taller than one tensor-core launch run as 64-row chunks --------------------------
+# ---- batches taller than one tensor-core launch run as chunks (64 rows integer kernel, 128 rows fp16 kernel) --------------------------
 @pytest.mark.parametrize("bits,group,tiled", [(8, 0, True), (8, 0, False), (4, 128, True), (4, 0, False)])
 def test_qgemv_tall_batch_runs_in_chunks(bits, group, tiled):
     from cacheir_b200 import ops
@@ -617,6 +617,38 @@ def test_qgemv_tall_batch_runs_in_chunks(bits, group, tiled):
     res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).half()
     y = quantized_matmul(x.cuda(), weight, epilogue=ops.EPI_RESIDUAL, residual=res.cuda(), workspace=ws)
     assert _rel(y, base + res.float().numpy()) <= TOL[torch.float16]
+    torch.cuda.synchronize()
+    _device_status_ok()
+
+
+# ---- 65..128 batch rows: one launch of the fp16 tensor-core kernel with the operand roles exchanged ----
+@pytest.mark.parametrize("m", [65, 100, 128])
+@pytest.mark.parametrize("bits,group,tiled", [(4, 128, True), (4, 128, False), (8, 128, True), (4, 0, False), (8, 0, True)])
+def test_qgemv_wide_batch_single_launch(m, bits, group, tiled):
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul, to_tiled
+    rng = np.random.default_rng(1000 * bits + group + m)
+    # (n, k): many tiles without split-K; few tiles so that two CTAs share the k range; rows that do not fill the last tile
+    for n, k in ((1024, 512), (256, 2048), (200, 1024)):
+        x, packed = _qgemv_case(rng, m, n, k, bits, torch.float16, group=group, reference_pack=not group)
+        dev = _device_pack(packed)
+        if group:
+            dev.scales = torch.from_numpy(packed.scales).cuda()
+        weight = to_tiled(dev) if tiled else dev
+        base = oracle.quantized_matmul(x.float().numpy(), packed)
+        y = quantized_matmul(x.cuda(), weight)            # no workspace: the fp16 kernel, not the integer one
+        assert y.shape == (m, n)
+        assert _rel(y, base) <= TOL[torch.float16], (n, k)
+        # a row's result does not depend on the batch it sits in: the 16-row kernel gives the same sums up to fp32 order
+        y_small = quantized_matmul(x[:16].cuda().contiguous(), weight)
+        assert _rel(y[:16], y_small.float().cpu().numpy()) <= 2e-3
+        res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).half()
+        y = quantized_matmul(x.cuda(), weight, epilogue=ops.EPI_RESIDUAL, residual=res.cuda())
+        assert _rel(y, base + res.float().numpy()) <= TOL[torch.float16], (n, k)
+        if n % 256 == 0:
+            y = quantized_matmul(x.cuda(), weight, epilogue=ops.EPI_SWIGLU)
+            gate, up = base[:, :n // 2], base[:, n // 2:]
+            assert _rel(y, gate / (1.0 + np.exp(-gate)) * up) <= 2 * TOL[torch.float16], (n, k)
     torch.cuda.synchronize()
     _device_status_ok()
 
