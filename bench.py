@@ -498,7 +498,7 @@ def run_micro(args) -> None:
         name = f"qgemv_int{bits}" + (f"_g{args.group}" if args.group else "")
         shape = {"M": m, "N": n, "K": k}
     else:
-        batch, heads, kv_heads, hd, page = args.batch, 32, 8, 128, 16
+        batch, heads, kv_heads, hd, page = args.batch, args.heads, args.kv_heads, 128, 16
         rng = np.random.default_rng(0)
         lens_np = rng.integers(args.ctx_min, args.ctx_max + 1, batch).astype(np.int32)
         pages = (lens_np + page - 1) // page
@@ -591,6 +591,8 @@ def main() -> None:
     parser.add_argument("--ctx-min", type=int, default=512)
     parser.add_argument("--ctx-max", type=int, default=8192)
     parser.add_argument("--splits", type=int, default=0)
+    parser.add_argument("--heads", type=int, default=32)
+    parser.add_argument("--kv-heads", type=int, default=8)
     args = parser.parse_args()
     claim_stdout()
     if args.micro:

@@ -150,6 +150,15 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t local_addr, uint32_t ran
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Bulk copy from this CTA's shared memory into CTA `rank` of the cluster; completion is counted in
+// bytes on that CTA's barrier at the same offset as `bar`.
+__device__ __forceinline__ void bulk_copy_to_rank(uint32_t dst, uint32_t src, uint32_t bytes, uint32_t bar, uint32_t rank) {
+  uint32_t rdst, rbar;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rdst) : "r"(dst), "r"(rank));
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(bar), "r"(rank));
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(rdst), "r"(src), "r"(bytes), "r"(rbar) : "memory");
+}
 
 // Shared-memory matrix descriptor (64 bit): start address, leading/stride byte offsets
 // (all >> 4), descriptor version 1 at bit 46, swizzle mode at bits 61-63.
@@ -245,6 +254,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   uint64_t* a_empty = a_full + kAStages;                   // [kAStages]  MMA commit (1)
   uint64_t* acc_full = a_empty + kAStages;                 // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* xch_bar = bars + 40;                              // [1] 128-row batches: the other ranks' partials have landed
   float* s_rowscale = reinterpret_cast<float*>(bars + 64);   // [2 passes][128 tile rows], used when MP == 128
   float* s_partial = reinterpret_cast<float*>(smem);       // split-K partials reuse the ring once it has drained
 
@@ -268,6 +278,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), kConvThreads + 1); }
     for (int t = 0; t < kAStages; ++t) { mbar_init(smem_u32(&a_full[t]), kConvThreads); mbar_init(smem_u32(&a_empty[t]), 1); }
     mbar_init(smem_u32(acc_full), 1);
+    mbar_init(smem_u32(xch_bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {   // TMEM allocation is a warp-wide operation
@@ -436,95 +447,142 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       //      tile rows [32 hsel, 32 hsel + 32) (accumulator columns) ----
       asm volatile("bar.sync 3, %0;" ::"n"(kConvThreads) : "memory");   // the row-scale table is complete
       constexpr int kCols = 32;
-      float acc[2][kCols];
-#pragma unroll
-      for (int a = 0; a < 2; ++a)
-#pragma unroll
-        for (int j = 0; j < kCols; ++j) acc[a][j] = 0.f;
+      if (threadIdx.x == 128) CB200_TRACE(3, 0, 0);
       ok = ok && mbar_wait(smem_u32(acc_full), 0, 6);
-      if (ok && total > 0) {
-        tc_fence_after();
+      if (threadIdx.x == 128) CB200_TRACE(3, 1, 0);
+      tc_fence_after();
+      const bool have = ok && total > 0;
+      __half* y = static_cast<__half*>(p.y);
+      const __half* res = static_cast<const __half*>(p.residual);
+      // The epilogue runs once per CTA from a cold instruction cache, so its loops stay rolled: straight-line
+      // code of a few thousand instructions costs more in fetches than the work it does.
+      // eight columns (c0 .. c0+7 of this warp's 32) of accumulator a: the rotating accumulators added in a fixed order
+      auto ld8 = [&](int a, int c0, float (&v8)[8]) {
 #pragma unroll
-        for (int a = 0; a < 2; ++a) {
-          if (a == 1 && !swiglu) break;
+        for (int j = 0; j < 8; ++j) v8[j] = 0.f;
+        if (have) {
+#pragma unroll 1
           for (int part = 0; part < nacc; ++part) {
+            uint32_t v[8];
+            tc_ld_x8(tmem_base + lane_addr + (a * nacc + part) * MP + hsel * kCols + c0, v);
+            tc_wait_ld();
 #pragma unroll
-            for (int c0 = 0; c0 < kCols; c0 += 8) {
-              uint32_t v[8];
-              tc_ld_x8(tmem_base + lane_addr + (a * nacc + part) * MP + hsel * kCols + c0, v);
-              tc_wait_ld();
+            for (int j = 0; j < 8; ++j) v8[j] += __uint_as_float(v[j]);
+          }
+        }
+      };
+      const bool vec = (p.n_out % 4) == 0 && (reinterpret_cast<uintptr_t>(y) & 7) == 0 && (reinterpret_cast<uintptr_t>(res) & 7) == 0;
+      // four finished outputs of row r, tile columns col0 .. col0+3
+      auto store4 = [&](int col0, const float* v4) {
+        const int n_idx = n0 + col0;
+        if (n_idx >= p.n_out || !ok || r >= p.M) return;
+        float out[4] = {v4[0], v4[1], v4[2], v4[3]};
+        const size_t o = static_cast<size_t>(r) * p.n_out + n_idx;
+        if (vec) {
+          if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
+            const uint2 rv = *reinterpret_cast<const uint2*>(res + o);
+            const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+            const float2 f0 = __half22float2(rh[0]), f1 = __half22float2(rh[1]);
+            out[0] += f0.x; out[1] += f0.y; out[2] += f1.x; out[3] += f1.y;
+          }
+          uint2 ov;
+          __half2* oh = reinterpret_cast<__half2*>(&ov);
+          oh[0] = __floats2half2_rn(out[0], out[1]);
+          oh[1] = __floats2half2_rn(out[2], out[3]);
+          *reinterpret_cast<uint2*>(y + o) = ov;
+        } else {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) acc[a][c0 + j] += __uint_as_float(v[j]);
+          for (int j = 0; j < 4; ++j) {
+            if (n_idx + j < p.n_out) {
+              float v = out[j];
+              if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) v += __half2float(res[o + j]);
+              y[o + j] = __float2half_rn(v);
             }
           }
         }
-      }
-      if (split > 1) {   // two ranks at most: rank 1 hands its partial to rank 0 through the drained ring
-        cluster_sync_all();
-        if (krank != 0) {
-#pragma unroll
-          for (int a = 0; a < 2; ++a) {
-            if (a == 1 && !swiglu) break;
-#pragma unroll
-            for (int j = 0; j < kCols; ++j)
-              st_cluster_f32(smem_u32(s_partial + (a * kBlockN + hsel * kCols + j) * 128 + r), 0, acc[a][j]);
-          }
-        }
-        cluster_sync_all();
-        if (krank == 0) {
-#pragma unroll
-          for (int a = 0; a < 2; ++a) {
-            if (a == 1 && !swiglu) break;
-#pragma unroll
-            for (int j = 0; j < kCols; ++j) acc[a][j] += s_partial[(a * kBlockN + hsel * kCols + j) * 128 + r];
-          }
-        }
-      }
-      if (ok && krank == 0 && r < p.M) {
-        __half* y = static_cast<__half*>(p.y);
-        const __half* res = static_cast<const __half*>(p.residual);
-        const bool vec = (p.n_out % 8) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 && (reinterpret_cast<uintptr_t>(res) & 15) == 0;
-#pragma unroll
-        for (int j0 = 0; j0 < kCols; j0 += 8) {
-          const int col0 = hsel * kCols + j0;
-          const int n_idx = n0 + col0;
-          if (n_idx >= p.n_out) break;
-          float out[8];
+      };
+      if (split == 1) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < kCols; c0 += 8) {
+          float g[8], u[8];
+          ld8(0, c0, g);
+          if (swiglu) ld8(1, c0, u);
+          const int col = hsel * kCols + c0;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            float v = acc[0][j0 + j] * s_rowscale[col0 + j];
-            if (swiglu) v = silu_fast(v) * (acc[1][j0 + j] * s_rowscale[kBlockN + col0 + j]);
-            out[j] = v;
+            const float v = g[j] * s_rowscale[col + j];
+            g[j] = swiglu ? silu_fast(v) * (u[j] * s_rowscale[kBlockN + col + j]) : v;
           }
-          const size_t o = static_cast<size_t>(r) * p.n_out + n_idx;
-          if (vec) {
-            if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) {
-              const uint4 rv = *reinterpret_cast<const uint4*>(res + o);
-              const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+          store4(col, g);
+          store4(col + 4, g + 4);
+        }
+      } else {
+        // Split-K (2, 4 or 8 ranks) as a reduce-scatter: rank d finishes columns [d W, (d+1) W) of the tile,
+        // W = 128 / split. Every rank stages its partial by destination in its drained ring, one bulk copy
+        // per destination moves a slot into that rank's receive area, and each rank adds the `split`
+        // partials of its own columns in rank order (deterministic). The two SwiGLU accumulators go one
+        // after the other through the same 64 KB + 64 KB; the gate sums wait in a third area.
+        const int W = kBlockN / split;                 // columns this rank finishes (64, 32 or 16)
+        const int log_w = 31 - __clz(W);
+        const int cnt = W / 4;                         // ... of which this thread handles cnt (4 column groups per row)
+        const int slot_floats = W * 128;
+        float* s_stage = s_partial;                    // [dest][W][128 rows]
+        float* s_recv = s_partial + kBlockN * 128;     // [src][W][128 rows]
+        float* s_keep = s_partial + 2 * kBlockN * 128; // [W][128 rows]: each thread parks its own gate sums here
+#pragma unroll 1
+        for (int a = 0; a < passes; ++a) {
+          if (threadIdx.x == 128) mbar_expect_tx(smem_u32(xch_bar), (split - 1) * slot_floats * 4);
+          cluster_sync_all();                          // every rank has drained its ring (and read the previous exchange) and armed its barrier
+          if (threadIdx.x == 128) CB200_TRACE(3, 2 + 4 * a, 0);
+#pragma unroll 1
+          for (int c0 = 0; c0 < kCols; c0 += 8) {
+            float v8[8];
+            ld8(a, c0, v8);
+            const int c = hsel * kCols + c0;           // eight consecutive columns share a destination (W >= 16)
+            float* dst = s_stage + (c >> log_w) * slot_floats + (c & (W - 1)) * 128 + r;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j * 128] = v8[j];
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync 3, %0;" ::"n"(kConvThreads) : "memory");
+          if (threadIdx.x == 128) CB200_TRACE(3, 3 + 4 * a, 0);
+          if (cw == 0 && lane < split - 1) {           // one lane per destination
+            const int dest = (krank + 1 + lane) % split;
+            bulk_copy_to_rank(smem_u32(s_recv + krank * slot_floats), smem_u32(s_stage + dest * slot_floats),
+                              slot_floats * 4, smem_u32(xch_bar), dest);
+          }
+          __syncwarp();
+          ok = mbar_wait(smem_u32(xch_bar), a & 1, 7) && ok;
+          if (threadIdx.x == 128) CB200_TRACE(3, 4 + 4 * a, 0);
+#pragma unroll 1
+          for (int i0 = 0; i0 < cnt; i0 += 4) {
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            const int mine = (hsel * cnt + i0) * 128 + r;
+#pragma unroll 1
+            for (int k = 0; k < split; ++k) {
+              const float* src = (k == krank ? s_stage : s_recv) + k * slot_floats + mine;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) sum[j] += src[j * 128];
+            }
+            const int col = krank * W + hsel * cnt + i0;
+            if (swiglu && a == 0) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) s_keep[mine + j * 128] = sum[j];
+            } else {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const float2 f = __half22float2(rh[j]);
-                out[2 * j] += f.x;
-                out[2 * j + 1] += f.y;
+                const float v = sum[j] * s_rowscale[a * kBlockN + col + j];
+                sum[j] = swiglu ? silu_fast(s_keep[mine + j * 128] * s_rowscale[col + j]) * v : v;
               }
-            }
-            uint4 ov;
-            __half2* oh = reinterpret_cast<__half2*>(&ov);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(out[2 * j], out[2 * j + 1]);
-            *reinterpret_cast<uint4*>(y + o) = ov;
-          } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (n_idx + j < p.n_out) {
-                float v = out[j];
-                if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) v += __half2float(res[o + j]);
-                y[o + j] = __float2half_rn(v);
-              }
+              store4(col, sum);
             }
           }
+          if (threadIdx.x == 128) CB200_TRACE(3, 5 + 4 * a, 0);
         }
+        cluster_sync_all();                            // all copies out of this CTA's shared memory have landed
+        if (threadIdx.x == 128) CB200_TRACE(3, 10, 0);
       }
+      if (threadIdx.x == 128) CB200_TRACE(3, 11, 0);
     } else if (cw >= 8) {   // the second eight converter warps have no epilogue share; they only join the cluster barriers
       if (split > 1) {
         __syncwarp();
@@ -607,10 +665,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     }
     }   // cw < 8
   } 
-  if (warp < 4 && split > 1) {   // warps without an epilogue still take part in the two cluster barriers
+  if (warp < 4 && split > 1) {   // warps without an epilogue still take part in the cluster barriers of the exchange
     __syncwarp();
-    cluster_sync_all();
-    cluster_sync_all();
+    const int syncs = kWide ? passes + 1 : 2;
+    for (int k = 0; k < syncs; ++k) cluster_sync_all();
   }
   tc_fence_before();
   __syncthreads();
@@ -686,9 +744,9 @@ int launch_tc(const QGemvParams& q, cudaStream_t stream) {
                     (static_cast<size_t>(kMaxSplitK - 1) * MP * kBlockN * 4 <= static_cast<size_t>(kStages) * stage_bytes(BITS, MP) &&
                      static_cast<size_t>(2) * MP * kBlockN * 4 <= static_cast<size_t>(kStages) * stage_bytes(BITS, MP)),
                 "split-K partials must fit in the pipeline ring");
-  static_assert(MP != 128 || static_cast<size_t>(2) * 128 * kBlockN * 4 <=
+  static_assert(MP != 128 || static_cast<size_t>(2) * 128 * kBlockN * 4 + 64 * kBlockN * 4 <=
                                  static_cast<size_t>(kStages) * stage_bytes(BITS, MP) + kAStages * kABytes,
-                "128-row batches: one rank's two partial accumulators must fit in the ring plus the operand tiles");
+                "128-row batches: staging, receive and gate areas of the split-K exchange must fit in the ring plus the operand tiles");
   CUtensorMap tmap_w, tmap_x;
   const uint64_t row_bytes = BITS == 8 ? static_cast<uint64_t>(q.K) : static_cast<uint64_t>(q.K / 2);
   constexpr uint32_t kTileRowBytes = BITS == 8 ? 128 : 64;
@@ -711,7 +769,14 @@ int launch_tc(const QGemvParams& q, cudaStream_t stream) {
   p.w_tiled = static_cast<const uint8_t*>(q.packed);
   const int n_tiles = (p.n_out + kBlockN - 1) / kBlockN;
   p.split_k = choose_split_k(n_tiles, q.K / kBlockK, q.epilogue);
-  if (MP == 128 && p.split_k > 2) p.split_k = 2;
+  if (MP == 128) {   // reduce-scatter exchange: 2, 4 or 8 ranks, the SwiGLU form as far as the plain one; few tiles split further
+    int want = kNumSMs / n_tiles;
+    if (want > q.K / kBlockK / 4) want = q.K / kBlockK / 4;
+    const int cap = n_tiles <= 16 ? 8 : kMaxSplitK;
+    int s = 1;
+    while (s * 2 <= want && s * 2 <= cap) s *= 2;
+    p.split_k = s;
+  }
   auto kern = qgemm_tc_kernel<BITS, MP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
   if (e != cudaSuccess) return static_cast<int>(e);

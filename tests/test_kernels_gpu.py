@@ -628,8 +628,9 @@ def test_qgemv_wide_batch_single_launch(m, bits, group, tiled):
     from cacheir_b200 import ops
     from cacheir_b200.quantization import quantized_matmul, to_tiled
     rng = np.random.default_rng(1000 * bits + group + m)
-    # (n, k): many tiles without split-K; few tiles so that two CTAs share the k range; rows that do not fill the last tile
-    for n, k in ((1024, 512), (256, 2048), (200, 1024)):
+    # (n, k): many tiles without split-K; few tiles so that four CTAs share the k range; rows that do not fill
+    # the last tile; one tile split over eight CTAs
+    for n, k in ((1024, 512), (256, 2048), (200, 1024), (128, 4096)):
         x, packed = _qgemv_case(rng, m, n, k, bits, torch.float16, group=group, reference_pack=not group)
         dev = _device_pack(packed)
         if group:
