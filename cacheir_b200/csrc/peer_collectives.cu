@@ -7,6 +7,12 @@
 //   2. wait, bounded, until every peer's slot in my own flag array shows the epoch;
 //   3. read all ranks' buffers with plain peer loads and combine them in rank order, so every
 //      rank computes bit-identical results (all-reduce), or copy the peers' slices (all-gather).
+// Large all-reduces take two steps inside one kernel (reduce-scatter, then all-gather): rank r adds only
+// slice r of every rank's buffer and pushes the finished slice into a gather buffer on every rank; a second
+// round of flags (raised by the last CTA of a rank to finish its slice) tells the peers that the slice has
+// landed, and each rank copies its gather buffer to the output. Every rank moves 2 (world-1)/world of the
+// message over NVLink instead of world-1 times the message, and the bits are identical everywhere because
+// one rank computes each slice.
 // Callers alternate between two data buffers from call to call: a rank may refill buffer A
 // only after the call that used buffer B, whose wait proves every peer has left buffer A.
 // The epoch lives on the device and advances with every call, so a captured CUDA graph can be
@@ -27,11 +33,12 @@ __device__ int g_peer_status = 0;
 struct PeerParams {
   const void* data[kMaxRanks];    // every rank's data buffer (index = rank), mapped into this process
   int* flags[kMaxRanks];          // every rank's flag array [kMaxRanks]
+  void* gather[kMaxRanks];        // two-step all-reduce: every rank's gather buffer
   void* out;
   size_t count;                   // all-reduce: elements; all-gather: elements of one rank's slice row
   int rows;                       // all-gather only: rows of the [rows, count] slices
   int rank, world;
-  int* state;                     // local: {epoch, CTAs finished}
+  int* state;                     // local: {epoch, CTAs finished, CTAs that finished their slice}
 };
 
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
@@ -98,6 +105,65 @@ __global__ void __launch_bounds__(256) all_reduce_kernel(const PeerParams p) {
       }
       VecIO<T, VEC>::st(static_cast<T*>(p.out) + i * VEC, acc);
     }
+  }
+  finish(p, epoch);
+}
+
+// Reduce-scatter + all-gather in one launch; count is a multiple of world * (16 / sizeof(T)). Every CTA of
+// a rank must be resident at once (the grid has at most one CTA per SM and the kernel owns the GPU when it
+// runs): CTAs that have finished their slice wait for the peers' second flags while the others still add.
+template <typename T>
+__global__ void __launch_bounds__(256) all_reduce_two_step_kernel(const PeerParams p) {
+  const int epoch = p.state[0] + 1;
+  constexpr int VEC = 16 / sizeof(T);
+  const size_t nvec = p.count / VEC;
+  const size_t per = nvec / p.world;             // vectors of one slice
+  __shared__ int s_ok2;
+  bool ok = announce_and_wait(p, epoch);
+  if (ok) {
+    const size_t base = per * p.rank;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < per;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+      float acc[VEC];
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+      for (int r = 0; r < p.world; ++r) {        // rank order
+        float v[VEC];
+        VecIO<T, VEC>::ld(static_cast<const T*>(p.data[r]) + (base + i) * VEC, v);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[j] += v[j];
+      }
+      for (int r = 0; r < p.world; ++r) VecIO<T, VEC>::st(static_cast<T*>(p.gather[r]) + (base + i) * VEC, acc);
+    }
+    __threadfence_system();                      // this thread's pushes are visible everywhere before the flag goes up
+  }
+  if (threadIdx.x == 0) s_ok2 = 1;
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(p.state + 2, 1) == static_cast<int>(gridDim.x) - 1) {
+    p.state[2] = 0;                              // last CTA of this rank: the whole slice has been pushed
+    __threadfence_system();
+    if (ok)
+      for (int r = 0; r < p.world; ++r) st_release_sys(p.flags[r] + kMaxRanks + p.rank, epoch);
+  }
+  if (ok && threadIdx.x < p.world) {
+    const int* slot = p.flags[p.rank] + kMaxRanks + threadIdx.x;
+    bool seen = false;
+    for (uint32_t i = 0; i < kPeerPollLimit; ++i) {
+      if (ld_acquire_sys(slot) - epoch >= 0) { seen = true; break; }
+      if (i > 64) __nanosleep(i > 4096 ? 2000 : 100);
+    }
+    if (!seen) {
+      s_ok2 = 0;
+      atomicCAS(&g_peer_status, 0, (4 << 8) | 2);
+    }
+  }
+  __syncthreads();
+  if (ok && s_ok2 != 0) {
+    const uint4* src = static_cast<const uint4*>(p.gather[p.rank]);
+    uint4* dst = static_cast<uint4*>(p.out);
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x)
+      dst[i] = __ldcg(src + i);                  // written by the peers: read past this SM's L1
   }
   finish(p, epoch);
 }
@@ -182,6 +248,32 @@ extern "C" int cacheir_b200_peer_all_reduce(void* const* data, void* const* flag
     case CACHEIR_B200_F32: all_reduce_kernel<float><<<grid, 256, 0, st>>>(p); break;
     case CACHEIR_B200_F16: all_reduce_kernel<__half><<<grid, 256, 0, st>>>(p); break;
     default: all_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p); break;
+  }
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_peer_all_reduce_two_step(void* const* data, void* const* gather, void* const* flags, void* out,
+                                                     size_t count, int dtype, int rank, int world, int* state, void* stream) {
+  if (count == 0) return 0;
+  PeerParams p{};
+  const int rc = fill(p, data, flags, out, rank, world, state);
+  if (rc != 0) return rc;
+  if (!gather) return CACHEIR_B200_EINVAL;
+  for (int r = 0; r < world; ++r) {
+    if (!gather[r] || !aligned_to(gather[r], 16)) return CACHEIR_B200_EINVAL;
+    p.gather[r] = gather[r];
+  }
+  const int esize = dtype_size(dtype);
+  if (esize == 0) return CACHEIR_B200_EINVAL;
+  if ((count * esize) % (16 * static_cast<size_t>(world)) != 0) return CACHEIR_B200_EALIGN;
+  p.count = count;
+  const size_t per = count * esize / 16 / world;
+  const unsigned grid = static_cast<unsigned>(per / 256 < 1 ? 1 : (per / 256 > kNumSMs ? kNumSMs : per / 256));
+  cudaStream_t st = as_stream(stream);
+  switch (dtype) {
+    case CACHEIR_B200_F32: all_reduce_two_step_kernel<float><<<grid, 256, 0, st>>>(p); break;
+    case CACHEIR_B200_F16: all_reduce_two_step_kernel<__half><<<grid, 256, 0, st>>>(p); break;
+    default: all_reduce_two_step_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p); break;
   }
   return launch_status();
 }

@@ -125,10 +125,12 @@ class _RawCudaBuffer:
 class PeerCollectives:
     """The library's own all-reduce / all-gather over NVLink peer memory (include/cacheir_b200.h,
     `cacheir_b200_peer_*`): three data buffers per rank (A and B alternate between consecutive
-    all-reduces, C carries the logits slice), one flag array, all mapped into every peer through
-    CUDA IPC. Unlike a library collective these are plain kernels of this package, so a whole
+    all-reduces, C carries the logits slice), one flag array and the gather buffer of the two-step
+    all-reduce (messages of `two_step_bytes` and more), all mapped into every peer through CUDA IPC. Unlike a library collective these are plain kernels of this package, so a whole
     tensor-parallel step can be captured into one CUDA graph. All ranks must construct it, and
     issue its calls, in the same order."""
+
+    two_step_bytes = 256 * 1024
 
     def __init__(self, tp: TensorParallel, device: torch.device, data_bytes: int):
         import ctypes
@@ -147,7 +149,7 @@ class PeerCollectives:
         self._opened: list[int] = []
         handles: list[bytes] = []
         with torch.cuda.device(device):
-            for nbytes in (self.data_bytes, self.data_bytes, self.data_bytes, 256):      # A, B, C, flags
+            for nbytes in (self.data_bytes, self.data_bytes, self.data_bytes, 256, self.data_bytes):   # A, B, C, flags, gather
                 ptr = ctypes.c_void_p()
                 handle = (ctypes.c_ubyte * 64)()
                 check(self._lib.cacheir_b200_peer_alloc(nbytes, ctypes.byref(ptr), handle), "peer_alloc")
@@ -156,9 +158,9 @@ class PeerCollectives:
             everyone: list[Any] = [None] * tp.world
             dist.all_gather_object(everyone, handles, group=tp.group)
             # pointer tables [buffer][rank]
-            self._ptrs: list[list[int]] = [[0] * tp.world for _ in range(4)]
+            self._ptrs: list[list[int]] = [[0] * tp.world for _ in range(5)]
             for r in range(tp.world):
-                for b in range(4):
+                for b in range(5):
                     if r == tp.rank:
                         self._ptrs[b][r] = self._local[b]
                     else:
@@ -167,8 +169,8 @@ class PeerCollectives:
                         check(self._lib.cacheir_b200_peer_open(blob, ctypes.byref(ptr)), "peer_open")
                         self._ptrs[b][r] = int(ptr.value)
                         self._opened.append(int(ptr.value))
-            self._tables = [(ctypes.c_void_p * tp.world)(*self._ptrs[b]) for b in range(4)]
-            self.state = torch.zeros((2,), device=device, dtype=torch.int32)
+            self._tables = [(ctypes.c_void_p * tp.world)(*self._ptrs[b]) for b in range(5)]
+            self.state = torch.zeros((4,), device=device, dtype=torch.int32)
             self._views = [torch.as_tensor(_RawCudaBuffer(self._local[b], self.data_bytes), device=device) for b in range(3)]
         dist.barrier(group=tp.group)
 
@@ -184,6 +186,13 @@ class PeerCollectives:
         from . import ops
         from ._lib import check
 
+        nbytes = out.numel() * out.element_size()
+        if nbytes >= self.two_step_bytes and nbytes % (16 * self.tp.world) == 0:
+            check(self._lib.cacheir_b200_peer_all_reduce_two_step(self._tables[index], self._tables[4], self._tables[3],
+                                                                  out.data_ptr(), out.numel(), ops.dtype_code(out.dtype),
+                                                                  self.tp.rank, self.tp.world, self.state.data_ptr(),
+                                                                  ops._stream()), "peer_all_reduce_two_step")
+            return
         check(self._lib.cacheir_b200_peer_all_reduce(self._tables[index], self._tables[3], out.data_ptr(), out.numel(),
                                                      ops.dtype_code(out.dtype), self.tp.rank, self.tp.world,
                                                      self.state.data_ptr(), ops._stream()), "peer_all_reduce")

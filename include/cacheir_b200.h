@@ -245,7 +245,7 @@ int cacheir_b200_pack_unrelayout(const uint8_t* tiled, uint8_t* packed, int N, i
  * peer_alloc: device memory (zero-filled) that other processes can map; `handle64` receives
  * the 64-byte CUDA IPC handle to send them. peer_open maps a peer's allocation from its
  * handle; peer_close / peer_free undo the two. Each rank needs data buffers and one flag
- * array of 8 ints, all from peer_alloc, and a local `state` of 2 zero ints.
+ * array of 16 ints, all from peer_alloc, and a local `state` of 4 zero ints.
  *
  * peer_all_reduce: out[i] = sum over ranks r = 0..world-1 (in that order, fp32 accumulation,
  * so every rank gets the same bits) of data[r][i]. peer_all_gather: out[rows, world*cols]
@@ -255,13 +255,23 @@ int cacheir_b200_pack_unrelayout(const uint8_t* tiled, uint8_t* packed, int N, i
  * recorded in cacheir_b200_device_status and the output is then undefined) and reads the
  * peers' buffers with plain loads. All ranks must issue the same sequence of calls, and a
  * data buffer may be refilled only after a later call that used a different buffer (alternate
- * between two). Safe to capture in a CUDA graph: the call counter lives in `state`. */
+ * between two). Safe to capture in a CUDA graph: the call counter lives in `state`.
+ *
+ * peer_all_reduce_two_step: the same result for large messages (count * element size a
+ * multiple of 16 * world) in two steps inside one launch: rank r adds slice r of every
+ * rank's buffer and pushes it into every rank's `gather` buffer (another peer_alloc buffer of
+ * the message size, `gather[r]` = rank r's), then every rank copies its gather buffer to
+ * `out`. Each rank moves 2 (world-1)/world of the message over NVLink instead of world-1
+ * messages. The kernel must own the GPU while it runs (its CTAs wait for one another). */
 int cacheir_b200_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
 int cacheir_b200_peer_open(const unsigned char* handle64, void** ptr);
 int cacheir_b200_peer_close(void* ptr);
 int cacheir_b200_peer_free(void* ptr);
 int cacheir_b200_peer_all_reduce(void* const* data, void* const* flags, void* out, size_t count,
                                  int dtype, int rank, int world, int* state, void* stream);
+int cacheir_b200_peer_all_reduce_two_step(void* const* data, void* const* gather, void* const* flags,
+                                          void* out, size_t count, int dtype, int rank, int world,
+                                          int* state, void* stream);
 int cacheir_b200_peer_all_gather(void* const* data, void* const* flags, void* out, int rows,
                                  size_t cols, int dtype, int rank, int world, int* state,
                                  void* stream);

@@ -129,37 +129,41 @@ def _peer_collectives_check(rank: int, world: int) -> dict:
     from cacheir_b200.tensor_parallel import PeerCollectives
 
     dev = torch.device("cuda", rank)
-    peer = PeerCollectives(TensorParallel(rank, world), dev, 64 * 1024)
-    rows, cols = 8, 512
+    peer = PeerCollectives(TensorParallel(rank, world), dev, 512 * 1024)
     gens = [torch.Generator(device="cpu") for _ in range(world)]
     report = {"reduce_ok": True, "gather_ok": True, "graph_ok": True}
-    out = torch.empty((rows, cols), device=dev, dtype=torch.float16)
-    wide = torch.empty((rows, cols * world), device=dev, dtype=torch.float16)
-    for call in range(6):                                   # every rank can regenerate every rank's data
-        parts = []
-        for r in range(world):
-            gens[r].manual_seed(1000 * call + r)
-            parts.append(torch.randn((rows, cols), generator=gens[r]).half())
-        which = call % 2
-        peer.buffer(which, rows, cols, torch.float16).copy_(parts[rank].to(dev))
-        peer.all_reduce(which, out)
-        want = sum(p.float() for p in parts).half()          # rank order, fp32 accumulation, one rounding
-        report["reduce_ok"] &= bool(torch.equal(out.cpu(), want))
-    peer.buffer(2, rows, cols, torch.float16).copy_(parts[rank].to(dev))
-    peer.all_gather_columns(2, wide)
-    report["gather_ok"] = bool(torch.equal(wide.cpu(), torch.cat(parts, dim=1)))
-    # captured: the producer copy and the collective replay together; the call counter lives on the device
-    src = parts[rank].to(dev)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        for which in (0, 1):
-            peer.buffer(which, rows, cols, torch.float16).copy_(src)
+    # a small message (one step: every rank reads every buffer) and one past the two-step threshold
+    # (reduce-scatter + all-gather inside one launch)
+    for rows, cols in ((8, 512), (128, 2048)):
+        assert (rows * cols * 2 >= PeerCollectives.two_step_bytes) == (rows == 128)
+        out = torch.empty((rows, cols), device=dev, dtype=torch.float16)
+        for call in range(6):                                   # every rank can regenerate every rank's data
+            parts = []
+            for r in range(world):
+                gens[r].manual_seed(1000 * call + r + rows)
+                parts.append(torch.randn((rows, cols), generator=gens[r]).half())
+            which = call % 2
+            peer.buffer(which, rows, cols, torch.float16).copy_(parts[rank].to(dev))
             peer.all_reduce(which, out)
-    for _ in range(3):
-        graph.replay()
-    torch.cuda.synchronize()
-    report["graph_ok"] = bool(torch.equal(out.cpu(), want))
+            want = sum(p.float() for p in parts).half()          # rank order, fp32 accumulation, one rounding
+            report["reduce_ok"] &= bool(torch.equal(out.cpu(), want))
+        if rows == 8:
+            wide = torch.empty((rows, cols * world), device=dev, dtype=torch.float16)
+            peer.buffer(2, rows, cols, torch.float16).copy_(parts[rank].to(dev))
+            peer.all_gather_columns(2, wide)
+            report["gather_ok"] = bool(torch.equal(wide.cpu(), torch.cat(parts, dim=1)))
+        # captured: the producer copy and the collective replay together; the call counter lives on the device
+        src = parts[rank].to(dev)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for which in (0, 1):
+                peer.buffer(which, rows, cols, torch.float16).copy_(src)
+                peer.all_reduce(which, out)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        report["graph_ok"] &= bool(torch.equal(out.cpu(), want))
     from cacheir_b200 import _lib
     report["status"] = int(_lib.load().cacheir_b200_device_status(1))
     dist.barrier()
