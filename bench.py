@@ -693,6 +693,25 @@ def main() -> None:
         gbs = k["bytes"] / k["seconds"] / 1e9
         kernels.append({"kernel": k["kernel"], "us": round(k["seconds"] * 1e6, 2), "algorithmic_bytes": int(k["bytes"]),
                         "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4), **({"shape": k["shape"]} if "shape" in k else {})})
+    if tp and rt._engine.peer_mode:
+        # the all-reduce that follows the o- and down-projection: [batch, hidden] over all ranks (every rank runs the
+        # same sequence of calls; NVLink bytes per rank: what it reads from and pushes to its peers)
+        peer = rt._engine.peer_collectives(cfg["batch"])
+        ar_out = torch.empty((cfg["batch"], cfg["hidden"]), device=rt.device, dtype=torch.float16)
+        calls = [0]
+
+        def one_all_reduce() -> None:
+            peer.all_reduce(calls[0] % 2, ar_out)
+            calls[0] += 1
+
+        dist.barrier()
+        ar_s = max_over_ranks(time_graph(one_all_reduce, 16), torch.device("cuda", local_rank))
+        msg = ar_out.numel() * 2
+        two_step = world >= peer.two_step_ranks and msg >= peer.two_step_bytes
+        link = msg * (2 * (world - 1) / world if two_step else (world - 1))
+        kernels.append({"kernel": "peer_all_reduce" + ("_two_step" if two_step else ""), "us": round(ar_s * 1e6, 2),
+                        "algorithmic_bytes": int(link), "achieved_gbs": round(link / ar_s / 1e9, 1), "bound": "nvlink",
+                        "shape": [cfg["batch"], cfg["hidden"]]})
     sb = step_bytes(cfg, kv_tokens_mid)
     shards = world if tp else 1                              # tensor parallel: each rank streams its share of the step
     step_gbs = sb["total"] / shards / (elapsed_s / args.steps) / 1e9

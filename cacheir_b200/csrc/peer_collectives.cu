@@ -86,6 +86,25 @@ __device__ __forceinline__ void finish(const PeerParams& p, int epoch) {
   }
 }
 
+// acc = sum over ranks (in rank order) of 16-byte vector `i` of their data buffers. All loads are issued
+// before the first add: a load from a peer takes microseconds, eight in a row would take eight times that.
+template <typename T>
+__device__ __forceinline__ void gather_sum(const PeerParams& p, size_t i, float (&acc)[16 / sizeof(T)]) {
+  constexpr int VEC = 16 / sizeof(T);
+  float v[kMaxRanks][VEC];
+#pragma unroll
+  for (int r = 0; r < kMaxRanks; ++r)
+    if (r < p.world) VecIO<T, VEC>::ld(static_cast<const T*>(p.data[r]) + i * VEC, v[r]);
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+#pragma unroll
+  for (int r = 0; r < kMaxRanks; ++r)
+    if (r < p.world) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[j] += v[r][j];
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) all_reduce_kernel(const PeerParams p) {
   const int epoch = p.state[0] + 1;
@@ -95,14 +114,7 @@ __global__ void __launch_bounds__(256) all_reduce_kernel(const PeerParams p) {
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
       float acc[VEC];
-#pragma unroll
-      for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
-      for (int r = 0; r < p.world; ++r) {        // rank order: the same sum, bit for bit, on every rank
-        float v[VEC];
-        VecIO<T, VEC>::ld(static_cast<const T*>(p.data[r]) + i * VEC, v);
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) acc[j] += v[j];
-      }
+      gather_sum<T>(p, i, acc);                  // rank order: the same sum, bit for bit, on every rank
       VecIO<T, VEC>::st(static_cast<T*>(p.out) + i * VEC, acc);
     }
   }
@@ -125,25 +137,22 @@ __global__ void __launch_bounds__(256) all_reduce_two_step_kernel(const PeerPara
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < per;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
       float acc[VEC];
-#pragma unroll
-      for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
-      for (int r = 0; r < p.world; ++r) {        // rank order
-        float v[VEC];
-        VecIO<T, VEC>::ld(static_cast<const T*>(p.data[r]) + (base + i) * VEC, v);
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) acc[j] += v[j];
-      }
+      gather_sum<T>(p, base + i, acc);           // rank order
       for (int r = 0; r < p.world; ++r) VecIO<T, VEC>::st(static_cast<T*>(p.gather[r]) + (base + i) * VEC, acc);
     }
     __threadfence_system();                      // this thread's pushes are visible everywhere before the flag goes up
   }
+  __shared__ int s_last;
   if (threadIdx.x == 0) s_ok2 = 1;
   __syncthreads();
-  if (threadIdx.x == 0 && atomicAdd(p.state + 2, 1) == static_cast<int>(gridDim.x) - 1) {
-    p.state[2] = 0;                              // last CTA of this rank: the whole slice has been pushed
-    __threadfence_system();
-    if (ok)
-      for (int r = 0; r < p.world; ++r) st_release_sys(p.flags[r] + kMaxRanks + p.rank, epoch);
+  if (threadIdx.x == 0) s_last = atomicAdd(p.state + 2, 1) == static_cast<int>(gridDim.x) - 1 ? 1 : 0;
+  __syncthreads();
+  if (s_last != 0) {                             // last CTA of this rank: the whole slice has been pushed
+    if (threadIdx.x == 0) p.state[2] = 0;
+    if (ok && threadIdx.x < p.world) {           // one thread per peer: the system-scope releases run side by side
+      __threadfence_system();
+      st_release_sys(p.flags[threadIdx.x] + kMaxRanks + p.rank, epoch);
+    }
   }
   if (ok && threadIdx.x < p.world) {
     const int* slot = p.flags[p.rank] + kMaxRanks + threadIdx.x;

@@ -126,11 +126,12 @@ class PeerCollectives:
     """The library's own all-reduce / all-gather over NVLink peer memory (include/cacheir_b200.h,
     `cacheir_b200_peer_*`): three data buffers per rank (A and B alternate between consecutive
     all-reduces, C carries the logits slice), one flag array and the gather buffer of the two-step
-    all-reduce (messages of `two_step_bytes` and more), all mapped into every peer through CUDA IPC. Unlike a library collective these are plain kernels of this package, so a whole
+    all-reduce (messages of `two_step_bytes` and more on `two_step_ranks` ranks and more), all mapped into every peer through CUDA IPC. Unlike a library collective these are plain kernels of this package, so a whole
     tensor-parallel step can be captured into one CUDA graph. All ranks must construct it, and
     issue its calls, in the same order."""
 
-    two_step_bytes = 256 * 1024
+    two_step_bytes = 256 * 1024       # the two-step all-reduce pays a second round of flags: worth it only when
+    two_step_ranks = 4                # it saves much NVLink traffic, (world-1) against 2 (world-1)/world messages
 
     def __init__(self, tp: TensorParallel, device: torch.device, data_bytes: int):
         import ctypes
@@ -187,7 +188,7 @@ class PeerCollectives:
         from ._lib import check
 
         nbytes = out.numel() * out.element_size()
-        if nbytes >= self.two_step_bytes and nbytes % (16 * self.tp.world) == 0:
+        if self.tp.world >= self.two_step_ranks and nbytes >= self.two_step_bytes and nbytes % (16 * self.tp.world) == 0:
             check(self._lib.cacheir_b200_peer_all_reduce_two_step(self._tables[index], self._tables[4], self._tables[3],
                                                                   out.data_ptr(), out.numel(), ops.dtype_code(out.dtype),
                                                                   self.tp.rank, self.tp.world, self.state.data_ptr(),

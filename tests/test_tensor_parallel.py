@@ -130,6 +130,7 @@ def _peer_collectives_check(rank: int, world: int) -> dict:
 
     dev = torch.device("cuda", rank)
     peer = PeerCollectives(TensorParallel(rank, world), dev, 512 * 1024)
+    peer.two_step_ranks = 2                                  # exercise the two-step kernel on two ranks as well
     gens = [torch.Generator(device="cpu") for _ in range(world)]
     report = {"reduce_ok": True, "gather_ok": True, "graph_ok": True}
     # a small message (one step: every rank reads every buffer) and one past the two-step threshold
