@@ -170,9 +170,13 @@ __global__ void __launch_bounds__(256) all_reduce_two_step_kernel(const PeerPara
   if (ok && s_ok2 != 0) {
     const uint4* src = static_cast<const uint4*>(p.gather[p.rank]);
     uint4* dst = static_cast<uint4*>(p.out);
-    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x)
-      dst[i] = __ldcg(src + i);                  // written by the peers: read past this SM's L1
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {   // four loads in flight per thread; written by the peers: read past this SM's L1
+      const uint4 a = __ldcg(src + i), b = __ldcg(src + i + stride), c = __ldcg(src + i + 2 * stride), d = __ldcg(src + i + 3 * stride);
+      dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+    }
+    for (; i < nvec; i += stride) dst[i] = __ldcg(src + i);
   }
   finish(p, epoch);
 }
@@ -276,8 +280,8 @@ extern "C" int cacheir_b200_peer_all_reduce_two_step(void* const* data, void* co
   if (esize == 0) return CACHEIR_B200_EINVAL;
   if ((count * esize) % (16 * static_cast<size_t>(world)) != 0) return CACHEIR_B200_EALIGN;
   p.count = count;
-  const size_t per = count * esize / 16 / world;
-  const unsigned grid = static_cast<unsigned>(per / 256 < 1 ? 1 : (per / 256 > kNumSMs ? kNumSMs : per / 256));
+  const size_t nvec = count * esize / 16;          // the copy to `out` covers the whole message: size the grid for it
+  const unsigned grid = static_cast<unsigned>(nvec / 1024 < 1 ? 1 : (nvec / 1024 > kNumSMs ? kNumSMs : nvec / 1024));
   cudaStream_t st = as_stream(stream);
   switch (dtype) {
     case CACHEIR_B200_F32: all_reduce_two_step_kernel<float><<<grid, 256, 0, st>>>(p); break;
