@@ -166,8 +166,9 @@ int cacheir_b200_qgemv(const void* x, const void* packed, const void* scales,
  * tensor cores: the uint8 codes are fed to the MMA as they are (int4 nibbles are widened to
  * bytes in shared memory), and x is first turned into 16-bit fixed point per row (two
  * signed bytes, 2^-15 of the row maximum) in the workspace. Batches above 64 rows run as
- * 64-row chunks. Other shapes ignore the workspace. workspace may be NULL (then this is
- * cacheir_b200_qgemv). The workspace is only used during the call's own kernels; two
+ * 64-row chunks (128-row chunks on the fp16 tensor-core kernel, which takes 65..128 rows in
+ * one launch with the activations as the 128-row operand). Other shapes ignore the
+ * workspace. workspace may be NULL (then this is cacheir_b200_qgemv). The workspace is only used during the call's own kernels; two
  * calls that may overlap on the GPU need separate workspaces. */
 size_t cacheir_b200_qgemv_workspace_bytes(int M, int K);
 int cacheir_b200_qgemv_ex(const void* x, const void* packed, const void* scales,
