@@ -232,7 +232,9 @@ __device__ __forceinline__ void unpack8_slow(const uint8_t* bytes, int first, fl
   }
 }
 
-template <int BITS, int MP>
+// GROUPED: group-wise scales (no zero-point array, codes centred on 2^(BITS-1)): the conversion loop then has
+// neither the per-row "exact offset or not" branch nor the "scaled or not" select.
+template <int BITS, int MP, bool GROUPED>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
   constexpr int kStages = num_stages(BITS, MP);
@@ -366,23 +368,26 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const bool row_valid = n < (swiglu ? (pass + 1) * (p.N / 2) : p.N);
       float zero = static_cast<float>(1 << (BITS - 1));
       float scale = 1.f;
-      if (row_valid && p.group_size == 0) {
+      if (!GROUPED && row_valid) {
         scale = load_scale(p.scales, p.scale_dtype, n);
         if (p.zero_points) zero = p.zero_points[n];
       }
       // exact in-register zero-point removal needs an integer zero point that fp16 can offset exactly
-      const bool fast = (zero == rintf(zero)) && fabsf(zero) <= 960.f;
-      row_scale[pass] = (p.group_size == 0 && fast) ? scale : 1.f;
+      const bool fast = GROUPED || ((zero == rintf(zero)) && fabsf(zero) <= 960.f);
+      row_scale[pass] = (!GROUPED && fast) ? scale : 1.f;
       if (kWide && hsel == 0) s_rowscale[pass * kBlockN + r] = row_scale[pass];
       const __half2 sub8 = __float2half2_rn(1024.f + zero);
       const __half2 mul4 = __floats2half2_rn(1.f, 0.0625f);
       const __half2 sub4 = __floats2half2_rn(-(1024.f + zero), -(64.f + zero));
-      const bool scaled = p.group_size > 0;
+      constexpr bool scaled = GROUPED;
       // group scales are fetched one k block ahead: the load must not sit between the barrier and the unpacking
       const int groups_per_row = scaled ? p.K / p.group_size : 1;
+      const size_t scale_row = static_cast<size_t>(n) * groups_per_row;
+      const int kb_per_group = scaled ? p.group_size / kBlockK : 1;       // the group size is a multiple of the k block
       auto group_scale = [&](int kbi) {
+        const int kb = kb_begin + kbi;
         return (scaled && row_valid && kbi < kblocks)
-                   ? load_scale(p.scales, p.scale_dtype, static_cast<size_t>(n) * groups_per_row + ((kb_begin + kbi) * kBlockK) / p.group_size)
+                   ? load_scale(p.scales, p.scale_dtype, scale_row + (kb_per_group == 1 ? kb : kb / kb_per_group))
                    : 1.f;
       };
       float next_scale = group_scale(0);
@@ -735,7 +740,7 @@ int choose_split_k(int n_tiles, int kblocks, int epilogue) {
   return s < 1 ? 1 : s;
 }
 
-template <int BITS, int MP>
+template <int BITS, int MP, bool GROUPED>
 int launch_tc(const QGemvParams& q, cudaStream_t stream) {
   constexpr int kStages = num_stages(BITS, MP);
   constexpr size_t kSmem = 1024 + static_cast<size_t>(kStages) * stage_bytes(BITS, MP) + kAStages * kABytes + 512 + 1024;
@@ -777,7 +782,7 @@ int launch_tc(const QGemvParams& q, cudaStream_t stream) {
     while (s * 2 <= want && s * 2 <= cap) s *= 2;
     p.split_k = s;
   }
-  auto kern = qgemm_tc_kernel<BITS, MP>;
+  auto kern = qgemm_tc_kernel<BITS, MP, GROUPED>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
   if (e != cudaSuccess) return static_cast<int>(e);
   cudaLaunchConfig_t cfg{};
@@ -797,12 +802,12 @@ int launch_tc(const QGemvParams& q, cudaStream_t stream) {
   return launch_status();
 }
 
-template <int BITS>
+template <int BITS, bool GROUPED>
 int launch_tc_mp(const QGemvParams& q, cudaStream_t stream) {
-  if (q.M <= 16) return launch_tc<BITS, 16>(q, stream);
-  if (q.M <= 32) return launch_tc<BITS, 32>(q, stream);
-  if (q.M <= 64) return launch_tc<BITS, 64>(q, stream);
-  return launch_tc<BITS, 128>(q, stream);
+  if (q.M <= 16) return launch_tc<BITS, 16, GROUPED>(q, stream);
+  if (q.M <= 32) return launch_tc<BITS, 32, GROUPED>(q, stream);
+  if (q.M <= 64) return launch_tc<BITS, 64, GROUPED>(q, stream);
+  return launch_tc<BITS, 128, GROUPED>(q, stream);
 }
 
 }  // namespace
@@ -819,7 +824,8 @@ bool qgemm_tc_supported(const QGemvParams& q) {
 }
 
 int launch_qgemm_tc(const QGemvParams& q, cudaStream_t stream) {
-  return q.bits == 8 ? launch_tc_mp<8>(q, stream) : launch_tc_mp<4>(q, stream);
+  if (q.group_size > 0) return q.bits == 8 ? launch_tc_mp<8, true>(q, stream) : launch_tc_mp<4, true>(q, stream);
+  return q.bits == 8 ? launch_tc_mp<8, false>(q, stream) : launch_tc_mp<4, false>(q, stream);
 }
 
 #ifdef CB200_QGEMM_TRACE
