@@ -42,20 +42,24 @@ namespace {
 
 constexpr int kBlockN = 128;      // weight rows per CTA (UMMA M)
 constexpr int kBlockK = 128;      // k elements per pipeline stage
-constexpr int kAStages = 2;       // converted fp16 operand tiles in shared memory
+// converted fp16 operand tiles in shared memory: three decouple the converters from the MMAs (two where the
+// 128-row int8 stages leave no room for a third)
+__host__ __device__ constexpr int a_stages(int bits, int mp) { return (bits == 8 && mp == 128) ? 2 : 3; }
 constexpr int kABytes = kBlockN * kBlockK * 2;          // 32 KB: two 64-element halves of [128 rows x 128 B], 128-byte swizzled
 constexpr int kAColBase = 256;                          // accumulators use tensor-memory columns [0, 256)
 constexpr int kTmemCols = 256;
 constexpr int kConvThreads = 512;                       // warps 4..19: the unpacking is latency-bound, more warps hide it
 constexpr int kThreads = 128 + kConvThreads;
 constexpr int kMaxSplitK = 4;
-constexpr int kRingBudget = 152 * 1024;                 // shared memory for the raw/x ring (the fp16 operand ring takes 64 KB more)
+constexpr int kSmemBudget = 216 * 1024;                 // raw/x ring + fp16 operand tiles
 
 __host__ __device__ constexpr int stage_bytes(int bits, int mp) {
   return (bits == 8 ? kBlockN * 128 : kBlockN * 64) + mp * kBlockK * 2;
 }
 __host__ __device__ constexpr int num_stages(int bits, int mp) {
-  return kRingBudget / stage_bytes(bits, mp) > 8 ? 8 : kRingBudget / stage_bytes(bits, mp);
+  return (kSmemBudget - a_stages(bits, mp) * kABytes) / stage_bytes(bits, mp) > 8
+             ? 8
+             : (kSmemBudget - a_stages(bits, mp) * kABytes) / stage_bytes(bits, mp);
 }
 constexpr uint32_t kPollLimit = 8u * 1000u * 1000u;
 
@@ -242,6 +246,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   constexpr int kXBytes = MP * kBlockK * 2;
   constexpr int kRawRow = BITS == 8 ? 128 : 64;                          // bytes of one row per stage
   constexpr int kChunksPerThread = kRawRow / 16 / 4;                     // 16-byte chunks per converter thread (a quarter row)
+  constexpr int kAStages = a_stages(BITS, MP);
   constexpr bool kWide = MP == 128;                                      // activations are the 128-row operand
 
   extern __shared__ uint8_t smem_raw[];
@@ -743,6 +748,7 @@ int choose_split_k(int n_tiles, int kblocks, int epilogue) {
 template <int BITS, int MP, bool GROUPED>
 int launch_tc(const QGemvParams& q, cudaStream_t stream) {
   constexpr int kStages = num_stages(BITS, MP);
+  constexpr int kAStages = a_stages(BITS, MP);
   constexpr size_t kSmem = 1024 + static_cast<size_t>(kStages) * stage_bytes(BITS, MP) + kAStages * kABytes + 512 + 1024;
   static_assert(kSmem <= 227 * 1024, "ring + operand tiles must fit the shared memory of one SM");
   static_assert(MP == 128 ||
