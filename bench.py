@@ -742,6 +742,7 @@ def main() -> None:
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d // e2e_steps, "d2h_bytes_per_step": d2h // e2e_steps,
                     "steps": e2e_steps, "api": "B200DecodeRuntime.run_decode_batch + argmax_tokens"},
             "gpu_launches": launches_per_step * args.steps,
+            "device_status": int(__import__("cacheir_b200")._lib.load().cacheir_b200_device_status(0)),   # 0: no bounded device wait ever gave up
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": attn["kernel"], "achieved": kernels[0]["achieved_gbs"], "peak": peak,
                          "unit": "GB/s", "frac": kernels[0]["frac"], "traffic": traffic, "peak_source": f"of {peak_kind}",

@@ -41,6 +41,16 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
          c_int, c_int, c_int, c_int, c_int, c_int, c_int,
          c_longlong, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "cacheir_b200_rmsnorm_qgemv": (
+        c_int,
+        [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,   # x norm_w eps packed scales zero residual y
+         c_int, c_int, c_int, c_int, c_int, c_longlong, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "cacheir_b200_qgemv_plan": (c_int, [c_int] * 8),
+    "cacheir_b200_rmsnorm_qkv_rope_append": (
+        c_int,
+        [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_int,
+         c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+         c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "cacheir_b200_qkv_rope_append": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_int,  # x..qkv M N K scale_dtype stride layout

@@ -52,7 +52,6 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     sources = sorted(CSRC.glob("*.cu"))
     headers = sorted(CSRC.glob("*.cuh")) + sorted(INCLUDE.glob("*.h")) + [Path(__file__)]
     extra = ["-Xptxas", "-v"] if verbose else []
-    extra += os.environ.get("CB200_NVCC_FLAGS", "").split()   # e.g. -DCB200_QGEMM_TRACE for the pipeline trace
 
     def compile_one(src: Path) -> Path:
         obj = BUILD_DIR / (src.stem + ".o")

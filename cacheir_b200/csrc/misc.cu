@@ -22,3 +22,4 @@ extern "C" const char* cacheir_b200_error_string(int code) {
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
   return "cacheir_b200: unknown error code";
 }
+

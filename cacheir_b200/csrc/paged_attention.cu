@@ -255,7 +255,8 @@ void resolve_attention_splits(int batch, int heads, int kv_heads, int max_pages,
     // far as needed: chunks of at most 4096 tokens bound the tail of the longest sequence of a
     // ragged batch, and small batches get enough splits to put one CTA on each of the 148 SMs.
     s = static_cast<int>((max_ctx + 4095) / 4096);
-    const long long units = static_cast<long long>(batch) * kv_heads * ((heads / kv_heads + 15) / 16);
+    long long units = static_cast<long long>(batch) * kv_heads * ((heads / kv_heads + 15) / 16);
+    if (units < 1) units = 1;   // fewer query heads than KV heads: rejected by the entry points, but this must not divide by zero
     const long long want = (kNumSMs + units - 1) / units;
     if (s < want) s = static_cast<int>(want);
     const int cap = static_cast<int>((max_ctx + 255) / 256);
@@ -287,7 +288,7 @@ extern "C" int cacheir_b200_paged_attention_auto_splits(int batch_size, int num_
                                                         int page_size, int head_dim) {
   (void)head_dim;
   if (batch_size <= 0 || num_heads <= 0 || num_kv_heads <= 0 || max_pages_per_seq <= 0 ||
-      page_size <= 0)
+      page_size <= 0 || num_heads % num_kv_heads != 0)
     return 1;
   int s = 1, chunk = 0;
   resolve_attention_splits(batch_size, num_heads, num_kv_heads, max_pages_per_seq, page_size, 0, &s,
@@ -361,6 +362,8 @@ namespace {
 constexpr int kMaxDevices = 64;
 // Device address of the array above, looked up once per device. In host code the
 // array's name is only a handle for the runtime, never a pointer a kernel may use.
+// (Host threads may fill a slot concurrently without a lock: every thread that looks the
+// symbol up for a device gets the same address, so a racing store writes the same value.)
 void* g_noalloc_ws_ptr[kMaxDevices] = {};
 }  // namespace
 
@@ -374,7 +377,7 @@ extern "C" int cacheir_b200_paged_attention_decode_batch_noalloc(
     int max_pages_per_seq, int page_size, int head_dim, int dtype, long long q_batch_stride,
     long long out_batch_stride, float softmax_scale, int num_splits, void* stream) {
   if (batch_size <= 0 || num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0) return 0;
-  if (max_pages_per_seq <= 0 || page_size <= 0 || num_splits < 0) return CACHEIR_B200_EINVAL;
+  if (max_pages_per_seq <= 0 || page_size <= 0 || num_splits < 0 || num_heads % num_kv_heads != 0) return CACHEIR_B200_EINVAL;
   int splits = 1, chunk = 0;
   resolve_attention_splits(batch_size, num_heads, num_kv_heads, max_pages_per_seq, page_size, num_splits,
                            &splits, &chunk);

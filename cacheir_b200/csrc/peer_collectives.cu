@@ -17,7 +17,10 @@
 // only after the call that used buffer B, whose wait proves every peer has left buffer A.
 // The epoch lives on the device and advances with every call, so a captured CUDA graph can be
 // replayed. Only plain peer loads and stores, no library collective. A wait that
-// runs out of polls records a code in the status word and the kernel returns (output undefined).
+// runs out of polls (about a second by default; state[3] > 0 sets the number of polls) records a code in the
+// status word and the kernel returns (output undefined). While the status word is non-zero every later
+// collective returns at once without waiting, so a lost peer costs one time-out, not one per call of a replayed
+// graph; the host reads and clears the word with cacheir_b200_device_status.
 #include <string.h>
 
 #include "common.cuh"
@@ -26,7 +29,7 @@ namespace cb200 {
 namespace {
 
 constexpr int kMaxRanks = 8;
-constexpr uint32_t kPeerPollLimit = 30u * 1000u * 1000u;  // with the sleep below: about a minute, then give up
+constexpr uint32_t kPeerPollLimit = 500u * 1000u;  // with the 2 us sleep below: about a second, then give up
 
 __device__ int g_peer_status = 0;
 
@@ -38,7 +41,7 @@ struct PeerParams {
   size_t count;                   // all-reduce: elements; all-gather: elements of one rank's slice row
   int rows;                       // all-gather only: rows of the [rows, count] slices
   int rank, world;
-  int* state;                     // local: {epoch, CTAs finished, CTAs that finished their slice}
+  int* state;                     // local: {epoch, CTAs finished, CTAs that finished their slice, poll limit (0 = default)}
 };
 
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
@@ -51,10 +54,18 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 }
 
 // Steps 1 and 2 for one CTA. Returns false when a peer never showed up.
+__device__ __forceinline__ uint32_t poll_limit(const PeerParams& p) {
+  const int configured = p.state[3];
+  return configured > 0 ? static_cast<uint32_t>(configured) : kPeerPollLimit;
+}
+__device__ __forceinline__ bool peer_already_lost() { return *reinterpret_cast<volatile int*>(&g_peer_status) != 0; }
+
 __device__ __forceinline__ bool announce_and_wait(const PeerParams& p, int epoch) {
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
+  __shared__ int s_ok, s_lost;
+  if (threadIdx.x == 0) { s_ok = 1; s_lost = peer_already_lost() ? 1 : 0; }   // one reader: the whole CTA takes the same branch
   __syncthreads();
+  if (s_lost != 0) return false;                 // an earlier wait gave up and the host has not cleared the word yet
+  const uint32_t limit = poll_limit(p);
   if (blockIdx.x == 0 && threadIdx.x < p.world && threadIdx.x != p.rank) {
     __threadfence_system();
     st_release_sys(p.flags[threadIdx.x] + p.rank, epoch);
@@ -62,7 +73,7 @@ __device__ __forceinline__ bool announce_and_wait(const PeerParams& p, int epoch
   if (threadIdx.x < p.world && threadIdx.x != p.rank) {
     const int* slot = p.flags[p.rank] + threadIdx.x;
     bool seen = false;
-    for (uint32_t i = 0; i < kPeerPollLimit; ++i) {
+    for (uint32_t i = 0; i < limit; ++i) {
       if (ld_acquire_sys(slot) - epoch >= 0) { seen = true; break; }   // (difference: survives wrap-around)
       if (i > 64) __nanosleep(i > 4096 ? 2000 : 100);
     }
@@ -156,8 +167,9 @@ __global__ void __launch_bounds__(256) all_reduce_two_step_kernel(const PeerPara
   }
   if (ok && threadIdx.x < p.world) {
     const int* slot = p.flags[p.rank] + kMaxRanks + threadIdx.x;
+    const uint32_t limit = poll_limit(p);
     bool seen = false;
-    for (uint32_t i = 0; i < kPeerPollLimit; ++i) {
+    for (uint32_t i = 0; i < limit; ++i) {
       if (ld_acquire_sys(slot) - epoch >= 0) { seen = true; break; }
       if (i > 64) __nanosleep(i > 4096 ? 2000 : 100);
     }

@@ -42,20 +42,19 @@ constexpr float kQMax = 32639.f;      // 127*256 + 127: every value splits into 
 
 __device__ int g_i8_status = 0;
 
-#ifdef CB200_QGEMM_TRACE
-__device__ unsigned long long g_i8_cta_trace[2048][4];   // per CTA: global timer at entry, first data, accumulator complete, exit
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
+// Fixed-point conversion of one activation: q = rint(v * inv) in [-32639, 32639], split as q = 256*hi + lo with
+// signed bytes. Adding 1.5*2^23 + 128 inside one fused multiply-add leaves q + 128 in the low 16 bits of the
+// float (one rounding, to nearest even, no conversion instruction): byte 1 is hi, byte 0 ^ 0x80 is lo.
+constexpr float kRoundMagic = 12582912.f + 128.f;
+__device__ __forceinline__ uint32_t fixed_point_bits(float v, float inv) { return __float_as_uint(fmaf(v, inv, kRoundMagic)); }
+// Four converted values -> the word of their high bytes, the word of their low bytes, and their sum.
+__device__ __forceinline__ void split_four(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t* hi, uint32_t* lo, int* sum) {
+  const uint32_t ab = __byte_perm(a, b, 0x5410), cd = __byte_perm(c, d, 0x5410);
+  *hi = __byte_perm(ab, cd, 0x7531);
+  *lo = __byte_perm(ab, cd, 0x6420) ^ 0x80808080u;
+  *sum = __dp4a(static_cast<int>(*lo), 0x01010101, *sum + 256 * __dp4a(static_cast<int>(*hi), 0x01010101, 0));
 }
-#define CB200_CTA_TRACE(slot) do { const int c_ = blockIdx.y * gridDim.x + blockIdx.x; if (c_ < 2048) g_i8_cta_trace[c_][slot] = global_ns(); } while (0)
-__device__ long long g_i8_trace[4][256][4];
-#define CB200_TRACE(role, i, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 256) g_i8_trace[role][i][slot] = clock64(); } while (0)
-#else
-#define CB200_TRACE(role, i, slot) do { } while (0)
-#define CB200_CTA_TRACE(slot) do { } while (0)
-#endif
+
 
 // (int4 weights add the raw 8 KB nibble tile in front of the 16 KB byte tile it is unpacked into)
 __host__ __device__ constexpr int stage_bytes(int mp, int bits = 8) {
@@ -113,17 +112,11 @@ quantize_rows_kernel(const __half* __restrict__ x, long long x_stride, int M, in
   for (int c = threadIdx.x; c < nvec; c += 256) {
     float v[8];
     VecIO<__half, 8>::ld(xr + c * 8, v);
-    uint32_t hi_w[2] = {0u, 0u}, lo_w[2] = {0u, 0u};
+    uint32_t hi_w[2], lo_w[2];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      int q = __float2int_rn(v[i] * inv);
-      q = max(-32639, min(32639, q));
-      const int hi = (q + 128) >> 8;            // arithmetic shift: floor((q+128)/256)
-      const int lo = q - (hi << 8);             // in [-128, 127]
-      sum += q;
-      hi_w[i >> 2] |= static_cast<uint32_t>(hi & 0xFF) << (8 * (i & 3));
-      lo_w[i >> 2] |= static_cast<uint32_t>(lo & 0xFF) << (8 * (i & 3));
-    }
+    for (int i = 0; i < 2; ++i)
+      split_four(fixed_point_bits(v[4 * i], inv), fixed_point_bits(v[4 * i + 1], inv), fixed_point_bits(v[4 * i + 2], inv),
+                 fixed_point_bits(v[4 * i + 3], inv), &hi_w[i], &lo_w[i], &sum);
     *reinterpret_cast<uint2*>(planes + plane_offset(mp, m, c * 8)) = make_uint2(hi_w[0], hi_w[1]);
     *reinterpret_cast<uint2*>(planes + plane_offset(mp, mp + m, c * 8)) = make_uint2(lo_w[0], lo_w[1]);
   }
@@ -177,17 +170,11 @@ __device__ __forceinline__ void quantize_row_from_registers(const float (&vals)[
   for (int i = 0; i < PT; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
     if (c < nvec) {
-      uint32_t hi_w[2] = {0u, 0u}, lo_w[2] = {0u, 0u};
+      uint32_t hi_w[2], lo_w[2];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        int q = __float2int_rn(vals[i][j] * inv);
-        q = max(-32639, min(32639, q));
-        const int hi = (q + 128) >> 8;
-        const int lo = q - (hi << 8);
-        sum += q;
-        hi_w[j >> 2] |= static_cast<uint32_t>(hi & 0xFF) << (8 * (j & 3));
-        lo_w[j >> 2] |= static_cast<uint32_t>(lo & 0xFF) << (8 * (j & 3));
-      }
+      for (int j = 0; j < 2; ++j)
+        split_four(fixed_point_bits(vals[i][4 * j], inv), fixed_point_bits(vals[i][4 * j + 1], inv),
+                   fixed_point_bits(vals[i][4 * j + 2], inv), fixed_point_bits(vals[i][4 * j + 3], inv), &hi_w[j], &lo_w[j], &sum);
       *reinterpret_cast<uint2*>(planes + plane_offset(mp, m, c * 8)) = make_uint2(hi_w[0], hi_w[1]);
       *reinterpret_cast<uint2*>(planes + plane_offset(mp, mp + m, c * 8)) = make_uint2(lo_w[0], lo_w[1]);
     }
@@ -301,6 +288,7 @@ struct I8Params {
   const int* qsum;
   const uint8_t* w_tiled;     // tile-ordered codes (tiled != 0)
   const int8_t* x_planes;     // activation byte tiles written by the pre-pass
+  int n_tiles;                // row tiles (128 output columns, or 64 gate|up pairs)
   int M, N, K;
   int n_out;
   int scale_dtype;
@@ -335,6 +323,8 @@ __device__ __forceinline__ float recombine(int32_t hi, int32_t lo, float zero, i
   return recombine_fractional(hi, lo, zero, qsum);
 }
 
+constexpr int kTailBytes = 1024;   // scratch behind the ring and the exchange buffer: barriers, TMEM base, per-row constants
+
 template <int MP, int SPLIT, bool ROPE, int BITS>
 __global__ void __launch_bounds__(kThreads, 2)
 qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
@@ -350,6 +340,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
   constexpr int MS = MP / SPLIT;
   constexpr int W = 2 * MS;
   constexpr int kSlotBytes = kBlockN * W * 4;         // what one rank sends to one other rank
+  constexpr bool kReadyBar = BITS == 4;               // a stage passes through the epilogue warps before the tensor core reads it
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -357,29 +348,28 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
   uint8_t* s_x = s_w + kStages * kWBytes;
   uint8_t* s_raw = s_x + kStages * kXBytes;              // int4 only
   int32_t* s_xch = reinterpret_cast<int32_t*>(s_raw + kStages * kRawBytes);   // [SPLIT senders][128 rows][W], written by the peers
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_xch) + exchange_bytes(MP, SPLIT));
+  uint8_t* tail = reinterpret_cast<uint8_t*>(s_xch) + exchange_bytes(MP, SPLIT);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
   uint64_t* full = bars;                  // [kStages] TMA landed
   uint64_t* empty = bars + kStages;       // [kStages] MMAs that read the stage have retired
   uint64_t* acc_full = empty + kStages;   // [1]
   uint64_t* xch_bar = acc_full + 1;       // [1] all partials of the other ranks have landed
-  uint64_t* unpacked = xch_bar + 1;       // [kStages] int4: the byte tile of the stage is complete (128 unpacking threads)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(unpacked + kStages);
-  float* s_sx = reinterpret_cast<float*>(tmem_slot + 2);     // [MP]
-  int* s_qsum = reinterpret_cast<int*>(s_sx + MP);           // [MP]
+  uint64_t* ready = xch_bar + 1;          // [kStages] the operand tiles of the stage are complete (epilogue warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ready + kStages);
+  float* s_sx = reinterpret_cast<float*>(tmem_slot + 2);     // [MP] fixed-point step of each batch row
+  int* s_qsum = reinterpret_cast<int*>(s_sx + MP);           // [MP] sum over k of the row's integers
   int32_t* s_stage = reinterpret_cast<int32_t*>(smem);       // outgoing partials [SPLIT dests][128 rows][W] reuse the drained ring
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (threadIdx.x == 64) CB200_TRACE(3, 0, 0);
-  if (threadIdx.x == 64) CB200_CTA_TRACE(0);
   const bool swiglu = p.epilogue == CACHEIR_B200_EPI_SWIGLU;
   constexpr int split = SPLIT;
+  constexpr bool clustered = SPLIT > 1;
   const int krank = split > 1 ? static_cast<int>(cluster_ctarank()) : 0;
   const int kblocks_all = p.K / kBlockK;
   const int kb_begin = (kblocks_all * krank) / split;
   const int kb_end = (kblocks_all * (krank + 1)) / split;
-  const int kblocks = kb_end - kb_begin;
-  const int total = kblocks;
+  const int total = kb_end - kb_begin;
   const int n0 = blockIdx.x * (swiglu ? kPairRows : kBlockN);   // first output column of this tile
 
   auto load_stage = [&](int i, int s) {
@@ -407,38 +397,33 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
       for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
       mbar_init(smem_u32(acc_full), 1);
       mbar_init(smem_u32(xch_bar), 1);
-      if (BITS == 4)
-        for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&unpacked[s]), 128);
+      if (kReadyBar)
+        for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&ready[s]), 128);
       mbar_fence_init();                       // visible to the copy engine and to the other CTAs of the cluster
       if (split > 1) mbar_expect_tx(smem_u32(xch_bar), (split - 1) * kSlotBytes);
     }
     __syncwarp();
     asm volatile("bar.arrive 2, %0;" ::"n"(kThreads) : "memory");
-    if (split > 1) cluster_arrive_relaxed();   // phase A: this CTA runs and its exchange barrier exists
+    if (clustered) cluster_arrive_relaxed();   // phase A: this CTA runs and its exchange barrier exists
     if (lane == 0) {
       for (int i = 0; i < pre; ++i) load_stage(i, i);
-      CB200_TRACE(0, 0, 2);
     }
   } else {
     if (warp == 1) tc_alloc(smem_u32(tmem_slot), kTmemCols);
-    if (split > 1) cluster_arrive_relaxed();
+    if (clustered) cluster_arrive_relaxed();
     tc_fence_before();
     asm volatile("bar.sync 2, %0;" ::"n"(kThreads) : "memory");
     tc_fence_after();
   }
   const uint32_t tmem_base = warp == 0 ? 0u : *tmem_slot;
-  if (threadIdx.x == 64) CB200_TRACE(3, 0, 1);
 
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- TMA producer (stages beyond the first ring) ----------------
       for (int i = pre; i < total; ++i) {
         const int s = i % kStages;
-        CB200_TRACE(0, i, 0);
         if (!mbar_wait(smem_u32(&empty[s]), ((i / kStages) & 1) ^ 1, &g_i8_status, (3 << 8) | 1)) break;
-        CB200_TRACE(0, i, 1);
         load_stage(i, s);
-        CB200_TRACE(0, i, 2);
       }
     }
   } else if (warp == 1) {
@@ -449,10 +434,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
                              (static_cast<uint32_t>(kBlockN >> 4) << 24);
       for (int i = 0; i < total; ++i) {
         const int s = i % kStages;
-        CB200_TRACE(1, i, 0);
-        if (!mbar_wait(smem_u32(BITS == 4 ? &unpacked[s] : &full[s]), (i / kStages) & 1, &g_i8_status, (3 << 8) | 2)) break;
-        CB200_TRACE(1, i, 1);
-        if (i == 0) CB200_CTA_TRACE(1);
+        if (!mbar_wait(smem_u32(kReadyBar ? &ready[s] : &full[s]), (i / kStages) & 1, &g_i8_status, (3 << 8) | 2)) break;
         tc_fence_after();
         const uint32_t d = tmem_base;
         const uint32_t w_base = smem_u32(s_w + s * kWBytes);
@@ -460,9 +442,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
 #pragma unroll
         for (int j = 0; j < kBlockK / 32; ++j)   // 32 bytes of k per instruction inside the 128-byte swizzle span
           tc_mma_i8_ss(d, smem_desc_sw128(w_base + j * 32), smem_desc_sw128(x_base + j * 32), idesc, (i > 0 || j > 0) ? 1u : 0u);
-        CB200_TRACE(1, i, 2);
         tc_commit(smem_u32(&empty[s]));
-        CB200_TRACE(1, i, 3);
       }
       tc_commit(smem_u32(acc_full));
     }
@@ -477,25 +457,26 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
     const int w_row = is_up ? p.N / 2 + n_out_idx : n_out_idx;
     __half* y = static_cast<__half*>(p.y);
     const __half* res = static_cast<const __half*>(p.residual);
-    // everything the epilogue needs from global memory is fetched while the main loop runs
+    // What the epilogue needs from global memory is requested here and first used after the main loop (a use
+    // stalls the warp until the line has arrived, cold from HBM, and would hold back the loads behind it).
     if (threadIdx.x - 64 < MP) {
       s_sx[threadIdx.x - 64] = p.sx[threadIdx.x - 64];
       s_qsum[threadIdx.x - 64] = p.qsum[threadIdx.x - 64];
     }
-    float scale = 0.f, zero = 128.f;
-    if (n_out_idx < p.n_out) {
-      scale = p.scale_dtype == CACHEIR_B200_F16 ? __half2float(static_cast<const __half*>(p.scales)[w_row])
-                                                : static_cast<const float*>(p.scales)[w_row];
+    const bool col_ok = n_out_idx < p.n_out;
+    uint32_t scale_raw = 0u;
+    float zero = 128.f;
+    if (col_ok) {
+      scale_raw = p.scale_dtype == CACHEIR_B200_F16 ? static_cast<uint32_t>(static_cast<const uint16_t*>(p.scales)[w_row])
+                                                    : static_cast<const uint32_t*>(p.scales)[w_row];
       if (p.zero_points) zero = p.zero_points[w_row];
     }
-    const bool zero_is_int = zero == rintf(zero) && fabsf(zero) <= 255.f;
-    const int zero_int = zero_is_int ? __float2int_rn(zero) : 0;
-    float res_v[MS];
+    uint16_t res_raw[MS];
 #pragma unroll
     for (int j = 0; j < MS; ++j) {
       const int m = krank * MS + j;
-      res_v[j] = (split > 1 && p.epilogue == CACHEIR_B200_EPI_RESIDUAL && m < p.M && n_out_idx < p.n_out)
-                     ? __half2float(res[static_cast<size_t>(m) * p.n_out + n_out_idx]) : 0.f;
+      res_raw[j] = (split > 1 && p.epilogue == CACHEIR_B200_EPI_RESIDUAL && m < p.M && col_ok)
+                       ? reinterpret_cast<const uint16_t*>(res)[static_cast<size_t>(m) * p.n_out + n_out_idx] : static_cast<uint16_t>(0);
     }
     // Fused QKV epilogue: per batch row, the (cos, sin) of this thread's pair and where its k/v element goes in the pool.
     [[maybe_unused]] constexpr bool rope_epi = ROPE;   // a template parameter: the other projections do not carry this code
@@ -541,20 +522,19 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
     };
     float2 cs_v[MS];
     long long off_v[MS];
+    [[maybe_unused]] int pos_v[MS], page_v[MS];
     if constexpr (SPLIT > 1 && ROPE) {
       // Two levels of dependent loads (position, then table entry and page id): each level is issued for all of
-      // this thread's rows at once, with clamped indices instead of branches, so the latencies overlap.
-      const bool col_ok = n_out_idx < p.n_out;
-      const bool is_qk = n_out_idx < ra.q_dim + ra.k_dim;
-      const int pair = (n_out_idx % ra.head_dim) >> 1;
-      const int col = n_out_idx >= ra.q_dim ? (n_out_idx - ra.q_dim) % ra.k_dim : 0;
-      int pos_v[MS];
+      // this thread's rows at once, with clamped indices instead of branches, so the latencies overlap; the
+      // values are put to use only after the main loop.
 #pragma unroll
       for (int j = 0; j < MS; ++j) {
         const int m = krank * MS + j;
         pos_v[j] = (m < p.M && col_ok) ? ra.positions[m] : -1;
       }
-      int page_v[MS];
+    }
+    if constexpr (SPLIT > 1 && ROPE) {
+      const int pair = (n_out_idx % ra.head_dim) >> 1;
 #pragma unroll
       for (int j = 0; j < MS; ++j) {
         const int m = min(krank * MS + j, p.M - 1);
@@ -562,17 +542,6 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
         const int page_idx = min(max(pos_v[j], 0) / ra.page_size, ra.max_pages - 1);
         cs_v[j] = reinterpret_cast<const float2*>(ra.table)[static_cast<size_t>(pos_t) * (ra.head_dim / 2) + pair];
         page_v[j] = ra.page_table[static_cast<size_t>(m) * ra.max_pages + page_idx];
-      }
-#pragma unroll
-      for (int j = 0; j < MS; ++j) {
-        const int pos = pos_v[j];
-        const bool row_ok = pos >= 0;
-        if (row_ok && is_qk && pos >= ra.table_positions) atomicCAS(&g_i8_status, 0, (3 << 8) | 5);   // outside the cos/sin table
-        if (!(row_ok && is_qk && pos < ra.table_positions)) cs_v[j] = make_float2(1.f, 0.f);
-        const bool write = row_ok && n_out_idx >= ra.q_dim && pos / ra.page_size < ra.max_pages;   // no page reserved: dropped
-        off_v[j] = write ? static_cast<long long>(((static_cast<size_t>(page_v[j]) * ra.kv_heads + col / ra.head_dim) * ra.page_size +
-                                                   pos % ra.page_size) * ra.head_dim + col % ra.head_dim)
-                         : -1;
       }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps: s_sx / s_qsum are in place
@@ -604,13 +573,34 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
           *reinterpret_cast<uint4*>(out_row + (((2 * c + 1) ^ (r & 7)) * 16)) = make_uint4(o[4], o[5], o[6], o[7]);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads these bytes through the async proxy
-        mbar_arrive(smem_u32(&unpacked[s]));
+        mbar_arrive(smem_u32(&ready[s]));
+      }
+    }
+    // Only now are the prefetched values put to use.
+    const float scale = !col_ok ? 0.f : (p.scale_dtype == CACHEIR_B200_F16 ? __half2float(__ushort_as_half(static_cast<unsigned short>(scale_raw)))
+                                                                             : __uint_as_float(scale_raw));
+    const bool zero_is_int = zero == rintf(zero) && fabsf(zero) <= 255.f;
+    const int zero_int = zero_is_int ? __float2int_rn(zero) : 0;
+    float res_v[MS];
+#pragma unroll
+    for (int j = 0; j < MS; ++j) res_v[j] = __half2float(__ushort_as_half(res_raw[j]));
+    if constexpr (SPLIT > 1 && ROPE) {
+      const bool is_qk = n_out_idx < ra.q_dim + ra.k_dim;
+      const int col = n_out_idx >= ra.q_dim ? (n_out_idx - ra.q_dim) % ra.k_dim : 0;
+#pragma unroll
+      for (int j = 0; j < MS; ++j) {
+        const int pos = pos_v[j];
+        const bool row_ok = pos >= 0;
+        if (row_ok && is_qk && pos >= ra.table_positions) atomicCAS(&g_i8_status, 0, (3 << 8) | 5);   // outside the cos/sin table
+        if (!(row_ok && is_qk && pos < ra.table_positions)) cs_v[j] = make_float2(1.f, 0.f);
+        const bool write = row_ok && n_out_idx >= ra.q_dim && pos / ra.page_size < ra.max_pages;   // no page reserved: dropped
+        off_v[j] = write ? static_cast<long long>(((static_cast<size_t>(page_v[j]) * ra.kv_heads + col / ra.head_dim) * ra.page_size +
+                                                   pos % ra.page_size) * ra.head_dim + col % ra.head_dim)
+                         : -1;
       }
     }
     bool ok = mbar_wait(smem_u32(acc_full), 0, &g_i8_status, (3 << 8) | 3);
     tc_fence_after();
-    if (threadIdx.x == 64) CB200_TRACE(3, 0, 2);
-    if (threadIdx.x == 64) CB200_CTA_TRACE(2);
     const bool store = ok && n_out_idx < p.n_out;
     if constexpr (SPLIT > 1) {
       // All-to-all over the cluster. Each rank lays its partial sums out per destination in its own
@@ -643,7 +633,6 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the bulk copies below read what was just stored
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) CB200_TRACE(3, 0, 3);
       cluster_wait();                                // phase A: every rank of the cluster runs and has armed its barrier
       if (warp == 2 && lane < SPLIT - 1 && ok) {     // one lane per destination
         const int dest = (krank + 1 + lane) % SPLIT;
@@ -652,9 +641,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
                           smem_u32(xch_bar), dest);
       }
       __syncwarp();
-      if (threadIdx.x == 64) CB200_TRACE(3, 1, 0);
       ok = mbar_wait(smem_u32(xch_bar), 0, &g_i8_status, (3 << 8) | 4) && ok;
-      if (threadIdx.x == 64) CB200_TRACE(3, 1, 1);
       cluster_arrive_relaxed();                      // phase B: nothing more will be written into this CTA
 #pragma unroll 1
       for (int u0 = 0; u0 < MS; u0 += G) {
@@ -714,7 +701,6 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) { hi[j] = 0u; lo[j] = 0u; }
         }
-        if (threadIdx.x == 64) CB200_TRACE(2, c0 / 8, 0);
         float g[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -722,9 +708,7 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
           g[j] = recombine(static_cast<int32_t>(hi[j]), static_cast<int32_t>(lo[j]), zero, zero_int, zero_is_int, s_qsum[m]) * (scale * s_sx[m]);
           if (is_up) s_up[m * kPairRows + (r - kPairRows)] = g[j];
         }
-        if (threadIdx.x == 64) CB200_TRACE(2, c0 / 8, 1);
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (threadIdx.x == 64) CB200_TRACE(2, c0 / 8, 2);
         if (!is_up && store) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -735,7 +719,6 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
             }
           }
         }
-        if (threadIdx.x == 64) CB200_TRACE(2, c0 / 8, 3);
       }
     } else {
 #pragma unroll 1
@@ -768,13 +751,12 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
       }
     }
   }
-  if (warp < 2 && split > 1) {   // warps without an epilogue still take part in both phases of the cluster barrier
+  if (warp < 2 && clustered) {   // warps without an epilogue still take part in every phase of the cluster barrier
     __syncwarp();
     cluster_wait();
     cluster_arrive_relaxed();
     cluster_wait();
   }
-  if (threadIdx.x == 64) CB200_TRACE(3, 1, 2);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -782,8 +764,6 @@ qgemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
     tc_fence_after();
     tc_dealloc(tmem_base, kTmemCols);
   }
-  if (threadIdx.x == 64) CB200_TRACE(3, 1, 3);
-  if (threadIdx.x == 64) CB200_CTA_TRACE(3);
 }
 
 // CTAs per cluster along K. Every doubling adds cluster-barrier and exchange time to the epilogue, so the
@@ -810,16 +790,17 @@ int launch_quantize(const __half* x, long long x_stride, int M, int K, int mp, v
 }
 
 template <int MP, int SPLIT, bool ROPE, int BITS>
-cudaError_t launch_i8_split(const CUtensorMap& tmap_w, const I8Params& p, int n_tiles, cudaStream_t stream) {
-  constexpr size_t kSmem = 1024 + static_cast<size_t>(num_stages(MP, SPLIT, BITS)) * stage_bytes(MP, BITS) + exchange_bytes(MP, SPLIT) + 1024;
+cudaError_t launch_i8_split(const CUtensorMap& tmap_w, const I8Params& p, cudaStream_t stream) {
+  constexpr size_t kSmem = 1024 + static_cast<size_t>(num_stages(MP, SPLIT, BITS)) * stage_bytes(MP, BITS) + exchange_bytes(MP, SPLIT) + kTailBytes;
   static_assert(num_stages(MP, SPLIT, BITS) >= 2, "the pipeline needs at least two stages");
   static_assert(num_stages(MP, SPLIT, BITS) * (kBlockN * kBlockK + 2 * MP * kBlockK) >= exchange_bytes(MP, SPLIT) || SPLIT == 1,
                 "outgoing partials are staged in the drained byte and activation tiles at the head of the ring");
+  static_assert(kTailBytes >= (3 * 8 + 2) * 8 + 8 + 2 * 64 * 4, "barriers, TMEM base and per-row constants fit behind the exchange buffer");
   auto kern = qgemm_i8_kernel<MP, SPLIT, ROPE, BITS>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(n_tiles, SPLIT, 1);
+  cfg.gridDim = dim3(p.n_tiles, SPLIT, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = kSmem;
   cfg.stream = stream;
@@ -833,13 +814,25 @@ cudaError_t launch_i8_split(const CUtensorMap& tmap_w, const I8Params& p, int n_
   return cudaLaunchKernelEx(&cfg, kern, tmap_w, p);
 }
 
+template <int MP, bool ROPE, int BITS>
+cudaError_t launch_i8_by_split(const CUtensorMap& tmap_w, const I8Params& p, cudaStream_t stream) {
+  switch (p.split_k) {
+    case 8: return launch_i8_split<MP, 8, ROPE, BITS>(tmap_w, p, stream);
+    case 4: return launch_i8_split<MP, 4, ROPE, BITS>(tmap_w, p, stream);
+    case 2: return launch_i8_split<MP, 2, ROPE, BITS>(tmap_w, p, stream);
+    default: return launch_i8_split<MP, 1, ROPE, BITS>(tmap_w, p, stream);
+  }
+}
+
 template <int MP>
 int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
   int8_t* planes = static_cast<int8_t*>(workspace);
   float* sx = reinterpret_cast<float*>(planes + static_cast<size_t>(2 * MP) * q.K);
   int* qsum = reinterpret_cast<int*>(sx + 64);
-  if (!q.x_prequantized) {
-    const int rc = launch_quantize(static_cast<const __half*>(q.x), q.x_stride, q.M, q.K, MP, workspace, stream);
+  if (!q.x_prequantized) {   // the activation pre-pass, with the RMSNorm in front of it if one was asked for
+    const int rc = q.norm_weight
+        ? qgemm_i8_rms_norm_quantize(q.x, nullptr, q.norm_weight, nullptr, nullptr, q.M, q.K, q.norm_eps, workspace, stream)
+        : launch_quantize(static_cast<const __half*>(q.x), q.x_stride, q.M, q.K, MP, workspace, stream);
     if (rc != 0) return rc;
   }
 
@@ -861,31 +854,12 @@ int launch_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
   p.n_out = q.epilogue == CACHEIR_B200_EPI_SWIGLU ? q.N / 2 : q.N;
   p.scale_dtype = q.scale_dtype; p.epilogue = q.epilogue; p.tiled = q.tiled ? 1 : 0;
   p.rope = q.rope;
-  const int n_tiles = swiglu ? (p.n_out + kPairRows - 1) / kPairRows : (p.n_out + kBlockN - 1) / kBlockN;
-  p.split_k = choose_split_k(n_tiles, q.K / kBlockK, q.epilogue, MP);
+  p.n_tiles = swiglu ? (p.n_out + kPairRows - 1) / kPairRows : (p.n_out + kBlockN - 1) / kBlockN;
+  p.split_k = choose_split_k(p.n_tiles, q.K / kBlockK, q.epilogue, MP);
   cudaError_t e;
-  if (q.epilogue == kEpiQkvRopeAppend) {
-    switch (p.split_k) {
-      case 8: e = launch_i8_split<MP, 8, true, 8>(tmap_w, p, n_tiles, stream); break;
-      case 4: e = launch_i8_split<MP, 4, true, 8>(tmap_w, p, n_tiles, stream); break;
-      case 2: e = launch_i8_split<MP, 2, true, 8>(tmap_w, p, n_tiles, stream); break;
-      default: e = launch_i8_split<MP, 1, true, 8>(tmap_w, p, n_tiles, stream); break;
-    }
-  } else if (q.bits == 4) {
-    switch (p.split_k) {
-      case 8: e = launch_i8_split<MP, 8, false, 4>(tmap_w, p, n_tiles, stream); break;
-      case 4: e = launch_i8_split<MP, 4, false, 4>(tmap_w, p, n_tiles, stream); break;
-      case 2: e = launch_i8_split<MP, 2, false, 4>(tmap_w, p, n_tiles, stream); break;
-      default: e = launch_i8_split<MP, 1, false, 4>(tmap_w, p, n_tiles, stream); break;
-    }
-  } else {
-    switch (p.split_k) {
-      case 8: e = launch_i8_split<MP, 8, false, 8>(tmap_w, p, n_tiles, stream); break;
-      case 4: e = launch_i8_split<MP, 4, false, 8>(tmap_w, p, n_tiles, stream); break;
-      case 2: e = launch_i8_split<MP, 2, false, 8>(tmap_w, p, n_tiles, stream); break;
-      default: e = launch_i8_split<MP, 1, false, 8>(tmap_w, p, n_tiles, stream); break;
-    }
-  }
+  if (q.epilogue == kEpiQkvRopeAppend) e = launch_i8_by_split<MP, true, 8>(tmap_w, p, stream);
+  else if (q.bits == 4) e = launch_i8_by_split<MP, false, 4>(tmap_w, p, stream);
+  else e = launch_i8_by_split<MP, false, 8>(tmap_w, p, stream);
   if (e != cudaSuccess) return static_cast<int>(e);
   return launch_status();
 }
@@ -906,7 +880,18 @@ bool qgemm_i8_supported(const QGemvParams& q, const void* workspace, size_t work
   if (q.paired && !(q.tiled && q.epilogue == CACHEIR_B200_EPI_SWIGLU)) return false;
   if (!workspace || workspace_bytes < qgemm_i8_workspace_bytes(q.M, q.K) || !aligned_to(workspace, 128)) return false;
   if (!aligned_to(q.packed, 16) || !aligned_to(q.x, 16) || (q.x_stride * 2) % 16 != 0) return false;
+  // an RMSNorm in front runs inside the pre-pass kernel: dense rows, K <= 8192
+  if (q.norm_weight && (!aligned_to(q.norm_weight, 16) || q.x_prequantized || q.K > 8192 || q.x_stride != q.K)) return false;
   return tensor_map_encoder() != nullptr;
+}
+
+// The split-K factor launch_qgemm_i8 would choose for these extents.
+int qgemm_i8_plan(const QGemvParams& q) {
+  const int mp = q.M <= 16 ? 16 : (q.M <= 32 ? 32 : 64);
+  const bool swiglu = q.epilogue == CACHEIR_B200_EPI_SWIGLU;
+  const int n_out = swiglu ? q.N / 2 : q.N;
+  const int n_tiles = swiglu ? (n_out + kPairRows - 1) / kPairRows : (n_out + kBlockN - 1) / kBlockN;
+  return choose_split_k(n_tiles, q.K / kBlockK, q.epilogue, mp);
 }
 
 int launch_qgemm_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) {
@@ -914,15 +899,6 @@ int launch_qgemm_i8(const QGemvParams& q, void* workspace, cudaStream_t stream) 
   if (q.M <= 32) return launch_i8<32>(q, workspace, stream);
   return launch_i8<64>(q, workspace, stream);
 }
-
-#ifdef CB200_QGEMM_TRACE
-extern "C" int cacheir_b200_debug_cta_trace_i8(unsigned long long* out) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_i8_cta_trace, sizeof(unsigned long long) * 2048 * 4));
-}
-extern "C" int cacheir_b200_debug_trace_i8(long long* out) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_i8_trace, sizeof(long long) * 4 * 256 * 4));
-}
-#endif
 
 int i8_plane_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
 

@@ -63,16 +63,7 @@ __host__ __device__ constexpr int num_stages(int bits, int mp) {
 }
 constexpr uint32_t kPollLimit = 8u * 1000u * 1000u;
 
-__device__ int g_qgemm_status = 0;
-
-// Optional pipeline trace (compile with -DCB200_QGEMM_TRACE): CTA 0 records clock64() at the
-// hand-over points of each role so that stage times can be read back and compared.
-#ifdef CB200_QGEMM_TRACE
-__device__ long long g_trace[4][256][4];
-#define CB200_TRACE(role, i, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 256) g_trace[role][i][slot] = clock64(); } while (0)
-#else
-#define CB200_TRACE(role, i, slot) do { } while (0)
-#endif   // 0 ok; otherwise (code << 8 | barrier id) of the first wait that gave up
+__device__ int g_qgemm_status = 0;   // 0 ok; otherwise (code << 8 | barrier id) of the first wait that gave up
 
 // ---- PTX wrappers ------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -303,9 +294,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       for (int i = 0; i < total; ++i) {
         const int s = i % kStages;
         const uint32_t ph = (i / kStages) & 1;
-        CB200_TRACE(0, i, 0);
         if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1, 1)) break;
-        CB200_TRACE(0, i, 1);
         const int pass = i / kblocks;
         const int kb = kb_begin + i % kblocks;
         const int row0 = n0 + pass * (p.N / 2);
@@ -321,7 +310,6 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         }
         // x viewed as [K/64 spans][M rows][64 elements]: both 64-element halves of the k block in one copy
         tma_load_3d(smem_u32(s_x + s * kXBytes), &tmap_x, bar, 0, 0, kb * 2);
-        CB200_TRACE(0, i, 2);
       }
     }
   } else if (warp == 1) {
@@ -332,11 +320,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       for (int i = 0; i < total; ++i) {
         const int s = i % kStages;
         const int t = i % kAStages;
-        CB200_TRACE(1, i, 0);
         if (!mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, 2)) break;
-        CB200_TRACE(1, i, 1);
         if (!mbar_wait(smem_u32(&a_full[t]), (i / kAStages) & 1, 3)) break;
-        CB200_TRACE(1, i, 2);
         tc_fence_after();
         const int pass = i / kblocks;
         const int kb = i % kblocks;
@@ -354,7 +339,6 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         }
         tc_commit(smem_u32(&a_empty[t]));   // operand columns and the x stage are free once these MMAs retire
         tc_commit(smem_u32(&empty[s]));
-        CB200_TRACE(1, i, 3);
       }
       tc_commit(smem_u32(acc_full));
     }
@@ -400,12 +384,9 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         const int i = pass * kblocks + kbi;
         const int s = i % kStages;
         const int t = i % kAStages;
-        if (threadIdx.x == 128) CB200_TRACE(2, i, 0);
         ok = mbar_wait(smem_u32(&full[s]), (i / kStages) & 1, 4);
-        if (threadIdx.x == 128) CB200_TRACE(2, i, 1);
         ok = ok && mbar_wait(smem_u32(&a_empty[t]), ((i / kAStages) & 1) ^ 1, 5);
         if (!ok) break;
-        if (threadIdx.x == 128) CB200_TRACE(2, i, 2);
         tc_fence_after();
         const uint8_t* raw_row = s_raw + s * kRawBytes + r * kRawRow;
         uint8_t* a_tile = s_a + t * kABytes;
@@ -449,7 +430,6 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads the tile through the async proxy
         mbar_arrive(smem_u32(&a_full[t]));
         mbar_arrive(smem_u32(&empty[s]));
-        if (threadIdx.x == 128) CB200_TRACE(2, i, 3);
       }
     }
     if constexpr (kWide) {
@@ -457,9 +437,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       //      tile rows [32 hsel, 32 hsel + 32) (accumulator columns) ----
       asm volatile("bar.sync 3, %0;" ::"n"(kConvThreads) : "memory");   // the row-scale table is complete
       constexpr int kCols = 32;
-      if (threadIdx.x == 128) CB200_TRACE(3, 0, 0);
       ok = ok && mbar_wait(smem_u32(acc_full), 0, 6);
-      if (threadIdx.x == 128) CB200_TRACE(3, 1, 0);
       tc_fence_after();
       const bool have = ok && total > 0;
       __half* y = static_cast<__half*>(p.y);
@@ -543,7 +521,6 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         for (int a = 0; a < passes; ++a) {
           if (threadIdx.x == 128) mbar_expect_tx(smem_u32(xch_bar), (split - 1) * slot_floats * 4);
           cluster_sync_all();                          // every rank has drained its ring (and read the previous exchange) and armed its barrier
-          if (threadIdx.x == 128) CB200_TRACE(3, 2 + 4 * a, 0);
 #pragma unroll 1
           for (int c0 = 0; c0 < kCols; c0 += 8) {
             float v8[8];
@@ -555,7 +532,6 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           asm volatile("bar.sync 3, %0;" ::"n"(kConvThreads) : "memory");
-          if (threadIdx.x == 128) CB200_TRACE(3, 3 + 4 * a, 0);
           if (cw == 0 && lane < split - 1) {           // one lane per destination
             const int dest = (krank + 1 + lane) % split;
             bulk_copy_to_rank(smem_u32(s_recv + krank * slot_floats), smem_u32(s_stage + dest * slot_floats),
@@ -563,7 +539,6 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           }
           __syncwarp();
           ok = mbar_wait(smem_u32(xch_bar), a & 1, 7) && ok;
-          if (threadIdx.x == 128) CB200_TRACE(3, 4 + 4 * a, 0);
 #pragma unroll 1
           for (int i0 = 0; i0 < cnt; i0 += 4) {
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
@@ -587,12 +562,9 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
               store4(col, sum);
             }
           }
-          if (threadIdx.x == 128) CB200_TRACE(3, 5 + 4 * a, 0);
         }
         cluster_sync_all();                            // all copies out of this CTA's shared memory have landed
-        if (threadIdx.x == 128) CB200_TRACE(3, 10, 0);
       }
-      if (threadIdx.x == 128) CB200_TRACE(3, 11, 0);
     } else if (cw >= 8) {   // the second eight converter warps have no epilogue share; they only join the cluster barriers
       if (split > 1) {
         __syncwarp();
@@ -833,12 +805,6 @@ int launch_qgemm_tc(const QGemvParams& q, cudaStream_t stream) {
   if (q.group_size > 0) return q.bits == 8 ? launch_tc_mp<8, true>(q, stream) : launch_tc_mp<4, true>(q, stream);
   return q.bits == 8 ? launch_tc_mp<8, false>(q, stream) : launch_tc_mp<4, false>(q, stream);
 }
-
-#ifdef CB200_QGEMM_TRACE
-extern "C" int cacheir_b200_debug_trace(long long* out) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 4 * 256 * 4));
-}
-#endif
 
 int qgemm_tc_device_status(bool reset) {
   int status = 0;

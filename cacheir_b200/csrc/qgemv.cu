@@ -192,21 +192,23 @@ using namespace cb200;
 
 extern "C" size_t cacheir_b200_qgemv_workspace_bytes(int M, int K) { return qgemm_i8_workspace_bytes(M, K); }
 
-extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const void* scales,
-                                     const float* zero_points, const void* residual, void* y, int M,
-                                     int N, int K, int bits, int group_size, int x_dtype,
-                                     int scale_dtype, long long x_stride, int epilogue, int weight_layout,
-                                     void* workspace, size_t workspace_bytes, void* stream) {
+namespace {
+
+// Shared body of cacheir_b200_qgemv_ex and cacheir_b200_rmsnorm_qgemv (norm_weight == nullptr: no norm).
+int qgemv_dispatch(const void* x, const void* norm_weight, float norm_eps, const void* packed, const void* scales,
+                   const float* zero_points, const void* residual, void* y, int M, int N, int K, int bits, int group_size,
+                   int x_dtype, int scale_dtype, long long x_stride, int epilogue, int weight_layout, void* workspace,
+                   size_t workspace_bytes, void* stream, bool plan_only) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (!x || !packed || !y) return CACHEIR_B200_EINVAL;
+  if (!plan_only && (!x || !packed || !y)) return CACHEIR_B200_EINVAL;
   const int esize = dtype_size(x_dtype);
   if (esize == 0) return CACHEIR_B200_EINVAL;
   if (bits != 0 && bits != 4 && bits != 8) return CACHEIR_B200_EINVAL;
   if (epilogue < CACHEIR_B200_EPI_NONE || epilogue > CACHEIR_B200_EPI_SWIGLU) return CACHEIR_B200_EINVAL;
   if (epilogue == CACHEIR_B200_EPI_SWIGLU && (N % 2) != 0) return CACHEIR_B200_EINVAL;
-  if (epilogue == CACHEIR_B200_EPI_RESIDUAL && !residual) return CACHEIR_B200_EINVAL;
+  if (!plan_only && epilogue == CACHEIR_B200_EPI_RESIDUAL && !residual) return CACHEIR_B200_EINVAL;
   if (bits != 0) {
-    if (!scales) return CACHEIR_B200_EINVAL;
+    if (!plan_only && !scales) return CACHEIR_B200_EINVAL;
     if (scale_dtype != CACHEIR_B200_F32 && scale_dtype != CACHEIR_B200_F16) return CACHEIR_B200_EINVAL;
     if (group_size < 0) return CACHEIR_B200_EINVAL;
     if (group_size > 0 && (group_size % 32 != 0 || K % group_size != 0 || zero_points != nullptr))
@@ -221,19 +223,21 @@ extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const vo
   p.x_dtype = x_dtype; p.scale_dtype = scale_dtype;
   p.x_stride = x_stride > 0 ? x_stride : K;
   p.epilogue = epilogue;
-  if (weight_layout < 0 || weight_layout > (CACHEIR_B200_LAYOUT_TILED | CACHEIR_B200_X_PREQUANTIZED | CACHEIR_B200_LAYOUT_PAIRED))
-    return CACHEIR_B200_EINVAL;
+  p.norm_weight = norm_weight; p.norm_eps = norm_eps;
+  constexpr int kAllFlags = CACHEIR_B200_LAYOUT_TILED | CACHEIR_B200_X_PREQUANTIZED | CACHEIR_B200_LAYOUT_PAIRED;
+  if (weight_layout < 0 || (weight_layout & ~kAllFlags) != 0) return CACHEIR_B200_EINVAL;
   p.tiled = (weight_layout & CACHEIR_B200_LAYOUT_TILED) != 0;
   p.paired = (weight_layout & CACHEIR_B200_LAYOUT_PAIRED) != 0;
   if (p.paired && !(p.tiled && epilogue == CACHEIR_B200_EPI_SWIGLU)) return CACHEIR_B200_EINVAL;
   p.x_prequantized = (weight_layout & CACHEIR_B200_X_PREQUANTIZED) != 0;
+  if (p.x_prequantized && norm_weight) return CACHEIR_B200_EINVAL;
   const size_t row_bytes = bits == 8 ? static_cast<size_t>(K)
                          : bits == 4 ? static_cast<size_t>((K + 1) / 2)
                                      : static_cast<size_t>(K) * esize;
   p.vector_ok = aligned_to(packed, 16) && row_bytes % 16 == 0 && aligned_to(x, 16) &&
                 (p.x_stride * esize) % 16 == 0;
   cudaStream_t st = as_stream(stream);
-  if (M > 64 && !p.x_prequantized) {
+  if (M > 64 && !p.x_prequantized && !norm_weight) {
     // The integer tensor-core kernel takes up to 64 batch rows per launch, the fp16 one up to 128. A taller
     // batch runs as chunks of that height (the weights stream once per chunk, still far cheaper than the
     // CUDA-core kernel at these heights) when a chunk-sized problem of the same shape is tensor-core eligible.
@@ -241,6 +245,7 @@ extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const vo
     c.M = 64;
     const bool i8_ok = qgemm_i8_supported(c, workspace, workspace_bytes);
     if (i8_ok || (!c.paired && qgemm_tc_supported(c))) {
+      if (plan_only) return i8_ok ? ((1 << 8) | qgemm_i8_plan(c)) : (2 << 8);
       const int rows = i8_ok ? 64 : 128;
       const size_t n_out = epilogue == CACHEIR_B200_EPI_SWIGLU ? static_cast<size_t>(N) / 2 : static_cast<size_t>(N);
       for (int m0 = 0; m0 < M; m0 += rows) {
@@ -254,12 +259,52 @@ extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const vo
       return 0;
     }
   }
-  if (qgemm_i8_supported(p, workspace, workspace_bytes)) return launch_qgemm_i8(p, workspace, st);
+  if (qgemm_i8_supported(p, workspace, workspace_bytes))
+    return plan_only ? ((1 << 8) | qgemm_i8_plan(p)) : launch_qgemm_i8(p, workspace, st);
+  if (norm_weight) return CACHEIR_B200_EUNSUPPORTED;  // the fused norm exists on the integer path only: run cacheir_b200_rms_norm first
   if (p.x_prequantized) return CACHEIR_B200_EINVAL;   // only the integer path can consume a quantized workspace
   if (p.paired) return CACHEIR_B200_EUNSUPPORTED;     // only the integer tensor-core kernel reads paired tiles
-  if (qgemm_tc_supported(p)) return launch_qgemm_tc(p, st);
+  if (qgemm_tc_supported(p)) return plan_only ? (2 << 8) : launch_qgemm_tc(p, st);
   if (p.tiled) return CACHEIR_B200_EUNSUPPORTED;   // the tile order only exists for the tensor-core kernels
-  return launch_qgemv_cuda_core(p, st);
+  return plan_only ? (3 << 8) : launch_qgemv_cuda_core(p, st);
+}
+
+}  // namespace
+
+extern "C" int cacheir_b200_qgemv_ex(const void* x, const void* packed, const void* scales,
+                                     const float* zero_points, const void* residual, void* y, int M,
+                                     int N, int K, int bits, int group_size, int x_dtype,
+                                     int scale_dtype, long long x_stride, int epilogue, int weight_layout,
+                                     void* workspace, size_t workspace_bytes, void* stream) {
+  return qgemv_dispatch(x, nullptr, 0.f, packed, scales, zero_points, residual, y, M, N, K, bits, group_size, x_dtype,
+                        scale_dtype, x_stride, epilogue, weight_layout, workspace, workspace_bytes, stream, false);
+}
+
+extern "C" int cacheir_b200_rmsnorm_qgemv(const void* x, const void* norm_weight, float eps, const void* packed,
+                                          const void* scales, const float* zero_points, const void* residual, void* y,
+                                          int M, int N, int K, int bits, int scale_dtype, long long x_stride, int epilogue,
+                                          int weight_layout, void* workspace, size_t workspace_bytes, void* stream) {
+  if (M > 0 && N > 0 && K > 0 && !norm_weight) return CACHEIR_B200_EINVAL;
+  return qgemv_dispatch(x, norm_weight, eps, packed, scales, zero_points, residual, y, M, N, K, bits, 0, CACHEIR_B200_F16,
+                        scale_dtype, x_stride, epilogue, weight_layout, workspace, workspace_bytes, stream, false);
+}
+
+extern "C" int cacheir_b200_qgemv_plan(int M, int N, int K, int bits, int group_size, int epilogue, int weight_layout,
+                                       int with_workspace) {
+  // Dummy, suitably aligned addresses: the choice depends on extents, flags and alignment only.
+  void* aligned = reinterpret_cast<void*>(static_cast<uintptr_t>(1) << 20);
+  const size_t ws_bytes = with_workspace ? qgemm_i8_workspace_bytes(M, K) : 0;
+  if (epilogue == kEpiQkvRopeAppend) {
+    QGemvParams p{};
+    p.x = aligned; p.packed = aligned; p.scales = aligned; p.y = aligned;
+    p.M = M; p.N = N; p.K = K; p.bits = 8; p.x_dtype = CACHEIR_B200_F16; p.x_stride = K; p.epilogue = kEpiQkvRopeAppend;
+    p.tiled = (weight_layout & CACHEIR_B200_LAYOUT_TILED) != 0;
+    p.x_prequantized = (weight_layout & CACHEIR_B200_X_PREQUANTIZED) != 0;
+    if (!qgemm_i8_supported(p, with_workspace ? aligned : nullptr, ws_bytes)) return CACHEIR_B200_EUNSUPPORTED;
+    return (1 << 8) | qgemm_i8_plan(p);
+  }
+  return qgemv_dispatch(aligned, nullptr, 0.f, aligned, aligned, nullptr, aligned, aligned, M, N, K, bits, group_size, CACHEIR_B200_F16,
+                        CACHEIR_B200_F32, K, epilogue, weight_layout, with_workspace ? aligned : nullptr, ws_bytes, nullptr, true);
 }
 
 extern "C" int cacheir_b200_qgemv(const void* x, const void* packed, const void* scales,
@@ -305,12 +350,12 @@ extern "C" int cacheir_b200_rms_norm_quantize(const void* x, const void* residua
   return qgemm_i8_rms_norm_quantize(x, residual, weight, sum_out, out, rows, hidden, eps, workspace, as_stream(stream));
 }
 
-extern "C" int cacheir_b200_qkv_rope_append(const void* x, const void* packed, const void* scales, const float* zero_points,
-                                            void* qkv, int M, int N, int K, int scale_dtype, long long x_stride,
-                                            int weight_layout, int q_dim, int k_dim, int head_dim, float theta,
-                                            const float* rope_table, int rope_table_positions, const int32_t* positions,
-                                            const int32_t* page_table, int max_pages_per_seq, int page_size, void* k_cache,
-                                            void* v_cache, void* workspace, size_t workspace_bytes, void* stream) {
+static int qkv_rope_append_dispatch(const void* x, const void* norm_weight, float norm_eps, const void* packed, const void* scales,
+                                    const float* zero_points, void* qkv, int M, int N, int K, int scale_dtype, long long x_stride,
+                                    int weight_layout, int q_dim, int k_dim, int head_dim, float theta,
+                                    const float* rope_table, int rope_table_positions, const int32_t* positions,
+                                    const int32_t* page_table, int max_pages_per_seq, int page_size, void* k_cache,
+                                    void* v_cache, void* workspace, size_t workspace_bytes, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (!packed || !scales || !qkv || !positions || !page_table || !k_cache || !v_cache) return CACHEIR_B200_EINVAL;
   if (head_dim <= 0 || (head_dim % 2) != 0 || q_dim <= 0 || k_dim <= 0 || q_dim % head_dim != 0 || k_dim % head_dim != 0 ||
@@ -327,7 +372,9 @@ extern "C" int cacheir_b200_qkv_rope_append(const void* x, const void* packed, c
   p.epilogue = kEpiQkvRopeAppend;
   p.tiled = (weight_layout & CACHEIR_B200_LAYOUT_TILED) != 0;
   p.x_prequantized = (weight_layout & CACHEIR_B200_X_PREQUANTIZED) != 0;
+  p.norm_weight = norm_weight; p.norm_eps = norm_eps;
   if (!p.x_prequantized && !x) return CACHEIR_B200_EINVAL;
+  if (p.x_prequantized && norm_weight) return CACHEIR_B200_EINVAL;
   p.vector_ok = true;
   p.rope.table = rope_table; p.rope.table_positions = rope_table_positions;
   p.rope.positions = positions; p.rope.page_table = page_table; p.rope.k_cache = k_cache; p.rope.v_cache = v_cache;
@@ -336,4 +383,28 @@ extern "C" int cacheir_b200_qkv_rope_append(const void* x, const void* packed, c
   // only the integer tensor-core kernel carries this epilogue; other shapes use the separate kernels
   if (!qgemm_i8_supported(p, workspace, workspace_bytes)) return CACHEIR_B200_EUNSUPPORTED;
   return launch_qgemm_i8(p, workspace, as_stream(stream));
+}
+
+extern "C" int cacheir_b200_qkv_rope_append(const void* x, const void* packed, const void* scales, const float* zero_points,
+                                            void* qkv, int M, int N, int K, int scale_dtype, long long x_stride,
+                                            int weight_layout, int q_dim, int k_dim, int head_dim, float theta,
+                                            const float* rope_table, int rope_table_positions, const int32_t* positions,
+                                            const int32_t* page_table, int max_pages_per_seq, int page_size, void* k_cache,
+                                            void* v_cache, void* workspace, size_t workspace_bytes, void* stream) {
+  return qkv_rope_append_dispatch(x, nullptr, 0.f, packed, scales, zero_points, qkv, M, N, K, scale_dtype, x_stride, weight_layout,
+                                  q_dim, k_dim, head_dim, theta, rope_table, rope_table_positions, positions, page_table,
+                                  max_pages_per_seq, page_size, k_cache, v_cache, workspace, workspace_bytes, stream);
+}
+
+extern "C" int cacheir_b200_rmsnorm_qkv_rope_append(const void* x, const void* norm_weight, float eps, const void* packed,
+                                                    const void* scales, const float* zero_points, void* qkv, int M, int N, int K,
+                                                    int scale_dtype, long long x_stride, int weight_layout, int q_dim, int k_dim,
+                                                    int head_dim, float theta, const float* rope_table, int rope_table_positions,
+                                                    const int32_t* positions, const int32_t* page_table, int max_pages_per_seq,
+                                                    int page_size, void* k_cache, void* v_cache, void* workspace,
+                                                    size_t workspace_bytes, void* stream) {
+  if (M > 0 && N > 0 && K > 0 && (!norm_weight || !x)) return CACHEIR_B200_EINVAL;
+  return qkv_rope_append_dispatch(x, norm_weight, eps, packed, scales, zero_points, qkv, M, N, K, scale_dtype, x_stride, weight_layout,
+                                  q_dim, k_dim, head_dim, theta, rope_table, rope_table_positions, positions, page_table,
+                                  max_pages_per_seq, page_size, k_cache, v_cache, workspace, workspace_bytes, stream);
 }

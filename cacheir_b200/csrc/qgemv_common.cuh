@@ -36,6 +36,8 @@ struct QGemvParams {
   bool tiled;      // codes are in the 128x128 tile order of cacheir_b200_pack_relayout
   bool paired;     // tiled, and every tile pairs 64 rows of the first half of W with the matching 64 of the second half
   bool x_prequantized;  // the workspace already holds the integer form of x (see cacheir_b200_quantize_activations)
+  const void* norm_weight;  // non-null: y = epilogue(rmsnorm(x; norm_weight, norm_eps) . W^T): the norm runs inside the activation pre-pass (integer tensor-core path only)
+  float norm_eps;
   RopeAppendParams rope;  // epilogue == kEpiQkvRopeAppend only
 };
 
@@ -49,6 +51,7 @@ int launch_qgemm_tc(const QGemvParams& p, cudaStream_t stream);
 size_t qgemm_i8_workspace_bytes(int M, int K);
 bool qgemm_i8_supported(const QGemvParams& p, const void* workspace, size_t workspace_bytes);
 int launch_qgemm_i8(const QGemvParams& p, void* workspace, cudaStream_t stream);
+int qgemm_i8_plan(const QGemvParams& p);   // the split-K factor the launcher would use
 int qgemm_i8_device_status(bool reset);
 int qgemm_i8_quantize_activations(const void* x, long long x_stride, int M, int K, void* workspace, cudaStream_t stream);
 int qgemm_i8_rms_norm_quantize(const void* x, const void* residual, const void* weight, void* sum_out, void* out, int M,

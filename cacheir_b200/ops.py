@@ -108,10 +108,11 @@ def qgemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor | None, ze
           bits: int, n: int, k: int, group_size: int = 0, epilogue: int = EPI_NONE,
           residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
           workspace: torch.Tensor | None = None, tiled: bool = False, prequantized: bool = False,
-          paired: bool = False) -> torch.Tensor:
+          paired: bool = False, norm_weight: torch.Tensor | None = None, norm_eps: float = 1e-6) -> torch.Tensor:
     """y[M, N_out] = x[M, K] . deq(W)[N, K]^T with the reference's pack format
-    (bits 8/4; bits 0 = dense weights of x's dtype). x: [..., K] with dense rows."""
-    _require_cuda(x, packed, scales, zero_points, residual, out)
+    (bits 8/4; bits 0 = dense weights of x's dtype). x: [..., K] with dense rows.
+    `norm_weight` puts an RMSNorm of x in front (integer tensor-core path only)."""
+    _require_cuda(x, packed, scales, zero_points, residual, out, norm_weight)
     if x.shape[-1] != k:
         raise ValueError(f"x has {x.shape[-1]} input features, weight expects {k}")
     _rows_dense(x, "x")
@@ -145,12 +146,33 @@ def qgemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor | None, ze
         raise ValueError("residual must be a contiguous [M, N_out] tensor of x's dtype")
     _require_cuda(workspace)
     ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    layout = (1 if tiled else 0) | (2 if prequantized else 0) | (4 if paired else 0)
+    scale_code = F16 if (scales is not None and scales.dtype == torch.float16) else F32
+    if norm_weight is not None:
+        if x.dtype != torch.float16 or norm_weight.dtype != torch.float16 or norm_weight.numel() != k or group_size:
+            raise ValueError("the fused RMSNorm needs fp16 activations, an fp16 norm weight [K] and per-row weights")
+        check(_lib.load().cacheir_b200_rmsnorm_qgemv(
+            x2.data_ptr(), norm_weight.data_ptr(), float(norm_eps), packed.data_ptr(), _ptr(scales), _ptr(zero_points),
+            _ptr(residual), out.data_ptr(), m, n, k, bits, scale_code, x2.stride(0), epilogue, layout, _ptr(workspace),
+            ws_bytes, _stream()), "rmsnorm_qgemv")
+        return out
     check(_lib.load().cacheir_b200_qgemv_ex(
         x2.data_ptr(), packed.data_ptr(), _ptr(scales), _ptr(zero_points), _ptr(residual), out.data_ptr(),
-        m, n, k, bits, group_size, dtype_code(x.dtype),
-        F16 if (scales is not None and scales.dtype == torch.float16) else F32,
-        x2.stride(0), epilogue, (1 if tiled else 0) | (2 if prequantized else 0) | (4 if paired else 0), _ptr(workspace), ws_bytes, _stream()), "qgemv")
+        m, n, k, bits, group_size, dtype_code(x.dtype), scale_code,
+        x2.stride(0), epilogue, layout, _ptr(workspace), ws_bytes, _stream()), "qgemv")
     return out
+
+
+def qgemv_plan(m: int, n: int, k: int, *, bits: int, group_size: int = 0, epilogue: int = EPI_NONE, tiled: bool = False,
+               prequantized: bool = False, paired: bool = False, workspace: bool = True) -> dict:
+    """Which kernel `qgemv` launches for these extents: {"family": "i8"|"f16"|"cuda_core", "split_k"}.
+    epilogue 3 asks about `qkv_rope_append`."""
+    layout = (1 if tiled else 0) | (2 if prequantized else 0) | (4 if paired else 0)
+    code = int(_lib.load().cacheir_b200_qgemv_plan(int(m), int(n), int(k), int(bits), int(group_size), int(epilogue), layout,
+                                                   1 if workspace else 0))
+    check(code if code < 0 else 0, "qgemv_plan")
+    family = {1: "i8", 2: "f16", 3: "cuda_core"}[code >> 8]
+    return {"family": family, "split_k": (code & 255) if family == "i8" else 1}
 
 
 def pack_tiled_bytes(n: int, k: int, bits: int) -> int:
@@ -344,11 +366,13 @@ def rope_table(positions: int, head_dim: int, theta: float, device: torch.device
 def qkv_rope_append(x: torch.Tensor | None, packed: torch.Tensor, scales: torch.Tensor, zero_points: torch.Tensor | None,
                     out: torch.Tensor, *, n: int, k: int, q_dim: int, k_dim: int, head_dim: int, theta: float,
                     table: torch.Tensor, positions: torch.Tensor, page_table: torch.Tensor, k_cache: torch.Tensor,
-                    v_cache: torch.Tensor, workspace: torch.Tensor, tiled: bool = False, prequantized: bool = False) -> torch.Tensor:
+                    v_cache: torch.Tensor, workspace: torch.Tensor, tiled: bool = False, prequantized: bool = False,
+                    norm_weight: torch.Tensor | None = None, norm_eps: float = 1e-6) -> torch.Tensor:
     """Fused QKV projection (int8 weights) + RoPE on q and k + append of the new k/v rows to the page pool.
-    `out` [M, N] fp16 receives q (roped), k (roped), v. Raises CacheIRB200Error (unsupported) outside the
+    `out` [M, N] fp16 receives q (roped), k (roped), v. `norm_weight` puts the RMSNorm of the reference's
+    fused_rmsnorm_qkv_rope op in front. Raises CacheIRB200Error (unsupported) outside the
     integer tensor-core shapes; the caller then uses qgemv + rope_inplace + kv_append."""
-    _require_cuda(x, packed, scales, zero_points, out, table, positions, page_table, k_cache, v_cache, workspace)
+    _require_cuda(x, packed, scales, zero_points, out, table, positions, page_table, k_cache, v_cache, workspace, norm_weight)
     m = int(out.shape[0])
     if out.dtype != torch.float16 or tuple(out.shape) != (m, n) or not out.is_contiguous():
         raise ValueError("out must be a contiguous fp16 [M, N] tensor")
@@ -363,10 +387,21 @@ def qkv_rope_append(x: torch.Tensor | None, packed: torch.Tensor, scales: torch.
         raise ValueError("pool geometry does not match k_dim / head_dim")
     if table.dtype != torch.float32 or not table.is_contiguous() or table.shape[1:] != (head_dim // 2, 2):
         raise ValueError("rope table must be float32 [positions, head_dim/2, 2]")
+    layout = (1 if tiled else 0) | (2 if prequantized else 0)
+    if norm_weight is not None:
+        if x is None or norm_weight.dtype != torch.float16 or norm_weight.numel() != k:
+            raise ValueError("the fused RMSNorm needs x and an fp16 norm weight [K]")
+        check(_lib.load().cacheir_b200_rmsnorm_qkv_rope_append(
+            x.data_ptr(), norm_weight.data_ptr(), float(norm_eps), packed.data_ptr(), scales.data_ptr(), _ptr(zero_points),
+            out.data_ptr(), m, n, k, F16 if scales.dtype == torch.float16 else F32, x.stride(0), layout, q_dim, k_dim,
+            head_dim, float(theta), table.data_ptr(), int(table.shape[0]), positions.data_ptr(), page_table.data_ptr(),
+            int(page_table.shape[1]), page_size, k_cache.data_ptr(), v_cache.data_ptr(), workspace.data_ptr(),
+            workspace.numel() * workspace.element_size(), _stream()), "rmsnorm_qkv_rope_append")
+        return out
     check(_lib.load().cacheir_b200_qkv_rope_append(
         _ptr(x), packed.data_ptr(), scales.data_ptr(), _ptr(zero_points), out.data_ptr(), m, n, k,
         F16 if scales.dtype == torch.float16 else F32, 0 if x is None else x.stride(0),
-        (1 if tiled else 0) | (2 if prequantized else 0), q_dim, k_dim, head_dim, float(theta),
+        layout, q_dim, k_dim, head_dim, float(theta),
         table.data_ptr(), int(table.shape[0]), positions.data_ptr(), page_table.data_ptr(),
         int(page_table.shape[1]), page_size, k_cache.data_ptr(), v_cache.data_ptr(), workspace.data_ptr(),
         workspace.numel() * workspace.element_size(), _stream()), "qkv_rope_append")

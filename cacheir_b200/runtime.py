@@ -33,7 +33,7 @@ import torch
 
 from . import ops
 from .artifact import CompileArtifact
-from .kv_cache import B200KVPageAllocator, B200PagedKVCache
+from .kv_cache import B200KVPageAllocator, B200PagedKVCache, KVPoolExhausted
 from .quantization import B200PackedWeight, concat_rows, quant_bits, to_tiled
 from .tensor_parallel import PeerCollectives, TensorParallel, shard_columns, shard_rows
 from .weights import B200WeightStore, TensorSource
@@ -361,6 +361,12 @@ class _DecodePlan:
                 role = "replicated"
                 if tp.enabled:   # o / down consume a rank-local activation slice; lm_head produces a vocabulary slice
                     role = {"o": "row", "down": "row", "lm_head": "column"}.get(projection, "replicated")
+                    if role == "replicated":
+                        # a stand-alone q / k / v / gate / up projection would stay full width while attention, the cache
+                        # append and the row-parallel projections work on this rank's heads and columns only
+                        raise NotImplementedError(
+                            f"tensor parallelism needs the fused graph (fused QKV and SwiGLU ops): found a separate matmul "
+                            f"{node.name or node.outputs[0]!r} with projection {projection!r}")
                 weight = eng.matmul_weight((node.inputs[1],), op == "quantized_matmul", self.batch, role)
                 out_name = node.outputs[0]
                 nxt = nodes[idx + 1] if idx + 1 < len(nodes) else None
@@ -443,6 +449,8 @@ class _DecodePlan:
                 env[node.outputs[1]] = qkv[:, q_dim:q_dim + k_dim]
                 env[node.outputs[2]] = qkv[:, q_dim + k_dim:]
             elif op == "qkv_projection":
+                if eng.tp.enabled:
+                    raise NotImplementedError("tensor parallelism needs the fused graph: qkv_projection is not sharded")
                 x = env[node.inputs[0]]
                 for w_name, out_name in zip(node.inputs[1:4], node.outputs[:3]):
                     env[out_name] = self._matmul(x, eng.matmul_weight((w_name,), False))
@@ -673,6 +681,7 @@ class B200DecodeRuntime:
         max_plans: int = 8,
         clone_outputs: bool = True,
         tensor_parallel: TensorParallel | None = None,
+        memory_limit_mb: float | None = None,
         _engine: _Engine | None = None,
     ):
         if isinstance(artifact, (str, Path)):
@@ -705,6 +714,7 @@ class B200DecodeRuntime:
         self.kv_cache = B200PagedKVCache(_engine.allocator, int(_engine.config.num_layers))
         self.clone_outputs = clone_outputs
         self.oom_recoveries = 0
+        self.memory_limit_mb = memory_limit_mb
 
     @classmethod
     def available(cls) -> bool:
@@ -712,17 +722,56 @@ class B200DecodeRuntime:
 
     def fork(self) -> "B200DecodeRuntime":
         """Independent KV session sharing weights, page pools, plans and prefix cache (cuda.py:491-506)."""
-        return B200DecodeRuntime(self.artifact, clone_outputs=self.clone_outputs, _engine=self._engine)
+        return B200DecodeRuntime(self.artifact, clone_outputs=self.clone_outputs, memory_limit_mb=self.memory_limit_mb,
+                                 _engine=self._engine)
 
     # -- decode ----------------------------------------------------------------------
     def run_decode_batch(self, sessions: list["B200DecodeRuntime"], token_ids: list[int] | tuple[int, ...]) -> torch.Tensor:
         """Advance one decode token for several sessions; returns logits [N, 1, vocab] (cuda.py:541-582)."""
-        plan = self._prepare_batch(sessions, token_ids)
-        with torch.cuda.device(self.device):
-            plan.run_program()
+        self._enforce_memory_limit()
+        try:
+            plan = self._prepare_batch(sessions, token_ids)
+            with torch.cuda.device(self.device):
+                plan.run_program()
+        except (torch.cuda.OutOfMemoryError, KVPoolExhausted) as exc:
+            self._recover_from_oom()
+            raise RuntimeError("CacheIR CUDA batch decode recovered from an out-of-memory condition; "
+                               "retry with fewer active requests") from exc
         self._engine.count("cacheir.b200_decode_batch_graph")
         logits = plan.logits.view(len(sessions), 1, -1)
         return logits.clone() if self.clone_outputs else logits
+
+    # -- memory pressure (cuda.py:696-714) ----------------------------------------------
+    def _enforce_memory_limit(self) -> None:
+        """`memory_limit_mb` is a soft cap on this device's allocated memory: above it the session drops its
+        own KV pages and cached blocks first and raises only if that was not enough."""
+        if self.memory_limit_mb is None:
+            return
+        limit = float(self.memory_limit_mb)
+        if float(torch.cuda.memory_allocated(self.device)) / (1024.0 * 1024.0) <= limit:
+            return
+        self._recover_from_oom()
+        after = float(torch.cuda.memory_allocated(self.device)) / (1024.0 * 1024.0)
+        if after > limit:
+            raise RuntimeError(f"CacheIR CUDA memory limit exceeded: {after:.1f} MB allocated after recovery, "
+                               f"limit is {limit:.1f} MB")
+
+    def _recover_from_oom(self) -> None:
+        """What the reference does after an allocation failure: count it, give this session's pages back to the
+        pool, return cached blocks to the driver. The step that failed is not retried here."""
+        self.oom_recoveries += 1
+        self.kv_cache.clear()
+        self._engine.validated_batch = None
+        torch.cuda.empty_cache()
+
+    def _check_positions(self, sessions) -> None:
+        """The cos/sin table and the page-table width cover `max_seq_len` positions; a longer sequence would read
+        RoPE angles outside the table (left unrotated, flagged only in the device status word)."""
+        limit = self._engine.max_seq_len
+        for session in sessions:
+            if session.kv_cache.tokens > limit:
+                raise ValueError(f"sequence of {session.kv_cache.tokens} tokens exceeds max_seq_len={limit}; "
+                                 "construct the runtime with a larger max_seq_len")
 
     def _prepare_batch(self, sessions, token_ids) -> _DecodePlan:
         if not sessions:
@@ -743,6 +792,7 @@ class B200DecodeRuntime:
         with torch.cuda.device(self.device):
             for session in sessions:
                 session.kv_cache.extend(1)      # opens a page when the new token starts one
+            self._check_positions(sessions)
             plan = self._engine.plan_for(list(sessions))
             plan.sync_sessions(list(sessions))
             ids = plan.host_ids.numpy()
@@ -761,6 +811,7 @@ class B200DecodeRuntime:
         with torch.cuda.device(self.device):
             for session in sessions:          # reserve the pages of the remaining steps up front
                 session.kv_cache.extend(steps - 1)
+            self._check_positions(sessions)
             if any(len(s.kv_cache.pages) > plan.width for s in sessions):
                 raise RuntimeError("decode_greedy_batch would outgrow the plan's page table; raise max_seq_len")
             if plan.pool_generation != self._engine.allocator.generation:
@@ -795,7 +846,13 @@ class B200DecodeRuntime:
         tokens = [int(t) for t in ids[0]]
         chunk = self._engine.prefill_chunk
         if mode == "prefill" and chunk > 1 and len(tokens) > chunk // 4:
-            return self._prefill_chunked(tokens, chunk)
+            self._enforce_memory_limit()
+            try:
+                return self._prefill_chunked(tokens, chunk)
+            except (torch.cuda.OutOfMemoryError, KVPoolExhausted) as exc:
+                self._recover_from_oom()
+                raise RuntimeError("CacheIR CUDA runtime recovered from an out-of-memory condition; "
+                                   "retry with a smaller batch/context") from exc
         steps = []
         keep = self.clone_outputs
         self.clone_outputs = True
@@ -821,6 +878,7 @@ class B200DecodeRuntime:
                 part = tokens[c0:c0 + chunk]
                 start = cache.tokens
                 cache.extend(len(part))
+                self._check_positions([self])
                 needed = (cache.tokens + eng.page_size - 1) // eng.page_size
                 plan = eng.prefill_plan(chunk, needed)
                 plan.sync_prefill_chunk(cache, start, part)
@@ -905,11 +963,24 @@ class B200DecodeRuntime:
         stats["kernel_counts"] = dict(self.kernel_counts)
         stats["gemm_plans"] = dict(self.gemm_plans)
         stats["oom_recoveries"] = self.oom_recoveries
-        stats["memory_limit_mb"] = None
+        stats["memory_limit_mb"] = self.memory_limit_mb
         return stats
 
     def synchronize(self) -> None:
         torch.cuda.synchronize(self.device)
+        if self._engine.tp.enabled and self._engine.peer_mode:
+            self.check_device_status()
+
+    def check_device_status(self) -> None:
+        """Raise if a bounded device wait gave up since the last check (a tensor-parallel peer that never answered,
+        a pipeline barrier that never completed): the outputs of that step are undefined. Synchronises the device
+        and clears the word."""
+        from . import _lib
+        with torch.cuda.device(self.device):
+            status = int(_lib.load().cacheir_b200_device_status(1))
+        if status != 0:
+            raise RuntimeError(f"cacheir_b200 device status {status:#x}: a bounded wait on the GPU gave up "
+                               f"(kernel class {status >> 8}, wait {status & 0xFF}); the last results are undefined")
 
 
 def create_runtime(artifact: Any, *, backend: str = "auto", **kwargs) -> B200DecodeRuntime:

@@ -208,6 +208,16 @@ class PeerCollectives:
                                                      ops.dtype_code(out.dtype), self.tp.rank, self.tp.world,
                                                      self.state.data_ptr(), ops._stream()), "peer_all_gather")
 
+    def set_poll_limit(self, polls: int) -> None:
+        """How many times a collective polls for a peer before it gives up (0: the library default, about a
+        second). A kernel that gives up records a code in the device status word and returns; until the host has
+        read and cleared that word (`device_status`), later collectives return at once."""
+        self.state[3] = int(polls)
+
+    def device_status(self, reset: bool = True) -> int:
+        """The library's device status word (0: every bounded wait so far was satisfied). Synchronises the device."""
+        return int(self._lib.cacheir_b200_device_status(1 if reset else 0))
+
     def close(self) -> None:
         """Unmap the peers' buffers and free the local ones (call on every rank, after a barrier)."""
         torch.cuda.synchronize(self.device)

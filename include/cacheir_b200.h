@@ -7,7 +7,8 @@
  *   - plain pointers and sizes only; every pointer is a DEVICE pointer owned
  *     by the caller for the duration of the launch, `stream` is a
  *     cudaStream_t passed as void*;
- *   - nothing here allocates, frees or synchronises;
+ *   - nothing here allocates, frees or synchronises, except where an entry point's
+ *     comment says so (cacheir_b200_peer_alloc / _free, cacheir_b200_device_status);
  *   - return value: 0 on success, a positive cudaError_t value when the CUDA
  *     runtime reported one, or a negative CACHEIR_B200_E* validation code.
  *     Non-positive extents return 0 without launching, exactly like the
@@ -165,7 +166,7 @@ int cacheir_b200_qgemv(const void* x, const void* packed, const void* scales,
  * int4 per-row weights with fp16 activations (K % 128 == 0, K <= 32768) run on the integer
  * tensor cores: the uint8 codes are fed to the MMA as they are (int4 nibbles are widened to
  * bytes in shared memory), and x is first turned into 16-bit fixed point per row (two
- * signed bytes, 2^-15 of the row maximum) in the workspace. Batches above 64 rows run as
+ * signed bytes, 2^-15 of the row maximum) in the workspace by a pre-pass kernel. Batches above 64 rows run as
  * 64-row chunks (128-row chunks on the fp16 tensor-core kernel, which takes 65..128 rows in
  * one launch with the activations as the 128-row operand). Other shapes ignore the
  * workspace. workspace may be NULL (then this is cacheir_b200_qgemv). The workspace is only used during the call's own kernels; two
@@ -177,6 +178,28 @@ int cacheir_b200_qgemv_ex(const void* x, const void* packed, const void* scales,
                           int x_dtype, int scale_dtype, long long x_stride,
                           int epilogue, int weight_layout, void* workspace,
                           size_t workspace_bytes, void* stream);
+
+/* RMSNorm in front of the projection: y = epilogue(rmsnorm(x; norm_weight, eps) . deq(W)^T), fp16 activations
+ * with dense rows, K <= 8192, int8 / int4 per-row weights on the integer tensor-core path only (the conditions of
+ * cacheir_b200_qgemv_ex with a workspace; otherwise CACHEIR_B200_EUNSUPPORTED: run cacheir_b200_rms_norm first).
+ *
+ * Replaces: `_rms_norm` (cacheir/runtime/cuda.py:889-895) followed by `_quantized_matmul` (:932-940) /
+ *   the quantized fused SwiGLU (:867-871), i.e. the body of the reference's fused_rmsnorm_* ops.
+ * Two launches: cacheir_b200_rms_norm_quantize into the workspace, then the GEMM on the quantized rows; the same
+ * results as those two calls, bit for bit. */
+int cacheir_b200_rmsnorm_qgemv(const void* x, const void* norm_weight, float eps, const void* packed,
+                               const void* scales, const float* zero_points, const void* residual,
+                               void* y, int M, int N, int K, int bits, int scale_dtype,
+                               long long x_stride, int epilogue, int weight_layout, void* workspace,
+                               size_t workspace_bytes, void* stream);
+
+/* Which kernel cacheir_b200_qgemv_ex would launch for these extents and flags (fp16 activations, aligned
+ * pointers): (family << 8) | detail, family 1 = integer tensor core with detail = its split-K factor,
+ * 2 = fp16 tensor core, 3 = CUDA cores; epilogue 3 asks about cacheir_b200_qkv_rope_append. Negative:
+ * the validation code the call would return. Launches nothing. No counterpart in the reference (its
+ * kernel choice is the declarative `attrs["kernel"]`, cacheir/passes/transformer.py:391-424). */
+int cacheir_b200_qgemv_plan(int M, int N, int K, int bits, int group_size, int epilogue,
+                            int weight_layout, int with_workspace);
 
 /* The fused QKV projection of a decode step on int8 weights (fp16 activations, M <= 64):
  * qkv[M, N] = x W^T with W = [Wq; Wk; Wv] (N = q_dim + 2*k_dim), then, in the same kernel,
@@ -202,6 +225,18 @@ int cacheir_b200_qkv_rope_append(const void* x, const void* packed, const void* 
                                  const int32_t* page_table, int max_pages_per_seq, int page_size,
                                  void* k_cache, void* v_cache, void* workspace,
                                  size_t workspace_bytes, void* stream);
+/* The same with the RMSNorm of the reference's `quantized_fused_rmsnorm_qkv_rope` op
+ * (cacheir/runtime/cuda.py:812-820) in front, as in cacheir_b200_rmsnorm_qgemv (norm + pre-pass kernel, then this kernel). */
+int cacheir_b200_rmsnorm_qkv_rope_append(const void* x, const void* norm_weight, float eps,
+                                         const void* packed, const void* scales,
+                                         const float* zero_points, void* qkv, int M, int N, int K,
+                                         int scale_dtype, long long x_stride, int weight_layout,
+                                         int q_dim, int k_dim, int head_dim, float theta,
+                                         const float* rope_table, int rope_table_positions,
+                                         const int32_t* positions, const int32_t* page_table,
+                                         int max_pages_per_seq, int page_size, void* k_cache,
+                                         void* v_cache, void* workspace, size_t workspace_bytes,
+                                         void* stream);
 /* table[pos][i] = (cos, sin)(pos * theta^(-2i/head_dim)) in fp32 for pos < positions, the
  * values cacheir_b200_rope_inplace evaluates on the fly. 8 * positions * head_dim/2 bytes. */
 int cacheir_b200_rope_table(float* table, int positions, int head_dim, float theta, void* stream);

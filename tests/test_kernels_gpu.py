@@ -441,6 +441,104 @@ def test_qgemm_int8_tensor_core_epilogues_offsets_and_determinism():
     _device_status_ok()
 
 
+# ---- the GEMM's own pre-pass == the stand-alone pre-pass entry point; strided activations; RMSNorm in front ----
+@pytest.mark.parametrize("m", [1, 7, 17, 32, 64])
+@pytest.mark.parametrize("n,k,tiled", [(512, 1024, True), (200, 256, False), (2304, 2048, True)])
+def test_qgemm_int8_prepass_forms_agree(m, n, k, tiled):
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import to_tiled
+    rng = np.random.default_rng(m * 13 + n + k)
+    x, packed = _qgemv_case(rng, m, n, k, 8, torch.float16)
+    x = (x.float() * torch.from_numpy(rng.uniform(0.01, 30.0, (m, 1)).astype(np.float32))).half()   # rows of very different size
+    dev = to_tiled(_device_pack(packed)) if tiled else _device_pack(packed)
+    ws = torch.zeros(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
+    kw = dict(bits=8, n=n, k=k, workspace=ws, tiled=tiled)
+    xd = x.cuda()
+    assert ops.qgemv_plan(m, n, k, bits=8, tiled=tiled)["family"] == "i8"
+    direct = ops.qgemv(xd, dev.packed_values, dev.scales, dev.zero_points, **kw)
+    ops.quantize_activations(xd, ws)
+    prequantized = ops.qgemv(xd, dev.packed_values, dev.scales, dev.zero_points, prequantized=True, **kw)
+    _device_status_ok()
+    assert torch.equal(direct, prequantized)                  # the same fixed-point integers, so the same bits
+    assert _rel(direct, oracle.quantized_matmul(x.float().numpy(), packed)) <= TOL[torch.float16]
+    # a strided view of a wider buffer (what the runtime passes for q / k / v slices)
+    wide = torch.zeros((m, k + 64), dtype=torch.float16, device="cuda")
+    wide[:, 8:8 + k] = xd
+    strided = ops.qgemv(wide[:, 8:8 + k], dev.packed_values, dev.scales, dev.zero_points, **kw)
+    assert torch.equal(strided, direct)
+    _device_status_ok()
+
+
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("n,k,tiled", [(512, 1024, True), (200, 256, False), (128, 4096, True), (2304, 2048, False)])
+def test_rmsnorm_in_front_of_the_integer_gemm(m, n, k, tiled):
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul, to_tiled
+    rng = np.random.default_rng(m * 17 + n + k)
+    x, packed = _qgemv_case(rng, m, n, k, 8, torch.float16)
+    x = (x.float() * torch.from_numpy(rng.uniform(0.05, 20.0, (m, 1)).astype(np.float32))).half()
+    w = torch.from_numpy((1.0 + 0.3 * rng.standard_normal(k)).astype(np.float32)).half()
+    dev = to_tiled(_device_pack(packed)) if tiled else _device_pack(packed)
+    ws = torch.zeros(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
+    fused = ops.qgemv(x.cuda(), dev.packed_values, dev.scales, dev.zero_points, bits=8, n=n, k=k, workspace=ws, tiled=tiled,
+                      norm_weight=w.cuda(), norm_eps=1e-5)
+    _device_status_ok()
+    # the same as its two launches called one by one, bit for bit
+    ops.rms_norm_quantize(x.cuda(), w.cuda(), 1e-5, ws)
+    two_calls = ops.qgemv(x.cuda(), dev.packed_values, dev.scales, dev.zero_points, bits=8, n=n, k=k, workspace=ws, tiled=tiled,
+                          prequantized=True)
+    assert torch.equal(fused, two_calls)
+    # and close to RMSNorm stored as fp16 followed by the GEMM with its own pre-pass, and to the oracle
+    normed = ops.rms_norm(x.cuda(), w.cuda(), 1e-5)
+    two_step = quantized_matmul(normed, dev, workspace=ws)
+    want = oracle.quantized_matmul(oracle.rms_norm(x.float().numpy(), w.float().numpy(), 1e-5), packed)
+    assert _rel(fused, want) <= TOL[torch.float16]
+    assert _rel(fused, two_step.float().cpu().numpy()) <= 1e-3
+    # an all-zero row stays zero (rms -> eps)
+    x0 = x.clone()
+    x0[0] = 0
+    out0 = ops.qgemv(x0.cuda(), dev.packed_values, dev.scales, dev.zero_points, bits=8, n=n, k=k, workspace=ws, tiled=tiled,
+                     norm_weight=w.cuda(), norm_eps=1e-5)
+    assert float(out0[0].abs().max()) == 0.0 and torch.equal(out0[1:], fused[1:])
+    _device_status_ok()
+
+
+def test_rmsnorm_qkv_rope_append_equals_its_two_launches():
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import to_tiled
+    rng = np.random.default_rng(77)
+    m, k, head_dim, heads, kv_heads, page, max_pages, theta = 19, 1024, 128, 4, 2, 16, 6, 10000.0
+    q_dim, k_dim = heads * head_dim, kv_heads * head_dim
+    n = q_dim + 2 * k_dim
+    x, packed = _qgemv_case(rng, m, n, k, 8, torch.float16)
+    weight = to_tiled(_device_pack(packed))
+    w = torch.from_numpy((1.0 + 0.3 * rng.standard_normal(k)).astype(np.float32)).half().cuda()
+    slots = m * max_pages + 3
+    table_np = rng.permutation(slots)[: m * max_pages].astype(np.int32).reshape(m, max_pages)
+    pos_np = rng.integers(0, page * max_pages, m).astype(np.int32)
+    positions, page_table = torch.from_numpy(pos_np).cuda(), torch.from_numpy(table_np).cuda()
+    pool = lambda: torch.zeros((slots, kv_heads, page, head_dim), dtype=torch.float16, device="cuda")
+    k_a, v_a, k_b, v_b = pool(), pool(), pool(), pool()
+    ws = torch.zeros(ops.qgemv_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
+    rope = ops.rope_table(page * max_pages, head_dim, theta, "cuda")
+    common = dict(n=n, k=k, q_dim=q_dim, k_dim=k_dim, head_dim=head_dim, theta=theta, table=rope, positions=positions,
+                  page_table=page_table, workspace=ws, tiled=True)
+    xd = x.cuda()
+    fused = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    ops.qkv_rope_append(xd, weight.packed_values, weight.scales, weight.zero_points, fused, k_cache=k_a, v_cache=v_a,
+                        norm_weight=w, norm_eps=1e-5, **common)
+    ops.rms_norm_quantize(xd, w, 1e-5, ws)
+    ref = torch.empty_like(fused)
+    ops.qkv_rope_append(None, weight.packed_values, weight.scales, weight.zero_points, ref, k_cache=k_b, v_cache=v_b,
+                        prequantized=True, **common)
+    _device_status_ok()
+    assert torch.equal(fused, ref) and torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
+    for b in range(m):     # the appended rows are bit copies of the k / v columns of the same launch
+        slot, off = int(table_np[b, pos_np[b] // page]), int(pos_np[b] % page)
+        assert torch.equal(k_a[slot, :, off].reshape(-1), fused[b, q_dim:q_dim + k_dim])
+        assert torch.equal(v_a[slot, :, off].reshape(-1), fused[b, q_dim + k_dim:])
+
+
 # ---- device pack layout: tile order is an exact permutation and changes no result ---------
 @pytest.mark.parametrize("bits", [8, 4])
 @pytest.mark.parametrize("n,k", [(512, 1024), (200, 256), (128, 4096)])

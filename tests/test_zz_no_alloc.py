@@ -77,3 +77,9 @@ def test_noalloc_entry_refuses_sizes_beyond_its_array():
     assert b"maximum" in lib.cacheir_b200_error_string(rc)
     rc, out = _call_noalloc(lib, q, k, v, table, seq, 1)    # one split needs no scratch
     assert rc == 0 and torch.isfinite(out).all()
+    # fewer query heads than KV heads is an argument error (checked on the host, before the split count is worked out)
+    rc = lib.cacheir_b200_paged_attention_decode_batch_noalloc(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), table.data_ptr(), seq.data_ptr(), out.data_ptr(),
+        64, 4, 8, table.shape[1], 16, 128, 1, 0, 0, 0.0, 0, torch.cuda.current_stream().cuda_stream)
+    assert rc == -1
+    assert lib.cacheir_b200_paged_attention_auto_splits(64, 4, 8, int(table.shape[1]), 16, 128) == 1
