@@ -259,6 +259,8 @@ int qgemv_dispatch(const void* x, const void* norm_weight, float norm_eps, const
       return 0;
     }
   }
+  // up to 8 batch rows of int4 codes in row order: the streaming GEMV reads every code once and needs no pre-pass
+  if (qgemv_mma_supported(p)) return plan_only ? (4 << 8) : launch_qgemv_mma(p, st);
   if (qgemm_i8_supported(p, workspace, workspace_bytes))
     return plan_only ? ((1 << 8) | qgemm_i8_plan(p)) : launch_qgemm_i8(p, workspace, st);
   if (norm_weight) return CACHEIR_B200_EUNSUPPORTED;  // the fused norm exists on the integer path only: run cacheir_b200_rms_norm first

@@ -42,6 +42,9 @@ struct QGemvParams {
 };
 
 int launch_qgemv_cuda_core(const QGemvParams& p, cudaStream_t stream);
+// Streaming int4 GEMV for up to 8 batch rows (mma.sync on nibbles unpacked in registers, row-major codes).
+bool qgemv_mma_supported(const QGemvParams& p);
+int launch_qgemv_mma(const QGemvParams& p, cudaStream_t stream);
 
 // Tensor-core (tcgen05) small-M GEMM: weights are the 128-row MMA operand.
 bool qgemm_tc_supported(const QGemvParams& p);

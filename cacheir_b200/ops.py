@@ -165,13 +165,13 @@ def qgemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor | None, ze
 
 def qgemv_plan(m: int, n: int, k: int, *, bits: int, group_size: int = 0, epilogue: int = EPI_NONE, tiled: bool = False,
                prequantized: bool = False, paired: bool = False, workspace: bool = True) -> dict:
-    """Which kernel `qgemv` launches for these extents: {"family": "i8"|"f16"|"cuda_core", "split_k"}.
+    """Which kernel `qgemv` launches for these extents: {"family": "i8"|"f16"|"cuda_core"|"stream_int4", "split_k"}.
     epilogue 3 asks about `qkv_rope_append`."""
     layout = (1 if tiled else 0) | (2 if prequantized else 0) | (4 if paired else 0)
     code = int(_lib.load().cacheir_b200_qgemv_plan(int(m), int(n), int(k), int(bits), int(group_size), int(epilogue), layout,
                                                    1 if workspace else 0))
     check(code if code < 0 else 0, "qgemv_plan")
-    family = {1: "i8", 2: "f16", 3: "cuda_core"}[code >> 8]
+    family = {1: "i8", 2: "f16", 3: "cuda_core", 4: "stream_int4"}[code >> 8]
     return {"family": family, "split_k": (code & 255) if family == "i8" else 1}
 
 

@@ -195,7 +195,8 @@ int cacheir_b200_rmsnorm_qgemv(const void* x, const void* norm_weight, float eps
 
 /* Which kernel cacheir_b200_qgemv_ex would launch for these extents and flags (fp16 activations, aligned
  * pointers): (family << 8) | detail, family 1 = integer tensor core with detail = its split-K factor,
- * 2 = fp16 tensor core, 3 = CUDA cores; epilogue 3 asks about cacheir_b200_qkv_rope_append. Negative:
+ * 2 = fp16 tensor core, 3 = CUDA cores, 4 = streaming int4 GEMV (up to 8 rows); epilogue 3 asks about
+ * cacheir_b200_qkv_rope_append. Negative:
  * the validation code the call would return. Launches nothing. No counterpart in the reference (its
  * kernel choice is the declarative `attrs["kernel"]`, cacheir/passes/transformer.py:391-424). */
 int cacheir_b200_qgemv_plan(int M, int N, int K, int bits, int group_size, int epilogue,

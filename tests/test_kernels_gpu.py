@@ -539,6 +539,50 @@ def test_rmsnorm_qkv_rope_append_equals_its_two_launches():
         assert torch.equal(v_a[slot, :, off].reshape(-1), fused[b, q_dim + k_dim:])
 
 
+# ---- streaming int4 GEMV (up to 8 batch rows, row-major codes): group-wise and the reference's per-row form ----
+@pytest.mark.parametrize("m", [1, 2, 5, 8])
+@pytest.mark.parametrize("n,k,group", [(200, 256, 128), (48, 1024, 128), (512, 4096, 128), (96, 8192, 256), (64, 14336, 128),
+                                       (200, 512, 0), (1024, 4096, 0), (33, 9216, 0)])
+def test_streaming_int4_gemv_small_batches(m, n, k, group):
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(m * 1000 + n + k + group)
+    x, packed = _qgemv_case(rng, m, n, k, 4, torch.float16, group=group)
+    dev = _device_pack(packed)
+    assert ops.qgemv_plan(m, n, k, bits=4, group_size=group, workspace=False)["family"] == "stream_int4"
+    want = oracle.quantized_matmul(x.float().numpy(), packed)
+    y = quantized_matmul(x.cuda(), dev)
+    assert y.shape == (m, n)
+    assert _rel(y, want) <= TOL[torch.float16]
+    assert torch.equal(y, quantized_matmul(x.cuda(), dev))          # fixed order of additions: the same bits every time
+    # a row-strided view of a wider buffer, and the residual epilogue
+    wide = torch.zeros((m, k + 32), dtype=torch.float16, device="cuda")
+    wide[:, 16:16 + k] = x.cuda()
+    assert torch.equal(quantized_matmul(wide[:, 16:16 + k], dev), y)
+    res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).half()
+    yr = quantized_matmul(x.cuda(), dev, epilogue=ops.EPI_RESIDUAL, residual=res.cuda())
+    assert _rel(yr, want + res.float().numpy()) <= TOL[torch.float16]
+
+
+def test_streaming_int4_gemv_swiglu_and_unclipped_zero_points():
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(4242)
+    m, n, k = 3, 256, 1024
+    for group in (128, 0):
+        x, packed = _qgemv_case(rng, m, n, k, 4, torch.float16, group=group)
+        dev = _device_pack(packed)
+        if group == 0:
+            dev.zero_points[5] = 100.0          # the reference packer does not clip zero points
+            dev.zero_points[9] = 7.5
+            packed = oracle.PackedQuantizedTensor(packed.packed_values, packed.scales, dev.zero_points.cpu().numpy(), 4, (n, k))
+        base = oracle.quantized_matmul(x.float().numpy(), packed)
+        y = quantized_matmul(x.cuda(), dev, epilogue=ops.EPI_SWIGLU)
+        assert y.shape == (m, n // 2)
+        assert _rel(y, oracle.silu_mul(base[:, : n // 2], base[:, n // 2:])) <= 2 * TOL[torch.float16]
+        assert _rel(quantized_matmul(x.cuda(), dev), base) <= TOL[torch.float16]
+
+
 # ---- device pack layout: tile order is an exact permutation and changes no result ---------
 @pytest.mark.parametrize("bits", [8, 4])
 @pytest.mark.parametrize("n,k", [(512, 1024), (200, 256), (128, 4096)])
