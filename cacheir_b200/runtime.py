@@ -162,7 +162,9 @@ class _Engine:
         self._rope_tables: dict[tuple[int, float], torch.Tensor] = {}
         self.attention_splits = int(attention_splits)
         self.max_plans = max(1, int(max_plans))
-        self.plans: OrderedDict[tuple[str, ...], "_DecodePlan"] = OrderedDict()
+        self.plans: OrderedDict[tuple, "_DecodePlan"] = OrderedDict()
+        self.plans_lowered = 0          # decode graphs lowered to launch lists so far
+        self.graph_captures = 0         # CUDA graphs captured so far
         self.kernel_counts: OrderedDict[str, int] = OrderedDict()
         self.gemm_plans: OrderedDict[str, str] = OrderedDict()
         self.fused_weights: dict[tuple[str, ...], B200PackedWeight | torch.Tensor] = {}
@@ -243,6 +245,7 @@ class _Engine:
         if plan is None:
             width = max(needed_pages, (self.max_seq_len + self.page_size - 1) // self.page_size)
             plan = _DecodePlan(self, rows, width)
+            self.plans_lowered += 1
             self.plans[key] = plan
             while len(self.plans) > self.max_plans:
                 self.plans.popitem(last=False)
@@ -251,7 +254,11 @@ class _Engine:
         return plan
 
     def plan_for(self, sessions: list["B200DecodeRuntime"]) -> "_DecodePlan":
-        key = tuple(s.kv_cache.owner_id for s in sessions)
+        """The plan for a decode batch of this size. Plans are keyed by batch size, not by who is in the batch:
+        a session is bound to a row for one step only, and `sync_sessions` rewrites the rows whose occupant,
+        length or page list changed. Admitting or retiring a request therefore costs a few small copies, not
+        a new lowering and a new CUDA-graph capture."""
+        key = ("decode", len(sessions))
         plan = self.plans.get(key)
         needed_pages = max((s.kv_cache.tokens + 1 + self.page_size - 1) // self.page_size for s in sessions)
         if plan is not None and (plan.pool_generation != self.allocator.generation or plan.width < needed_pages):
@@ -260,6 +267,7 @@ class _Engine:
         if plan is None:
             width = max(needed_pages, (self.max_seq_len + self.page_size - 1) // self.page_size)
             plan = _DecodePlan(self, len(sessions), width)
+            self.plans_lowered += 1
             self.plans[key] = plan
             while len(self.plans) > self.max_plans:
                 self.plans.popitem(last=False)
@@ -634,6 +642,7 @@ class _DecodePlan:
                     if feedback:
                         self.feedback_tail()
                 setattr(self, attr, graph)
+                eng.graph_captures += 1
             graph.replay()
         else:
             for fn in self.program:
@@ -962,6 +971,8 @@ class B200DecodeRuntime:
         stats["prefix_cache"] = self.prefix_cache.stats()
         stats["kernel_counts"] = dict(self.kernel_counts)
         stats["gemm_plans"] = dict(self.gemm_plans)
+        stats["plans_lowered"] = self._engine.plans_lowered
+        stats["graph_captures"] = self._engine.graph_captures
         stats["oom_recoveries"] = self.oom_recoveries
         stats["memory_limit_mb"] = self.memory_limit_mb
         return stats

@@ -199,3 +199,87 @@ def test_wide_batches_match_single_sequence_decoding(batch):
         assert oracle.rel_l2(wide2[i], a2) <= 4e-3
     from cacheir_b200 import _lib
     assert _lib.load().cacheir_b200_device_status(1) == 0
+
+
+# ---- the batched-decode launcher on the real runtime: changing batch composition, row slots, limits ----
+def test_launcher_on_the_b200_runtime_batched_equals_one_at_a_time(golden_dir, tmp_path):
+    """What the reference checks for its scheduler (tests/test_scheduler.py:146-183): requests decoded together give
+    the ids they get one at a time, and the counters add up -- here on the CUDA runtime, with token budgets that
+    make requests retire at different rounds, so the batch shrinks and refills while it runs."""
+    from cacheir_b200.scheduler import BatchedDecodeLauncher
+
+    rt, meta, g = _tiny(golden_dir, "int8", tmp_path, dtype="float16", max_seq_len=128)
+    prompt = g["prompt"].tolist()
+    requests = [(prompt[:7], 5), (prompt[3:30], 12), (prompt[10:11], 3), (prompt[:32], 9), (prompt[5:9], 12), (prompt[20:28], 1)]
+
+    def run(max_batch):
+        launcher = BatchedDecodeLauncher(rt, max_batch_size=max_batch)
+        ids = [launcher.submit(p, max_new_tokens=n) for p, n in requests]
+        results = launcher.run_until_complete()
+        return [results[i] for i in ids], launcher.metrics
+
+    lowered_before = rt.cache_stats()["plans_lowered"]
+    batched, metrics = run(4)
+    single, single_metrics = run(1)
+    assert batched == single
+    assert [len(t) for t in batched] == [n for _, n in requests]
+    assert metrics.completed_requests == len(requests) and metrics.generated_tokens == sum(n for _, n in requests)
+    assert metrics.batched_decode_tokens == metrics.generated_tokens
+    assert metrics.batched_decode_rounds < single_metrics.batched_decode_rounds
+    # plans are keyed by batch size: four sizes were seen (4, 3, 2, 1), however often the occupants changed
+    stats = rt.cache_stats()
+    assert stats["plans_lowered"] - lowered_before <= 4 + 1          # + the prefill plan
+    assert stats["graph_captures"] <= stats["plans_lowered"] + 4
+    rt.synchronize()
+    from cacheir_b200 import _lib
+    assert _lib.load().cacheir_b200_device_status(1) == 0
+
+
+def test_reference_scheduler_drives_the_b200_runtime(golden_dir, tmp_path):
+    """The reference's own ContinuousBatchScheduler (cacheir/runtime/scheduler.py:109, 456-478, 508-509) accepts any
+    object with the runtime duck type. Runs where the reference package is importable."""
+    cacheir_scheduler = pytest.importorskip("cacheir.runtime.scheduler")
+    rt, meta, g = _tiny(golden_dir, "int8", tmp_path, dtype="float16", max_seq_len=256)
+    prompts = ["paged attention", "decode", "a longer prompt that spans more than one page of sixteen tokens", "kv"]
+    budgets = [6, 11, 4, 9]
+
+    def run(max_batch):
+        sched = cacheir_scheduler.ContinuousBatchScheduler(rt, max_batch_size=max_batch, use_prefix_cache=False)
+        for p, n in zip(prompts, budgets):
+            sched.submit(p, max_new_tokens=n)
+        results = sched.run_until_complete()
+        return {r.request_id: list(r.generated_ids) for r in results}, sched.metrics
+
+    batched, metrics = run(4)
+    single, _ = run(1)
+    assert batched == single
+    assert metrics.batched_decode_rounds > 0 and metrics.completed_requests == len(prompts)
+
+
+def test_pool_exhaustion_and_position_limit_are_reported_like_the_reference(golden_dir, tmp_path):
+    from cacheir_b200 import B200KVPageAllocator
+    rt, meta, g = _tiny(golden_dir, "fp32", tmp_path, dtype="float32", max_seq_len=64,
+                        kv_allocator=B200KVPageAllocator(page_size=16, initial_slots=3, max_slots=3))
+    prompt = g["prompt"].tolist()
+    s = rt.fork()
+    s.run([prompt[:30]], mode="prefill")                 # two pages
+    t = rt.fork()
+    t.run([prompt[:10]], mode="prefill")                 # the third and last page
+    # the next page cannot be allocated: wrapped like the reference's out-of-memory path (cuda.py:577-579), the caller's
+    # session is cleared and counted
+    with pytest.raises(RuntimeError, match="out-of-memory"):
+        for tok in range(10):
+            s.run_decode_batch([s], [tok])
+    assert s.oom_recoveries == 1 and s.kv_cache.tokens == 0
+    assert s.cache_stats()["oom_recoveries"] == 1
+    # the freed pages serve a new request
+    u = rt.fork()
+    u.run([prompt[:20]], mode="prefill")
+    assert u.kv_cache.tokens == 20
+    # a sequence may not grow past the cos/sin table
+    rt2, _, _ = _tiny(golden_dir, "fp32", tmp_path / "b", dtype="float32", max_seq_len=40)
+    v = rt2.fork()
+    v.run([prompt[:32]], mode="prefill")
+    with pytest.raises(ValueError, match="max_seq_len"):
+        for tok in range(12):
+            v.run_decode_batch([v], [tok])
