@@ -64,6 +64,22 @@ WORKLOADS = {
 }
 
 
+ATTENTION_TRAFFIC_RATIO = 1.024     # ncu: DRAM bytes / algorithmic bytes of the paged decode attention kernel
+
+
+def workload_config(cfg: dict, workload: str, world: int, tp: bool) -> dict:
+    """The `config` object of a result line; both arms (B200 and the CPU reference arm) print the same keys."""
+    return {"workload": workload, "batch_per_gpu": cfg["batch"],
+            "context": (f"log-uniform {cfg['ctx_range'][0]}..{cfg['ctx_range'][1]} (mean {cfg['ctx_mean']}), "
+                        f"{cfg['shared_prefix'][0]}-way shared {cfg['shared_prefix'][1]}-token prefixes"
+                        if "ctx_range" in cfg else cfg["ctx"]),
+            "layers": cfg["layers"],
+            "weights": ("int4 group-128 symmetric (fp16 scales)" if "g128" in cfg["quant"]
+                        else "int8 per-row affine (fp32 scale+zero)"), "kv": "fp16 pages of 16",
+            "parallelism": (f"tp{world}: heads and FFN split, own all-reduce kernels over NVLink peer memory" if tp
+                            else f"dp{world} by sequence, no collective"), "l2_policy": "inputs larger than L2 (16 GB/step)"}
+
+
 def context_lengths(cfg: dict) -> list[int]:
     """Per-sequence context: the fixed `ctx`, or log-uniform in `ctx_range` (seed 0) for the ragged workloads."""
     if "ctx_range" not in cfg:
@@ -370,6 +386,28 @@ def make_cpu_sample(cfg: dict, batch: int, ctx: int, seed: int = 0):
     return rng, weights, kv, x
 
 
+def cpu_lm_head_seconds(cfg: dict, batch: int) -> float:
+    """The lm_head of one decode step with the reference's CPU algorithm (dequantize, then matmul), timed once over
+    the whole vocabulary in slices of 16384 rows (the dense fp32 form of the full weight would be 2 GB)."""
+    from oracle import oracle
+
+    rng = np.random.default_rng(7)
+    h, v = cfg["hidden"], cfg["vocab"]
+    bits = 8 if cfg["quant"] == "int8" else 4
+    x = rng.standard_normal((batch, 1, h), dtype=np.float32)
+    rows = 16384
+    codes = rng.integers(0, 1 << bits, (rows, h), dtype=np.uint8)
+    part = oracle.PackedQuantizedTensor(oracle.pack_int4(codes) if bits == 4 else codes, rng.uniform(1e-4, 2e-4, rows).astype(np.float32),
+                                        np.full(rows, 1 << (bits - 1), dtype=np.int32), bits, (rows, h))
+    oracle.quantized_matmul(x, part)       # warm
+    t0 = time.perf_counter()
+    done = 0
+    while done < v:
+        oracle.quantized_matmul(x, part)   # every slice costs the same: the codes' values do not matter for the time
+        done += rows
+    return (time.perf_counter() - t0) * min(1.0, v / done)
+
+
 def cpu_threads() -> int:
     try:
         from threadpoolctl import threadpool_info
@@ -396,14 +434,13 @@ def run_cpu_baseline(cfg: dict, budget_s: float = 20.0) -> dict:
         cpu_reference_layer_step(cfg, rng, weights, kv, x)
         times.append(time.perf_counter() - t0)
     layer_s = float(np.median(times))
-    layer_rows = 2 * cfg["hidden"] + 2 * cfg["kv_heads"] * (cfg["hidden"] // cfg["heads"]) + 3 * cfg["ffn"]
-    lm_head_s = layer_s * cfg["vocab"] / (layer_rows * 1.6)   # matmul share of a layer step, by rows
+    lm_head_s = cpu_lm_head_seconds(cfg, cfg["batch"])
     step_s = layer_s * cfg["layers"] + lm_head_s
     return {"value": cfg["batch"] / step_s, "unit": UNIT, "cores": cpu_threads(), "kind": "port",
             "sample": (f"{len(times)} x one decoder layer of one decode step (batch {cfg['batch']}, ctx {cfg['ctx']}; "
                        f"NumPy dequantize-then-matmul + gather attention"
                        f"{', reference C++/OpenMP rms_norm+silu_mul' if ref_native.available() else ''}), "
-                       f"median {layer_s:.3f} s/layer, extrapolated to {cfg['layers']} layers + lm_head")}
+                       f"median {layer_s:.3f} s/layer, extrapolated to {cfg['layers']} layers + the lm_head timed once ({lm_head_s:.2f} s)")}
 
 
 def run_reference_arm(args, cfg: dict, workload: str) -> None:
@@ -437,21 +474,151 @@ def run_reference_arm(args, cfg: dict, workload: str) -> None:
         done += 1
     elapsed = time.perf_counter() - t0
     layer_s = elapsed / max(1, done)
-    layer_rows = 2 * cfg["hidden"] + 2 * cfg["kv_heads"] * (cfg["hidden"] // cfg["heads"]) + 3 * cfg["ffn"]
-    step_s = layer_s * cfg["layers"] + layer_s * cfg["vocab"] / (layer_rows * 1.6)
+    lm_head_s = cpu_lm_head_seconds(cfg, sample_batch)
+    step_s = layer_s * cfg["layers"] + lm_head_s
     value = sample_batch / step_s
     sample = (f"each step = one decoder layer of one decode step (batch {sample_batch} of {cfg['batch']}, ctx {cfg['ctx']}) with "
               f"the reference CPU algorithm (NumPy dequantize-then-matmul, gather attention"
               f"{', reference C++/OpenMP rms_norm+silu_mul' if ref_native.available() else ''}); "
-              f"tokens/s extrapolated to {cfg['layers']} layers + lm_head")
+              f"tokens/s extrapolated to {cfg['layers']} layers + the lm_head timed once ({lm_head_s:.2f} s)")
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "ms_per_timed_step": layer_s * 1e3,
+            "timed_step": "one decoder layer of one decode step", "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload, "batch": cfg["batch"], "context": cfg["ctx"], "layers": cfg["layers"],
-                       "l2_policy": "inputs larger than L2"},
+            "config": workload_config(cfg, workload, world, False),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cpu_threads(), "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     emit(line)
+
+
+
+# --------------------------------------------------------------------------------------
+def parity_self_check(rt, sessions, cfg: dict) -> dict:
+    """Outside the timed region: the kernels of the first decoder layer, on this run's own device-generated
+    weights and page pool, against the CPU oracle (dequantize-then-matmul, gather attention). One fp16 batch of
+    activations goes through the entry points the step uses (RMSNorm + pre-pass, the tiled integer GEMMs with
+    their epilogues, paged decode attention); the worst rel-L2 is reported next to the 2e-3 gate."""
+    import torch
+
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import to_rows
+    from oracle import oracle
+
+    eng = rt._engine
+    dev = rt.device
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(99)
+    B = min(cfg["batch"], 32)
+    worst: dict[str, float] = {}
+
+    def host_pack(w):
+        rows = to_rows(w)
+        return oracle.PackedQuantizedTensor(rows.packed_values.cpu().numpy(), rows.scales.float().cpu().numpy() if not w.group_size else rows.scales.cpu().numpy(),
+                                            None if w.zero_points is None else w.zero_points.cpu().numpy(), w.bits, tuple(w.shape),
+                                            group_size=w.group_size or None)
+
+    def oracle_mm(x, packed):
+        out = []
+        for r0 in range(0, packed.shape[0], 8192):
+            r1 = min(packed.shape[0], r0 + 8192)
+            part = oracle.PackedQuantizedTensor(packed.packed_values[r0:r1], packed.scales[r0:r1],
+                                                None if packed.zero_points is None else packed.zero_points[r0:r1],
+                                                packed.bits, (r1 - r0, packed.shape[1]), group_size=packed.group_size)
+            out.append(oracle.quantized_matmul(x, part))
+        return np.concatenate(out, axis=-1)
+
+    for names, w in eng.fused_weights.items():
+        n0 = names[0]
+        if not n0.startswith("layer0_"):
+            continue
+        if not hasattr(w, "bits"):
+            continue
+        role = "qkv" if n0.endswith("_q_w") else "o" if n0.endswith("_o_w") else "gate_up" if n0.endswith("_gate_w") else "down" if n0.endswith("_down_w") else None
+        if role is None or role in worst:
+            continue
+        n, k = w.shape
+        x = torch.randn((B, k), device=dev, dtype=torch.float16, generator=gen)
+        ws = torch.zeros(ops.qgemv_workspace_bytes(B, k), device=dev, dtype=torch.uint8) if not w.group_size else None
+        epi = ops.EPI_SWIGLU if role == "gate_up" else ops.EPI_NONE
+        y = ops.qgemv(x, w.packed_values, w.scales, w.zero_points, bits=w.bits, n=n, k=k, group_size=w.group_size or 0,
+                      epilogue=epi, workspace=ws, tiled=w.tiled, paired=w.paired)
+        want = oracle_mm(x.float().cpu().numpy(), host_pack(w))
+        if role == "gate_up":
+            want = oracle.silu_mul(want[:, : n // 2], want[:, n // 2:])
+        worst[role] = oracle.rel_l2(y.float().cpu().numpy(), want) / (2.0 if role == "gate_up" else 1.0)   # a product of two projections
+    # attention over the real pool of layer 0 (its rows were written by the timed steps), first 4 sequences
+    hd = cfg["hidden"] // cfg["heads"]
+    tpw = eng.tp.world
+    H, KVH = cfg["heads"] // tpw, cfg["kv_heads"] // tpw
+    pool = rt.kv_allocator.pool_for_layer(0)
+    sub = sessions[:4]
+    width = max(len(s.kv_cache.pages) for s in sub)
+    table = np.stack([s.kv_cache.page_table_row(width) for s in sub]).astype(np.int32)
+    lens = np.array([min(s.kv_cache.tokens, 4096) for s in sub], dtype=np.int32)
+    q = torch.randn((len(sub), H, hd), device=dev, dtype=torch.float16, generator=gen)
+    out = ops.paged_attention_decode_batch(q, pool["keys"], pool["values"], torch.from_numpy(table).to(dev), torch.from_numpy(lens).to(dev))
+    used = np.unique(table)
+    remap = np.zeros(int(table.max()) + 1, dtype=np.int32)
+    remap[used] = np.arange(len(used), dtype=np.int32)
+    idx = torch.from_numpy(used.astype(np.int64)).to(dev)
+    want = oracle.paged_attention_decode(q.cpu().numpy(), pool["keys"][idx].cpu().numpy(), pool["values"][idx].cpu().numpy(), remap[table], lens)
+    worst["attention"] = oracle.rel_l2(out.float().cpu().numpy(), want)
+    torch.cuda.synchronize()
+    return {"rel_l2": round(max(worst.values()), 6), "gate": 2e-3, "per_kernel": {k: round(v, 6) for k, v in worst.items()},
+            "against": "CPU oracle on this run's layer-0 weights and page pool"}
+
+
+def tensor_parallel_parity(rank: int, world: int, local_rank: int) -> dict | None:
+    """A two-layer int8 model decoded tensor parallel on all ranks and on rank 0 alone, teacher-forced with the same
+    tokens: logits rel-L2 and whether the greedy tokens agree wherever the single-GPU top-1 / top-2 margin is clear."""
+    import zlib
+
+    import torch
+    import torch.distributed as dist
+
+    from cacheir_b200 import B200DecodeRuntime
+    from cacheir_b200.artifact import ModelConfig, build_decoder_artifact
+    from cacheir_b200.tensor_parallel import TensorParallel
+    from oracle import oracle
+
+    heads = max(4, world)
+    cfg = ModelConfig(architecture="LlamaForCausalLM", hidden_size=128 * heads, intermediate_size=256 * world * 2, num_layers=2,
+                      num_attention_heads=heads, num_key_value_heads=world, vocab_size=512 * world, max_position_embeddings=256,
+                      rope_theta=10000.0, rms_norm_eps=1e-5, dtype="float16")
+    artifact = build_decoder_artifact(cfg, quant="int8")
+
+    def source(key, shape):
+        g = torch.Generator(device="cpu")
+        g.manual_seed(zlib.crc32(key.encode()))
+        return torch.ones(shape) if len(shape) == 1 else torch.randn(shape, generator=g) * 0.05
+
+    rng = np.random.default_rng(5)
+    prompts = [[int(t) for t in rng.integers(0, cfg.vocab_size, 9)] for _ in range(4)]
+    forced = [[int(t) for t in rng.integers(0, cfg.vocab_size, 4)] for _ in range(6)]
+    traces = {}
+    for name, tp in (("tp", TensorParallel(rank, world)), ("single", None)):
+        if name == "single" and rank != 0:
+            continue
+        rt = B200DecodeRuntime(artifact, device=f"cuda:{local_rank}", dtype="float16", tensor_source=source, max_seq_len=256,
+                               tensor_parallel=tp)
+        sessions = [rt.fork() for _ in prompts]
+        logits = rt.run_prefill_batch(sessions, prompts)
+        trace = [logits[:, -1].float().cpu().numpy()]
+        for tokens in forced:
+            trace.append(rt.run_decode_batch(sessions, tokens)[:, -1].float().cpu().numpy())
+        traces[name] = np.stack(trace)
+        if name == "tp":
+            rt.synchronize()
+            dist.barrier()
+    if rank != 0:
+        return None
+    tp_l, one_l = traces["tp"], traces["single"]
+    rel = oracle.rel_l2(tp_l, one_l)
+    top2 = np.sort(one_l, axis=-1)[..., -2:]
+    clear = (top2[..., 1] - top2[..., 0]) > 8e-3 * np.abs(one_l).max(axis=-1)
+    equal = bool(np.array_equal(tp_l.argmax(-1)[clear], one_l.argmax(-1)[clear]))
+    return {"parity_rel_l2": round(float(rel), 6), "tokens_equal": equal, "tokens_compared": int(clear.sum()), "gate": 4e-3}
 
 
 # --------------------------------------------------------------------------------------
@@ -577,6 +744,7 @@ def main() -> None:
     parser.add_argument("--tp", action="store_true",
                         help="all ranks form one tensor-parallel group decoding one batch (default: data parallel by sequence)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-tp-leg", action="store_true", help="with --gpus N > 1: skip the tensor-parallel leg attached to the line")
     parser.add_argument("--micro", choices=["qgemv", "attention"], help="time one kernel alone (profiling aid)")
     parser.add_argument("--m", type=int, default=32)
     parser.add_argument("--n", type=int, default=14336)
@@ -622,12 +790,45 @@ def main() -> None:
         import torch.distributed as dist  # type: ignore[no-redef]
         dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
 
+    line = measure(args, cfg, args.workload, bool(args.tp and world > 1), world, rank, local_rank, dist,
+                   steps=args.steps, warmup=warmup, e2e_steps=max(4, args.e2e_steps), full=True)
+    if world > 1 and not args.tp and not args.no_tp_leg:
+        # A tensor-parallel leg in the same process group, attached to the data-parallel line: the 70B-shaped
+        # configuration on 8 GPUs, the same code path at a small size on 2 and 4.
+        tp_workload = "llama3-70b-int4g128-b128-tp8" if world == 8 else "small-tp"
+        tp_cfg = dict(WORKLOADS[tp_workload])
+        lens_all = context_lengths(tp_cfg)
+        tp_cfg["ctx"] = max(lens_all)
+        tp_cfg["ctx_mean"] = int(np.mean(lens_all))
+        tp_line = measure(args, tp_cfg, tp_workload, True, world, rank, local_rank, dist,
+                          steps=min(args.steps, 16), warmup=3, e2e_steps=4, full=False)
+        parity = tensor_parallel_parity(rank, world, local_rank)
+        if rank == 0 and line is not None and tp_line is not None:
+            ar = [k for k in tp_line["kernels"] if k["kernel"].startswith("peer_all_reduce")]
+            line["tp"] = {"workload": tp_workload, "tokens_per_s": tp_line["value"], "ms_per_step": tp_line["ms_per_step"],
+                          "e2e_tokens_per_s": tp_line["e2e"]["value"], "steps": tp_line["steps"],
+                          "frac_of_hbm_roofline": tp_line["step"]["frac_of_hbm_roofline"],
+                          "all_reduce_us": ar[0]["us"] if ar else None, "device_status": tp_line["device_status"],
+                          "kernels": tp_line["kernels"], "parallelism": tp_line["config"]["parallelism"], **(parity or {})}
+    if rank == 0 and line is not None:
+        emit(line)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def measure(args, cfg: dict, workload: str, use_tp: bool, world: int, rank: int, local_rank: int, dist, *, steps: int,
+            warmup: int, e2e_steps: int, full: bool) -> dict | None:
+    """One measurement of `workload`: data parallel by sequence (every rank its own batch), or, with `use_tp`, all
+    ranks as one tensor-parallel group on one batch. Returns the result line on rank 0. `full` adds the CPU
+    baseline and the parity self-check."""
+    import torch
+
     from cacheir_b200.sharding import max_over_ranks
 
-    e2e_steps = max(4, args.e2e_steps)
-    extra = warmup + args.steps + e2e_steps + 3 + 48
+    extra = warmup + steps + e2e_steps + 3 + 48
     tp = None
-    if args.tp and world > 1:
+    if use_tp:
         from cacheir_b200.tensor_parallel import TensorParallel
         tp = TensorParallel(rank, world)
     rt, _ = build_runtime(cfg, local_rank, extra, tp)
@@ -651,15 +852,15 @@ def main() -> None:
     sampler.start()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    toks = rt.decode_greedy_batch(sessions, last, args.steps)
+    toks = rt.decode_greedy_batch(sessions, last, steps)
     end.record()
     barrier()
     elapsed_s = start.elapsed_time(end) * 1e-3
     clocks = sampler.stop()
     last = [int(t) for t in toks[-1].tolist()]
-    kv_tokens_mid = unique_kv_tokens(cfg, warmup + args.steps // 2)
+    kv_tokens_mid = unique_kv_tokens(cfg, warmup + steps // 2)
     elapsed_s = max_over_ranks(elapsed_s, torch.device("cuda", local_rank))
-    tokens_total = replicas * cfg["batch"] * args.steps
+    tokens_total = replicas * cfg["batch"] * steps
     value = tokens_total / elapsed_s
 
     # ---- host-facing loop: `e2e` ------------------------------------------------------
@@ -714,38 +915,30 @@ def main() -> None:
                         "shape": [cfg["batch"], cfg["hidden"]]})
     sb = step_bytes(cfg, kv_tokens_mid)
     shards = world if tp else 1                              # tensor parallel: each rank streams its share of the step
-    step_gbs = sb["total"] / shards / (elapsed_s / args.steps) / 1e9
+    step_gbs = sb["total"] / shards / (elapsed_s / steps) / 1e9
+    parity = parity_self_check(rt, sessions, cfg) if (full and rank == 0) else None
+    torch.cuda.synchronize()
+    from cacheir_b200 import _lib
+    status = int(_lib.load().cacheir_b200_device_status(0))   # 0: no bounded device wait ever gave up
 
+    line = None
     if rank == 0:
-        # DRAM traffic of the attention kernel: the ratio measured by ncu on a small case (the profile
-        # summary states the capture) times this workload's algorithmic bytes per launch
-        traffic = None
-        prof = ROOT / "profiles" / "paged_decode_mma_b16_ctx2048-4096.md"
-        if prof.exists():
-            import re
-            found = re.search(r"dram_traffic_over_algorithmic_bytes\s*=\s*([0-9.]+)", prof.read_text())
-            if found:
-                traffic = int(float(found.group(1)) * attn["bytes"])
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
-            "ms_per_step": elapsed_s / args.steps * 1e3, "higher_is_better": True, "scaling": "strong" if tp else "weak",
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": elapsed_s / steps * 1e3, "higher_is_better": True, "scaling": "strong" if tp else "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": args.workload, "batch_per_gpu": cfg["batch"],
-                       "context": (f"log-uniform {cfg['ctx_range'][0]}..{cfg['ctx_range'][1]} (mean {cfg['ctx_mean']}), "
-                                   f"{cfg['shared_prefix'][0]}-way shared {cfg['shared_prefix'][1]}-token prefixes"
-                                   if "ctx_range" in cfg else cfg["ctx"]),
-                       "layers": cfg["layers"],
-                       "weights": ("int4 group-128 symmetric (fp16 scales)" if "g128" in cfg["quant"]
-                                   else "int8 per-row affine (fp32 scale+zero)"), "kv": "fp16 pages of 16",
-                       "parallelism": (f"tp{world}: heads and FFN split, own all-reduce kernels over NVLink peer memory" if tp
-                                       else f"dp{world} by sequence, no collective"), "l2_policy": "inputs larger than L2 (16 GB/step)"},
+            "config": workload_config(cfg, workload, world, bool(tp)),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d // e2e_steps, "d2h_bytes_per_step": d2h // e2e_steps,
                     "steps": e2e_steps, "api": "B200DecodeRuntime.run_decode_batch + argmax_tokens"},
-            "gpu_launches": launches_per_step * args.steps,
-            "device_status": int(__import__("cacheir_b200")._lib.load().cacheir_b200_device_status(0)),   # 0: no bounded device wait ever gave up
+            "gpu_launches": launches_per_step * steps,
+            "device_status": status,
             "clocks": clocks,
+            # DRAM traffic of the attention kernel: ncu measured dram__bytes_read + dram__bytes_write = 1.024 x the
+            # algorithmic bytes on a small case (K/V bytes dominate both, so the ratio carries over to this workload)
             "roofline": {"bound": "hbm", "kernel": attn["kernel"], "achieved": kernels[0]["achieved_gbs"], "peak": peak,
-                         "unit": "GB/s", "frac": kernels[0]["frac"], "traffic": traffic, "peak_source": f"of {peak_kind}",
+                         "unit": "GB/s", "frac": kernels[0]["frac"], "traffic": int(ATTENTION_TRAFFIC_RATIO * attn["bytes"]),
+                         "traffic_source": f"{ATTENTION_TRAFFIC_RATIO} x algorithmic bytes (ncu, profiles/paged_decode_mma_b16_ctx2048-4096.md)",
+                         "peak_source": f"of {peak_kind}",
                          "algorithmic_bytes_per_launch": int(attn["bytes"]), "us_per_launch": kernels[0]["us"]},
             "kernels": kernels,
             "step": {"algorithmic_bytes": int(sb["total"]), "weight_bytes": int(sb["weights"]), "kv_bytes": int(sb["kv"]),
@@ -753,12 +946,20 @@ def main() -> None:
                      "roofline_tokens_per_s": round(cfg["batch"] * peak * 1e9 * shards / sb["total"], 1),
                      "launches_per_step": launches_per_step},
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if parity is not None:
+            line["parity"] = parity
+        if full and world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = run_cpu_baseline(dict(cfg, ctx=cfg.get("ctx_mean", cfg["ctx"])))
-        emit(line)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    # give the memory back before another measurement in the same process
+    if rt._engine.peer is not None:
+        if dist is not None:
+            dist.barrier()
+        rt._engine.peer.close()
+    del plan, sessions, rt, attn, gemvs
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return line
 
 
 if __name__ == "__main__":

@@ -248,8 +248,64 @@ def test_tp2_matches_single_gpu(collectives):
             assert results[r]["collectives"] == {"reduce_ok": True, "gather_ok": True, "graph_ok": True, "status": 0}
     single, tp0, tp1 = results[0]["single"], results[0]["tp"], results[1]["tp"]
     np.testing.assert_array_equal(tp0["logits"], tp1["logits"])          # both ranks hold the same gathered logits
-    # fp16 partial sums and per-rank activation scales: a little looser than the single-kernel gates
-    assert oracle.rel_l2(tp0["logits"], single["logits"]) <= 1e-2
+    # fp16 partial sums and per-rank activation scales across two layers: twice the single-kernel gate
+    assert oracle.rel_l2(tp0["logits"], single["logits"]) <= 4e-3
     assert tp0["tokens"] == tp1["tokens"]
-    agree = np.mean(np.array(tp0["tokens"]) == np.array(single["tokens"]))
-    assert agree >= 0.7                                                     # near-flat random logits may flip a tie
+    # identical greedy tokens wherever the single-GPU top-1 / top-2 margin is clear of that tolerance
+    one = single["logits"]
+    top2 = np.sort(one, axis=-1)[..., -2:]
+    clear = (top2[..., 1] - top2[..., 0]) > 8e-3 * np.abs(one).max(axis=-1)
+    assert clear.sum() >= clear.size // 2
+    np.testing.assert_array_equal(tp0["logits"].argmax(-1)[clear], one.argmax(-1)[clear])
+
+
+def _lost_peer_worker():
+    """One GPU, world = 2: the second rank's buffers are local stand-ins whose flag never advances."""
+    import ctypes
+
+    from cacheir_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    n = 4096
+    data0 = torch.ones((n,), device=dev, dtype=torch.float16)
+    data1 = torch.full((n,), 2.0, device=dev, dtype=torch.float16)
+    flags0 = torch.zeros((64,), device=dev, dtype=torch.int32)
+    flags1 = torch.zeros((64,), device=dev, dtype=torch.int32)      # the "peer" never announces into flags0
+    out = torch.zeros((n,), device=dev, dtype=torch.float16)
+    state = torch.zeros((4,), device=dev, dtype=torch.int32)
+    state[3] = 2000                                                 # polls before a wait gives up: a few milliseconds
+    data = (ctypes.c_void_p * 2)(data0.data_ptr(), data1.data_ptr())
+    flags = (ctypes.c_void_p * 2)(flags0.data_ptr(), flags1.data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        return lib.cacheir_b200_peer_all_reduce(data, flags, out.data_ptr(), n, 1, 0, 2, state.data_ptr(), stream)
+
+    import time
+    assert lib.cacheir_b200_device_status(1) == 0
+    t0 = time.perf_counter()
+    assert call() == 0
+    torch.cuda.synchronize()
+    first = time.perf_counter() - t0
+    assert lib.cacheir_b200_device_status(0) == (4 << 8) | 1        # the wait for rank 1 ran out; the kernel returned
+    t0 = time.perf_counter()
+    for _ in range(50):                                             # later calls do not wait again
+        assert call() == 0
+    torch.cuda.synchronize()
+    later = (time.perf_counter() - t0) / 50
+    assert later < max(first / 4, 2e-3), (first, later)
+    assert lib.cacheir_b200_device_status(1) == (4 << 8) | 1        # read and cleared
+    assert lib.cacheir_b200_device_status(0) == 0
+    # a healthy call: the stand-in peer has "announced" every epoch to come
+    flags0[1] = 1 << 30
+    assert call() == 0
+    torch.cuda.synchronize()
+    assert lib.cacheir_b200_device_status(1) == 0
+    assert torch.equal(out, torch.full_like(out, 3.0))              # 1 + 2, in rank order
+
+
+@pytest.mark.gpu
+def test_lost_peer_times_out_once_and_is_reported():
+    """A rank that never shows up costs the others one short, bounded wait; the status word says so and later
+    collectives return at once until the host has read it. Made on the host: nothing on the GPU faults or hangs."""
+    _lost_peer_worker()
