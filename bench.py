@@ -75,7 +75,8 @@ def workload_config(cfg: dict, workload: str, world: int, tp: bool) -> dict:
                         if "ctx_range" in cfg else cfg["ctx"]),
             "layers": cfg["layers"],
             "weights": ("int4 group-128 symmetric (fp16 scales)" if "g128" in cfg["quant"]
-                        else "int8 per-row affine (fp32 scale+zero)"), "kv": "fp16 pages of 16",
+                        else "int8 per-row affine (fp32 scale+zero)"),
+            "kv": "int8 pages of 16 (fp16 scale per cached row)" if cfg.get("kv_dtype") == "int8" else "fp16 pages of 16",
             "parallelism": (f"tp{world}: heads and FFN split, own all-reduce kernels over NVLink peer memory" if tp
                             else f"dp{world} by sequence, no collective"), "l2_policy": "inputs larger than L2 (16 GB/step)"}
 
@@ -160,7 +161,7 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------
-def build_runtime(cfg: dict, device_index: int, extra_tokens: int, tensor_parallel=None):
+def build_runtime(cfg: dict, device_index: int, extra_tokens: int, tensor_parallel=None, kv_dtype: str = "same"):
     import zlib
 
     import torch
@@ -188,7 +189,7 @@ def build_runtime(cfg: dict, device_index: int, extra_tokens: int, tensor_parall
     alloc = B200KVPageAllocator(page_size=page, initial_slots=total_pages + 8)
     rt = B200DecodeRuntime(art, device=f"cuda:{device_index}", dtype="float16", tensor_source=synth,
                            kv_allocator=alloc, max_seq_len=cfg["ctx"] + extra_tokens, clone_outputs=False,
-                           tensor_parallel=tensor_parallel)
+                           tensor_parallel=tensor_parallel, kv_dtype=kv_dtype)
     del head_dim
     return rt, art
 
@@ -208,8 +209,13 @@ def prefill_synthetic_context(rt, cfg: dict):
     gen.manual_seed(1234)
     for layer in range(cfg["layers"]):
         pool = rt.kv_allocator.pool_for_layer(layer)
-        pool["keys"].normal_(generator=gen)
-        pool["values"].normal_(generator=gen)
+        if "scales" in pool:                              # 8-bit pages: uniform bytes, scales of N(0,1) rows (max|row| / 127 ~ 0.02 .. 0.03)
+            pool["keys"].random_(0, 256, generator=gen)
+            pool["values"].random_(0, 256, generator=gen)
+            pool["scales"].copy_(torch.rand(pool["scales"].shape, device=rt.device, generator=gen) * 0.01 + 0.02)
+        else:
+            pool["keys"].normal_(generator=gen)
+            pool["values"].normal_(generator=gen)
     return sessions
 
 
@@ -219,6 +225,14 @@ def unique_kv_tokens(cfg: dict, generated: int) -> int:
     group, shared = cfg.get("shared_prefix", (1, 0))
     aliased = (shared // 16) * 16 * (cfg["batch"] - (cfg["batch"] + group - 1) // group) if group > 1 else 0
     return sum(lens) - aliased + cfg["batch"] * generated
+
+
+def kv_row_bytes(cfg: dict) -> int:
+    """Bytes of one cached token of one layer: K and V rows of every KV head (8-bit pages: plus an fp16 scale per row)."""
+    hd = cfg["hidden"] // cfg["heads"]
+    if cfg.get("kv_dtype", "same") == "int8":
+        return cfg["kv_heads"] * 2 * (hd + 2)
+    return cfg["kv_heads"] * 2 * hd * 2
 
 
 def step_bytes(cfg: dict, kv_tokens: int) -> dict:
@@ -234,7 +248,8 @@ def step_bytes(cfg: dict, kv_tokens: int) -> dict:
     meta = elems // group * 2 if group else rows * 8            # fp16 group scales | fp32 scale + zero per row
     layer_w = elems * bits // 8 + meta
     weights = L * layer_w + v * h * bits // 8 + (v * h // group * 2 if group else v * 8)
-    kv = L * kv_tokens * kvd * 2 * 2
+    del kvd
+    kv = L * kv_tokens * kv_row_bytes(cfg)
     return {"weights": weights, "kv": kv, "total": weights + kv}
 
 
@@ -280,13 +295,13 @@ def time_attention_kernel(rt, sessions, cfg: dict, iters: int = 3) -> dict:
     def sweep() -> None:
         for pool in pools:
             ops.paged_attention_decode_batch(q, pool["keys"], pool["values"], plan.page_table, lens, out=out,
-                                             num_splits=splits, workspace=ws)
+                                             num_splits=splits, workspace=ws, kv_scales=pool.get("scales"))
 
     per_launch_s = time_graph(sweep, iters) / len(pools)
     group, shared = cfg.get("shared_prefix", (1, 0))      # physical pages of a shared prefix are read (and count) once
     aliased = (shared // 16) * 16 * (B - (B + group - 1) // group) if group > 1 else 0
     total_ctx = int(lens.sum().item()) - aliased
-    algo = total_ctx * KVH * hd * 2 * 2 + 2 * B * H * hd * 2 + B * plan.width * 4 + B * 4
+    algo = total_ctx * kv_row_bytes(cfg) // tp_world + 2 * B * H * hd * 2 + B * plan.width * 4 + B * 4
     return {"kernel": "paged_attention_decode_batch", "seconds": per_launch_s, "bytes": algo, "splits": splits}
 
 
@@ -557,12 +572,17 @@ def parity_self_check(rt, sessions, cfg: dict) -> dict:
     table = np.stack([s.kv_cache.page_table_row(width) for s in sub]).astype(np.int32)
     lens = np.array([min(s.kv_cache.tokens, 4096) for s in sub], dtype=np.int32)
     q = torch.randn((len(sub), H, hd), device=dev, dtype=torch.float16, generator=gen)
-    out = ops.paged_attention_decode_batch(q, pool["keys"], pool["values"], torch.from_numpy(table).to(dev), torch.from_numpy(lens).to(dev))
+    out = ops.paged_attention_decode_batch(q, pool["keys"], pool["values"], torch.from_numpy(table).to(dev), torch.from_numpy(lens).to(dev),
+                                           kv_scales=pool.get("scales"))
     used = np.unique(table)
     remap = np.zeros(int(table.max()) + 1, dtype=np.int32)
     remap[used] = np.arange(len(used), dtype=np.int32)
     idx = torch.from_numpy(used.astype(np.int64)).to(dev)
-    want = oracle.paged_attention_decode(q.cpu().numpy(), pool["keys"][idx].cpu().numpy(), pool["values"][idx].cpu().numpy(), remap[table], lens)
+    keys, values = pool["keys"][idx].cpu().numpy(), pool["values"][idx].cpu().numpy()
+    if "scales" in pool:                                  # 8-bit pages: the oracle sees the same bytes, dequantised in fp32
+        sc = pool["scales"][idx].cpu().numpy()
+        keys, values = oracle.dequantize_kv_pool(keys, sc, 0), oracle.dequantize_kv_pool(values, sc, 1)
+    want = oracle.paged_attention_decode(q.cpu().numpy(), keys, values, remap[table], lens)
     worst["attention"] = oracle.rel_l2(out.float().cpu().numpy(), want)
     torch.cuda.synchronize()
     return {"rel_l2": round(max(worst.values()), 6), "gate": 2e-3, "per_kernel": {k: round(v, 6) for k, v in worst.items()},
@@ -744,6 +764,8 @@ def main() -> None:
     parser.add_argument("--tp", action="store_true",
                         help="all ranks form one tensor-parallel group decoding one batch (default: data parallel by sequence)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--kv", default="fp16", choices=["fp16", "int8"],
+                        help="KV page format: fp16 (the benchmark's configuration) or 8-bit pages with a scale per cached row (an extra)")
     parser.add_argument("--no-tp-leg", action="store_true", help="with --gpus N > 1: skip the tensor-parallel leg attached to the line")
     parser.add_argument("--micro", choices=["qgemv", "attention"], help="time one kernel alone (profiling aid)")
     parser.add_argument("--m", type=int, default=32)
@@ -767,6 +789,8 @@ def main() -> None:
         run_micro(args)
         return
     cfg = dict(WORKLOADS[args.workload])
+    if args.kv == "int8":
+        cfg["kv_dtype"] = "int8"
     if "ctx_range" in cfg:
         lens_all = context_lengths(cfg)
         cfg["ctx"] = max(lens_all)                      # sizing (positions, page-table width)
@@ -831,7 +855,7 @@ def measure(args, cfg: dict, workload: str, use_tp: bool, world: int, rank: int,
     if use_tp:
         from cacheir_b200.tensor_parallel import TensorParallel
         tp = TensorParallel(rank, world)
-    rt, _ = build_runtime(cfg, local_rank, extra, tp)
+    rt, _ = build_runtime(cfg, local_rank, extra, tp, cfg.get("kv_dtype", "same"))
     sessions = prefill_synthetic_context(rt, cfg)
     first_tokens = [int(t) for t in np.random.default_rng(0 if tp else rank).integers(0, cfg["vocab"], cfg["batch"])]
     replicas = 1 if tp else world                          # independent batches in flight

@@ -24,6 +24,12 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
          c_int, c_int, c_int, c_int, c_int, c_int, c_int,              # batch heads kv_heads max_pages page D dtype
          c_longlong, c_longlong, c_float, c_int,                       # q_stride out_stride scale num_splits
          c_void_p, c_size_t, c_void_p]),                               # workspace bytes stream
+    "cacheir_b200_paged_attention_decode_batch_ex": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+         c_longlong, c_longlong, c_float, c_int,
+         c_void_p, c_size_t, c_int, c_int, c_void_p, c_void_p]),      # workspace bytes num_slots kv_dtype kv_scales stream
     "cacheir_b200_paged_attention_noalloc_max_workspace_bytes": (c_size_t, []),
     "cacheir_b200_paged_attention_decode_batch_noalloc": (
         c_int,
@@ -78,6 +84,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "cacheir_b200_rope_inplace": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p]),
     "cacheir_b200_kv_append": (
         c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p]),
+    "cacheir_b200_kv_append_q8": (
+        c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p]),
     "cacheir_b200_silu_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "cacheir_b200_add": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "cacheir_b200_embedding_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),

@@ -165,6 +165,59 @@ __global__ void kv_append_kernel(const T* __restrict__ k, const T* __restrict__ 
   v_cache[dst] = v[static_cast<size_t>(b) * v_stride + idx];
 }
 
+// ---- KV append into 8-bit pools: each new row is quantised with its own scale --------------------
+// scale = fp16(max|row| / 127) (1 for an all-zero row), byte = clamp(rint(value / scale), -127, 127) + 128.
+// One CTA per (kv head, request); k and v rows of head_dim values each.
+template <typename T>
+__global__ void __launch_bounds__(128)
+kv_append_q8_kernel(const T* __restrict__ k, const T* __restrict__ v, uint8_t* __restrict__ k_cache, uint8_t* __restrict__ v_cache,
+                    __half* __restrict__ kv_scales, const int32_t* __restrict__ page_table, const int32_t* __restrict__ positions,
+                    int num_kv_heads, int max_pages, int page_size, int head_dim, long long k_stride, long long v_stride) {
+  __shared__ float s_max[2][4];
+  const int kvh = blockIdx.x, b = blockIdx.y;
+  const int pos = positions[b];
+  const int page_idx = pos / page_size;
+  if (pos < 0 || page_idx >= max_pages) return;  // no page reserved: drop rather than write out of range
+  const int page = page_table[static_cast<size_t>(b) * max_pages + page_idx];
+  const size_t chunk = static_cast<size_t>(page) * num_kv_heads + kvh;
+  const size_t dst = (chunk * page_size + pos % page_size) * static_cast<size_t>(head_dim);
+  const T* src[2] = {k + static_cast<size_t>(b) * k_stride + static_cast<size_t>(kvh) * head_dim,
+                     v + static_cast<size_t>(b) * v_stride + static_cast<size_t>(kvh) * head_dim};
+  uint8_t* out[2] = {k_cache + dst, v_cache + dst};
+  float vals[2][2];        // up to 256 dims: two per thread
+  float amax[2] = {0.f, 0.f};
+#pragma unroll
+  for (int w = 0; w < 2; ++w)
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int d = threadIdx.x + i * 128;
+      vals[w][i] = d < head_dim ? Elem<T>::ld(src[w] + d) : 0.f;
+      amax[w] = fmaxf(amax[w], fabsf(vals[w][i]));
+    }
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    amax[w] = warp_max(amax[w]);
+    if ((threadIdx.x & 31) == 0) s_max[w][threadIdx.x >> 5] = amax[w];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    const float m = fmaxf(fmaxf(s_max[w][0], s_max[w][1]), fmaxf(s_max[w][2], s_max[w][3]));
+    __half sh = __float2half_rn(m / 127.f);
+    if (__half2float(sh) == 0.f) sh = __float2half_rn(1.f);
+    const float scale = __half2float(sh);
+    if (threadIdx.x == 0) kv_scales[(chunk * 2 + w) * page_size + pos % page_size] = sh;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int d = threadIdx.x + i * 128;
+      if (d < head_dim) {
+        const float qv = fminf(127.f, fmaxf(-127.f, rintf(__fdiv_rn(vals[w][i], scale))));
+        out[w][d] = static_cast<uint8_t>(static_cast<int>(qv) + 128);
+      }
+    }
+  }
+}
+
 // ---- elementwise ------------------------------------------------------------------
 template <typename T, bool SILU_MUL>
 __global__ void binary_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, size_t total) {
@@ -309,6 +362,26 @@ extern "C" int cacheir_b200_kv_append(const void* k, const void* v, void* k_cach
                                   static_cast<const T*>(k), static_cast<const T*>(v), static_cast<T*>(k_cache),
                                   static_cast<T*>(v_cache), page_table, positions, num_kv_heads,
                                   max_pages_per_seq, page_size, head_dim, ks, vs)));
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_kv_append_q8(const void* k, const void* v, void* k_cache, void* v_cache, void* kv_scales,
+                                         const int32_t* page_table, const int32_t* positions, int batch_size,
+                                         int num_kv_heads, int max_pages_per_seq, int page_size, int head_dim, int dtype,
+                                         long long k_batch_stride, long long v_batch_stride, void* stream) {
+  if (batch_size <= 0 || num_kv_heads <= 0 || head_dim <= 0) return 0;
+  if (!k || !v || !k_cache || !v_cache || !kv_scales || !page_table || !positions || max_pages_per_seq <= 0 ||
+      page_size <= 0 || batch_size > 65535)
+    return CACHEIR_B200_EINVAL;
+  if (head_dim > 256) return CACHEIR_B200_EUNSUPPORTED;
+  const long long dense = static_cast<long long>(num_kv_heads) * head_dim;
+  const long long ks = k_batch_stride > 0 ? k_batch_stride : dense;
+  const long long vs = v_batch_stride > 0 ? v_batch_stride : dense;
+  const dim3 grid(num_kv_heads, batch_size);
+  CB200_DISPATCH_DTYPE(dtype, (kv_append_q8_kernel<T><<<grid, 128, 0, as_stream(stream)>>>(
+                                  static_cast<const T*>(k), static_cast<const T*>(v), static_cast<uint8_t*>(k_cache),
+                                  static_cast<uint8_t*>(v_cache), static_cast<__half*>(kv_scales), page_table, positions,
+                                  num_kv_heads, max_pages_per_seq, page_size, head_dim, ks, vs)));
   return launch_status();
 }
 

@@ -18,7 +18,24 @@ namespace cb200 {
 namespace {
 
 constexpr int kWarps = 4;
-template <typename T, int VEC, int LPT, int R, int GC>
+
+// VEC consecutive cached values as fp32: elements of type T, or (KV8) unsigned bytes with the row's scale.
+template <typename T, int VEC, bool KV8>
+__device__ __forceinline__ void load_cached(const void* cache, size_t elem, float scale, float (&out)[VEC]) {
+  if constexpr (!KV8) {
+    VecIO<T, VEC>::ld(static_cast<const T*>(cache) + elem, out);
+  } else {
+    const uint8_t* src = static_cast<const uint8_t*>(cache) + elem;
+    uint8_t bytes[VEC];
+    if constexpr (VEC == 8) *reinterpret_cast<uint2*>(bytes) = *reinterpret_cast<const uint2*>(src);
+    else if constexpr (VEC == 4) *reinterpret_cast<uint32_t*>(bytes) = *reinterpret_cast<const uint32_t*>(src);
+    else bytes[0] = src[0];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) out[v] = (static_cast<float>(bytes[v]) - 128.f) * scale;
+  }
+}
+
+template <typename T, int VEC, int LPT, int R, int GC, bool KV8>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_decode_general_kernel(const AttnParams p) {
   constexpr int TPW = 32 / LPT;         // rows handled per warp instruction
@@ -45,8 +62,6 @@ paged_decode_general_kernel(const AttnParams p) {
   const int t_end = min(seq_len, t_begin + p.chunk_tokens);
 
   const T* qb = static_cast<const T*>(p.q) + static_cast<size_t>(b) * p.q_stride;
-  const T* kc = static_cast<const T*>(p.k_cache);
-  const T* vc = static_cast<const T*>(p.v_cache);
   const int g0 = hc * GC;       // first head of this chunk inside the group
   const int h0 = kvh * p.group + g0;
 
@@ -86,12 +101,19 @@ paged_decode_general_kernel(const AttnParams p) {
       const int page = pt[t / p.page_size];
       const size_t row = ((static_cast<size_t>(page) * p.kv_heads + kvh) * p.page_size +
                           (t % p.page_size)) * static_cast<size_t>(D);
+      float ks = 1.f, vs = 1.f;
+      if constexpr (KV8) {
+        const __half* sc = static_cast<const __half*>(p.kv_scales) +
+                           (static_cast<size_t>(page) * p.kv_heads + kvh) * 2 * p.page_size + (t % p.page_size);
+        ks = __half2float(sc[0]);
+        vs = __half2float(sc[p.page_size]);
+      }
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         const int d0 = (sub + r * LPT) * VEC;
         if (d0 < D) {
-          VecIO<T, VEC>::ld(kc + row + d0, kf[r]);
-          VecIO<T, VEC>::ld(vc + row + d0, vf[r]);
+          load_cached<T, VEC, KV8>(p.k_cache, row + d0, ks, kf[r]);
+          load_cached<T, VEC, KV8>(p.v_cache, row + d0, vs, vf[r]);
         }
       }
     }
@@ -167,7 +189,7 @@ paged_decode_general_kernel(const AttnParams p) {
   }
 }
 
-template <typename T, int VEC, int LPT, int R>
+template <typename T, int VEC, int LPT, int R, bool KV8 = false>
 int launch_general_gc(const AttnParams& p0, cudaStream_t stream) {
   AttnParams p = p0;
   const int gc = p.group >= 8 ? 8 : (p.group > 2 ? 4 : (p.group > 1 ? 2 : 1));
@@ -178,7 +200,7 @@ int launch_general_gc(const AttnParams& p0, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(kWarps * tpw) * gc * (2 + dp) * sizeof(float);
 #define CB200_LAUNCH_GC(GCV)                                                              \
   do {                                                                                    \
-    auto kern = paged_decode_general_kernel<T, VEC, LPT, R, GCV>;                         \
+    auto kern = paged_decode_general_kernel<T, VEC, LPT, R, GCV, KV8>;                    \
     if (smem > 48 * 1024) {                                                               \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                            static_cast<int>(smem));                       \
@@ -196,18 +218,18 @@ int launch_general_gc(const AttnParams& p0, cudaStream_t stream) {
   return launch_status();
 }
 
-template <typename T, int VEC>
+template <typename T, int VEC, bool KV8 = false>
 int launch_general(const AttnParams& p, bool vector_ok, cudaStream_t stream) {
   const int D = p.head_dim;
   if (VEC > 1 && vector_ok && D % VEC == 0) {
     const int lpt = D / VEC;
-    if (lpt == 32) return launch_general_gc<T, VEC, 32, 1>(p, stream);
-    if (lpt == 16) return launch_general_gc<T, VEC, 16, 1>(p, stream);
-    if (lpt == 8) return launch_general_gc<T, VEC, 8, 1>(p, stream);
+    if (lpt == 32) return launch_general_gc<T, VEC, 32, 1, KV8>(p, stream);
+    if (lpt == 16) return launch_general_gc<T, VEC, 16, 1, KV8>(p, stream);
+    if (lpt == 8) return launch_general_gc<T, VEC, 8, 1, KV8>(p, stream);
   }
   // scalar lanes: lane i owns dims i, i+32, ...
-  if (D <= 32) return launch_general_gc<T, 1, 32, 1>(p, stream);
-  if (D <= 256) return launch_general_gc<T, 1, 32, 8>(p, stream);
+  if (D <= 32) return launch_general_gc<T, 1, 32, 1, KV8>(p, stream);
+  if (D <= 256) return launch_general_gc<T, 1, 32, 8, KV8>(p, stream);
   return CACHEIR_B200_EUNSUPPORTED;
 }
 
@@ -296,23 +318,27 @@ extern "C" int cacheir_b200_paged_attention_auto_splits(int batch_size, int num_
   return s;
 }
 
-extern "C" int cacheir_b200_paged_attention_decode_batch(
+extern "C" int cacheir_b200_paged_attention_decode_batch_ex(
     const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
     const int32_t* seq_lens, void* out, int batch_size, int num_heads, int num_kv_heads,
     int max_pages_per_seq, int page_size, int head_dim, int dtype, long long q_batch_stride,
     long long out_batch_stride, float softmax_scale, int num_splits, void* workspace,
-    size_t workspace_bytes, void* stream) {
+    size_t workspace_bytes, int num_slots, int kv_dtype, const void* kv_scales, void* stream) {
   if (batch_size <= 0 || num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0) return 0;
-  if (max_pages_per_seq <= 0 || page_size <= 0) return CACHEIR_B200_EINVAL;
+  if (max_pages_per_seq <= 0 || page_size <= 0 || num_slots < 0) return CACHEIR_B200_EINVAL;
   if (num_heads % num_kv_heads != 0) return CACHEIR_B200_EINVAL;
   if (!q || !k_cache || !v_cache || !page_table || !seq_lens || !out) return CACHEIR_B200_EINVAL;
   const int esize = dtype_size(dtype);
   if (esize == 0 || num_splits < 0) return CACHEIR_B200_EINVAL;
+  if (kv_dtype != CACHEIR_B200_KV_SAME && kv_dtype != CACHEIR_B200_KV_INT8) return CACHEIR_B200_EINVAL;
+  const bool kv8 = kv_dtype == CACHEIR_B200_KV_INT8;
+  if (kv8 && !kv_scales) return CACHEIR_B200_EINVAL;
   if (head_dim > 256) return CACHEIR_B200_EUNSUPPORTED;
   if (batch_size > 65535 || static_cast<long long>(num_heads) > 65535) return CACHEIR_B200_ELIMIT;
 
   AttnParams p{};
   p.q = q; p.k_cache = k_cache; p.v_cache = v_cache;
+  p.kv_scales = kv_scales; p.kv8 = kv8 ? 1 : 0; p.num_slots = num_slots;
   p.page_table = page_table; p.seq_lens = seq_lens; p.out = out;
   p.batch = batch_size; p.heads = num_heads; p.kv_heads = num_kv_heads;
   p.max_pages = max_pages_per_seq; p.page_size = page_size; p.head_dim = head_dim;
@@ -331,13 +357,21 @@ extern "C" int cacheir_b200_paged_attention_decode_batch(
     p.ws_acc = p.ws_ml + static_cast<size_t>(batch_size) * num_heads * p.splits * 2;
   }
   cudaStream_t st = as_stream(stream);
-  // 128-bit row chunks need 16-byte aligned rows everywhere they are used.
+  // 128-bit row chunks need 16-byte aligned rows everywhere they are used (8-bit pools: 8-byte chunks of the cached rows).
+  const int kv_esize = kv8 ? 1 : esize;
   const bool vector_ok = aligned_to(q, 16) && aligned_to(k_cache, 16) && aligned_to(v_cache, 16) &&
                          (p.q_stride * esize) % 16 == 0 &&
-                         (static_cast<long long>(head_dim) * esize) % 16 == 0;
+                         (static_cast<long long>(head_dim) * esize) % 16 == 0 &&
+                         (static_cast<long long>(head_dim) * kv_esize) % 8 == 0;
   int rc;
   if (paged_attention_fast_supported(p, dtype)) {
     rc = launch_paged_attention_fast(p, dtype, st);
+  } else if (kv8) {
+    switch (dtype) {
+      case CACHEIR_B200_F32: rc = launch_general<float, 4, true>(p, vector_ok, st); break;
+      case CACHEIR_B200_F16: rc = launch_general<__half, 8, true>(p, vector_ok, st); break;
+      default: rc = launch_general<__nv_bfloat16, 8, true>(p, vector_ok, st); break;
+    }
   } else
   switch (dtype) {
     case CACHEIR_B200_F32: rc = launch_general<float, 4>(p, vector_ok, st); break;
@@ -350,6 +384,18 @@ extern "C" int cacheir_b200_paged_attention_decode_batch(
     case CACHEIR_B200_F16: return launch_combine<__half>(p, st);
     default: return launch_combine<__nv_bfloat16>(p, st);
   }
+}
+
+extern "C" int cacheir_b200_paged_attention_decode_batch(
+    const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
+    const int32_t* seq_lens, void* out, int batch_size, int num_heads, int num_kv_heads,
+    int max_pages_per_seq, int page_size, int head_dim, int dtype, long long q_batch_stride,
+    long long out_batch_stride, float softmax_scale, int num_splits, void* workspace,
+    size_t workspace_bytes, void* stream) {
+  return cacheir_b200_paged_attention_decode_batch_ex(q, k_cache, v_cache, page_table, seq_lens, out, batch_size, num_heads,
+                                                      num_kv_heads, max_pages_per_seq, page_size, head_dim, dtype, q_batch_stride,
+                                                      out_batch_stride, softmax_scale, num_splits, workspace, workspace_bytes, 0,
+                                                      CACHEIR_B200_KV_SAME, nullptr, stream);
 }
 
 // ---- allocation-free variant -------------------------------------------------------

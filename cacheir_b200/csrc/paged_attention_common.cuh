@@ -16,6 +16,9 @@ struct AttnParams {
   const void* q;
   const void* k_cache;
   const void* v_cache;
+  const void* kv_scales;   // 8-bit pools only: fp16 [slots][kv_heads][2 (K, V)][page_size], one scale per cached row
+  int kv8;                 // the pools hold unsigned bytes: value = (byte - 128) * scale of its row
+  int num_slots;           // slots of the pool (0: unknown); bounds the tensor maps of the fast kernels
   const int32_t* page_table;
   const int32_t* seq_lens;
   void* out;
@@ -35,6 +38,7 @@ void resolve_attention_splits(int batch, int heads, int kv_heads, int max_pages,
                               int requested, int* splits, int* chunk_tokens);
 
 // Tensor-core path (fp16/bf16, head_dim 64/128, 16-token pages, GQA group <= 16).
+// (8-bit pools: fp16 queries, head_dim 128.)
 bool paged_attention_fast_supported(const AttnParams& p, int dtype);
 int launch_paged_attention_fast(const AttnParams& p, int dtype, cudaStream_t stream);
 int paged_attention_device_status(bool reset);

@@ -316,6 +316,279 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
   }
 }
 
+// ---- 8-bit pools -----------------------------------------------------------------------------------------
+// The same kernel shape for pools of unsigned bytes, value = (byte - 128) * scale[row] (fp16 queries, head_dim 128):
+// a (page, kv head) chunk is 16 rows x 128 bytes of K, the same of V, and 64 bytes of scales (16 fp16 for K, 16 for V),
+// half the bytes of the fp16 pool. ldmatrix reads the byte tiles as 16-bit units, so a thread receives four
+// consecutive dims of a K row (or, transposed, two dims of two V rows); a byte permute with 0x64 high bytes turns two
+// of them into the fp16 pair (1024 + b0, 1024 + b1), minus 1152 is (b - 128) exactly. The k order of the QK^T product
+// inside a 16-dim step is therefore 4t, 4t+1 | 4t+2, 4t+3 for thread t of a quad, and Q is loaded in that order; the
+// PV product yields the dims of a 16-dim block as two tiles, even dims and odd dims. The row scales multiply the scores
+// (K) and the probabilities (V) instead of the 2 x 2048 cached values.
+__device__ __forceinline__ void bulk_load_bytes(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// bytes i and j of w as the fp16 pair (b_i - 128, b_j - 128)
+template <uint32_t SEL>
+__device__ __forceinline__ uint32_t byte_pair(uint32_t w) {
+  const uint32_t biased = __byte_perm(w, 0x64646464u, SEL);                 // (1024 + b_i, 1024 + b_j)
+  const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&biased), __half2half2(__ushort_as_half(0x6480)));   // 0x6480 = 1152
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Six consumer warps (a page each per stage): the chain per page is longer than with fp16 pages (byte -> fp16
+// conversions in front of every MMA) while the page has half the bytes, so more pages must be in work per SM (two CTAs of six warps).
+constexpr int kQ8Warps = 6;
+constexpr int kQ8Threads = (kQ8Warps + 1) * 32;
+
+__global__ void __launch_bounds__(kQ8Threads, 2)
+paged_decode_mma_q8_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                           const AttnParams p, const int stages) {
+  constexpr int D = 128;
+  constexpr int kTileBytes = kPage * D;            // one K or V page chunk of bytes: 2 KB
+  constexpr int kScaleBytes = 2 * kPage * 2;       // 16 K scales + 16 V scales, fp16
+  constexpr int kStageBytes = kQ8Warps * 2 * kTileBytes + 1024;   // tiles (1 KB aligned), then the pages' scales
+  constexpr int kKSteps = D / 16;
+  constexpr int kDimTiles = D / 8;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + stages * kStageBytes);
+  uint64_t* empty = full + stages;
+
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int b = blockIdx.z;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int seq_len = p.seq_lens[b];
+  const int t_begin = split * p.chunk_tokens;
+  if (p.splits > 1 && t_begin >= seq_len) return;      // combine never reads this split
+  const int t_end = min(seq_len, t_begin + p.chunk_tokens);
+  const int page_begin = t_begin / kPage;
+  const int n_pages = t_end > t_begin ? (t_end - t_begin + kPage - 1) / kPage : 0;
+  const int n_iters = (n_pages + kQ8Warps - 1) / kQ8Warps;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&full[s]), 1);
+      mbar_init(smem_u32(&empty[s]), kQ8Warps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int g = lane >> 2;
+  const int t4 = lane & 3;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  float o[kDimTiles][4];       // tile 2c: even dims of the 16-dim block c, tile 2c+1: its odd dims
+#pragma unroll
+  for (int i = 0; i < kDimTiles; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  bool ok = true;
+
+  if (warp == kQ8Warps) {
+    // ---------------- producer warp: lane j copies page j of each stage ----------------
+    const int32_t* pt = p.page_table + static_cast<size_t>(b) * p.max_pages + page_begin;
+    const __half* scales = static_cast<const __half*>(p.kv_scales);
+    int next_id = lane < min(kQ8Warps, n_pages) ? pt[lane] : 0;
+    for (int it = 0; it < n_iters && ok; ++it) {
+      const int s = it % stages;
+      const uint32_t ph = (it / stages) & 1;
+      const int first = it * kQ8Warps;
+      const int cnt = min(kQ8Warps, n_pages - first);
+      const int page_id = next_id;
+      if (first + kQ8Warps + lane < n_pages && lane < kQ8Warps) next_id = pt[first + kQ8Warps + lane];
+      if (lane == 0) {
+        ok = mbar_wait(smem_u32(&empty[s]), ph ^ 1, 1);
+        if (ok) mbar_expect_tx(smem_u32(&full[s]), cnt * (2 * kTileBytes + kScaleBytes));
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (ok && lane < cnt) {
+        uint8_t* stage = smem + s * kStageBytes;
+        const int chunk = page_id * p.kv_heads + kvh;
+        tma_load_2d_tile(smem_u32(stage + lane * 2 * kTileBytes), &tmap_k, smem_u32(&full[s]), 0, chunk * kPage);
+        tma_load_2d_tile(smem_u32(stage + lane * 2 * kTileBytes + kTileBytes), &tmap_v, smem_u32(&full[s]), 0, chunk * kPage);
+        bulk_load_bytes(smem_u32(stage + kQ8Warps * 2 * kTileBytes + lane * kScaleBytes),
+                        scales + static_cast<size_t>(chunk) * 2 * kPage, kScaleBytes, smem_u32(&full[s]));
+      }
+    }
+  } else {
+    // ---------------- consumer warps ----------------
+    // Q as the A operand, k order of a 16-dim step: thread t of a quad holds dims 4t, 4t+1 (first half) and 4t+2, 4t+3
+    uint32_t qa[kKSteps][4];
+    {
+      const __half* qb = static_cast<const __half*>(p.q) + static_cast<size_t>(b) * p.q_stride + static_cast<size_t>(kvh) * p.group * D;
+#pragma unroll
+      for (int ks = 0; ks < kKSteps; ++ks) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int row = g + (r & 1) * 8;
+          const int col = ks * 16 + 4 * t4 + (r >> 1) * 2;
+          qa[ks][r] = row < p.group ? *reinterpret_cast<const uint32_t*>(qb + static_cast<size_t>(row) * D + col) : 0u;
+        }
+      }
+    }
+    const uint32_t lrow = lane & 7;
+    const uint32_t lmat = lane >> 3;
+    for (int it = 0; it < n_iters && ok; ++it) {
+      const int s = it % stages;
+      ok = mbar_wait(smem_u32(&full[s]), (it / stages) & 1, 2);
+      if (!ok) break;
+      const int pg = it * kQ8Warps + warp;
+      if (pg < n_pages) {
+        const uint8_t* stage = smem + s * kStageBytes;
+        const uint32_t kbase = smem_u32(stage + warp * 2 * kTileBytes);
+        const uint32_t vbase = kbase + kTileBytes;
+        const __half* sc_k = reinterpret_cast<const __half*>(stage + kQ8Warps * 2 * kTileBytes + warp * kScaleBytes);
+        const __half* sc_v = sc_k + kPage;
+        // ---- S = Q K^T for the 16 tokens of the page: two n tiles of 8 tokens; one ldmatrix covers four k steps ----
+        float sc[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+          const uint32_t token = nt * 8 + lrow;
+#pragma unroll
+          for (int kk = 0; kk < kKSteps / 4; ++kk) {
+            const uint32_t c = 4 * kk + lmat;          // 16-byte chunk of the row = k step
+            uint32_t kb[4];
+            ldmatrix_x4(kbase + token * 128 + (((c & 7) ^ (token & 7)) << 4), kb);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              mma_16816<__half>(sc[nt], qa[4 * kk + i], byte_pair<0x4140>(kb[i]), byte_pair<0x4342>(kb[i]));
+          }
+        }
+        // ---- online softmax over the page (rows g and g+8; columns 2*t4, 2*t4+1 of each tile) ----
+        const int tok0 = t_begin + pg * kPage;
+        float pmax[2] = {-INFINITY, -INFINITY};
+        float vscale[2][2];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const float ks0 = __half2float(sc_k[nt * 8 + 2 * t4]), ks1 = __half2float(sc_k[nt * 8 + 2 * t4 + 1]);
+          vscale[nt][0] = __half2float(sc_v[nt * 8 + 2 * t4]);
+          vscale[nt][1] = __half2float(sc_v[nt * 8 + 2 * t4 + 1]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int tok = tok0 + nt * 8 + 2 * t4 + (e & 1);
+            const float v = tok < t_end ? sc[nt][e] * ((e & 1) ? ks1 : ks0) * p.scale_log2 : -INFINITY;
+            sc[nt][e] = v;
+            pmax[e >> 1] = fmaxf(pmax[e >> 1], v);
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          pmax[r] = fmaxf(pmax[r], __shfl_xor_sync(0xffffffffu, pmax[r], 1));
+          pmax[r] = fmaxf(pmax[r], __shfl_xor_sync(0xffffffffu, pmax[r], 2));
+        }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const float m_new = fmaxf(m_run[r], pmax[r]);
+          corr[r] = exp2f(m_run[r] - m_new);
+          m_run[r] = m_new;
+        }
+        uint32_t pa[4];
+        {
+          float pr[2][4];
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pr[nt][e] = exp2f(sc[nt][e] - m_run[e >> 1]);
+#pragma unroll
+          for (int r = 0; r < 2; ++r)
+            l_run[r] = l_run[r] * corr[r] + (pr[0][2 * r] + pr[0][2 * r + 1] + pr[1][2 * r] + pr[1][2 * r + 1]);
+          // P times the V row scales as the A operand of the PV product (a masked token has p = 0; its stale scale must not turn that into NaN)
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pr[nt][e] = pr[nt][e] > 0.f ? pr[nt][e] * vscale[nt][e & 1] : 0.f;
+          pa[0] = pack2<__half>(pr[0][0], pr[0][1]);
+          pa[1] = pack2<__half>(pr[0][2], pr[0][3]);
+          pa[2] = pack2<__half>(pr[1][0], pr[1][1]);
+          pa[3] = pack2<__half>(pr[1][2], pr[1][3]);
+        }
+        // ---- O = O * corr + P V: one transposed ldmatrix covers two 16-dim blocks = four n tiles ----
+#pragma unroll
+        for (int j = 0; j < kDimTiles / 4; ++j) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            o[4 * j + i][0] *= corr[0]; o[4 * j + i][1] *= corr[0]; o[4 * j + i][2] *= corr[1]; o[4 * j + i][3] *= corr[1];
+          }
+          const uint32_t token = (lmat & 1) * 8 + lrow;
+          const uint32_t c = 2 * j + (lmat >> 1);
+          uint32_t vb[4];       // [block 2j: tokens 0-7, tokens 8-15], [block 2j+1: tokens 0-7, tokens 8-15]
+          ldmatrix_x4_trans(vbase + token * 128 + (((c & 7) ^ (token & 7)) << 4), vb);
+          mma_16816<__half>(o[4 * j], pa, byte_pair<0x4240>(vb[0]), byte_pair<0x4240>(vb[1]));          // even dims of block 2j
+          mma_16816<__half>(o[4 * j + 1], pa, byte_pair<0x4341>(vb[0]), byte_pair<0x4341>(vb[1]));      // odd dims
+          mma_16816<__half>(o[4 * j + 2], pa, byte_pair<0x4240>(vb[2]), byte_pair<0x4240>(vb[3]));      // block 2j+1
+          mma_16816<__half>(o[4 * j + 3], pa, byte_pair<0x4341>(vb[2]), byte_pair<0x4341>(vb[3]));
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty[s]));
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+  }
+
+  // ---------------- merge the consumer warps in warp order ----------------
+  __syncthreads();
+  float* s_m = reinterpret_cast<float*>(smem);
+  float* s_l = s_m + kQ8Warps * 16;
+  float* s_o = s_l + kQ8Warps * 16;
+  if (warp < kQ8Warps) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + r * 8;
+      if (t4 == 0) { s_m[warp * 16 + row] = m_run[r]; s_l[warp * 16 + row] = l_run[r]; }
+#pragma unroll
+      for (int i = 0; i < kDimTiles; ++i) {
+        // tile i = block i/2, parity i&1; its columns 2*t4, 2*t4+1 are dims 16*(i/2) + 2*column + parity
+        const int d0 = 16 * (i >> 1) + 4 * t4 + (i & 1);
+        s_o[(warp * 16 + row) * D + d0] = o[i][2 * r];
+        s_o[(warp * 16 + row) * D + d0 + 2] = o[i][2 * r + 1];
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < p.group * D; idx += kQ8Threads) {
+    const int row = idx / D;
+    const int d = idx % D;
+    float m_tot = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kQ8Warps; ++w) m_tot = fmaxf(m_tot, s_m[w * 16 + row]);
+    float l_tot = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kQ8Warps; ++w) {
+      const float mi = s_m[w * 16 + row];
+      const float wgt = (mi == -INFINITY) ? 0.f : exp2f(mi - m_tot);
+      l_tot = fmaf(s_l[w * 16 + row], wgt, l_tot);
+      acc = fmaf(s_o[(w * 16 + row) * D + d], wgt, acc);
+    }
+    const int h = kvh * p.group + row;
+    if (p.splits == 1) {
+      __half* ob = static_cast<__half*>(p.out) + static_cast<size_t>(b) * p.out_stride;
+      ob[static_cast<size_t>(h) * D + d] = __float2half_rn(l_tot > 0.f ? acc / l_tot : 0.f);
+    } else {
+      const size_t unit = (static_cast<size_t>(b) * p.heads + h) * p.splits + split;
+      p.ws_acc[unit * D + d] = acc;
+      if (d == 0) {
+        p.ws_ml[unit * 2] = m_tot;
+        p.ws_ml[unit * 2 + 1] = l_tot;
+      }
+    }
+  }
+}
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -366,9 +639,42 @@ int launch_fast(const AttnParams& p, int dtype, uint64_t pool_rows, cudaStream_t
   return launch_status();
 }
 
+
+// 8-bit pool [slots * kv_heads * 16 rows][128 bytes]: box {128, 16}, 128-byte swizzle.
+bool encode_pool_q8(CUtensorMap* map, const void* base, uint64_t rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {128, rows};
+  const cuuint64_t strides[1] = {128};
+  const cuuint32_t box[2] = {128, kPage};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int launch_fast_q8(const AttnParams& p, uint64_t pool_rows, cudaStream_t stream) {
+  CUtensorMap tmap_k, tmap_v;
+  if (!encode_pool_q8(&tmap_k, p.k_cache, pool_rows) || !encode_pool_q8(&tmap_v, p.v_cache, pool_rows)) return CACHEIR_B200_EUNSUPPORTED;
+  constexpr int kStageBytes = kQ8Warps * 2 * kPage * 128 + 1024;
+  const int stages = 4;
+  size_t smem = 1024 + static_cast<size_t>(stages) * kStageBytes + 256;
+  const size_t merge = static_cast<size_t>(kQ8Warps) * 16 * (128 + 2) * sizeof(float) + 1024;
+  if (smem < merge) smem = merge;
+  cudaError_t e = cudaFuncSetAttribute(paged_decode_mma_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const dim3 grid(p.splits, p.kv_heads, p.batch);
+  paged_decode_mma_q8_kernel<<<grid, kQ8Threads, smem, stream>>>(tmap_k, tmap_v, p, stages);
+  return launch_status();
+}
+
 }  // namespace
 
 bool paged_attention_fast_supported(const AttnParams& p, int dtype) {
+  if (p.kv8) {
+    return dtype == CACHEIR_B200_F16 && p.head_dim == 128 && p.page_size == kPage && p.group <= 16 && p.chunk_tokens % kPage == 0 &&
+           aligned_to(p.k_cache, 128) && aligned_to(p.v_cache, 128) && aligned_to(p.kv_scales, 16) && aligned_to(p.q, 4) &&
+           (p.q_stride % 2) == 0 && encode_fn() != nullptr;
+  }
   if (dtype != CACHEIR_B200_F16 && dtype != CACHEIR_B200_BF16) return false;
   if (p.head_dim != 64 && p.head_dim != 128) return false;
   if (p.page_size != kPage || p.group > 16) return false;
@@ -378,9 +684,11 @@ bool paged_attention_fast_supported(const AttnParams& p, int dtype) {
 }
 
 int launch_paged_attention_fast(const AttnParams& p, int dtype, cudaStream_t stream) {
-  // The C ABI (like the reference's) does not carry the slot count of the pool; the tensor map only
-  // needs an upper bound for its bounds check, and page ids are trusted exactly as in every other kernel.
-  const uint64_t rows = 1ull << 30;
+  // With the pool's slot count the tensor maps carry the true row bound: the copy engine then zero-fills a chunk
+  // whose page id lies outside the pool instead of reading past it. Without it (the reference's launcher signature
+  // has no such argument) the bound is a formality and page ids are trusted.
+  const uint64_t rows = p.num_slots > 0 ? static_cast<uint64_t>(p.num_slots) * p.kv_heads * kPage : (1ull << 30);
+  if (p.kv8) return launch_fast_q8(p, rows, stream);
   if (dtype == CACHEIR_B200_F16)
     return p.head_dim == 128 ? launch_fast<__half, 128>(p, dtype, rows, stream) : launch_fast<__half, 64>(p, dtype, rows, stream);
   return p.head_dim == 128 ? launch_fast<__nv_bfloat16, 128>(p, dtype, rows, stream)

@@ -115,7 +115,15 @@ class B200KVPageAllocator:
         return len(self._refcount)
 
     # ---- pools ---------------------------------------------------------------------
-    def configure(self, *, torch: Any, device: Any, dtype: Any, num_layers: int, kv_heads: int, head_dim: int) -> None:
+    def configure(self, *, torch: Any, device: Any, dtype: Any, num_layers: int, kv_heads: int, head_dim: int,
+                  kv_dtype: str = "same") -> None:
+        """`kv_dtype` "int8": pools of unsigned bytes with one fp16 scale per cached row (pool["scales"],
+        [slots, kv_heads, 2, page]); "same": pools of the activation type, the reference's layout."""
+        if kv_dtype not in {"same", "int8"}:
+            raise ValueError(f"unsupported kv_dtype {kv_dtype!r}")
+        self.kv_dtype = kv_dtype
+        if kv_dtype == "int8":
+            dtype = torch.uint8
         spec = (str(device), str(dtype), int(kv_heads), int(head_dim))
         if self._pool_spec is not None:
             if self._pool_spec[:4] != spec or len(self._pools) != num_layers:
@@ -130,11 +138,17 @@ class B200KVPageAllocator:
         self.generation += 1
         elem = torch.empty((), dtype=dtype).element_size()
         self.page_bytes = 2 * self._kv_heads * self.page_size * self._head_dim * elem
+        if kv_dtype == "int8":
+            self.page_bytes += 2 * self._kv_heads * self.page_size * 2
 
     def _new_pool(self, slots: int) -> dict[str, Any]:
         shape = (slots, self._kv_heads, self.page_size, self._head_dim)
-        return {"keys": self._torch.zeros(shape, device=self._device, dtype=self._dtype),
+        pool = {"keys": self._torch.zeros(shape, device=self._device, dtype=self._dtype),
                 "values": self._torch.zeros(shape, device=self._device, dtype=self._dtype)}
+        if getattr(self, "kv_dtype", "same") == "int8":
+            pool["scales"] = self._torch.zeros((slots, self._kv_heads, 2, self.page_size), device=self._device,
+                                               dtype=self._torch.float16)
+        return pool
 
     def reserve_slots(self, slots: int) -> None:
         """Pre-size the pools so that no growth (and no pointer change) happens later."""
@@ -151,8 +165,8 @@ class B200KVPageAllocator:
             return
         for layer, pool in self._pools.items():
             grown = self._new_pool(new_capacity)
-            grown["keys"][:old] = pool["keys"]
-            grown["values"][:old] = pool["values"]
+            for name in pool:
+                grown[name][:old] = pool[name]
             self._pools[layer] = grown
         self.pool_grows += 1
         self.generation += 1

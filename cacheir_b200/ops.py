@@ -59,19 +59,27 @@ def attention_workspace_bytes(batch: int, heads: int, head_dim: int, num_splits:
 def paged_attention_decode_batch(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                                  page_table: torch.Tensor, seq_lens: torch.Tensor, *,
                                  out: torch.Tensor | None = None, softmax_scale: float | None = None,
-                                 num_splits: int = 0, workspace: torch.Tensor | None = None) -> torch.Tensor:
+                                 num_splits: int = 0, workspace: torch.Tensor | None = None,
+                                 kv_scales: torch.Tensor | None = None) -> torch.Tensor:
     """out[b,h,:] = softmax(scale * q[b,h].K_b^T) V_b over the pages of sequence b.
 
     q: [B, H, D] (rows may be strided views of a wider buffer); k_cache/v_cache:
     [slots, KVH, page, D] contiguous, same dtype as q; page_table: int32
     [B, max_pages]; seq_lens: int32 [B]. Same contract as the reference's
-    Triton launch (cacheir/runtime/cuda.py:1238-1251)."""
-    _require_cuda(q, k_cache, v_cache, page_table, seq_lens, out, workspace)
+    Triton launch (cacheir/runtime/cuda.py:1238-1251). With `kv_scales` (fp16
+    [slots, KVH, 2, page]) the pools are uint8: value = (byte - 128) * scale of its row."""
+    _require_cuda(q, k_cache, v_cache, page_table, seq_lens, out, workspace, kv_scales)
     if q.dim() != 3 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape:
         raise ValueError("expected q [B,H,D] and k_cache/v_cache [slots,KVH,page,D]")
     batch, heads, head_dim = (int(s) for s in q.shape)
     _, kv_heads, page_size, pool_dim = (int(s) for s in k_cache.shape)
-    if pool_dim != head_dim or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+    kv8 = kv_scales is not None
+    if kv8:
+        if k_cache.dtype != torch.uint8 or v_cache.dtype != torch.uint8 or pool_dim != head_dim:
+            raise ValueError("8-bit KV pools must be uint8 with q's head_dim")
+        if kv_scales.dtype != torch.float16 or tuple(kv_scales.shape) != (int(k_cache.shape[0]), kv_heads, 2, page_size) or not kv_scales.is_contiguous():
+            raise ValueError("kv_scales must be a contiguous fp16 [slots, KVH, 2, page] tensor")
+    elif pool_dim != head_dim or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
         raise ValueError("q and the KV pool must share head_dim and dtype")
     if page_table.dtype != torch.int32 or seq_lens.dtype != torch.int32:
         raise TypeError("page_table and seq_lens must be int32")
@@ -92,10 +100,11 @@ def paged_attention_decode_batch(q: torch.Tensor, k_cache: torch.Tensor, v_cache
     if need > 0 and workspace is None:
         workspace = torch.empty((need + 3) // 4, device=q.device, dtype=torch.float32)
     ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
-    check(lib.cacheir_b200_paged_attention_decode_batch(
+    check(lib.cacheir_b200_paged_attention_decode_batch_ex(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(),
         out.data_ptr(), batch, heads, kv_heads, max_pages, page_size, head_dim, dtype_code(q.dtype),
-        q.stride(0), out.stride(0), float(softmax_scale or 0.0), int(splits), _ptr(workspace), ws_bytes, _stream()),
+        q.stride(0), out.stride(0), float(softmax_scale or 0.0), int(splits), _ptr(workspace), ws_bytes,
+        int(k_cache.shape[0]), 1 if kv8 else 0, _ptr(kv_scales), _stream()),
         "paged_attention_decode_batch")
     return out
 
@@ -300,6 +309,24 @@ def kv_append(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: 
                                              page_table.data_ptr(), positions.data_ptr(), batch, kv_heads,
                                              int(page_table.shape[1]), page_size, head_dim, dtype_code(k.dtype),
                                              k.stride(0), v.stride(0), _stream()), "kv_append")
+
+
+def kv_append_q8(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_scales: torch.Tensor,
+                 page_table: torch.Tensor, positions: torch.Tensor) -> None:
+    """`kv_append` into uint8 pools: each new row is quantised with its own fp16 scale (kv_scales [slots, KVH, 2, page])."""
+    _require_cuda(k, v, k_cache, v_cache, kv_scales, page_table, positions)
+    _, kv_heads, page_size, head_dim = (int(s) for s in k_cache.shape)
+    batch = int(k.shape[0])
+    if k.shape != v.shape or k.shape[1] != kv_heads * head_dim or k.stride(1) != 1 or v.stride(1) != 1:
+        raise ValueError("k and v must be [B, KVH*D] with dense rows")
+    if k_cache.dtype != torch.uint8 or v_cache.dtype != torch.uint8 or kv_scales.dtype != torch.float16:
+        raise TypeError("8-bit KV pools are uint8 with fp16 scales")
+    if page_table.dtype != torch.int32 or positions.dtype != torch.int32:
+        raise TypeError("page_table and positions must be int32")
+    check(_lib.load().cacheir_b200_kv_append_q8(k.data_ptr(), v.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                                kv_scales.data_ptr(), page_table.data_ptr(), positions.data_ptr(), batch,
+                                                kv_heads, int(page_table.shape[1]), page_size, head_dim, dtype_code(k.dtype),
+                                                k.stride(0), v.stride(0), _stream()), "kv_append_q8")
 
 
 def silu_mul(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -125,7 +125,8 @@ class _Engine:
 
     def __init__(self, artifact: Any, *, device: torch.device, dtype: torch.dtype, weights: B200WeightStore | None,
                  tensor_source: Any, kv_allocator: B200KVPageAllocator | None, max_seq_len: int | None,
-                 use_cuda_graph: bool, attention_splits: int, max_plans: int, tensor_parallel: TensorParallel | None = None):
+                 use_cuda_graph: bool, attention_splits: int, max_plans: int, tensor_parallel: TensorParallel | None = None,
+                 kv_dtype: str = "same"):
         self.artifact = artifact
         self.tp = tensor_parallel or TensorParallel(0, 1)
         self.device = device
@@ -148,7 +149,7 @@ class _Engine:
         # under tensor parallelism a rank's pool holds only its own KV heads
         self.allocator.configure(torch=torch, device=device, dtype=dtype, num_layers=int(self.config.num_layers),
                                  kv_heads=int(self.config.num_key_value_heads) // self.tp.world,
-                                 head_dim=int(self.config.head_dim))
+                                 head_dim=int(self.config.head_dim), kv_dtype=kv_dtype)
         self.max_seq_len = int(max_seq_len or self.config.max_position_embeddings)
         # Tensor-parallel collectives: this package's own kernels over peer memory (graph-capturable), or the
         # process group's library collectives launched eagerly (CB200_TP_COLLECTIVES=nccl; never captured).
@@ -235,8 +236,8 @@ class _Engine:
         return self._rope_tables[key]
 
     def prefill_plan(self, rows: int, needed_pages: int) -> "_DecodePlan":
-        """The plan that pushes `rows` consecutive prompt tokens of ONE sequence through the decode graph at once:
-        row i is the token at position start+i, reads the sequence's page table and attends to start+i+1 tokens."""
+        """The plan that pushes `rows` prompt tokens through the decode graph at once: row i is one (sequence,
+        position) pair, reads that sequence's page table and attends to position+1 tokens."""
         key = ("prefill", rows)
         plan = self.plans.get(key)
         if plan is not None and (plan.pool_generation != self.allocator.generation or plan.width < needed_pages):
@@ -572,7 +573,7 @@ class _DecodePlan:
         pool = eng.allocator.pool_for_layer(layer)
         if pool is None:
             raise RuntimeError(f"no KV page pool for layer {layer}")
-        k_pool, v_pool = pool["keys"], pool["values"]
+        k_pool, v_pool, kv_scales = pool["keys"], pool["values"], pool.get("scales")
         out = self._buf(heads * head_dim)
         q3 = q.as_strided((self.batch, heads, head_dim), (q.stride(0), head_dim, 1), q.storage_offset())
         out3 = out.view(self.batch, heads, head_dim)
@@ -583,9 +584,12 @@ class _DecodePlan:
             self._attn_ws = torch.empty((max(1, (ws_bytes + 3) // 4),), device=eng.device, dtype=torch.float32)
         ws = self._attn_ws if ws_bytes else None
         if not appended:   # (the fused QKV kernel has already written the new rows)
-            self._emit(lambda: ops.kv_append(k, v, k_pool, v_pool, self.page_table, self.positions), "b200.kv_append")
+            if kv_scales is not None:
+                self._emit(lambda: ops.kv_append_q8(k, v, k_pool, v_pool, kv_scales, self.page_table, self.positions), "b200.kv_append_q8")
+            else:
+                self._emit(lambda: ops.kv_append(k, v, k_pool, v_pool, self.page_table, self.positions), "b200.kv_append")
         self._emit(lambda: ops.paged_attention_decode_batch(q3, k_pool, v_pool, self.page_table, self.seq_lens, out=out3,
-                                                            num_splits=splits, workspace=ws),
+                                                            num_splits=splits, workspace=ws, kv_scales=kv_scales),
                    "b200.paged_attention_decode_batch.persistent_shared", launches=2 if splits > 1 else 1)
         return out
 
@@ -610,23 +614,35 @@ class _DecodePlan:
             self.seq_lens.copy_(self.host_lens, non_blocking=True)
         self.synced_owner_state = state
 
-    def sync_prefill_chunk(self, cache: B200PagedKVCache, start: int, token_ids: list[int]) -> None:
-        """Rows 0..n-1 are the tokens at positions start..start+n-1 of one sequence whose pages already cover
-        them; rows beyond n repeat the last token (same position, same values: harmless duplicates)."""
-        n = len(token_ids)
+    def sync_prefill_rows(self, rows: list[tuple[B200PagedKVCache, int, int]]) -> None:
+        """Row r of the pass is the prompt token `rows[r] = (cache, position, token id)`: it reads that sequence's
+        page table, appends its K/V row at `position` and attends to `position + 1` tokens. Rows may belong to
+        different sequences; rows of one sequence see each other's K/V through the pool (all rows append before
+        any row attends). Rows beyond the list repeat the last entry (same position, same values: harmless
+        duplicates). The pages of every position must already be reserved."""
+        n = len(rows)
         self.h2d_done.synchronize()
         ids = self.host_ids.numpy()
         lens = self.host_lens.numpy()
+        table = self.host_table.numpy()
+        cached_rows: dict[int, np.ndarray] = {}
         for row in range(self.batch):
-            i = min(row, n - 1)
-            ids[row] = int(token_ids[i])
-            lens[row] = start + i            # the step turns this into position start+i and length start+i+1
-        self.host_table.numpy()[:] = cache.page_table_row(self.width)[None, :]
+            cache, position, token = rows[min(row, n - 1)]
+            ids[row] = int(token)
+            lens[row] = int(position)            # the step turns this into position and length position + 1
+            key = id(cache)
+            if key not in cached_rows:
+                cached_rows[key] = cache.page_table_row(self.width)
+            table[row] = cached_rows[key]
         self.ids.copy_(self.host_ids, non_blocking=True)
         self.seq_lens.copy_(self.host_lens, non_blocking=True)
         self.page_table.copy_(self.host_table, non_blocking=True)
         self.h2d_done.record()
         self.synced_owner_state = None
+
+    def sync_prefill_chunk(self, cache: B200PagedKVCache, start: int, token_ids: list[int]) -> None:
+        """Rows 0..n-1 are the tokens at positions start..start+n-1 of one sequence."""
+        self.sync_prefill_rows([(cache, start + i, int(t)) for i, t in enumerate(token_ids)])
 
     def run_program(self, *, feedback: bool = False) -> None:
         """One decode step: eager launches on the first step, CUDA-graph replay afterwards."""
@@ -691,6 +707,7 @@ class B200DecodeRuntime:
         clone_outputs: bool = True,
         tensor_parallel: TensorParallel | None = None,
         memory_limit_mb: float | None = None,
+        kv_dtype: str = "same",
         _engine: _Engine | None = None,
     ):
         if isinstance(artifact, (str, Path)):
@@ -709,7 +726,8 @@ class B200DecodeRuntime:
             with torch.cuda.device(dev):
                 _engine = _Engine(artifact, device=dev, dtype=selected, weights=weights, tensor_source=tensor_source,
                                   kv_allocator=kv_allocator, max_seq_len=max_seq_len, use_cuda_graph=use_cuda_graph,
-                                  attention_splits=attention_splits, max_plans=max_plans, tensor_parallel=tensor_parallel)
+                                  attention_splits=attention_splits, max_plans=max_plans, tensor_parallel=tensor_parallel,
+                                  kv_dtype=kv_dtype)
         self._engine = _engine
         self.artifact = _engine.artifact
         self.device = _engine.device
@@ -896,6 +914,34 @@ class B200DecodeRuntime:
         eng.count("cacheir.b200_prefill_chunk", (len(tokens) + chunk - 1) // chunk)
         return out
 
+    def _prefill_packed(self, sessions: list["B200DecodeRuntime"], token_id_batches: list[list[int]], out: torch.Tensor) -> None:
+        """Prefill of several sequences through shared passes (cuda.py:584-629 pads every prompt to the longest and
+        masks; here nothing is padded): the (sequence, position) pairs are laid out in order and cut into passes of
+        `prefill_chunk` rows; a pass appends all its K/V rows, then every row attends to the tokens up to itself
+        through its own sequence's page table. `out[i, t]` receives the logits of token t of sequence i."""
+        eng = self._engine
+        chunk = eng.prefill_chunk
+        work: list[tuple[int, int]] = []                       # (sequence index, position)
+        for i, (session, ids) in enumerate(zip(sessions, token_id_batches)):
+            start = session.kv_cache.tokens
+            session.kv_cache.extend(len(ids))                  # reserves the pages of the whole prompt
+            work.extend((i, start + t) for t in range(len(ids)))
+        self._check_positions(sessions)
+        needed = max((s.kv_cache.tokens + eng.page_size - 1) // eng.page_size for s in sessions)
+        starts = [s.kv_cache.tokens - len(ids) for s, ids in zip(sessions, token_id_batches)]
+        passes = 0
+        with torch.cuda.device(self.device):
+            for w0 in range(0, len(work), chunk):
+                part = work[w0:w0 + chunk]
+                plan = eng.prefill_plan(chunk, needed)
+                plan.sync_prefill_rows([(sessions[i].kv_cache, pos, int(token_id_batches[i][pos - starts[i]])) for i, pos in part])
+                plan.run_program()
+                seq = torch.tensor([i for i, _ in part], device=self.device, dtype=torch.long)
+                tok = torch.tensor([pos - starts[i] for i, pos in part], device=self.device, dtype=torch.long)
+                out[seq, tok] = plan.logits[: len(part)]
+                passes += 1
+        eng.count("cacheir.b200_prefill_chunk", passes)
+
     def run_prefill_batch(self, sessions: list["B200DecodeRuntime"], token_id_batches: list[list[int]]) -> torch.Tensor:
         """Variable-length batched prefill (cuda.py:584-629): returns zero-padded logits [N, max_len, vocab]."""
         if not sessions:
@@ -910,10 +956,16 @@ class B200DecodeRuntime:
         vocab = int(self._engine.config.vocab_size)
         out = torch.zeros((len(sessions), max(lens), vocab), device=self.device, dtype=self.dtype)
         chunk = self._engine.prefill_chunk
-        if chunk > 1 and max(lens) > chunk // 4:
-            # long prompts: each sequence goes through the chunked prefill (its tokens are the rows of a step)
-            for i, (session, ids) in enumerate(zip(sessions, token_id_batches)):
-                out[i, : lens[i]] = session.run([list(ids)], mode="prefill", reset_kv=True)[0]
+        if chunk > 1 and sum(lens) > chunk // 4:
+            # Packed prefill: the prompt tokens of all sequences are the rows of 64-row passes through the decode
+            # graph, sequence after sequence, so short prompts share a pass and a long prompt spans several.
+            self._enforce_memory_limit()
+            try:
+                self._prefill_packed(sessions, token_id_batches, out)
+            except (torch.cuda.OutOfMemoryError, KVPoolExhausted) as exc:
+                self._recover_from_oom()
+                raise RuntimeError("CacheIR CUDA runtime recovered from an out-of-memory condition; "
+                                   "retry with a smaller batch/context") from exc
         else:
             for pos in range(max(lens)):
                 rows = [i for i, n in enumerate(lens) if pos < n]

@@ -102,6 +102,25 @@ int cacheir_b200_paged_attention_decode_batch(
     long long out_batch_stride, float softmax_scale, int num_splits,
     void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same with two more inputs.
+ *   num_slots: slots of the pool (k_cache.shape[0]); 0 = unknown. With it the tensor maps of the fast kernel carry
+ *     the pool's true extent, so a page id outside the pool reads zeros instead of memory past the pool.
+ *   kv_dtype / kv_scales: CACHEIR_B200_KV_INT8 selects pools of unsigned bytes, half the bytes of an fp16 pool:
+ *     value = (byte - 128) * kv_scales[slot][kv_head][0 (K) | 1 (V)][token % page_size], fp16 scales, one per cached
+ *     row, written by cacheir_b200_kv_append_q8. q and out keep `dtype`. CACHEIR_B200_KV_SAME: pools of `dtype`.
+ * The reference only models the byte cost of a smaller cache (cacheir/runtime/kv_cache.py:138-259); its kernels
+ * read pools of the activation type. */
+#define CACHEIR_B200_KV_SAME 0
+#define CACHEIR_B200_KV_INT8 1
+int cacheir_b200_paged_attention_decode_batch_ex(
+    const void* q, const void* k_cache, const void* v_cache,
+    const int32_t* page_table, const int32_t* seq_lens, void* out,
+    int batch_size, int num_heads, int num_kv_heads, int max_pages_per_seq,
+    int page_size, int head_dim, int dtype, long long q_batch_stride,
+    long long out_batch_stride, float softmax_scale, int num_splits,
+    void* workspace, size_t workspace_bytes, int num_slots, int kv_dtype,
+    const void* kv_scales, void* stream);
+
 /* Allocation-free variant of cacheir_b200_paged_attention_decode_batch. It has no
  * counterpart in the reference; it exists for callers that have inputs and outputs
  * but no way to get scratch memory on the device: code bound to the reference's own
@@ -373,6 +392,16 @@ int cacheir_b200_kv_append(const void* k, const void* v, void* k_cache, void* v_
                            int page_size, int head_dim, int dtype,
                            long long k_batch_stride, long long v_batch_stride,
                            void* stream);
+
+/* The same into 8-bit pools (see cacheir_b200_paged_attention_decode_batch_ex): every new row is quantised with its
+ * own scale, scale = fp16(max|row| / 127) (1 for an all-zero row), byte = clamp(rint(value / scale), -127, 127) + 128;
+ * the scale goes to kv_scales[slot][kv_head][0 (K) | 1 (V)][pos % page_size] (fp16). head_dim <= 256.
+ * No counterpart in the reference beyond the cost model of cacheir/runtime/kv_cache.py:138-259. */
+int cacheir_b200_kv_append_q8(const void* k, const void* v, void* k_cache, void* v_cache, void* kv_scales,
+                              const int32_t* page_table, const int32_t* positions, int batch_size,
+                              int num_kv_heads, int max_pages_per_seq, int page_size, int head_dim,
+                              int dtype, long long k_batch_stride, long long v_batch_stride,
+                              void* stream);
 
 /* Replaces `cacheir_cuda_fused_swiglu` (cacheir_cuda_kernels.cu:286-295),
  * Triton `silu_mul_kernel` (triton_kernels.py:51-59), `_silu_mul`

@@ -311,6 +311,24 @@ def paged_attention_decode(q: np.ndarray, k_pool: np.ndarray, v_pool: np.ndarray
     return out
 
 
+def quantize_kv_rows(rows: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """8-bit KV pages (an extension: the reference only models the byte cost of a smaller cache,
+    cacheir/runtime/kv_cache.py:138-259). Each cached row [..., D] gets its own scale:
+    scale = fp16(max|row| / 127) (1 for an all-zero row), byte = clip(rint(row / scale), -127, 127) + 128.
+    Returns (uint8 bytes, fp16 scales [...])."""
+    rows = np.asarray(rows, dtype=np.float32)
+    amax = np.max(np.abs(rows), axis=-1)
+    scale = (amax / np.float32(127.0)).astype(np.float16)
+    scale = np.where(scale.astype(np.float32) == 0.0, np.float16(1.0), scale).astype(np.float16)
+    q = np.clip(np.rint(rows / scale.astype(np.float32)[..., None]), -127, 127)
+    return (q + 128).astype(np.uint8), scale
+
+
+def dequantize_kv_pool(pool_u8: np.ndarray, scales: np.ndarray, which: int) -> np.ndarray:
+    """[slots, kv_heads, page, D] bytes and scales [slots, kv_heads, 2, page] -> float32 values; which: 0 = K, 1 = V."""
+    return (pool_u8.astype(np.float32) - np.float32(128.0)) * scales[:, :, which, :].astype(np.float32)[..., None]
+
+
 # --------------------------------------------------------------------------
 # Decode-graph executor (cacheir/runtime/cpu.py:82-381), one session per object
 # --------------------------------------------------------------------------

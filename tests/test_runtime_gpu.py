@@ -283,3 +283,36 @@ def test_pool_exhaustion_and_position_limit_are_reported_like_the_reference(gold
     with pytest.raises(ValueError, match="max_seq_len"):
         for tok in range(12):
             v.run_decode_batch([v], [tok])
+
+
+def test_packed_prefill_of_several_sequences_equals_one_by_one(golden_dir, tmp_path):
+    """`run_prefill_batch` lays the prompt tokens of all sequences out as the rows of shared 64-row passes (short
+    prompts share a pass, a long one spans several): same logits, same K/V rows and page boundaries as prefilling
+    each sequence on its own, and decoding continues identically."""
+    rng = np.random.default_rng(11)
+    rt, meta, _ = _tiny(golden_dir, "fp32", tmp_path, dtype="float32", max_seq_len=256)
+    vocab = meta["shape"]["vocab_size"]
+    lens = [5, 70, 1, 33, 64]                                            # 173 tokens: three passes
+    prompts = [[int(t) for t in rng.integers(0, vocab, n)] for n in lens]
+    packed = [rt.fork() for _ in prompts]
+    before = rt.cache_stats()["kernel_counts"].get("cacheir.b200_prefill_chunk", 0)
+    out = rt.run_prefill_batch(packed, prompts)
+    assert rt.cache_stats()["kernel_counts"]["cacheir.b200_prefill_chunk"] - before == 3
+    assert tuple(out.shape) == (len(prompts), max(lens), vocab)
+    pools = [rt.kv_allocator.pool_for_layer(layer) for layer in range(2)]
+    for i, (p, n) in enumerate(zip(prompts, lens)):
+        alone = rt.fork()
+        rt._engine.prefill_chunk = 0                                      # one token per step
+        want = alone.run([p], mode="prefill")
+        rt._engine.prefill_chunk = 64
+        np.testing.assert_allclose(out[i, :n].float().cpu().numpy(), want[0].float().cpu().numpy(), rtol=2e-4, atol=2e-4)
+        assert float(out[i, n:].abs().max()) == 0.0 if n < max(lens) else True
+        assert [(pg.start, pg.length) for pg in packed[i].kv_cache.pages] == [(pg.start, pg.length) for pg in alone.kv_cache.pages]
+        for pool in pools:
+            for pa, pb in zip(packed[i].kv_cache.pages, alone.kv_cache.pages):
+                for name in ("keys", "values"):
+                    np.testing.assert_allclose(pool[name][pa.page_id][:, : pa.length].float().cpu().numpy(),
+                                               pool[name][pb.page_id][:, : pb.length].float().cpu().numpy(), rtol=2e-4, atol=2e-4)
+        a = packed[i].run([[7]], mode="decode")
+        b = alone.run([[7]], mode="decode")
+        np.testing.assert_allclose(a.float().cpu().numpy(), b.float().cpu().numpy(), rtol=2e-4, atol=2e-4)
