@@ -655,6 +655,9 @@ def run_micro(args) -> None:
     gen = torch.Generator(device=dev)
     gen.manual_seed(0)
     peak, kind = measured_peaks()
+    if args.micro == "layer":
+        run_micro_layer(args, dev, gen, peak, kind)
+        return
     if args.micro == "qgemv":
         m, n, k, bits = args.m, args.n, args.k, args.bits
         row_bytes = k if bits == 8 else k // 2
@@ -696,8 +699,15 @@ def run_micro(args) -> None:
         for b in range(batch):
             table_np[b, : pages[b]] = perm[cur:cur + pages[b]]
             cur += int(pages[b])
-        k_pool = torch.randn((total, kv_heads, page, hd), device=dev, dtype=torch.float16, generator=gen)
-        v_pool = torch.randn((total, kv_heads, page, hd), device=dev, dtype=torch.float16, generator=gen)
+        kv8 = args.kv == "int8"
+        scales = None
+        if kv8:      # 8-bit pages: uniform bytes and per-row scales of N(0,1) data
+            k_pool = torch.randint(0, 256, (total, kv_heads, page, hd), device=dev, dtype=torch.uint8, generator=gen)
+            v_pool = torch.randint(0, 256, (total, kv_heads, page, hd), device=dev, dtype=torch.uint8, generator=gen)
+            scales = (torch.rand((total, kv_heads, 2, page), device=dev, generator=gen) * 0.01 + 0.02).half()
+        else:
+            k_pool = torch.randn((total, kv_heads, page, hd), device=dev, dtype=torch.float16, generator=gen)
+            v_pool = torch.randn((total, kv_heads, page, hd), device=dev, dtype=torch.float16, generator=gen)
         q = torch.randn((batch, heads, hd), device=dev, dtype=torch.float16, generator=gen)
         table = torch.from_numpy(table_np).to(dev)
         lens = torch.from_numpy(lens_np).to(dev)
@@ -706,10 +716,11 @@ def run_micro(args) -> None:
         ws = torch.empty(max(1, ops.attention_workspace_bytes(batch, heads, hd, splits) // 4), device=dev, dtype=torch.float32)
 
         def launch(i: int) -> None:
-            ops.paged_attention_decode_batch(q, k_pool, v_pool, table, lens, out=out, num_splits=splits, workspace=ws)
+            ops.paged_attention_decode_batch(q, k_pool, v_pool, table, lens, out=out, num_splits=splits, workspace=ws, kv_scales=scales)
 
-        algo = int(lens_np.sum()) * kv_heads * hd * 2 * 2 + 2 * batch * heads * hd * 2 + table.numel() * 4 + batch * 4
-        name = "paged_attention_decode_batch"
+        row_bytes = kv_heads * 2 * (hd + 2) if kv8 else kv_heads * hd * 2 * 2
+        algo = int(lens_np.sum()) * row_bytes + 2 * batch * heads * hd * 2 + table.numel() * 4 + batch * 4
+        name = "paged_attention_decode_batch" + ("_int8_pages" if kv8 else "")
         shape = {"batch": batch, "heads": heads, "kv_heads": kv_heads, "head_dim": hd, "total_ctx": int(lens_np.sum()), "splits": splits}
     for i in range(max(1, args.warmup)):
         launch(i)
@@ -732,6 +743,75 @@ def run_micro(args) -> None:
     emit({"micro": name, **shape, "us_per_launch": round(sec * 1e6, 2), "algorithmic_bytes": int(algo),
           "achieved_gbs": round(algo / sec / 1e9, 1), "frac": round(algo / sec / 1e9 / peak, 4),
           "peak": peak, "peak_source": f"of {kind}", "device_status": _lib.load().cacheir_b200_device_status(0)})
+
+
+def run_micro_layer(args, dev, gen, peak: float, kind: str) -> None:
+    """The nine launches of one decoder layer of the 8B-shaped decode step, with the entry points and flags the runtime
+    uses (RMSNorm + pre-pass, fused QKV + RoPE + cache append, paged decode attention, pre-pass, o with residual,
+    RMSNorm + pre-pass, paired gate|up with SwiGLU, pre-pass, down with residual), batch `--m`, context `--ctx-max`;
+    the weights alternate between two copies. A profiling aid: small enough to capture whole under ncu."""
+    import torch
+
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import pack_weight_device, to_tiled
+
+    B, H, KVD, FFN, hd, kvh, page, theta = args.m, 4096, 1024, 14336, 128, 8, 16, 500000.0
+    ctx = args.ctx_max
+    copies = 2
+
+    def weight(n, k, paired=False):
+        return [to_tiled(pack_weight_device(torch.randn((n, k), device=dev, generator=gen) * 0.02, "int8"), paired=paired) for _ in range(copies)]
+
+    w_qkv, w_o, w_gu, w_down = weight(H + 2 * KVD, H), weight(H, H), weight(2 * FFN, H, True), weight(H, FFN)
+    norm = torch.ones((H,), device=dev, dtype=torch.float16)
+    pages = (ctx + 64 + page - 1) // page
+    slots = B * pages
+    k_pool = torch.randn((slots, kvh, page, hd), device=dev, dtype=torch.float16, generator=gen)
+    v_pool = torch.randn((slots, kvh, page, hd), device=dev, dtype=torch.float16, generator=gen)
+    table = torch.from_numpy(np.random.default_rng(1).permutation(slots).astype(np.int32).reshape(B, pages)).to(dev)
+    positions = torch.full((B,), ctx, device=dev, dtype=torch.int32)
+    lens = positions + 1
+    rope = ops.rope_table(ctx + 64, hd, theta, dev)
+    h0 = torch.randn((B, H), device=dev, dtype=torch.float16, generator=gen)
+    qkv = torch.empty((B, H + 2 * KVD), device=dev, dtype=torch.float16)
+    attn = torch.empty((B, H), device=dev, dtype=torch.float16)
+    h1, h2 = torch.empty_like(h0), torch.empty_like(h0)
+    act = torch.empty((B, FFN), device=dev, dtype=torch.float16)
+    ws = torch.zeros(ops.qgemv_workspace_bytes(B, FFN), device=dev, dtype=torch.uint8)
+
+    def launch(i: int) -> None:
+        c = i % copies
+        ops.rms_norm_quantize(h0, norm, 1e-5, ws)
+        w = w_qkv[c]
+        ops.qkv_rope_append(None, w.packed_values, w.scales, w.zero_points, qkv, n=H + 2 * KVD, k=H, q_dim=H, k_dim=KVD, head_dim=hd,
+                            theta=theta, table=rope, positions=positions, page_table=table, k_cache=k_pool, v_cache=v_pool,
+                            workspace=ws, tiled=True, prequantized=True)
+        ops.paged_attention_decode_batch(qkv[:, :H].as_strided((B, 32, hd), (qkv.stride(0), hd, 1)), k_pool, v_pool, table, lens,
+                                         out=attn.view(B, 32, hd), num_splits=args.splits or 1)
+        w = w_o[c]
+        ops.qgemv(attn, w.packed_values, w.scales, w.zero_points, bits=8, n=H, k=H, epilogue=ops.EPI_RESIDUAL, residual=h0, out=h1,
+                  workspace=ws, tiled=True)
+        ops.rms_norm_quantize(h1, norm, 1e-5, ws)
+        w = w_gu[c]
+        ops.qgemv(h1, w.packed_values, w.scales, w.zero_points, bits=8, n=2 * FFN, k=H, epilogue=ops.EPI_SWIGLU, out=act, workspace=ws,
+                  tiled=True, paired=True, prequantized=True)
+        w = w_down[c]
+        ops.qgemv(act, w.packed_values, w.scales, w.zero_points, bits=8, n=H, k=FFN, epilogue=ops.EPI_RESIDUAL, residual=h1, out=h2,
+                  workspace=ws, tiled=True)
+
+    for i in range(max(1, args.warmup)):
+        launch(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        launch(i)
+    end.record()
+    torch.cuda.synchronize()
+    from cacheir_b200 import _lib
+    emit({"micro": "decoder_layer", "batch": B, "context": ctx, "launches_per_step": 9, "steps": args.steps,
+          "us_per_step_eager": round(start.elapsed_time(end) * 1e3 / args.steps, 2), "peak": peak, "peak_source": f"of {kind}",
+          "device_status": _lib.load().cacheir_b200_device_status(0)})
 
 
 _RESULT_STREAM = None
@@ -767,7 +847,8 @@ def main() -> None:
     parser.add_argument("--kv", default="fp16", choices=["fp16", "int8"],
                         help="KV page format: fp16 (the benchmark's configuration) or 8-bit pages with a scale per cached row (an extra)")
     parser.add_argument("--no-tp-leg", action="store_true", help="with --gpus N > 1: skip the tensor-parallel leg attached to the line")
-    parser.add_argument("--micro", choices=["qgemv", "attention"], help="time one kernel alone (profiling aid)")
+    parser.add_argument("--micro", choices=["qgemv", "attention", "layer"],
+                        help="time one kernel alone, or the kernels of one decoder layer of the 8B-shaped step (profiling aid)")
     parser.add_argument("--m", type=int, default=32)
     parser.add_argument("--n", type=int, default=14336)
     parser.add_argument("--k", type=int, default=4096)
