@@ -5,13 +5,14 @@
 //   per-row affine:       deq = (code - zero[n]) * scale[n]        (the reference's int4 pack)
 //
 // HBM-bound byte streaming: the packed rows are read exactly once, in the reference's row-major layout, with
-// 16-byte loads; nibbles become fp16 in registers (two per instruction: (w >> 4i) & 0x000F000F | 0x64006400 is
-// the pair (1024 + n_i, 1024 + n_{i+4}), minus 1032 gives n - 8 exactly) and go straight into mma.sync m16n8k16
-// as the 16-row operand, with the batch rows as the 8 columns and fp32 accumulation. A warp owns 16 weight rows
-// and half of K; per 128-column block it issues 8 MMAs, then folds the block's sums into its running result
-// with the group scales of its two rows. The k order inside an MMA is whatever the nibble pairing gives: x is
-// staged in shared memory in the same order, so a lane's four (b0, b1) pairs of a packed word are one 16-byte
-// load. The two K halves of a row tile meet in shared memory and are added in a fixed order.
+// 16-byte loads; nibbles become fp16 in registers, two per shift-and-mask: (w >> 4i) & 0x000F000F | 0x64006400 is
+// the pair (1024 + n_i, 1024 + n_{i+4}), exact in fp16. They go straight into mma.sync m16n8k16 as the 16-row
+// operand, with the batch rows as the 8 columns and fp32 accumulation; the constant 1024 + zero leaves through the
+// sum of x over the 128-column block, which the accumulators start from. The k order inside an MMA is whatever the
+// nibble pairing gives: x is staged in shared memory in the same order, so a lane's four (b0, b1) pairs of a packed
+// word are one 16-byte load.
+#include <type_traits>
+
 #include "common.cuh"
 #include "qgemv_common.cuh"
 
@@ -19,8 +20,12 @@ namespace cb200 {
 namespace {
 
 constexpr int kTileRows = 16;
-constexpr int kChunkK = 4096;        // columns of x staged at a time
 constexpr int kRowPadBytes = 64;     // staged rows are 64 bytes apart modulo 128: eight lanes of a load phase hit eight bank groups
+constexpr int kWarps = 16;
+constexpr int kThreadsMma = kWarps * 32;
+constexpr int kRoundTiles = 16;      // weight tiles a CTA works on at a time: a warp's share of them spans at most two
+constexpr int kRing = 4;             // 128-column blocks of codes in flight per warp
+constexpr size_t kStageBudget = 160 * 1024;   // bytes of shared memory the staged activations may take
 
 struct MmaGemvParams {
   const __half* x;
@@ -31,9 +36,10 @@ struct MmaGemvParams {
   __half* y;
   int M, N, K;
   int n_out;
-  int group_size;     // 0: one scale (and zero point) per row
-  int scale_dtype;
+  int group_shift;    // group size = 128 << group_shift (group-wise form)
   int epilogue;
+  int chunk_cols;     // columns of x staged at a time (a multiple of 128; K when everything fits)
+  int max_tiles;      // weight tiles of the busiest CTA (sizes the cross-chunk sums)
   long long x_stride;
 };
 
@@ -42,59 +48,76 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// nibbles i and i+4 of `w` as the fp16 pair (n_i - 8, n_{i+4} - 8)
+// nibbles i and i+4 of `w` as the fp16 pair (1024 + n_i, 1024 + n_{i+4}): exact, one shift and one logic operation.
+// The offset leaves through the block's sum of x: sum (n - z) x = sum (1024 + n) x - (1024 + z) sum x.
 __device__ __forceinline__ uint32_t nibble_pair(uint32_t w, int i) {
-  const uint32_t biased = ((w >> (4 * i)) & 0x000F000Fu) | 0x64006400u;     // (1024 + n_i, 1024 + n_{i+4})
-  const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&biased), __half2half2(__ushort_as_half(0x6408)));   // 0x6408 = 1032
-  return *reinterpret_cast<const uint32_t*>(&v);
+  return ((w >> (4 * i)) & 0x000F000Fu) | 0x64006400u;
 }
-__device__ __forceinline__ float scale_value(const void* scales, int scale_dtype, size_t idx) {
-  return scale_dtype == CACHEIR_B200_F16 ? __half2float(static_cast<const __half*>(scales)[idx]) : static_cast<const float*>(scales)[idx];
+__device__ __forceinline__ uint4 load_codes(const uint8_t* ptr) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+  return v;
 }
-
-// One CTA per SM: 8 tile slots x 2 K halves = 16 warps. x is staged once per CTA (per 4096-column chunk) and serves
-// every row tile the CTA visits; tile t belongs to CTA t % grid, slot (t / grid) % 8, so the tiles spread evenly over
-// the SMs. With the SwiGLU epilogue a slot handles the 16 gate rows and then the 16 up rows of its output columns.
-// Shared memory: the staged chunk of x, [M batch rows][row_bytes], inside a row the 16-byte units of a 128-column
-// block at unit (j*4 + q) for columns q*32 + j*8 .. +7, the eight values in the order 0,4,1,5,2,6,3,7; then the
-// per-warp partial results and the row sums of x.
-constexpr int kSlots = 8;
-constexpr int kKSplit = 2;
-constexpr int kThreadsMma = kSlots * kKSplit * 32;
 
 struct CodeRegs {
   uint4 lo, hi;        // 32 codes of row g and of row g+8
   float s_lo, s_hi;    // their group scales
 };
 
-template <bool SWIGLU>
+// One CTA per SM, 16 warps. The CTA owns the output tiles blockIdx.x + grid * i (16 output columns each; with the
+// SwiGLU epilogue a gate and an up weight tile per output tile). It takes its weight tiles 16 at a time and deals the
+// (tile, 128-column block) units of such a round out evenly: warp w gets units [U w / 16, U (w+1) / 16), a run along K
+// that crosses at most one tile boundary, so every warp streams the same number of bytes whatever the tile count.
+// A warp keeps four blocks of codes in flight in registers; per block it issues 8 MMAs (two chains) whose
+// accumulators start at -(1024 + zero) * sum(x over the block), then folds them into its running sums with the two
+// rows' group scales. Partial sums meet in shared memory and are added in warp order.
+// Shared memory: x of the current chunk, [M][row_bytes], inside a row the 16-byte units of a 128-column block at unit
+// (j*4 + q) for columns q*32 + j*8 .. +7, the eight values in the order 0,4,1,5,2,6,3,7; the block sums of x
+// [block][8]; the warps' partial sums [16][2][8][16]; their tile ranges; the cross-chunk sums [tile][8][16].
+template <bool SWIGLU, bool GROUPED, bool F16SCALE>
 __global__ void __launch_bounds__(kThreadsMma, 1)
 qgemv_mma_int4_kernel(const MmaGemvParams p) {
   constexpr int HALVES = SWIGLU ? 2 : 1;     // weight tiles per output tile
+  using scale_t = typename std::conditional<F16SCALE, __half, float>::type;
   extern __shared__ __align__(16) uint8_t smem[];
-  const int chunk_cols = p.K < kChunkK ? p.K : kChunkK;
-  const int row_bytes = chunk_cols * 2 + kRowPadBytes;
+  const int row_bytes = p.chunk_cols * 2 + kRowPadBytes;
   uint8_t* xs = smem;
-  float* s_red = reinterpret_cast<float*>(smem + p.M * row_bytes);    // [16 warps][HALVES][16 rows][8 columns]
-  float* s_xsum = s_red + kSlots * kKSplit * HALVES * kTileRows * 8;  // [8]
+  float* s_xblk = reinterpret_cast<float*>(smem + p.M * row_bytes);
+  float* s_part = s_xblk + (p.chunk_cols / 128) * 8;
+  int* s_rng = reinterpret_cast<int*>(s_part + kWarps * 2 * 128);
+  float* s_tile = reinterpret_cast<float*>(s_rng + kWarps * 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
-  const int slot = warp >> 1, kh = warp & 1;
+  const int grid = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
   const size_t row_stride = static_cast<size_t>(p.K) / 2;
-  const int groups_per_row = p.group_size > 0 ? p.K / p.group_size : 1;
+  const int groups_per_row = GROUPED ? ((p.K / 128) >> p.group_shift) : 1;
+  const scale_t* scales = static_cast<const scale_t*>(p.scales);
   const int n_units = (p.n_out + kTileRows - 1) / kTileRows;
-  const uint8_t* x_lane = xs + min(g, p.M - 1) * row_bytes + q * 16;   // MMA column g is batch row g; columns past M repeat the last row and are never stored
+  const int tiles = ((n_units - cta + grid - 1) / grid) * HALVES;            // weight tiles of this CTA (>= HALVES)
+  const uint8_t* x_lane = xs + min(g, p.M - 1) * row_bytes + q * 16;         // MMA column g is batch row g; columns past M repeat the last row and are never stored
+  const float* xblk_lane = s_xblk + 2 * q;
+  const bool multi_chunk = p.chunk_cols < p.K;
 
-  // Stage x[:, c0 : c0 + cols] in MMA order: 16-byte units (8 columns), four loads in flight per thread.
+  // first weight row of weight tile `wt` of this CTA
+  auto tile_row0 = [&](int wt) {
+    const int i = wt / HALVES, h = wt - i * HALVES;
+    return (cta + grid * i) * kTileRows + h * (p.N / 2);
+  };
+
+  for (int i = threadIdx.x; i < (p.chunk_cols / 128) * 8; i += kThreadsMma)
+    if ((i & 7) >= p.M) s_xblk[i] = 0.f;
+
+  // Stage x[:, c0 : c0 + cols] in MMA order (16-byte units of 8 columns, four loads in flight per thread) and the
+  // sum of every (128-column block, batch row): eight values in order, then a butterfly over the block's 16 lanes.
   auto stage_x = [&](int c0, int cols) {
     const int units = cols / 8;
-    const int total_units = p.M * units;
-    for (int u0 = threadIdx.x; u0 < total_units; u0 += 4 * kThreadsMma) {
+    const int total_units = p.M * units;          // a multiple of 16: a half-warp is inside or outside as a whole
+    for (int base = warp * 32; base < total_units; base += 4 * kThreadsMma) {
       uint4 raw[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int u = u0 + i * kThreadsMma;
+        const int u = base + lane + i * kThreadsMma;
         raw[i] = make_uint4(0u, 0u, 0u, 0u);
         if (u < total_units) {
           const int m = u / units, unit = u - m * units;
@@ -103,156 +126,201 @@ qgemv_mma_int4_kernel(const MmaGemvParams p) {
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int u = u0 + i * kThreadsMma;
-        if (u < total_units) {
-          const int m = u / units, unit = u - m * units;
-          const uint32_t w0 = raw[i].x, w1 = raw[i].y, w2 = raw[i].z, w3 = raw[i].w;   // (h0,h1) (h2,h3) (h4,h5) (h6,h7)
+        const int u = base + lane + i * kThreadsMma;
+        const bool valid = u < total_units;
+        const int m = valid ? u / units : 0, unit = u - m * units;
+        const uint32_t w0 = raw[i].x, w1 = raw[i].y, w2 = raw[i].z, w3 = raw[i].w;   // (h0,h1) (h2,h3) (h4,h5) (h6,h7)
+        const int kb = unit >> 4, in_block = unit & 15, qq = in_block >> 2, jj = in_block & 3;
+        if (valid) {
           const uint4 o = make_uint4(__byte_perm(w0, w2, 0x5410), __byte_perm(w0, w2, 0x7632),      // order 0,4,1,5,2,6,3,7
                                      __byte_perm(w1, w3, 0x5410), __byte_perm(w1, w3, 0x7632));
-          const int kb = unit >> 4, in_block = unit & 15, qq = in_block >> 2, jj = in_block & 3;
           *reinterpret_cast<uint4*>(xs + m * row_bytes + (kb * 16 + jj * 4 + qq) * 16) = o;
         }
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w0)), f1 = __half22float2(*reinterpret_cast<const __half2*>(&w1));
+        const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w2)), f3 = __half22float2(*reinterpret_cast<const __half2*>(&w3));
+        float sum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (valid && (lane & 15) == 0) s_xblk[kb * 8 + m] = sum;
       }
     }
   };
 
-  if (p.group_size == 0) {                   // per-row affine form: the sums of the batch rows, each by one warp in a fixed order
-    for (int m = warp; m < p.M; m += kSlots * kKSplit) {
-      const __half* xr = p.x + static_cast<size_t>(m) * p.x_stride;
-      float s = 0.f;
-      for (int k = lane * 8; k < p.K; k += 256) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(xr + k);
-        const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h2[i]); s += f.x + f.y; }
-      }
-      s = warp_sum(s);
-      if (lane == 0) s_xsum[m] = s;
-    }
-  }
+  int chunk = 0;
+  for (int c0 = 0; c0 < p.K; c0 += p.chunk_cols, ++chunk) {
+    const int cols = min(p.chunk_cols, p.K - c0);
+    const int kbc = cols / 128;                    // blocks of this chunk
+    const int kb0 = c0 / 128;
+    const bool last_chunk = c0 + cols >= p.K;
+    for (int r0 = 0; r0 < tiles; r0 += kRoundTiles) {
+      const int round_tiles = min(kRoundTiles, tiles - r0);
+      const int units = round_tiles * kbc;
+      const int ub = (units * warp) / kWarps, ue = (units * (warp + 1)) / kWarps;
+      const int first_tile = ub / kbc;
 
-  // Tiles of this slot: t = blockIdx.x + grid * (slot + 8 i). Every warp of the CTA runs the same number of rounds and
-  // chunks (the barriers around the staging of x are CTA-wide); a warp without a tile in a round only takes part in them.
-  const int rounds = (n_units + static_cast<int>(gridDim.x) * kSlots - 1) / (static_cast<int>(gridDim.x) * kSlots);
-  for (int round = 0; round < rounds; ++round) {
-    const int unit = static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) * (slot + kSlots * round);
-    const bool have = unit < n_units;
-    const int n0 = unit * kTileRows;                                       // first output column of the tile
-    float acc[HALVES][4];
+      // ---- fetch cursor: the tile and block the next load reads ----
+      int f_t = first_tile, f_b = ub - first_tile * kbc;
+      const uint8_t *f_lo, *f_hi;
+      const scale_t *f_slo, *f_shi;
+      auto point_fetch_at = [&](int t) {
+        const int row0 = tile_row0(r0 + min(t, round_tiles - 1));
+        // rows this lane feeds (clamped: rows past N are computed on a valid row and never stored)
+        const int r_lo = min(row0 + g, p.N - 1), r_hi = min(row0 + g + 8, p.N - 1);
+        f_lo = p.packed + static_cast<size_t>(r_lo) * row_stride + (static_cast<size_t>(kb0) * 64 + q * 16);
+        f_hi = p.packed + static_cast<size_t>(r_hi) * row_stride + (static_cast<size_t>(kb0) * 64 + q * 16);
+        if (GROUPED) {
+          f_slo = scales + static_cast<size_t>(r_lo) * groups_per_row;
+          f_shi = scales + static_cast<size_t>(r_hi) * groups_per_row;
+        }
+      };
+      point_fetch_at(f_t);
+      auto fetch = [&](CodeRegs& r) {
+        r.lo = load_codes(f_lo + f_b * 64);
+        r.hi = load_codes(f_hi + f_b * 64);
+        if (GROUPED) {
+          const int grp = (kb0 + f_b) >> p.group_shift;
+          r.s_lo = static_cast<float>(f_slo[grp]);
+          r.s_hi = static_cast<float>(f_shi[grp]);
+        }
+        if (++f_b == kbc) { f_b = 0; point_fetch_at(++f_t); }
+      };
+      CodeRegs ring[kRing];
 #pragma unroll
-    for (int h = 0; h < HALVES; ++h)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[h][i] = 0.f;
+      for (int i = 0; i < kRing; ++i)
+        if (ub + i < ue) fetch(ring[i]);
 
-    for (int c0 = 0; c0 < p.K; c0 += chunk_cols) {
-      const int cols = min(chunk_cols, p.K - c0);
-      if (round == 0 || chunk_cols < p.K) {   // (a single chunk stays staged for all rounds)
-        __syncthreads();                      // the previous chunk has been consumed
+      if (r0 == 0) {                         // (the codes above are on their way while x is staged)
         stage_x(c0, cols);
         __syncthreads();
       }
-      if (!have) continue;
-      const int blocks = cols / 128;
-      const int b_begin = (blocks * kh) / kKSplit, b_end = (blocks * (kh + 1)) / kKSplit;
-      const int kb0 = c0 / 128;
-#pragma unroll
-      for (int h = 0; h < HALVES; ++h) {
-        const int w_row0 = n0 + h * (p.N / 2);
-        // rows this lane feeds (clamped: rows past N are computed on a valid row and never stored)
-        const int r_lo = min(w_row0 + g, p.N - 1), r_hi = min(w_row0 + g + 8, p.N - 1);
-        const uint8_t* w_lo = p.packed + static_cast<size_t>(r_lo) * row_stride + q * 16;
-        const uint8_t* w_hi = p.packed + static_cast<size_t>(r_hi) * row_stride + q * 16;
-        auto fetch = [&](int b) {
-          CodeRegs r;
-          r.lo = *reinterpret_cast<const uint4*>(w_lo + static_cast<size_t>(kb0 + b) * 64);
-          r.hi = *reinterpret_cast<const uint4*>(w_hi + static_cast<size_t>(kb0 + b) * 64);
-          r.s_lo = 1.f; r.s_hi = 1.f;
-          if (p.group_size > 0) {
-            const int grp = ((kb0 + b) * 128) / p.group_size;
-            r.s_lo = scale_value(p.scales, p.scale_dtype, static_cast<size_t>(r_lo) * groups_per_row + grp);
-            r.s_hi = scale_value(p.scales, p.scale_dtype, static_cast<size_t>(r_hi) * groups_per_row + grp);
-          }
-          return r;
-        };
-        // One 128-column block: 8 MMAs on the unpacked nibbles (two chains), then the block's sums join the result with the rows' group scales.
-        auto do_block = [&](int b, const CodeRegs& r) {
-          float c[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};
-          const uint32_t wa[4] = {r.lo.x, r.lo.y, r.lo.z, r.lo.w};
-          const uint32_t wb[4] = {r.hi.x, r.hi.y, r.hi.z, r.hi.w};
-          const uint8_t* xrow = x_lane + b * 256;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint4 xv = *reinterpret_cast<const uint4*>(xrow + j * 64);     // (x0,x4) (x1,x5) (x2,x6) (x3,x7) of the word's 8 columns
-            mma_16816(c, nibble_pair(wa[j], 0), nibble_pair(wb[j], 0), nibble_pair(wa[j], 1), nibble_pair(wb[j], 1), xv.x, xv.y);
-            mma_16816(d, nibble_pair(wa[j], 2), nibble_pair(wb[j], 2), nibble_pair(wa[j], 3), nibble_pair(wb[j], 3), xv.z, xv.w);
-          }
-          acc[h][0] = fmaf(c[0] + d[0], r.s_lo, acc[h][0]); acc[h][1] = fmaf(c[1] + d[1], r.s_lo, acc[h][1]);
-          acc[h][2] = fmaf(c[2] + d[2], r.s_hi, acc[h][2]); acc[h][3] = fmaf(c[3] + d[3], r.s_hi, acc[h][3]);
-        };
-        // four blocks of codes (and their scales) are on their way while one is multiplied
-        CodeRegs ring[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          if (b_begin + i < b_end) ring[i] = fetch(b_begin + i);
-        for (int b = b_begin; b < b_end; b += 4) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            if (b + i < b_end) {
-              const CodeRegs cur = ring[i];
-              if (b + 4 + i < b_end) ring[i] = fetch(b + 4 + i);
-              do_block(b + i, cur);
-            }
-          }
-        }
-      }
-    }
 
-    // ---- the two K halves of a tile meet in shared memory and are added in order (named barrier of the slot's 64 threads) ----
-    if (have) {
+      // ---- consume cursor ----
+      int c_b = ub - first_tile * kbc, c_t = first_tile, pieces = 0;
+      float kz_lo = -1032.f, kz_hi = -1032.f;                     // -(1024 + zero point) of the two rows
+      auto point_consume_at = [&](int t) {
+        if (!GROUPED && p.zero_points) {
+          const int row0 = tile_row0(r0 + min(t, round_tiles - 1));
+          kz_lo = -(1024.f + p.zero_points[min(row0 + g, p.N - 1)]);
+          kz_hi = -(1024.f + p.zero_points[min(row0 + g + 8, p.N - 1)]);
+        }
+      };
+      point_consume_at(c_t);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      auto flush = [&]() {
+        if (pieces >= 2) return;                                   // (a warp's run never crosses two tile boundaries)
+        float* mine = s_part + (warp * 2 + pieces) * 128;          // [m][row]
+        mine[(2 * q) * 16 + g] = acc[0]; mine[(2 * q + 1) * 16 + g] = acc[1];
+        mine[(2 * q) * 16 + g + 8] = acc[2]; mine[(2 * q + 1) * 16 + g + 8] = acc[3];
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+        ++pieces;
+      };
+      auto consume = [&](const CodeRegs& r) {
+        const float2 xb = *reinterpret_cast<const float2*>(xblk_lane + c_b * 8);
+        float c[4], d[4] = {0.f, 0.f, 0.f, 0.f};
+        if (GROUPED) { c[0] = c[2] = -1032.f * xb.x; c[1] = c[3] = -1032.f * xb.y; }
+        else { c[0] = kz_lo * xb.x; c[1] = kz_lo * xb.y; c[2] = kz_hi * xb.x; c[3] = kz_hi * xb.y; }
+        const uint32_t wa[4] = {r.lo.x, r.lo.y, r.lo.z, r.lo.w};
+        const uint32_t wb[4] = {r.hi.x, r.hi.y, r.hi.z, r.hi.w};
+        const uint8_t* xrow = x_lane + c_b * 256;
 #pragma unroll
-      for (int h = 0; h < HALVES; ++h) {
-        float* mine = s_red + ((warp * HALVES + h) * kTileRows) * 8;
-        mine[g * 8 + 2 * q] = acc[h][0]; mine[g * 8 + 2 * q + 1] = acc[h][1];
-        mine[(g + 8) * 8 + 2 * q] = acc[h][2]; mine[(g + 8) * 8 + 2 * q + 1] = acc[h][3];
-      }
-    }
-    asm volatile("bar.sync %0, 64;" ::"r"(1 + slot) : "memory");
-    if (have) {
-      // 16 x 8 results, two per thread of the slot
-      const int tt = (kh << 5) | lane;
+        for (int j = 0; j < 4; ++j) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(xrow + j * 64);     // (x0,x4) (x1,x5) (x2,x6) (x3,x7) of the word's 8 columns
+          mma_16816(c, nibble_pair(wa[j], 0), nibble_pair(wb[j], 0), nibble_pair(wa[j], 1), nibble_pair(wb[j], 1), xv.x, xv.y);
+          mma_16816(d, nibble_pair(wa[j], 2), nibble_pair(wb[j], 2), nibble_pair(wa[j], 3), nibble_pair(wb[j], 3), xv.z, xv.w);
+        }
+        if (GROUPED) {
+          acc[0] = fmaf(c[0] + d[0], r.s_lo, acc[0]); acc[1] = fmaf(c[1] + d[1], r.s_lo, acc[1]);
+          acc[2] = fmaf(c[2] + d[2], r.s_hi, acc[2]); acc[3] = fmaf(c[3] + d[3], r.s_hi, acc[3]);
+        } else {
+          acc[0] += c[0] + d[0]; acc[1] += c[1] + d[1]; acc[2] += c[2] + d[2]; acc[3] += c[3] + d[3];
+        }
+        if (++c_b == kbc) { flush(); c_b = 0; point_consume_at(++c_t); }
+      };
+      for (int u = ub; u < ue; u += kRing) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int idx = tt * 2 + e, row = idx >> 3, m = idx & 7;
-        const int n = n0 + row;
-        if (m < p.M && n < p.n_out) {
-          auto finish = [&](int h, int wrow) {     // halves in order; then the per-row scale / zero point of the affine form
-            float v = 0.f;
-#pragma unroll
-            for (int k = 0; k < kKSplit; ++k) v += s_red[((((slot * kKSplit + k) * HALVES) + h) * kTileRows + row) * 8 + m];
-            if (p.group_size == 0) {
-              const float zp = p.zero_points ? p.zero_points[wrow] : 8.f;
-              v = (v + (8.f - zp) * s_xsum[m]) * scale_value(p.scales, p.scale_dtype, wrow);
-            }
-            return v;
-          };
-          const size_t o = static_cast<size_t>(m) * p.n_out + n;
-          if (SWIGLU) {
-            p.y[o] = __float2half_rn(silu_fast(finish(0, n)) * finish(1, p.N / 2 + n));
-          } else {
-            float v = finish(0, n);
-            if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) v += __half2float(p.residual[o]);
-            p.y[o] = __float2half_rn(v);
+        for (int i = 0; i < kRing; ++i) {
+          if (u + i < ue) {
+            const CodeRegs cur = ring[i];
+            if (u + i + kRing < ue) fetch(ring[i]);
+            consume(cur);
           }
         }
       }
+      if (c_b != 0 && ue > ub) flush();
+      if (lane == 0) { s_rng[warp * 2] = first_tile; s_rng[warp * 2 + 1] = pieces; }
+      __syncthreads();
+
+      // ---- the warps' partial sums are added in warp order; the last chunk finishes the outputs ----
+      const int out_tiles = round_tiles / HALVES;
+      for (int idx = threadIdx.x; idx < out_tiles * 128; idx += kThreadsMma) {
+        const int row = idx & 15, m = (idx >> 4) & 7, ot = idx >> 7;
+        if (m >= p.M) continue;
+        float v[HALVES];
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h) {
+          const int t = ot * HALVES + h;                // weight tile inside the round
+          float sum = multi_chunk && chunk > 0 ? s_tile[((r0 + t) * 8 + m) * 16 + row] : 0.f;
+          for (int w = 0; w < kWarps; ++w) {
+            const int piece = t - s_rng[w * 2];
+            if (piece >= 0 && piece < s_rng[w * 2 + 1]) sum += s_part[((w * 2 + piece) * 8 + m) * 16 + row];
+          }
+          v[h] = sum;
+        }
+        if (!last_chunk) {
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h) s_tile[((r0 + ot * HALVES + h) * 8 + m) * 16 + row] = v[h];
+          continue;
+        }
+        const int wrow0 = tile_row0(r0 + ot * HALVES) + row;      // weight row of v[0]; the output column too (h = 0)
+        const int n = wrow0;
+        if (n >= p.n_out) continue;
+        if (!GROUPED) {
+          v[0] *= static_cast<float>(scales[wrow0]);
+          if (SWIGLU) v[HALVES - 1] *= static_cast<float>(scales[wrow0 + p.N / 2]);
+        }
+        const size_t o = static_cast<size_t>(m) * p.n_out + n;
+        if (SWIGLU) {
+          p.y[o] = __float2half_rn(silu_fast(v[0]) * v[HALVES - 1]);
+        } else {
+          float out = v[0];
+          if (p.epilogue == CACHEIR_B200_EPI_RESIDUAL) out += __half2float(p.residual[o]);
+          p.y[o] = __float2half_rn(out);
+        }
+      }
+      __syncthreads();       // the partial sums (and, after a chunk's last round, the staged x) are free again
     }
-    asm volatile("bar.sync %0, 64;" ::"r"(1 + slot) : "memory");     // the partial results are free for the slot's next tile
   }
 }
 
-size_t mma_gemv_smem_bytes(int M, int K, bool swiglu) {
-  const int chunk_cols = K < kChunkK ? K : kChunkK;
-  return static_cast<size_t>(M) * (chunk_cols * 2 + kRowPadBytes) + (kSlots * kKSplit * (swiglu ? 2 : 1) * kTileRows * 8 + 8) * sizeof(float);
+struct MmaGemvShape {
+  int chunk_cols, grid, max_tiles;
+  size_t smem;
+};
+
+MmaGemvShape mma_gemv_shape(int M, int N, int K, bool swiglu) {
+  MmaGemvShape s{};
+  const int kb = K / 128;
+  const size_t per_block = static_cast<size_t>(M) * 256;
+  int max_blocks = static_cast<int>((kStageBudget - static_cast<size_t>(M) * kRowPadBytes) / per_block);
+  if (max_blocks < 1) max_blocks = 1;
+  const int chunks = (kb + max_blocks - 1) / max_blocks;
+  s.chunk_cols = ((kb + chunks - 1) / chunks) * 128;
+  const int n_out = swiglu ? N / 2 : N;
+  const int n_units = (n_out + kTileRows - 1) / kTileRows;
+  s.grid = n_units < kNumSMs ? n_units : kNumSMs;
+  s.max_tiles = ((n_units + s.grid - 1) / s.grid) * (swiglu ? 2 : 1);
+  s.smem = static_cast<size_t>(M) * (s.chunk_cols * 2 + kRowPadBytes) + static_cast<size_t>(s.chunk_cols / 128) * 8 * sizeof(float) +
+           kWarps * 2 * 128 * sizeof(float) + kWarps * 2 * sizeof(int) +
+           (s.chunk_cols < K ? static_cast<size_t>(s.max_tiles) * 128 * sizeof(float) : 0);
+  return s;
+}
+
+template <bool SWIGLU, bool GROUPED, bool F16SCALE>
+int launch_mma_variant(const MmaGemvParams& p, int grid, size_t smem, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(qgemv_mma_int4_kernel<SWIGLU, GROUPED, F16SCALE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  qgemv_mma_int4_kernel<SWIGLU, GROUPED, F16SCALE><<<grid, kThreadsMma, smem, stream>>>(p);
+  return launch_status();
 }
 
 }  // namespace
@@ -260,10 +328,15 @@ size_t mma_gemv_smem_bytes(int M, int K, bool swiglu) {
 bool qgemv_mma_supported(const QGemvParams& q) {
   if (q.bits != 4 || q.x_dtype != CACHEIR_B200_F16 || q.tiled || q.paired || q.x_prequantized || q.norm_weight) return false;
   if (q.M < 1 || q.M > 8 || q.K % 128 != 0 || q.K < 128) return false;
-  if (q.group_size != 0 && q.group_size % 128 != 0) return false;
-  if (q.group_size != 0 && q.zero_points) return false;
+  if (q.group_size != 0) {           // 128 << s columns per group, no zero points
+    if (q.group_size % 128 != 0 || q.zero_points) return false;
+    const int g = q.group_size / 128;
+    if ((g & (g - 1)) != 0 || (q.K / 128) % g != 0) return false;
+  }
+  if (q.scale_dtype != CACHEIR_B200_F16 && q.scale_dtype != CACHEIR_B200_F32) return false;
   if (q.epilogue == CACHEIR_B200_EPI_SWIGLU && (q.N / 2) % kTileRows != 0) return false;
   if (q.epilogue == kEpiQkvRopeAppend) return false;
+  if (mma_gemv_shape(q.M, q.N, q.K, q.epilogue == CACHEIR_B200_EPI_SWIGLU).smem > 220 * 1024) return false;
   return aligned_to(q.packed, 16) && aligned_to(q.x, 16) && (q.x_stride * 2) % 16 == 0;
 }
 
@@ -277,22 +350,22 @@ int launch_qgemv_mma(const QGemvParams& q, cudaStream_t stream) {
   p.M = q.M; p.N = q.N; p.K = q.K;
   const bool swiglu = q.epilogue == CACHEIR_B200_EPI_SWIGLU;
   p.n_out = swiglu ? q.N / 2 : q.N;
-  p.group_size = q.group_size; p.scale_dtype = q.scale_dtype; p.epilogue = q.epilogue; p.x_stride = q.x_stride;
-  const size_t smem = mma_gemv_smem_bytes(q.M, q.K, swiglu);
-  // One CTA per SM (fewer when there are fewer tiles than slots); tiles are dealt out round robin over the CTAs first.
-  const int n_units = (p.n_out + kTileRows - 1) / kTileRows;
-  const int grid = n_units < kNumSMs ? n_units : kNumSMs;
-  cudaError_t e;
+  const bool grouped = q.group_size != 0;
+  p.group_shift = 0;
+  for (int g = q.group_size / 128; g > 1; g >>= 1) ++p.group_shift;
+  p.epilogue = q.epilogue; p.x_stride = q.x_stride;
+  const MmaGemvShape shape = mma_gemv_shape(q.M, q.N, q.K, swiglu);
+  p.chunk_cols = shape.chunk_cols; p.max_tiles = shape.max_tiles;
+  const bool f16 = q.scale_dtype == CACHEIR_B200_F16;
+  // One CTA per SM (fewer when there are fewer output tiles); output tiles are dealt out round robin over the CTAs.
+#define CB200_MMA_GEMV(SW, GR, F16) launch_mma_variant<SW, GR, F16>(p, shape.grid, shape.smem, stream)
   if (swiglu) {
-    e = cudaFuncSetAttribute(qgemv_mma_int4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    qgemv_mma_int4_kernel<true><<<grid, kThreadsMma, smem, stream>>>(p);
-  } else {
-    e = cudaFuncSetAttribute(qgemv_mma_int4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    qgemv_mma_int4_kernel<false><<<grid, kThreadsMma, smem, stream>>>(p);
+    if (grouped) return f16 ? CB200_MMA_GEMV(true, true, true) : CB200_MMA_GEMV(true, true, false);
+    return f16 ? CB200_MMA_GEMV(true, false, true) : CB200_MMA_GEMV(true, false, false);
   }
-  return launch_status();
+  if (grouped) return f16 ? CB200_MMA_GEMV(false, true, true) : CB200_MMA_GEMV(false, true, false);
+  return f16 ? CB200_MMA_GEMV(false, false, true) : CB200_MMA_GEMV(false, false, false);
+#undef CB200_MMA_GEMV
 }
 
 }  // namespace cb200

@@ -583,6 +583,27 @@ def test_streaming_int4_gemv_swiglu_and_unclipped_zero_points():
         assert _rel(quantized_matmul(x.cuda(), dev), base) <= TOL[torch.float16]
 
 
+@pytest.mark.parametrize("m,n,k,group,swiglu", [(2, 40000, 256, 128, False), (3, 40960, 128, 128, True), (8, 40000, 384, 0, False),
+                                                (7, 2400, 14336, 128, False)])
+def test_streaming_int4_gemv_many_tiles_per_sm(m, n, k, group, swiglu):
+    """More than 16 weight tiles per SM (several rounds) and several chunks of x with full rounds."""
+    from cacheir_b200 import ops
+    from cacheir_b200.quantization import quantized_matmul
+    rng = np.random.default_rng(n + k + m)
+    x, packed = _qgemv_case(rng, m, n, k, 4, torch.float16, group=group)
+    dev = _device_pack(packed)
+    assert ops.qgemv_plan(m, n, k, bits=4, group_size=group, workspace=False,
+                          epilogue=ops.EPI_SWIGLU if swiglu else ops.EPI_NONE)["family"] == "stream_int4"
+    base = oracle.quantized_matmul(x.float().numpy(), packed)
+    if swiglu:
+        y = quantized_matmul(x.cuda(), dev, epilogue=ops.EPI_SWIGLU)
+        assert _rel(y, oracle.silu_mul(base[:, : n // 2], base[:, n // 2:])) <= 2 * TOL[torch.float16]
+    else:
+        y = quantized_matmul(x.cuda(), dev)
+        assert _rel(y, base) <= TOL[torch.float16]
+    _device_status_ok()
+
+
 # ---- device pack layout: tile order is an exact permutation and changes no result ---------
 @pytest.mark.parametrize("bits", [8, 4])
 @pytest.mark.parametrize("n,k", [(512, 1024), (200, 256), (128, 4096)])
