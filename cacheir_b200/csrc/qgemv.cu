@@ -326,7 +326,8 @@ extern "C" int cacheir_b200_device_status(int reset) {
   const int attn = paged_attention_device_status(reset != 0);
   const int i8 = qgemm_i8_device_status(reset != 0);
   const int peer = peer_collectives_device_status(reset != 0);
-  return gemm != 0 ? gemm : (attn != 0 ? attn : (i8 != 0 ? i8 : peer));
+  const int gemv = qgemv_mma_device_status(reset != 0);
+  return gemm != 0 ? gemm : (attn != 0 ? attn : (i8 != 0 ? i8 : (peer != 0 ? peer : gemv)));
 }
 
 extern "C" int cacheir_b200_quantize_activations(const void* x, int M, int K, long long x_stride, int x_dtype,

@@ -56,6 +56,7 @@ bool qgemm_i8_supported(const QGemvParams& p, const void* workspace, size_t work
 int launch_qgemm_i8(const QGemvParams& p, void* workspace, cudaStream_t stream);
 int qgemm_i8_plan(const QGemvParams& p);   // the split-K factor the launcher would use
 int qgemm_i8_device_status(bool reset);
+int qgemv_mma_device_status(bool reset);
 int qgemm_i8_quantize_activations(const void* x, long long x_stride, int M, int K, void* workspace, cudaStream_t stream);
 int qgemm_i8_rms_norm_quantize(const void* x, const void* residual, const void* weight, void* sum_out, void* out, int M,
                                int hidden, float eps, void* workspace, cudaStream_t stream);

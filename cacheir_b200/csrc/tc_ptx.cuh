@@ -151,5 +151,19 @@ inline bool encode_u8_rows_sw64(CUtensorMap* map, const void* base, uint64_t inn
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 2-D tensor of 32-bit words [rows][inner_words], box {box_words, box_rows}, no swizzle; what lies outside reads as zero.
+inline bool encode_u32_rows_plain(CUtensorMap* map, const void* base, uint64_t inner_words, uint64_t rows,
+                                  uint64_t row_stride_bytes, uint32_t box_words, uint32_t box_rows) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {inner_words, rows};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {box_words, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace ptx
 }  // namespace cb200

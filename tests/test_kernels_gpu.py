@@ -583,7 +583,7 @@ def test_streaming_int4_gemv_swiglu_and_unclipped_zero_points():
         assert _rel(quantized_matmul(x.cuda(), dev), base) <= TOL[torch.float16]
 
 
-@pytest.mark.parametrize("m,n,k,group,swiglu", [(2, 40000, 256, 128, False), (3, 40960, 128, 128, True), (8, 40000, 384, 0, False),
+@pytest.mark.parametrize("m,n,k,group,swiglu", [(2, 40000, 256, 128, False), (3, 40960, 256, 128, True), (8, 40000, 512, 0, False),
                                                 (7, 2400, 14336, 128, False)])
 def test_streaming_int4_gemv_many_tiles_per_sm(m, n, k, group, swiglu):
     """More than 16 weight tiles per SM (several rounds) and several chunks of x with full rounds."""
