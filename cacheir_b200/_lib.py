@@ -30,6 +30,12 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
          c_int, c_int, c_int, c_int, c_int, c_int, c_int,
          c_longlong, c_longlong, c_float, c_int,
          c_void_p, c_size_t, c_int, c_int, c_void_p, c_void_p]),      # workspace bytes num_slots kv_dtype kv_scales stream
+    "cacheir_b200_paged_attention_decode_batch_quantize": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+         c_longlong, c_float, c_int, c_void_p, c_size_t, c_void_p]),  # q_stride scale num_slots gemm_workspace bytes stream
+    "cacheir_b200_paged_attention_quantize_supported": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     "cacheir_b200_paged_attention_noalloc_max_workspace_bytes": (c_size_t, []),
     "cacheir_b200_paged_attention_decode_batch_noalloc": (
         c_int,

@@ -318,12 +318,21 @@ extern "C" int cacheir_b200_paged_attention_auto_splits(int batch_size, int num_
   return s;
 }
 
-extern "C" int cacheir_b200_paged_attention_decode_batch_ex(
+namespace cb200 {
+size_t qgemm_i8_workspace_bytes(int M, int K);
+int i8_plane_rows(int M);
+}
+
+namespace {
+// `gemm_workspace` non-null: the launch must also leave the output as the integer GEMM's activation planes
+// (CACHEIR_B200_EUNSUPPORTED when the fast single-split kernel cannot take the case). `probe`: decide only, launch nothing.
+int attention_dispatch(
     const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
     const int32_t* seq_lens, void* out, int batch_size, int num_heads, int num_kv_heads,
     int max_pages_per_seq, int page_size, int head_dim, int dtype, long long q_batch_stride,
     long long out_batch_stride, float softmax_scale, int num_splits, void* workspace,
-    size_t workspace_bytes, int num_slots, int kv_dtype, const void* kv_scales, void* stream) {
+    size_t workspace_bytes, int num_slots, int kv_dtype, const void* kv_scales, void* gemm_workspace,
+    size_t gemm_workspace_bytes, bool probe, void* stream) {
   if (batch_size <= 0 || num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0) return 0;
   if (max_pages_per_seq <= 0 || page_size <= 0 || num_slots < 0) return CACHEIR_B200_EINVAL;
   if (num_heads % num_kv_heads != 0) return CACHEIR_B200_EINVAL;
@@ -356,6 +365,17 @@ extern "C" int cacheir_b200_paged_attention_decode_batch_ex(
     p.ws_ml = static_cast<float*>(workspace);
     p.ws_acc = p.ws_ml + static_cast<size_t>(batch_size) * num_heads * p.splits * 2;
   }
+  if (gemm_workspace) {
+    const int k_total = num_heads * head_dim;
+    if (!paged_attention_quantize_supported(p, dtype)) return CACHEIR_B200_EUNSUPPORTED;
+    if (gemm_workspace_bytes < qgemm_i8_workspace_bytes(batch_size, k_total)) return CACHEIR_B200_EWORKSPACE;
+    if (!aligned_to(gemm_workspace, 128) || !aligned_to(out, 8)) return CACHEIR_B200_EALIGN;
+    p.quant_rows = i8_plane_rows(batch_size);
+    p.quant_planes = static_cast<int8_t*>(gemm_workspace);
+    p.quant_sx = reinterpret_cast<float*>(p.quant_planes + static_cast<size_t>(2 * p.quant_rows) * k_total);
+    p.quant_qsum = reinterpret_cast<int*>(p.quant_sx + 64);
+    if (probe) return 0;
+  }
   cudaStream_t st = as_stream(stream);
   // 128-bit row chunks need 16-byte aligned rows everywhere they are used (8-bit pools: 8-byte chunks of the cached rows).
   const int kv_esize = kv8 ? 1 : esize;
@@ -384,6 +404,41 @@ extern "C" int cacheir_b200_paged_attention_decode_batch_ex(
     case CACHEIR_B200_F16: return launch_combine<__half>(p, st);
     default: return launch_combine<__nv_bfloat16>(p, st);
   }
+}
+}  // namespace
+
+extern "C" int cacheir_b200_paged_attention_decode_batch_ex(
+    const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
+    const int32_t* seq_lens, void* out, int batch_size, int num_heads, int num_kv_heads,
+    int max_pages_per_seq, int page_size, int head_dim, int dtype, long long q_batch_stride,
+    long long out_batch_stride, float softmax_scale, int num_splits, void* workspace,
+    size_t workspace_bytes, int num_slots, int kv_dtype, const void* kv_scales, void* stream) {
+  return attention_dispatch(q, k_cache, v_cache, page_table, seq_lens, out, batch_size, num_heads, num_kv_heads,
+                            max_pages_per_seq, page_size, head_dim, dtype, q_batch_stride, out_batch_stride, softmax_scale,
+                            num_splits, workspace, workspace_bytes, num_slots, kv_dtype, kv_scales, nullptr, 0, false, stream);
+}
+
+extern "C" int cacheir_b200_paged_attention_decode_batch_quantize(
+    const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
+    const int32_t* seq_lens, void* out, int batch_size, int num_heads, int num_kv_heads,
+    int max_pages_per_seq, int page_size, int head_dim, int dtype, long long q_batch_stride,
+    float softmax_scale, int num_slots, void* gemm_workspace, size_t gemm_workspace_bytes, void* stream) {
+  if (!gemm_workspace) return CACHEIR_B200_EINVAL;
+  return attention_dispatch(q, k_cache, v_cache, page_table, seq_lens, out, batch_size, num_heads, num_kv_heads,
+                            max_pages_per_seq, page_size, head_dim, dtype, q_batch_stride, 0, softmax_scale, 1, nullptr, 0,
+                            num_slots, CACHEIR_B200_KV_SAME, nullptr, gemm_workspace, gemm_workspace_bytes, false, stream);
+}
+
+extern "C" int cacheir_b200_paged_attention_quantize_supported(int batch_size, int num_heads, int num_kv_heads,
+                                                               int max_pages_per_seq, int page_size, int head_dim, int dtype) {
+  if (batch_size <= 0 || num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0) return 0;
+  // Dummy, suitably aligned addresses: the answer depends on extents and alignment only.
+  void* aligned = reinterpret_cast<void*>(static_cast<uintptr_t>(1) << 20);
+  const int rc = attention_dispatch(aligned, aligned, aligned, static_cast<const int32_t*>(aligned), static_cast<const int32_t*>(aligned),
+                                    aligned, batch_size, num_heads, num_kv_heads, max_pages_per_seq, page_size, head_dim, dtype, 0, 0,
+                                    0.f, 1, nullptr, 0, 0, CACHEIR_B200_KV_SAME, nullptr, aligned,
+                                    qgemm_i8_workspace_bytes(batch_size, num_heads * head_dim), true, nullptr);
+  return rc == 0 ? 1 : 0;
 }
 
 extern "C" int cacheir_b200_paged_attention_decode_batch(

@@ -19,6 +19,12 @@ struct AttnParams {
   const void* kv_scales;   // 8-bit pools only: fp16 [slots][kv_heads][2 (K, V)][page_size], one scale per cached row
   int kv8;                 // the pools hold unsigned bytes: value = (byte - 128) * scale of its row
   int num_slots;           // slots of the pool (0: unknown); bounds the tensor maps of the fast kernels
+  // Fused activation pre-pass of the projection that follows (null: off): the [batch][heads*head_dim] output also
+  // leaves as the integer GEMM's fixed-point planes, scales and sums, rows batch..quant_rows-1 zeroed.
+  int8_t* quant_planes;
+  float* quant_sx;
+  int* quant_qsum;
+  int quant_rows;          // padded row count of the planes (16, 32 or 64)
   const int32_t* page_table;
   const int32_t* seq_lens;
   void* out;
@@ -41,6 +47,9 @@ void resolve_attention_splits(int batch, int heads, int kv_heads, int max_pages,
 // (8-bit pools: fp16 queries, head_dim 128.)
 bool paged_attention_fast_supported(const AttnParams& p, int dtype);
 int launch_paged_attention_fast(const AttnParams& p, int dtype, cudaStream_t stream);
+// Can the fast kernel also write the fixed-point planes (single split, fp16 pages and queries, head_dim 128,
+// the kv heads of a sequence as one thread-block cluster)?
+bool paged_attention_quantize_supported(const AttnParams& p, int dtype);
 int paged_attention_device_status(bool reset);
 
 }  // namespace cb200

@@ -14,7 +14,10 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include <type_traits>
+
 #include "paged_attention_common.cuh"
+#include "fixed_point.cuh"
 
 namespace cb200 {
 namespace {
@@ -94,7 +97,22 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <typename T, int D>
+// DSMEM helpers of the quantising epilogue: a 32-bit store into the same shared-memory offset of another CTA of the
+// cluster, and the cluster barrier with release / acquire ordering (all threads of all CTAs, at uniform points).
+__device__ __forceinline__ void store_to_rank(void* local_ptr, uint32_t rank, uint32_t value) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_ptr)), "r"(rank));
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(value) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// QUANT: single split, launched as clusters of the kv heads of one sequence (grid z = padded row count of the
+// planes); the epilogue also writes the output row as the integer GEMM's fixed-point planes, bit for bit what the
+// stand-alone pre-pass makes of the stored fp16 output.
+template <typename T, int D, bool QUANT>
 __global__ void __launch_bounds__(kFastThreads)
 paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                         const AttnParams p, const int stages) {
@@ -114,6 +132,17 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
   const int b = blockIdx.z;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if constexpr (QUANT) {
+    if (b >= p.batch) {        // padding rows of the planes (the whole cluster is here): zeros, no barrier
+      const int k0 = kvh * p.group * D;
+      for (int i = threadIdx.x; i < p.group * D / 4; i += kFastThreads) {
+        *reinterpret_cast<uint32_t*>(p.quant_planes + plane_offset(p.quant_rows, b, k0 + 4 * i)) = 0u;
+        *reinterpret_cast<uint32_t*>(p.quant_planes + plane_offset(p.quant_rows, p.quant_rows + b, k0 + 4 * i)) = 0u;
+      }
+      if (kvh == 0 && threadIdx.x == 0) { p.quant_sx[b] = 0.f; p.quant_qsum[b] = 0; }
+      return;
+    }
+  }
   const int seq_len = p.seq_lens[b];
   const int t_begin = split * p.chunk_tokens;
   if (p.splits > 1 && t_begin >= seq_len) return;      // combine never reads this split
@@ -287,6 +316,81 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     }
   }
   __syncthreads();
+  if constexpr (QUANT) {
+    // One item (four consecutive dims of one head) per thread; exchange area behind the ring's barriers.
+    float* x_amax = reinterpret_cast<float*>(empty + stages);      // [8] one slot per CTA of the cluster, written by it
+    int* x_qsum = reinterpret_cast<int*>(x_amax + 8);              // [8] the same for the sums (read by rank 0)
+    float* s_redf = reinterpret_cast<float*>(x_qsum + 8);          // [8] per warp
+    int* s_redi = reinterpret_cast<int*>(s_redf + 8);              // [8] per warp
+    const int item = threadIdx.x;
+    const bool has = item < p.group * (D / 4);
+    const int row = has ? item / (D / 4) : 0, d0 = (item % (D / 4)) * 4;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (has) {
+      float m_tot = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) m_tot = fmaxf(m_tot, s_m[w * 16 + row]);
+      float l_tot = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        const float mi = s_m[w * 16 + row];
+        const float wgt = (mi == -INFINITY) ? 0.f : exp2f(mi - m_tot);
+        l_tot = fmaf(s_l[w * 16 + row], wgt, l_tot);
+        const float4 part = *reinterpret_cast<const float4*>(s_o + (w * 16 + row) * D + d0);
+        acc[0] = fmaf(part.x, wgt, acc[0]); acc[1] = fmaf(part.y, wgt, acc[1]);
+        acc[2] = fmaf(part.z, wgt, acc[2]); acc[3] = fmaf(part.w, wgt, acc[3]);
+      }
+      const int h = kvh * p.group + row;
+      __half2 lo2 = __floats2half2_rn(l_tot > 0.f ? acc[0] / l_tot : 0.f, l_tot > 0.f ? acc[1] / l_tot : 0.f);
+      __half2 hi2 = __floats2half2_rn(l_tot > 0.f ? acc[2] / l_tot : 0.f, l_tot > 0.f ? acc[3] / l_tot : 0.f);
+      __half* ob = static_cast<__half*>(p.out) + static_cast<size_t>(b) * p.out_stride + static_cast<size_t>(h) * D + d0;
+      *reinterpret_cast<uint2*>(ob) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo2), *reinterpret_cast<const uint32_t*>(&hi2));
+      const float2 a = __half22float2(lo2), c = __half22float2(hi2);       // the stored (rounded) values are what gets quantised
+      v[0] = a.x; v[1] = a.y; v[2] = c.x; v[3] = c.y;
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if (lane == 0) s_redf[warp] = amax;
+    __syncthreads();
+    const uint32_t rank = static_cast<uint32_t>(kvh), ranks = static_cast<uint32_t>(p.kv_heads);     // cluster = (1, kv_heads, 1)
+    if (threadIdx.x < ranks) {
+      float cta_max = 0.f;
+#pragma unroll
+      for (int w = 0; w < kFastThreads / 32; ++w) cta_max = fmaxf(cta_max, s_redf[w]);
+      store_to_rank(x_amax + rank, threadIdx.x, __float_as_uint(cta_max));
+    }
+    cluster_sync_all();
+    amax = 0.f;
+    for (uint32_t r = 0; r < ranks; ++r) amax = fmaxf(amax, x_amax[r]);
+    const float inv = amax > 0.f ? kQMax / amax : 0.f;
+    int sum = 0;
+    if (has) {
+      uint32_t hi_w, lo_w;
+      split_four(fixed_point_bits(v[0], inv), fixed_point_bits(v[1], inv), fixed_point_bits(v[2], inv), fixed_point_bits(v[3], inv),
+                 &hi_w, &lo_w, &sum);
+      const int k = (kvh * p.group + row) * D + d0;
+      *reinterpret_cast<uint32_t*>(p.quant_planes + plane_offset(p.quant_rows, b, k)) = hi_w;
+      *reinterpret_cast<uint32_t*>(p.quant_planes + plane_offset(p.quant_rows, p.quant_rows + b, k)) = lo_w;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane == 0) s_redi[warp] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int cta_sum = 0;
+#pragma unroll
+      for (int w = 0; w < kFastThreads / 32; ++w) cta_sum += s_redi[w];
+      store_to_rank(x_qsum + rank, 0u, static_cast<uint32_t>(cta_sum));
+    }
+    cluster_sync_all();
+    if (rank == 0 && threadIdx.x == 0) {
+      int tot = 0;
+      for (uint32_t r = 0; r < ranks; ++r) tot += x_qsum[r];
+      p.quant_qsum[b] = tot;
+      p.quant_sx[b] = amax > 0.f ? amax / kQMax : 0.f;
+    }
+  } else {
   for (int idx = threadIdx.x; idx < p.group * D; idx += kFastThreads) {
     const int row = idx / D;
     const int d = idx % D;
@@ -313,6 +417,7 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
         p.ws_ml[unit * 2 + 1] = l_tot;
       }
     }
+  }
   }
 }
 
@@ -631,7 +736,29 @@ int launch_fast(const AttnParams& p, int dtype, uint64_t pool_rows, cudaStream_t
   size_t smem = 1024 + static_cast<size_t>(stages) * kStageBytes + 256;
   const size_t merge = static_cast<size_t>(kConsumerWarps) * 16 * (D + 2) * sizeof(float) + 1024;
   if (smem < merge) smem = merge;
-  auto kern = paged_decode_mma_kernel<T, D>;
+  if constexpr (std::is_same<T, __half>::value && D == 128) {
+    if (p.quant_planes) {      // the kv heads of a sequence form a cluster; grid z covers the padding rows of the planes too
+      auto kern = paged_decode_mma_kernel<T, D, true>;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(1, p.kv_heads, p.quant_rows);
+      cfg.blockDim = dim3(kFastThreads, 1, 1);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = p.kv_heads;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      e = cudaLaunchKernelEx(&cfg, kern, tmap_k, tmap_v, p, stages);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      return launch_status();
+    }
+  }
+  auto kern = paged_decode_mma_kernel<T, D, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
   const dim3 grid(p.splits, p.kv_heads, p.batch);
@@ -681,6 +808,15 @@ bool paged_attention_fast_supported(const AttnParams& p, int dtype) {
   if (p.chunk_tokens % kPage != 0) return false;
   if (!aligned_to(p.k_cache, 16) || !aligned_to(p.v_cache, 16) || !aligned_to(p.q, 4) || (p.q_stride % 2) != 0) return false;
   return encode_fn() != nullptr;
+}
+
+bool paged_attention_quantize_supported(const AttnParams& p, int dtype) {
+  if (p.kv8 || dtype != CACHEIR_B200_F16 || p.head_dim != 128 || p.splits != 1) return false;
+  if (!paged_attention_fast_supported(p, dtype)) return false;
+  if (p.kv_heads < 1 || p.kv_heads > 8 || p.heads != p.group * p.kv_heads) return false;      // one portable cluster per sequence
+  if (p.group * (p.head_dim / 4) > kFastThreads) return false;                                // one four-dim item per thread
+  if (p.batch > 64 || p.out_stride != static_cast<long long>(p.heads) * p.head_dim) return false;
+  return true;
 }
 
 int launch_paged_attention_fast(const AttnParams& p, int dtype, cudaStream_t stream) {

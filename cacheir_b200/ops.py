@@ -56,6 +56,48 @@ def attention_workspace_bytes(batch: int, heads: int, head_dim: int, num_splits:
     return int(_lib.load().cacheir_b200_paged_attention_workspace_bytes(batch, heads, head_dim, num_splits))
 
 
+def attention_quantize_supported(batch: int, heads: int, kv_heads: int, max_pages: int, page_size: int, head_dim: int,
+                                 dtype: torch.dtype) -> bool:
+    """Can `paged_attention_decode_batch_quantize` take these extents (single split, fp16, head_dim 128, ...)?"""
+    if dtype != torch.float16:
+        return False
+    return bool(_lib.load().cacheir_b200_paged_attention_quantize_supported(int(batch), int(heads), int(kv_heads), int(max_pages),
+                                                                            int(page_size), int(head_dim), dtype_code(dtype)))
+
+
+def paged_attention_decode_batch_quantize(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                                          page_table: torch.Tensor, seq_lens: torch.Tensor, *, out: torch.Tensor,
+                                          gemm_workspace: torch.Tensor, softmax_scale: float | None = None) -> torch.Tensor:
+    """`paged_attention_decode_batch` in one split that also leaves `out` ([B, H, D], dense rows) in
+    `gemm_workspace` as the activation planes of the integer GEMM, exactly as `quantize_activations(out.view(B, H*D),
+    gemm_workspace)` would: the projection behind it runs with `prequantized=True` and no pre-pass launch."""
+    _require_cuda(q, k_cache, v_cache, page_table, seq_lens, out, gemm_workspace)
+    if q.dim() != 3 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape:
+        raise ValueError("expected q [B,H,D] and k_cache/v_cache [slots,KVH,page,D]")
+    batch, heads, head_dim = (int(s) for s in q.shape)
+    _, kv_heads, page_size, pool_dim = (int(s) for s in k_cache.shape)
+    if pool_dim != head_dim or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise ValueError("q and the KV pool must share head_dim and dtype")
+    if page_table.dtype != torch.int32 or seq_lens.dtype != torch.int32:
+        raise TypeError("page_table and seq_lens must be int32")
+    if page_table.dim() != 2 or page_table.shape[0] != batch or seq_lens.numel() != batch:
+        raise ValueError("page_table must be [B, max_pages] and seq_lens [B]")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous() and page_table.is_contiguous() and seq_lens.is_contiguous()):
+        raise ValueError("KV pool, page_table and seq_lens must be contiguous")
+    if q.stride(2) != 1 or q.stride(1) != head_dim:
+        raise ValueError("q heads must be dense: only the batch stride may differ from H*D")
+    if out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous tensor of q's shape and dtype")
+    if gemm_workspace.dtype != torch.uint8 or not gemm_workspace.is_contiguous():
+        raise ValueError("gemm_workspace must be a contiguous uint8 tensor")
+    check(_lib.load().cacheir_b200_paged_attention_decode_batch_quantize(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(),
+        batch, heads, kv_heads, int(page_table.shape[1]), page_size, head_dim, dtype_code(q.dtype), q.stride(0),
+        float(softmax_scale or 0.0), int(k_cache.shape[0]), gemm_workspace.data_ptr(), gemm_workspace.numel(), _stream()),
+        "paged_attention_decode_batch_quantize")
+    return out
+
+
 def paged_attention_decode_batch(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                                  page_table: torch.Tensor, seq_lens: torch.Tensor, *,
                                  out: torch.Tensor | None = None, softmax_scale: float | None = None,

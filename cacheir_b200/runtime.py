@@ -126,8 +126,9 @@ class _Engine:
     def __init__(self, artifact: Any, *, device: torch.device, dtype: torch.dtype, weights: B200WeightStore | None,
                  tensor_source: Any, kv_allocator: B200KVPageAllocator | None, max_seq_len: int | None,
                  use_cuda_graph: bool, attention_splits: int, max_plans: int, tensor_parallel: TensorParallel | None = None,
-                 kv_dtype: str = "same"):
+                 kv_dtype: str = "same", fuse_attention_prepass: bool = True):
         self.artifact = artifact
+        self.fuse_attention_prepass = bool(fuse_attention_prepass)   # attention writes the next projection's activation planes
         self.tp = tensor_parallel or TensorParallel(0, 1)
         self.device = device
         self.dtype = dtype
@@ -473,8 +474,20 @@ class _DecodePlan:
                                "b200.rope")
                     env[out_name] = t
             elif op in {"paged_attention_decode", "grouped_query_attention"}:
-                env[node.outputs[0]] = self._attention(env[node.inputs[0]], env[node.inputs[1]], env[node.inputs[2]], attrs,
-                                                       appended=node.inputs[1] in self._kv_appended)
+                # The projection behind the attention: when it runs on the integer tensor cores, the attention kernel
+                # itself can leave the activation planes it needs (no pre-pass launch in between).
+                nxt = nodes[idx + 1] if idx + 1 < len(nodes) else None
+                quant_ws = None
+                if (nxt is not None and nxt.op == "quantized_matmul" and nxt.inputs[0] == node.outputs[0]
+                        and uses.get(node.outputs[0], 0) == 1 and not eng.tp.enabled and eng.fuse_attention_prepass):
+                    k_total = int(attrs["num_heads"]) * int(attrs["head_dim"])
+                    if self._i8_eligible(eng.matmul_weight((nxt.inputs[1],), True, self.batch), k_total):
+                        quant_ws = self._gemm_workspace(k_total)
+                out, fused = self._attention(env[node.inputs[0]], env[node.inputs[1]], env[node.inputs[2]], attrs,
+                                             appended=node.inputs[1] in self._kv_appended, quant_ws=quant_ws)
+                env[node.outputs[0]] = out
+                if fused:
+                    self._prequantized.add(node.outputs[0])
             elif op == "add":
                 a, b = env[node.inputs[0]], env[node.inputs[1]]
                 out = self._buf(int(a.shape[1]))
@@ -565,7 +578,9 @@ class _DecodePlan:
         return None
 
     def _attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attrs: dict[str, Any], *,
-                   appended: bool = False) -> torch.Tensor:
+                   appended: bool = False, quant_ws: torch.Tensor | None = None) -> tuple[torch.Tensor, bool]:
+        """Emits the cache append (unless the QKV kernel did it) and the attention launch; returns the output and
+        whether the launch also left it in `quant_ws` as the next projection's activation planes."""
         eng = self.engine
         layer = int(attrs.get("layer", 0))
         heads, kv_heads, head_dim = int(attrs["num_heads"]), int(attrs["num_kv_heads"]), int(attrs["head_dim"])
@@ -588,10 +603,17 @@ class _DecodePlan:
                 self._emit(lambda: ops.kv_append_q8(k, v, k_pool, v_pool, kv_scales, self.page_table, self.positions), "b200.kv_append_q8")
             else:
                 self._emit(lambda: ops.kv_append(k, v, k_pool, v_pool, self.page_table, self.positions), "b200.kv_append")
+        if (quant_ws is not None and splits == 1 and kv_scales is None
+                and ops.attention_quantize_supported(self.batch, heads, kv_heads, self.width, eng.page_size, head_dim, out.dtype)):
+            self._emit(lambda: ops.paged_attention_decode_batch_quantize(q3, k_pool, v_pool, self.page_table, self.seq_lens,
+                                                                         out=out3, gemm_workspace=quant_ws),
+                       "b200.paged_attention_decode_batch.persistent_shared")
+            eng.count("b200.attention_prepass_fused")         # attention launches lowered in the fused form
+            return out, True
         self._emit(lambda: ops.paged_attention_decode_batch(q3, k_pool, v_pool, self.page_table, self.seq_lens, out=out3,
                                                             num_splits=splits, workspace=ws, kv_scales=kv_scales),
                    "b200.paged_attention_decode_batch.persistent_shared", launches=2 if splits > 1 else 1)
-        return out
+        return out, False
 
     # -- stepping --------------------------------------------------------------------
     def sync_sessions(self, sessions: list["B200DecodeRuntime"]) -> None:
@@ -708,6 +730,7 @@ class B200DecodeRuntime:
         tensor_parallel: TensorParallel | None = None,
         memory_limit_mb: float | None = None,
         kv_dtype: str = "same",
+        fuse_attention_prepass: bool = True,
         _engine: _Engine | None = None,
     ):
         if isinstance(artifact, (str, Path)):
@@ -727,7 +750,7 @@ class B200DecodeRuntime:
                 _engine = _Engine(artifact, device=dev, dtype=selected, weights=weights, tensor_source=tensor_source,
                                   kv_allocator=kv_allocator, max_seq_len=max_seq_len, use_cuda_graph=use_cuda_graph,
                                   attention_splits=attention_splits, max_plans=max_plans, tensor_parallel=tensor_parallel,
-                                  kv_dtype=kv_dtype)
+                                  kv_dtype=kv_dtype, fuse_attention_prepass=fuse_attention_prepass)
         self._engine = _engine
         self.artifact = _engine.artifact
         self.device = _engine.device

@@ -121,6 +121,26 @@ int cacheir_b200_paged_attention_decode_batch_ex(
     void* workspace, size_t workspace_bytes, int num_slots, int kv_dtype,
     const void* kv_scales, void* stream);
 
+/* Decode attention that also hands its output to the projection behind it: besides `out` ([batch][num_heads*head_dim],
+ * dense rows) the launch fills `gemm_workspace` with what cacheir_b200_quantize_activations would make of `out`
+ * (fixed-point byte planes, scale and sum per row, bit for bit), so that cacheir_b200_qgemv_ex can follow with
+ * CACHEIR_B200_X_PREQUANTIZED and no pre-pass launch of its own. One split; the kv heads of a sequence run as one
+ * thread-block cluster and exchange the row maximum and sum through distributed shared memory.
+ * Needs: fp16 q/out and fp16 pools, head_dim 128, pages of 16, at most 8 kv heads, num_heads / num_kv_heads <= 5,
+ * batch_size <= 64, gemm_workspace of cacheir_b200_qgemv_workspace_bytes(batch_size, num_heads*head_dim) bytes,
+ * 128-byte aligned; CACHEIR_B200_EUNSUPPORTED otherwise (cacheir_b200_paged_attention_quantize_supported tells
+ * beforehand: 1 or 0). In the reference the two steps are separate ops of the decode graph
+ * (cacheir/runtime/cuda.py:1238-1251 the attention launch, :932-954 the quantized matmul). */
+int cacheir_b200_paged_attention_decode_batch_quantize(
+    const void* q, const void* k_cache, const void* v_cache,
+    const int32_t* page_table, const int32_t* seq_lens, void* out,
+    int batch_size, int num_heads, int num_kv_heads, int max_pages_per_seq,
+    int page_size, int head_dim, int dtype, long long q_batch_stride,
+    float softmax_scale, int num_slots, void* gemm_workspace,
+    size_t gemm_workspace_bytes, void* stream);
+int cacheir_b200_paged_attention_quantize_supported(int batch_size, int num_heads, int num_kv_heads,
+                                                    int max_pages_per_seq, int page_size, int head_dim, int dtype);
+
 /* Allocation-free variant of cacheir_b200_paged_attention_decode_batch. It has no
  * counterpart in the reference; it exists for callers that have inputs and outputs
  * but no way to get scratch memory on the device: code bound to the reference's own

@@ -135,6 +135,60 @@ def test_attention_workspace_contract():
 
 
 # ---- dequant GEMV -------------------------------------------------------------------
+@pytest.mark.parametrize("batch,heads,kv_heads,lens", [
+    (32, 32, 8, None), (5, 16, 4, [1, 16, 17, 300, 0]), (16, 8, 8, None), (17, 20, 4, None), (3, 4, 1, [40, 2, 129])])
+def test_attention_with_fused_activation_prepass(batch, heads, kv_heads, lens):
+    """The single-split fast kernel run as clusters over the kv heads: the same output bits as the plain launch, and a
+    GEMM workspace that is bit for bit what the stand-alone pre-pass makes of that output (padding rows zeroed)."""
+    ops = _ops()
+    rng = np.random.default_rng(batch * 100 + heads)
+    D, page = 128, 16
+    if lens is None:
+        lens = [int(v) for v in rng.integers(1, 700, batch)]
+    assert ops.attention_quantize_supported(batch, heads, kv_heads, (max(lens) + page - 1) // page, page, D, torch.float16)
+    q, k_pool, v_pool, table, lens_np = _make_paged(rng, batch, heads, kv_heads, D, page, lens, torch.float16)
+    q = (q.float() * torch.from_numpy(rng.uniform(0.05, 8.0, (batch, 1, 1)).astype(np.float32))).half()
+    args = (q.cuda(), k_pool.cuda(), v_pool.cuda(), torch.from_numpy(table).cuda(), torch.from_numpy(lens_np).cuda())
+    plain = ops.paged_attention_decode_batch(*args, num_splits=1)
+    k_total = heads * D
+    nbytes = ops.qgemv_workspace_bytes(batch, k_total)
+    ws_ref = torch.full((nbytes,), 0xAB, dtype=torch.uint8, device="cuda")
+    ops.quantize_activations(plain.view(batch, k_total), ws_ref)
+    ws = torch.full((nbytes,), 0xCD, dtype=torch.uint8, device="cuda")          # stale bytes must all be overwritten
+    out = torch.empty_like(plain)
+    ops.paged_attention_decode_batch_quantize(*args, out=out, gemm_workspace=ws)
+    _device_status_ok()
+    assert torch.equal(out, plain)
+    mp = 16 if batch <= 16 else (32 if batch <= 32 else 64)
+    planes = 2 * mp * k_total
+    assert torch.equal(ws[:planes], ws_ref[:planes])
+    sx, sx_ref = ws[planes:planes + 256].view(torch.float32), ws_ref[planes:planes + 256].view(torch.float32)
+    qs, qs_ref = ws[planes + 256:planes + 512].view(torch.int32), ws_ref[planes + 256:planes + 512].view(torch.int32)
+    assert torch.equal(sx[:mp], sx_ref[:mp]) and torch.equal(qs[:mp], qs_ref[:mp])
+    want = oracle.paged_attention_decode(q.float().numpy(), k_pool.float().numpy(), v_pool.float().numpy(), table, lens_np)
+    assert _rel(out, want) <= TOL[torch.float16]
+    # the projection behind it takes the planes as they are
+    n = 256
+    x, packed = _qgemv_case(rng, batch, n, k_total, 8, torch.float16)
+    dev = _device_pack(packed)
+    kw = dict(bits=8, n=n, k=k_total)
+    y_fused = ops.qgemv(out.view(batch, k_total), dev.packed_values, dev.scales, dev.zero_points, workspace=ws, prequantized=True, **kw)
+    y_two = ops.qgemv(plain.view(batch, k_total), dev.packed_values, dev.scales, dev.zero_points, workspace=ws_ref, **kw)
+    assert torch.equal(y_fused, y_two)
+    _device_status_ok()
+
+
+def test_attention_fused_prepass_support_limits():
+    ops = _ops()
+    ok = lambda **kw: ops.attention_quantize_supported(**{**dict(batch=8, heads=32, kv_heads=8, max_pages=64, page_size=16,
+                                                                  head_dim=128, dtype=torch.float16), **kw})
+    assert ok()
+    assert not ok(head_dim=64) and not ok(dtype=torch.bfloat16) and not ok(page_size=32)
+    assert not ok(kv_heads=16, heads=32)            # more kv heads than a portable cluster holds
+    assert not ok(heads=64, kv_heads=8)             # more query heads per kv head than one item per thread covers
+    assert not ok(batch=65)
+
+
 def _qgemv_case(rng, m, n, k, bits, dtype, group=0, reference_pack=True):
     x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(dtype)
     if group:

@@ -316,3 +316,45 @@ def test_packed_prefill_of_several_sequences_equals_one_by_one(golden_dir, tmp_p
         a = packed[i].run([[7]], mode="decode")
         b = alone.run([[7]], mode="decode")
         np.testing.assert_allclose(a.float().cpu().numpy(), b.float().cpu().numpy(), rtol=2e-4, atol=2e-4)
+
+
+def test_attention_prepass_fusion_changes_no_bit(tmp_path):
+    """A 2-layer int8 model with head_dim 128 (the shape class the fused launch takes): with and without the attention
+    kernel writing the o-projection's activation planes, batched greedy decoding yields the same logits bits."""
+    import zlib
+
+    from cacheir_b200 import B200DecodeRuntime, B200KVPageAllocator, ModelConfig, build_decoder_artifact
+
+    mc = ModelConfig(architecture="LlamaForCausalLM", hidden_size=1024, intermediate_size=2048, num_layers=2,
+                     num_attention_heads=8, num_key_value_heads=2, vocab_size=512, max_position_embeddings=256,
+                     rope_theta=10000.0, rms_norm_eps=1e-5, dtype="float16")
+    art = build_decoder_artifact(mc, target="cuda", quant="int8", modes=("decode",))
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev)
+
+    def synth(key, shape):
+        if len(shape) == 1:
+            return torch.ones(shape, device=dev, dtype=torch.float32)
+        gen.manual_seed(zlib.crc32(key.encode()))
+        return torch.randn(shape, device=dev, dtype=torch.float32, generator=gen) * 0.05
+
+    rng = np.random.default_rng(5)
+    prompts = [[int(t) for t in rng.integers(0, 512, n)] for n in (5, 40, 17, 3, 64, 9)]
+    results = []
+    for fuse in (True, False):
+        rt = B200DecodeRuntime(art, dtype="float16", tensor_source=synth, kv_allocator=B200KVPageAllocator(page_size=16),
+                               max_seq_len=256, fuse_attention_prepass=fuse)
+        sessions = [rt.fork() for _ in prompts]
+        prefill = rt.run_prefill_batch(sessions, prompts)
+        tokens = [int(torch.argmax(prefill[i, len(p) - 1]).item()) for i, p in enumerate(prompts)]
+        steps = [prefill.clone()]
+        for _ in range(6):
+            logits = rt.run_decode_batch(sessions, tokens)
+            steps.append(logits[:, 0].clone())
+            tokens = [int(torch.argmax(row).item()) for row in logits[:, 0]]
+        counts = rt.cache_stats()["kernel_counts"]
+        assert (counts.get("b200.attention_prepass_fused", 0) > 0) == fuse
+        rt.check_device_status()
+        results.append(steps)
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
