@@ -69,6 +69,7 @@ class B200KVPageAllocator:
         self.pool_writes = 0
         self.pool_grows = 0
         self.generation = 0          # bumps whenever pool storage is (re)allocated
+        self.version = 0             # bumps whenever a page changes hands (allocate, retain, release)
         self.page_bytes: int | None = None
         self._pools: dict[int, dict[str, Any]] = {}
         self._pool_spec: tuple[Any, Any, int, int] | None = None  # device, dtype, kv_heads, head_dim
@@ -90,6 +91,7 @@ class B200KVPageAllocator:
         self._refcount[slot] = 1
         self._owners.setdefault(owner, []).append(slot)
         self.allocated_pages_total += 1
+        self.version += 1
         return KVPage(page_id=slot, start=start, length=length)
 
     def retain(self, *, owner: str, page: KVPage) -> KVPage:
@@ -97,12 +99,14 @@ class B200KVPageAllocator:
         self._refcount[page.page_id] += 1
         self._owners.setdefault(owner, []).append(page.page_id)
         self.shared_page_refs += 1
+        self.version += 1
         return KVPage(page_id=page.page_id, start=page.start, length=page.length)
 
     def refcount(self, slot: int) -> int:
         return self._refcount.get(int(slot), 0)
 
     def release_owner(self, owner: str) -> None:
+        self.version += 1
         for slot in self._owners.pop(owner, []):
             self._refcount[slot] -= 1
             if self._refcount[slot] == 0:

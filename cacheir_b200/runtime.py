@@ -296,6 +296,10 @@ class _DecodePlan:
         self.host_lens = torch.zeros((batch,), dtype=torch.int32).pin_memory()
         self.host_table = torch.zeros((batch, width), dtype=torch.int32).pin_memory()
         self.synced_owner_state: list[tuple[str, int, int, int]] | None = None
+        self.repeat_key: tuple | None = None     # the session list whose next steps need only new token ids (see _repeat_step)
+        self.repeat_tokens: list[int] = []
+        self.repeat_left = 0
+        self.repeat_version = -1
         self.program: list[Callable[[], None]] = []
         self.launches_per_step = 0
         self.cuda_graph: torch.cuda.CUDAGraph | None = None
@@ -665,6 +669,7 @@ class _DecodePlan:
         self.page_table.copy_(self.host_table, non_blocking=True)
         self.h2d_done.record()
         self.synced_owner_state = None
+        self.repeat_left = 0            # the device rows now belong to this pass
 
     def sync_prefill_chunk(self, cache: B200PagedKVCache, start: int, token_ids: list[int]) -> None:
         """Rows 0..n-1 are the tokens at positions start..start+n-1 of one sequence."""
@@ -784,9 +789,12 @@ class B200DecodeRuntime:
         """Advance one decode token for several sessions; returns logits [N, 1, vocab] (cuda.py:541-582)."""
         self._enforce_memory_limit()
         try:
-            plan = self._prepare_batch(sessions, token_ids)
-            with torch.cuda.device(self.device):
-                plan.run_program()
+            plan = self._repeat_step(sessions, token_ids)
+            if plan is None:
+                plan = self._prepare_batch(sessions, token_ids)
+                with torch.cuda.device(self.device):
+                    plan.run_program()
+                self._arm_repeat(plan, sessions)
         except (torch.cuda.OutOfMemoryError, KVPoolExhausted) as exc:
             self._recover_from_oom()
             raise RuntimeError("CacheIR CUDA batch decode recovered from an out-of-memory condition; "
@@ -826,6 +834,47 @@ class B200DecodeRuntime:
             if session.kv_cache.tokens > limit:
                 raise ValueError(f"sequence of {session.kv_cache.tokens} tokens exceeds max_seq_len={limit}; "
                                  "construct the runtime with a larger max_seq_len")
+
+    # -- the steady state of a decode loop ---------------------------------------------------
+    # While the same sessions step together and none of them opens a page, the device already holds everything a
+    # step needs except the token ids (lengths advance on the device, the page table is unchanged). Such a step is
+    # launched first and the host bookkeeping (one more token per session) runs while the GPU works.
+    def _arm_repeat(self, plan: "_DecodePlan", sessions) -> None:
+        eng = self._engine
+        page, limit = eng.page_size, eng.max_seq_len
+        caches = [s.kv_cache for s in sessions]
+        plan.repeat_key = eng.validated_batch
+        plan.repeat_tokens = [c.tokens for c in caches]
+        plan.repeat_left = min(min(page * len(c.pages) - c.tokens, limit - c.tokens) for c in caches)
+        plan.repeat_version = eng.allocator.version
+
+    def _repeat_step(self, sessions, token_ids) -> "_DecodePlan | None":
+        eng = self._engine
+        n = len(sessions)
+        if n == 0 or n != len(token_ids):
+            return None
+        plan = eng.plans.get(("decode", n))
+        if (plan is None or plan.repeat_left <= 0 or plan.repeat_key != tuple(map(id, sessions)) or plan.repeat_key != eng.validated_batch
+                or plan.repeat_version != eng.allocator.version or plan.pool_generation != eng.allocator.generation):
+            return None
+        caches = [s.kv_cache for s in sessions]
+        if [c.tokens for c in caches] != plan.repeat_tokens:      # someone moved a cache between the steps
+            plan.repeat_left = 0
+            return None
+        with torch.cuda.device(self.device):
+            plan.h2d_done.synchronize()   # the pinned staging buffer must not change under a pending copy
+            plan.host_ids.numpy()[:] = token_ids
+            plan.ids.copy_(plan.host_ids, non_blocking=True)
+            plan.h2d_done.record()
+            plan.run_program()
+        # bookkeeping of the step just launched (no page opens: `repeat_left` counted the room in the open pages)
+        for c in caches:
+            c.extend(1)
+        plan.repeat_tokens = [t + 1 for t in plan.repeat_tokens]
+        plan.repeat_left -= 1
+        plan.synced_owner_state = [(c.owner_id, c.tokens, len(c.pages), c.epoch) for c in caches]
+        eng.plans.move_to_end(("decode", n))
+        return plan
 
     def _prepare_batch(self, sessions, token_ids) -> _DecodePlan:
         if not sessions:
@@ -876,6 +925,7 @@ class B200DecodeRuntime:
                 table[row] = s.kv_cache.page_table_row(plan.width)
             plan.page_table.copy_(plan.host_table, non_blocking=True)
             plan.h2d_done.record()
+            plan.repeat_left = 0
             tokens = plan.run_feedback_steps(steps)
             plan.synced_owner_state = [(s.kv_cache.owner_id, s.kv_cache.tokens, len(s.kv_cache.pages), s.kv_cache.epoch)
                                        for s in sessions]
