@@ -746,9 +746,10 @@ def run_micro(args) -> None:
 
 
 def run_micro_layer(args, dev, gen, peak: float, kind: str) -> None:
-    """The nine launches of one decoder layer of the 8B-shaped decode step, with the entry points and flags the runtime
-    uses (RMSNorm + pre-pass, fused QKV + RoPE + cache append, paged decode attention, pre-pass, o with residual,
-    RMSNorm + pre-pass, paired gate|up with SwiGLU, pre-pass, down with residual), batch `--m`, context `--ctx-max`;
+    """The eight launches of one decoder layer of the 8B-shaped decode step, with the entry points and flags the runtime
+    uses (RMSNorm + pre-pass, fused QKV + RoPE + cache append, paged decode attention that also writes the pre-pass of
+    o, o with residual, RMSNorm + pre-pass, paired gate|up with SwiGLU, pre-pass, down with residual; with `--splits`
+    above 1 the attention is split and o runs its own pre-pass: nine and a combine), batch `--m`, context `--ctx-max`;
     the weights alternate between two copies. A profiling aid: small enough to capture whole under ncu."""
     import torch
 
@@ -779,6 +780,8 @@ def run_micro_layer(args, dev, gen, peak: float, kind: str) -> None:
     act = torch.empty((B, FFN), device=dev, dtype=torch.float16)
     ws = torch.zeros(ops.qgemv_workspace_bytes(B, FFN), device=dev, dtype=torch.uint8)
 
+    fused_prepass = (args.splits or 1) == 1 and ops.attention_quantize_supported(B, 32, kvh, pages, page, hd, torch.float16)
+
     def launch(i: int) -> None:
         c = i % copies
         ops.rms_norm_quantize(h0, norm, 1e-5, ws)
@@ -786,11 +789,14 @@ def run_micro_layer(args, dev, gen, peak: float, kind: str) -> None:
         ops.qkv_rope_append(None, w.packed_values, w.scales, w.zero_points, qkv, n=H + 2 * KVD, k=H, q_dim=H, k_dim=KVD, head_dim=hd,
                             theta=theta, table=rope, positions=positions, page_table=table, k_cache=k_pool, v_cache=v_pool,
                             workspace=ws, tiled=True, prequantized=True)
-        ops.paged_attention_decode_batch(qkv[:, :H].as_strided((B, 32, hd), (qkv.stride(0), hd, 1)), k_pool, v_pool, table, lens,
-                                         out=attn.view(B, 32, hd), num_splits=args.splits or 1)
+        q3 = qkv[:, :H].as_strided((B, 32, hd), (qkv.stride(0), hd, 1))
         w = w_o[c]
+        if fused_prepass:
+            ops.paged_attention_decode_batch_quantize(q3, k_pool, v_pool, table, lens, out=attn.view(B, 32, hd), gemm_workspace=ws)
+        else:
+            ops.paged_attention_decode_batch(q3, k_pool, v_pool, table, lens, out=attn.view(B, 32, hd), num_splits=args.splits or 1)
         ops.qgemv(attn, w.packed_values, w.scales, w.zero_points, bits=8, n=H, k=H, epilogue=ops.EPI_RESIDUAL, residual=h0, out=h1,
-                  workspace=ws, tiled=True)
+                  workspace=ws, tiled=True, prequantized=fused_prepass)
         ops.rms_norm_quantize(h1, norm, 1e-5, ws)
         w = w_gu[c]
         ops.qgemv(h1, w.packed_values, w.scales, w.zero_points, bits=8, n=2 * FFN, k=H, epilogue=ops.EPI_SWIGLU, out=act, workspace=ws,
@@ -809,7 +815,7 @@ def run_micro_layer(args, dev, gen, peak: float, kind: str) -> None:
     end.record()
     torch.cuda.synchronize()
     from cacheir_b200 import _lib
-    emit({"micro": "decoder_layer", "batch": B, "context": ctx, "launches_per_step": 9, "steps": args.steps,
+    emit({"micro": "decoder_layer", "batch": B, "context": ctx, "launches_per_step": 8 if fused_prepass else 9, "steps": args.steps,
           "us_per_step_eager": round(start.elapsed_time(end) * 1e3 / args.steps, 2), "peak": peak, "peak_source": f"of {kind}",
           "device_status": _lib.load().cacheir_b200_device_status(0)})
 
