@@ -161,7 +161,8 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------
-def build_runtime(cfg: dict, device_index: int, extra_tokens: int, tensor_parallel=None, kv_dtype: str = "same"):
+def build_runtime(cfg: dict, device_index: int, extra_tokens: int, tensor_parallel=None, kv_dtype: str = "same",
+                  fuse_attention_prepass: bool = True):
     import zlib
 
     import torch
@@ -189,7 +190,7 @@ def build_runtime(cfg: dict, device_index: int, extra_tokens: int, tensor_parall
     alloc = B200KVPageAllocator(page_size=page, initial_slots=total_pages + 8)
     rt = B200DecodeRuntime(art, device=f"cuda:{device_index}", dtype="float16", tensor_source=synth,
                            kv_allocator=alloc, max_seq_len=cfg["ctx"] + extra_tokens, clone_outputs=False,
-                           tensor_parallel=tensor_parallel, kv_dtype=kv_dtype)
+                           tensor_parallel=tensor_parallel, kv_dtype=kv_dtype, fuse_attention_prepass=fuse_attention_prepass)
     del head_dim
     return rt, art
 
@@ -852,6 +853,8 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--kv", default="fp16", choices=["fp16", "int8"],
                         help="KV page format: fp16 (the benchmark's configuration) or 8-bit pages with a scale per cached row (an extra)")
+    parser.add_argument("--separate-attention-prepass", action="store_true",
+                        help="diagnostic: run the o projection's activation pre-pass as its own launch instead of inside the attention kernel")
     parser.add_argument("--no-tp-leg", action="store_true", help="with --gpus N > 1: skip the tensor-parallel leg attached to the line")
     parser.add_argument("--micro", choices=["qgemv", "attention", "layer"],
                         help="time one kernel alone, or the kernels of one decoder layer of the 8B-shaped step (profiling aid)")
@@ -942,7 +945,7 @@ def measure(args, cfg: dict, workload: str, use_tp: bool, world: int, rank: int,
     if use_tp:
         from cacheir_b200.tensor_parallel import TensorParallel
         tp = TensorParallel(rank, world)
-    rt, _ = build_runtime(cfg, local_rank, extra, tp, cfg.get("kv_dtype", "same"))
+    rt, _ = build_runtime(cfg, local_rank, extra, tp, cfg.get("kv_dtype", "same"), not args.separate_attention_prepass)
     sessions = prefill_synthetic_context(rt, cfg)
     first_tokens = [int(t) for t in np.random.default_rng(0 if tp else rank).integers(0, cfg["vocab"], cfg["batch"])]
     replicas = 1 if tp else world                          # independent batches in flight
