@@ -426,7 +426,9 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
 // a (page, kv head) chunk is 16 rows x 128 bytes of K, the same of V, and 64 bytes of scales (16 fp16 for K, 16 for V),
 // half the bytes of the fp16 pool. ldmatrix reads the byte tiles as 16-bit units, so a thread receives four
 // consecutive dims of a K row (or, transposed, two dims of two V rows); a byte permute with 0x64 high bytes turns two
-// of them into the fp16 pair (1024 + b0, 1024 + b1), minus 1152 is (b - 128) exactly. The k order of the QK^T product
+// of them into the fp16 pair (1024 + b0, 1024 + b1) = (b - 128) + 1152, exact in fp16; the constant leaves through sums
+// the MMAs' accumulators account for (scores start at -1152 * sum(q) of their row, outputs lose 1152 * sum(p) of their
+// row at the end), so no subtraction is spent per value. The k order of the QK^T product
 // inside a 16-dim step is therefore 4t, 4t+1 | 4t+2, 4t+3 for thread t of a quad, and Q is loaded in that order; the
 // PV product yields the dims of a 16-dim block as two tiles, even dims and odd dims. The row scales multiply the scores
 // (K) and the probabilities (V) instead of the 2 x 2048 cached values.
@@ -442,10 +444,9 @@ __device__ __forceinline__ void tma_load_2d_tile(uint32_t dst, const CUtensorMap
 // bytes i and j of w as the fp16 pair (b_i - 128, b_j - 128)
 template <uint32_t SEL>
 __device__ __forceinline__ uint32_t byte_pair(uint32_t w) {
-  const uint32_t biased = __byte_perm(w, 0x64646464u, SEL);                 // (1024 + b_i, 1024 + b_j)
-  const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&biased), __half2half2(__ushort_as_half(0x6480)));   // 0x6480 = 1152
-  return *reinterpret_cast<const uint32_t*>(&v);
+  return __byte_perm(w, 0x64646464u, SEL);                                  // (1024 + b_i, 1024 + b_j), exact in fp16
 }
+constexpr float kByteBias = 1152.f;     // 1024 + 128: what every operand built by byte_pair carries on top of (b - 128)
 
 // Six consumer warps (a page each per stage): the chain per page is longer than with fp16 pages (byte -> fp16
 // conversions in front of every MMA) while the page has half the bytes, so more pages must be in work per SM (two CTAs of six warps).
@@ -540,6 +541,22 @@ paged_decode_mma_q8_kernel(const __grid_constant__ CUtensorMap tmap_k, const __g
         }
       }
     }
+    // -1152 * (sum of the row's query values, as the MMA sees them): where the score accumulators start
+    float qbias[2] = {0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < kKSteps; ++ks)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][r]));
+        qbias[r & 1] += f.x + f.y;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      qbias[r] += __shfl_xor_sync(0xffffffffu, qbias[r], 1);
+      qbias[r] += __shfl_xor_sync(0xffffffffu, qbias[r], 2);
+      qbias[r] *= -kByteBias;
+    }
+    float p_run[2] = {0.f, 0.f};         // running sum of the probabilities (times V scales) fed to the PV product, per thread
     const uint32_t lrow = lane & 7;
     const uint32_t lmat = lane >> 3;
     for (int it = 0; it < n_iters && ok; ++it) {
@@ -557,7 +574,7 @@ paged_decode_mma_q8_kernel(const __grid_constant__ CUtensorMap tmap_k, const __g
         float sc[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-          sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+          sc[nt][0] = sc[nt][1] = qbias[0]; sc[nt][2] = sc[nt][3] = qbias[1];
           const uint32_t token = nt * 8 + lrow;
 #pragma unroll
           for (int kk = 0; kk < kKSteps / 4; ++kk) {
@@ -617,6 +634,11 @@ paged_decode_mma_q8_kernel(const __grid_constant__ CUtensorMap tmap_k, const __g
           pa[1] = pack2<__half>(pr[0][2], pr[0][3]);
           pa[2] = pack2<__half>(pr[1][0], pr[1][1]);
           pa[3] = pack2<__half>(pr[1][2], pr[1][3]);
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {     // the rounded values the MMA multiplies: their sum carries the byte offset out again
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&pa[r])), c = __half22float2(*reinterpret_cast<const __half2*>(&pa[2 + r]));
+            p_run[r] = fmaf(p_run[r], corr[r], (a.x + a.y) + (c.x + c.y));
+          }
         }
         // ---- O = O * corr + P V: one transposed ldmatrix covers two 16-dim blocks = four n tiles ----
 #pragma unroll
@@ -642,6 +664,11 @@ paged_decode_mma_q8_kernel(const __grid_constant__ CUtensorMap tmap_k, const __g
     for (int r = 0; r < 2; ++r) {
       l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
       l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+      p_run[r] += __shfl_xor_sync(0xffffffffu, p_run[r], 1);
+      p_run[r] += __shfl_xor_sync(0xffffffffu, p_run[r], 2);
+      const float off = kByteBias * p_run[r];        // every output column of the row carries 1152 * sum(p)
+#pragma unroll
+      for (int i = 0; i < kDimTiles; ++i) { o[i][2 * r] -= off; o[i][2 * r + 1] -= off; }
     }
   }
 
