@@ -863,7 +863,7 @@ class B200DecodeRuntime:
             return None
         with torch.cuda.device(self.device):
             plan.h2d_done.synchronize()   # the pinned staging buffer must not change under a pending copy
-            plan.host_ids.numpy()[:] = token_ids
+            plan.host_ids.numpy()[:] = [int(t) for t in token_ids]
             plan.ids.copy_(plan.host_ids, non_blocking=True)
             plan.h2d_done.record()
             plan.run_program()
