@@ -235,7 +235,15 @@ __global__ void embedding_gather_kernel(const T* __restrict__ table, const int64
   long long id = ids[r];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // clamp instead of faulting on a bad id
   const T* src = table + static_cast<size_t>(id) * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) out[static_cast<size_t>(r) * hidden + c] = src[c];
+  T* dst = out + static_cast<size_t>(r) * hidden;
+  constexpr int VEC = 16 / sizeof(T);
+  if (hidden % VEC == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {   // 16-byte copies
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (int c = threadIdx.x; c < hidden / VEC; c += blockDim.x) d4[c] = s4[c];
+    return;
+  }
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = src[c];
 }
 
 // Row argmax; ties resolve to the lowest index like torch/numpy argmax.
