@@ -483,14 +483,11 @@ class _DecodePlan:
                 nxt = nodes[idx + 1] if idx + 1 < len(nodes) else None
                 quant_ws = None
                 if (nxt is not None and nxt.op == "quantized_matmul" and nxt.inputs[0] == node.outputs[0]
-                        and uses.get(node.outputs[0], 0) == 1 and eng.fuse_attention_prepass):
-                    # (tensor parallel: this rank's heads feed its column slice of the row-parallel o projection)
-                    role = "row" if nxt.attrs.get("projection") == "o" else "replicated"
-                    if not eng.tp.enabled or role == "row":
-                        k_total = int(attrs["num_heads"]) // eng.tp.world * int(attrs["head_dim"])
-                        weight = eng.matmul_weight((nxt.inputs[1],), True, self.batch, role if eng.tp.enabled else "replicated")
-                        if self._i8_eligible(weight, k_total):
-                            quant_ws = self._gemm_workspace(k_total)
+                        and uses.get(node.outputs[0], 0) == 1 and eng.fuse_attention_prepass and not eng.tp.enabled):
+                    # (single GPU only: under tensor parallelism the o projection keeps its own pre-pass)
+                    k_total = int(attrs["num_heads"]) * int(attrs["head_dim"])
+                    if self._i8_eligible(eng.matmul_weight((nxt.inputs[1],), True, self.batch, "replicated"), k_total):
+                        quant_ws = self._gemm_workspace(k_total)
                 out, fused = self._attention(env[node.inputs[0]], env[node.inputs[1]], env[node.inputs[2]], attrs,
                                              appended=node.inputs[1] in self._kv_appended, quant_ws=quant_ws)
                 env[node.outputs[0]] = out
