@@ -47,6 +47,11 @@ struct PeerParams {
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ int ld_relaxed_sys(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -66,16 +71,15 @@ __device__ __forceinline__ bool announce_and_wait(const PeerParams& p, int epoch
   __syncthreads();
   if (s_lost != 0) return false;                 // an earlier wait gave up and the host has not cleared the word yet
   const uint32_t limit = poll_limit(p);
-  if (blockIdx.x == 0 && threadIdx.x < p.world && threadIdx.x != p.rank) {
-    __threadfence_system();
-    st_release_sys(p.flags[threadIdx.x] + p.rank, epoch);
-  }
+  if (blockIdx.x == 0 && threadIdx.x < p.world && threadIdx.x != p.rank)
+    st_release_sys(p.flags[threadIdx.x] + p.rank, epoch);   // (a release store carries its own system-scope fence)
   if (threadIdx.x < p.world && threadIdx.x != p.rank) {
     const int* slot = p.flags[p.rank] + threadIdx.x;
     bool seen = false;
+    // Relaxed polls (an acquire load carries a system-scope fence: microseconds per poll), one acquire once the epoch shows.
     for (uint32_t i = 0; i < limit; ++i) {
-      if (ld_acquire_sys(slot) - epoch >= 0) { seen = true; break; }   // (difference: survives wrap-around)
-      if (i > 64) __nanosleep(i > 4096 ? 2000 : 100);
+      if (ld_relaxed_sys(slot) - epoch >= 0) { seen = ld_acquire_sys(slot) - epoch >= 0; break; }   // (difference: survives wrap-around)
+      if (i > 256) __nanosleep(i > 16384 ? 2000 : 100);
     }
     if (!seen) {
       s_ok = 0;
@@ -151,27 +155,31 @@ __global__ void __launch_bounds__(256) all_reduce_two_step_kernel(const PeerPara
       gather_sum<T>(p, base + i, acc);           // rank order
       for (int r = 0; r < p.world; ++r) VecIO<T, VEC>::st(static_cast<T*>(p.gather[r]) + (base + i) * VEC, acc);
     }
-    __threadfence_system();                      // this thread's pushes are visible everywhere before the flag goes up
   }
   __shared__ int s_last;
   if (threadIdx.x == 0) s_ok2 = 1;
-  __syncthreads();
-  if (threadIdx.x == 0) s_last = atomicAdd(p.state + 2, 1) == static_cast<int>(gridDim.x) - 1 ? 1 : 0;
+  __syncthreads();                               // every thread of the CTA has issued its pushes
+  if (threadIdx.x == 0) {
+    // One system-scope fence per CTA, after the barrier: it orders the whole CTA's pushes (fences are cumulative over
+    // what the barrier made visible to this thread) before the counter, and through the counter before the flag that
+    // the last CTA raises.
+    __threadfence_system();
+    s_last = atomicAdd(p.state + 2, 1) == static_cast<int>(gridDim.x) - 1 ? 1 : 0;
+    __threadfence();                             // (acquire side of the counter: what the other CTAs fenced is ordered before the flag)
+  }
   __syncthreads();
   if (s_last != 0) {                             // last CTA of this rank: the whole slice has been pushed
     if (threadIdx.x == 0) p.state[2] = 0;
-    if (ok && threadIdx.x < p.world) {           // one thread per peer: the system-scope releases run side by side
-      __threadfence_system();
+    if (ok && threadIdx.x < p.world)             // one thread per peer: the system-scope releases run side by side
       st_release_sys(p.flags[threadIdx.x] + kMaxRanks + p.rank, epoch);
-    }
   }
   if (ok && threadIdx.x < p.world) {
     const int* slot = p.flags[p.rank] + kMaxRanks + threadIdx.x;
     const uint32_t limit = poll_limit(p);
     bool seen = false;
     for (uint32_t i = 0; i < limit; ++i) {
-      if (ld_acquire_sys(slot) - epoch >= 0) { seen = true; break; }
-      if (i > 64) __nanosleep(i > 4096 ? 2000 : 100);
+      if (ld_relaxed_sys(slot) - epoch >= 0) { seen = ld_acquire_sys(slot) - epoch >= 0; break; }
+      if (i > 256) __nanosleep(i > 16384 ? 2000 : 100);
     }
     if (!seen) {
       s_ok2 = 0;
