@@ -82,6 +82,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "cacheir_b200_peer_all_reduce": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p]),
     "cacheir_b200_peer_all_reduce_two_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_void_p,
                                                       c_void_p]),
+    "cacheir_b200_peer_all_reduce_ll": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_void_p,
+                                                c_void_p]),
     "cacheir_b200_peer_all_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p]),
     "cacheir_b200_device_status": (c_int, [c_int]),
     "cacheir_b200_pack_rows": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_void_p]),

@@ -37,6 +37,8 @@ struct PeerParams {
   const void* data[kMaxRanks];    // every rank's data buffer (index = rank), mapped into this process
   int* flags[kMaxRanks];          // every rank's flag array [kMaxRanks]
   void* gather[kMaxRanks];        // two-step all-reduce: every rank's gather buffer
+  unsigned long long* ll_rs[kMaxRanks];   // flagged-word all-reduce: every rank's receive area of the reduce-scatter step
+  unsigned long long* ll_ag[kMaxRanks];   // and of the all-gather step; each [2 parities][world senders][words per slice]
   void* out;
   size_t count;                   // all-reduce: elements; all-gather: elements of one rank's slice row
   int rows;                       // all-gather only: rows of the [rows, count] slices
@@ -201,6 +203,113 @@ __global__ void __launch_bounds__(256) all_reduce_two_step_kernel(const PeerPara
   finish(p, epoch);
 }
 
+// ---- all-reduce with the flag inside every word ("low latency" protocol) --------------------------------------
+// No flag rounds and no fences: a 32-bit data word travels as one 64-bit store {data, epoch}, which is single-copy
+// atomic, so a receiver that reads the epoch of this call in the upper half holds valid data in the lower half.
+//   A. every rank pushes slice j of its own buffer into rank j's reduce-scatter area [parity][sender];
+//   B. rank r adds slice r of all ranks in rank order (its own from local memory, the others as they arrive),
+//      writes the result to its output and pushes it into every rank's all-gather area [parity][owner];
+//   C. every rank copies the other owners' slices from its all-gather area to its output as they arrive.
+// Twice the bytes of the two-step form on the wire, about half its latency for the messages of a decode step.
+// The areas alternate with the parity of the epoch: a sender can reach call k + 2 only after this rank has taken
+// part in call k + 1, i.e. after it has read everything of call k. Stale words carry an older epoch and never match.
+__device__ __forceinline__ void st_word_sys(unsigned long long* p, uint32_t data, uint32_t epoch) {
+  const unsigned long long v = (static_cast<unsigned long long>(epoch) << 32) | data;
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// Bounded wait for a flagged word; on time-out records the status and returns 0 with *ok cleared.
+__device__ __forceinline__ uint32_t wait_word_sys(const unsigned long long* p, uint32_t epoch, uint32_t limit, bool* ok) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    if (static_cast<uint32_t>(v >> 32) == epoch) return static_cast<uint32_t>(v);
+    if (i > 1024) __nanosleep(i > 16384 ? 2000 : 100);
+  }
+  *ok = false;
+  atomicCAS(&g_peer_status, 0, (4 << 8) | 3);
+  return 0u;
+}
+template <typename T>
+__device__ __forceinline__ void add_word(uint32_t w, float (&acc)[2]);
+template <>
+__device__ __forceinline__ void add_word<float>(uint32_t w, float (&acc)[2]) { acc[0] += __uint_as_float(w); }
+template <>
+__device__ __forceinline__ void add_word<__half>(uint32_t w, float (&acc)[2]) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+  acc[0] += f.x; acc[1] += f.y;
+}
+template <>
+__device__ __forceinline__ void add_word<__nv_bfloat16>(uint32_t w, float (&acc)[2]) {
+  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+  acc[0] += f.x; acc[1] += f.y;
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack_word(const float (&acc)[2]);
+template <>
+__device__ __forceinline__ uint32_t pack_word<float>(const float (&acc)[2]) { return __float_as_uint(acc[0]); }
+template <>
+__device__ __forceinline__ uint32_t pack_word<__half>(const float (&acc)[2]) {
+  const __half2 h = __floats2half2_rn(acc[0], acc[1]);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_word<__nv_bfloat16>(const float (&acc)[2]) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(acc[0], acc[1]);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// count * sizeof(T) is a multiple of 4 * world; every CTA of the grid is resident (at most one per SM).
+template <typename T>
+__global__ void __launch_bounds__(256) all_reduce_ll_kernel(const PeerParams p) {
+  const int epoch_i = p.state[0] + 1;
+  const uint32_t epoch = static_cast<uint32_t>(epoch_i);
+  __shared__ int s_lost;
+  if (threadIdx.x == 0) s_lost = peer_already_lost() ? 1 : 0;     // one reader: the whole CTA takes the same branch
+  __syncthreads();
+  if (s_lost == 0) {
+    const uint32_t limit = poll_limit(p);
+    const size_t words = p.count * sizeof(T) / 4;
+    const size_t wps = words / p.world;                            // words per slice
+    const size_t area = (static_cast<size_t>(epoch & 1u) * p.world) * wps;      // this call's parity half of an area
+    const uint32_t* local = static_cast<const uint32_t*>(p.data[p.rank]);
+    uint32_t* out = static_cast<uint32_t*>(p.out);
+    const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const size_t nthreads = static_cast<size_t>(gridDim.x) * blockDim.x;
+    bool ok = true;
+    // A: my contribution to every other owner's slice
+    for (int d = 1; d < p.world; ++d) {
+      const int j = (p.rank + d) % p.world;                        // (each rank starts with a different peer)
+      unsigned long long* dst = p.ll_rs[j] + area + static_cast<size_t>(p.rank) * wps;
+      const uint32_t* src = local + static_cast<size_t>(j) * wps;
+      for (size_t o = tid; o < wps; o += nthreads) st_word_sys(dst + o, src[o], epoch);
+    }
+    // B: my slice, summed in rank order, to my output and to everybody's all-gather area
+    const unsigned long long* rs = p.ll_rs[p.rank] + area;
+    for (size_t o = tid; o < wps; o += nthreads) {
+      float acc[2] = {0.f, 0.f};
+      for (int r = 0; r < p.world; ++r) {
+        const uint32_t w = r == p.rank ? local[static_cast<size_t>(p.rank) * wps + o]
+                                       : wait_word_sys(rs + static_cast<size_t>(r) * wps + o, epoch, limit, &ok);
+        add_word<T>(w, acc);
+      }
+      const uint32_t res = pack_word<T>(acc);
+      out[static_cast<size_t>(p.rank) * wps + o] = res;
+      for (int d = 1; d < p.world; ++d) {
+        const int j = (p.rank + d) % p.world;
+        st_word_sys(p.ll_ag[j] + area + static_cast<size_t>(p.rank) * wps + o, res, epoch);
+      }
+    }
+    // C: the other owners' slices
+    const unsigned long long* ag = p.ll_ag[p.rank] + area;
+    for (int d = 1; d < p.world && ok; ++d) {
+      const int j = (p.rank + d) % p.world;
+      for (size_t o = tid; o < wps && ok; o += nthreads)
+        out[static_cast<size_t>(j) * wps + o] = wait_word_sys(ag + static_cast<size_t>(j) * wps + o, epoch, limit, &ok);
+    }
+  }
+  finish(p, epoch_i);
+}
+
 // out[rows, world*count]: rank r's [rows, count] slice lands in columns [r*count, (r+1)*count)
 template <typename T>
 __global__ void __launch_bounds__(256) all_gather_kernel(const PeerParams p) {
@@ -307,6 +416,35 @@ extern "C" int cacheir_b200_peer_all_reduce_two_step(void* const* data, void* co
     case CACHEIR_B200_F32: all_reduce_two_step_kernel<float><<<grid, 256, 0, st>>>(p); break;
     case CACHEIR_B200_F16: all_reduce_two_step_kernel<__half><<<grid, 256, 0, st>>>(p); break;
     default: all_reduce_two_step_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p); break;
+  }
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_peer_all_reduce_ll(const void* local_data, void* const* ll_rs, void* const* ll_ag, void* out,
+                                               size_t count, int dtype, int rank, int world, int* state, void* stream) {
+  if (count == 0) return 0;
+  if (!local_data || !ll_rs || !ll_ag || !out || !state || world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+    return CACHEIR_B200_EINVAL;
+  PeerParams p{};
+  for (int r = 0; r < world; ++r) {
+    if (!ll_rs[r] || !ll_ag[r] || !aligned_to(ll_rs[r], 8) || !aligned_to(ll_ag[r], 8)) return CACHEIR_B200_EINVAL;
+    p.ll_rs[r] = static_cast<unsigned long long*>(ll_rs[r]);
+    p.ll_ag[r] = static_cast<unsigned long long*>(ll_ag[r]);
+  }
+  if (!aligned_to(local_data, 4) || !aligned_to(out, 4)) return CACHEIR_B200_EALIGN;
+  p.data[rank] = local_data;
+  p.out = out; p.rank = rank; p.world = world; p.state = state;
+  const int esize = dtype_size(dtype);
+  if (esize == 0) return CACHEIR_B200_EINVAL;
+  if ((count * esize) % (4 * static_cast<size_t>(world)) != 0) return CACHEIR_B200_EALIGN;
+  p.count = count;
+  const size_t words = count * esize / 4;
+  const unsigned grid = static_cast<unsigned>(words / 1024 < 1 ? 1 : (words / 1024 > kNumSMs ? kNumSMs : words / 1024));
+  cudaStream_t st = as_stream(stream);
+  switch (dtype) {
+    case CACHEIR_B200_F32: all_reduce_ll_kernel<float><<<grid, 256, 0, st>>>(p); break;
+    case CACHEIR_B200_F16: all_reduce_ll_kernel<__half><<<grid, 256, 0, st>>>(p); break;
+    default: all_reduce_ll_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p); break;
   }
   return launch_status();
 }

@@ -125,13 +125,16 @@ class _RawCudaBuffer:
 class PeerCollectives:
     """The library's own all-reduce / all-gather over NVLink peer memory (include/cacheir_b200.h,
     `cacheir_b200_peer_*`): three data buffers per rank (A and B alternate between consecutive
-    all-reduces, C carries the logits slice), one flag array and the gather buffer of the two-step
-    all-reduce (messages of `two_step_bytes` and more on `two_step_ranks` ranks and more), all mapped into every peer through CUDA IPC. Unlike a library collective these are plain kernels of this package, so a whole
+    all-reduces, C carries the logits slice), one flag array, the gather buffer of the two-step
+    all-reduce (messages of `two_step_bytes` and more on `two_step_ranks` ranks and more) and the two receive
+    areas of the flagged-word all-reduce (messages up to `flagged_word_bytes`), all mapped into every peer through CUDA IPC. Unlike a library collective these are plain kernels of this package, so a whole
     tensor-parallel step can be captured into one CUDA graph. All ranks must construct it, and
     issue its calls, in the same order."""
 
     two_step_bytes = 256 * 1024       # the two-step all-reduce pays a second round of flags: worth it only when
     two_step_ranks = 4                # it saves much NVLink traffic, (world-1) against 2 (world-1)/world messages
+    flagged_word_bytes = 1024 * 1024  # up to this size the all-reduce with the flag inside every word is the fastest
+                                      # (8 GPUs: 14 / 15 / 23 us for 128 KB / 512 KB / 2 MB against 21 / 18 / 22 us with flag rounds)
 
     def __init__(self, tp: TensorParallel, device: torch.device, data_bytes: int):
         import ctypes
@@ -150,7 +153,8 @@ class PeerCollectives:
         self._opened: list[int] = []
         handles: list[bytes] = []
         with torch.cuda.device(device):
-            for nbytes in (self.data_bytes, self.data_bytes, self.data_bytes, 256, self.data_bytes):   # A, B, C, flags, gather
+            # A, B, C, flags, gather, and the two areas of the flagged-word all-reduce (2 parities x 2 x the message each)
+            for nbytes in (self.data_bytes, self.data_bytes, self.data_bytes, 256, self.data_bytes, 4 * self.data_bytes, 4 * self.data_bytes):
                 ptr = ctypes.c_void_p()
                 handle = (ctypes.c_ubyte * 64)()
                 check(self._lib.cacheir_b200_peer_alloc(nbytes, ctypes.byref(ptr), handle), "peer_alloc")
@@ -159,9 +163,9 @@ class PeerCollectives:
             everyone: list[Any] = [None] * tp.world
             dist.all_gather_object(everyone, handles, group=tp.group)
             # pointer tables [buffer][rank]
-            self._ptrs: list[list[int]] = [[0] * tp.world for _ in range(5)]
+            self._ptrs: list[list[int]] = [[0] * tp.world for _ in range(7)]
             for r in range(tp.world):
-                for b in range(5):
+                for b in range(7):
                     if r == tp.rank:
                         self._ptrs[b][r] = self._local[b]
                     else:
@@ -170,7 +174,7 @@ class PeerCollectives:
                         check(self._lib.cacheir_b200_peer_open(blob, ctypes.byref(ptr)), "peer_open")
                         self._ptrs[b][r] = int(ptr.value)
                         self._opened.append(int(ptr.value))
-            self._tables = [(ctypes.c_void_p * tp.world)(*self._ptrs[b]) for b in range(5)]
+            self._tables = [(ctypes.c_void_p * tp.world)(*self._ptrs[b]) for b in range(7)]
             self.state = torch.zeros((4,), device=device, dtype=torch.int32)
             self._views = [torch.as_tensor(_RawCudaBuffer(self._local[b], self.data_bytes), device=device) for b in range(3)]
         dist.barrier(group=tp.group)
@@ -188,6 +192,12 @@ class PeerCollectives:
         from ._lib import check
 
         nbytes = out.numel() * out.element_size()
+        if nbytes <= min(self.flagged_word_bytes, self.data_bytes) and nbytes % (4 * self.tp.world) == 0:
+            check(self._lib.cacheir_b200_peer_all_reduce_ll(self._ptrs[index][self.tp.rank], self._tables[5], self._tables[6],
+                                                            out.data_ptr(), out.numel(), ops.dtype_code(out.dtype),
+                                                            self.tp.rank, self.tp.world, self.state.data_ptr(),
+                                                            ops._stream()), "peer_all_reduce_ll")
+            return
         if self.tp.world >= self.two_step_ranks and nbytes >= self.two_step_bytes and nbytes % (16 * self.tp.world) == 0:
             check(self._lib.cacheir_b200_peer_all_reduce_two_step(self._tables[index], self._tables[4], self._tables[3],
                                                                   out.data_ptr(), out.numel(), ops.dtype_code(out.dtype),

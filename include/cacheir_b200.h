@@ -338,7 +338,13 @@ int cacheir_b200_pack_unrelayout(const uint8_t* tiled, uint8_t* packed, int N, i
  * rank's buffer and pushes it into every rank's `gather` buffer (another peer_alloc buffer of
  * the message size, `gather[r]` = rank r's), then every rank copies its gather buffer to
  * `out`. Each rank moves 2 (world-1)/world of the message over NVLink instead of world-1
- * messages. The kernel must own the GPU while it runs (its CTAs wait for one another). */
+ * messages. The kernel must own the GPU while it runs (its CTAs wait for one another).
+ * peer_all_reduce_ll: the same result again with the flag inside every word (count * element size a multiple of
+ * 4 * world): each 32-bit word travels as one 64-bit store {word, epoch}; rank r receives slice r of every rank in
+ * its `ll_rs` area, adds in rank order, and pushes the sum into every rank's `ll_ag` area; no flag rounds, no fences,
+ * twice the bytes on the wire: the fastest form for the messages of a decode step. `ll_rs[r]` / `ll_ag[r]` are rank
+ * r's areas (peer_alloc, zero-filled, 4 x the largest message each); `local_data` is this rank's own buffer and
+ * needs no peer mapping. */
 int cacheir_b200_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
 int cacheir_b200_peer_open(const unsigned char* handle64, void** ptr);
 int cacheir_b200_peer_close(void* ptr);
@@ -348,6 +354,8 @@ int cacheir_b200_peer_all_reduce(void* const* data, void* const* flags, void* ou
 int cacheir_b200_peer_all_reduce_two_step(void* const* data, void* const* gather, void* const* flags,
                                           void* out, size_t count, int dtype, int rank, int world,
                                           int* state, void* stream);
+int cacheir_b200_peer_all_reduce_ll(const void* local_data, void* const* ll_rs, void* const* ll_ag, void* out,
+                                    size_t count, int dtype, int rank, int world, int* state, void* stream);
 int cacheir_b200_peer_all_gather(void* const* data, void* const* flags, void* out, int rows,
                                  size_t cols, int dtype, int rank, int world, int* state,
                                  void* stream);

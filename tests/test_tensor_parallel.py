@@ -134,9 +134,12 @@ def _peer_collectives_check(rank: int, world: int) -> dict:
     gens = [torch.Generator(device="cpu") for _ in range(world)]
     report = {"reduce_ok": True, "gather_ok": True, "graph_ok": True}
     # a small message (one step: every rank reads every buffer) and one past the two-step threshold
-    # (reduce-scatter + all-gather inside one launch)
-    for rows, cols in ((8, 512), (128, 2048)):
+    # (reduce-scatter + all-gather inside one launch), each first with the flag inside every word (the default for
+    # messages of this size), then with the flag rounds
+    for rows, cols, flagged in ((8, 512, True), (128, 2048, True), (8, 512, False), (128, 2048, False)):
         assert (rows * cols * 2 >= PeerCollectives.two_step_bytes) == (rows == 128)
+        peer.flagged_word_bytes = PeerCollectives.flagged_word_bytes if flagged else 0
+        assert rows * cols * 2 <= PeerCollectives.flagged_word_bytes
         out = torch.empty((rows, cols), device=dev, dtype=torch.float16)
         for call in range(6):                                   # every rank can regenerate every rank's data
             parts = []
@@ -302,6 +305,59 @@ def _lost_peer_worker():
     torch.cuda.synchronize()
     assert lib.cacheir_b200_device_status(1) == 0
     assert torch.equal(out, torch.full_like(out, 3.0))              # 1 + 2, in rank order
+
+
+def _lost_peer_flagged_word_worker():
+    """The all-reduce with the flag inside every word, one GPU, world = 2: rank 1's words never arrive, then a call whose
+    words the host has put in place (epoch in the upper half of every 64-bit word)."""
+    import ctypes
+
+    from cacheir_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    n, world = 4096, 2
+    words = n // 2                  # 32-bit words of an fp16 message
+    wps = words // world
+    mine = torch.ones((n,), device=dev, dtype=torch.float16)
+    areas = [torch.zeros((2 * world * wps,), device=dev, dtype=torch.int64) for _ in range(4)]   # rs0, rs1, ag0, ag1
+    out = torch.zeros((n,), device=dev, dtype=torch.float16)
+    state = torch.zeros((4,), device=dev, dtype=torch.int32)
+    state[3] = 2000
+    rs = (ctypes.c_void_p * 2)(areas[0].data_ptr(), areas[1].data_ptr())
+    ag = (ctypes.c_void_p * 2)(areas[2].data_ptr(), areas[3].data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        return lib.cacheir_b200_peer_all_reduce_ll(mine.data_ptr(), rs, ag, out.data_ptr(), n, 1, 0, world, state.data_ptr(), stream)
+
+    assert lib.cacheir_b200_device_status(1) == 0
+    assert call() == 0
+    torch.cuda.synchronize()
+    assert lib.cacheir_b200_device_status(0) == (4 << 8) | 3        # a word of rank 1 never came; the kernel returned
+    for _ in range(20):                                             # later calls return at once
+        assert call() == 0
+    torch.cuda.synchronize()
+    assert lib.cacheir_b200_device_status(1) == (4 << 8) | 3
+    # a healthy call: what rank 1 would have sent (2.0 everywhere) and its finished slice (1 + 2 = 3)
+    epoch = int(state[0].item()) + 1
+    half = lambda v: int(torch.tensor([v, v], dtype=torch.float16).view(torch.int32).item()) & 0xFFFFFFFF
+    base = (epoch & 1) * world * wps
+    areas[0][base + 1 * wps: base + 2 * wps] = (epoch << 32) | half(2.0)       # reduce-scatter area, sender 1
+    areas[2][base + 1 * wps: base + 2 * wps] = (epoch << 32) | half(3.0)       # all-gather area, owner 1
+    assert call() == 0
+    torch.cuda.synchronize()
+    assert lib.cacheir_b200_device_status(1) == 0
+    assert torch.equal(out, torch.full_like(out, 3.0))
+    # rank 0 pushed its contribution and its finished slice into "rank 1's" areas, flagged with the epoch
+    sent = areas[1][base: base + wps]
+    assert torch.equal(sent, torch.full_like(sent, (epoch << 32) | half(1.0)))
+    done = areas[3][base: base + wps]
+    assert torch.equal(done, torch.full_like(done, (epoch << 32) | half(3.0)))
+
+
+@pytest.mark.gpu
+def test_lost_peer_flagged_word_all_reduce():
+    _lost_peer_flagged_word_worker()
 
 
 @pytest.mark.gpu
