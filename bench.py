@@ -691,7 +691,10 @@ def run_micro(args) -> None:
     else:
         batch, heads, kv_heads, hd, page = args.batch, args.heads, args.kv_heads, 128, 16
         rng = np.random.default_rng(0)
-        lens_np = rng.integers(args.ctx_min, args.ctx_max + 1, batch).astype(np.int32)
+        if args.ctx_log:      # log-uniform lengths (many short sequences, a few long ones)
+            lens_np = np.exp(rng.uniform(np.log(args.ctx_min), np.log(args.ctx_max), batch)).astype(np.int32)
+        else:
+            lens_np = rng.integers(args.ctx_min, args.ctx_max + 1, batch).astype(np.int32)
         pages = (lens_np + page - 1) // page
         total = int(pages.sum())
         table_np = np.zeros((batch, int(pages.max())), dtype=np.int32)
@@ -871,6 +874,7 @@ def main() -> None:
     parser.add_argument("--ctx-min", type=int, default=512)
     parser.add_argument("--ctx-max", type=int, default=8192)
     parser.add_argument("--splits", type=int, default=0)
+    parser.add_argument("--ctx-log", action="store_true", help="--micro attention: log-uniform context lengths")
     parser.add_argument("--heads", type=int, default=32)
     parser.add_argument("--kv-heads", type=int, default=8)
     args = parser.parse_args()
