@@ -26,7 +26,7 @@ constexpr int kRowPadBytes = 64;     // staged rows are 64 bytes apart modulo 12
 #define CB200_GEMV_TEAMS 4
 #endif
 #ifndef CB200_GEMV_STAGE_BLOCKS
-#define CB200_GEMV_STAGE_BLOCKS 8
+#define CB200_GEMV_STAGE_BLOCKS 16
 #endif
 constexpr int kTeams = CB200_GEMV_TEAMS;             // a team shares one ring of stages and one run of (tile, stage) units
 constexpr int kTeamWarps = 4;         // each warp of a team multiplies a quarter of every stage
@@ -34,8 +34,11 @@ constexpr int kWarps = kTeams * kTeamWarps;
 constexpr int kThreadsMma = kWarps * 32;
 constexpr int kRoundTiles = 2 * kTeams;      // weight tiles a CTA works on at a time: a team's run then touches at most three
 constexpr int kPieces = 3;
-constexpr int kStages = 4;                   // stages per team ring
-constexpr int kStageBlocks = CB200_GEMV_STAGE_BLOCKS;              // 128-column blocks per stage: 16 rows x 512 bytes of codes, one TMA copy
+#ifndef CB200_GEMV_STAGES
+#define CB200_GEMV_STAGES 2
+#endif
+constexpr int kStages = CB200_GEMV_STAGES;                   // stages per team ring
+constexpr int kStageBlocks = CB200_GEMV_STAGE_BLOCKS;              // 128-column blocks per stage: 16 rows x 1024 bytes of codes, one TMA copy
 constexpr int kStageRowBytes = kStageBlocks * 64;
 constexpr int kStageBytes = kTileRows * kStageRowBytes;
 constexpr int kWarpBlocks = kStageBlocks / kTeamWarps;
@@ -76,9 +79,9 @@ constexpr uint32_t kNibLo = 0x000F000Fu, kNibHi = 0x00F000F0u, kFp16Magic = 0x64
 // epilogue a gate and an up weight tile per output tile). It takes its weight tiles 8 at a time and deals the
 // (tile, stage) units of such a round out evenly over four teams of four warps: team t gets units [U t / 4, U (t+1) / 4),
 // a run along K that touches at most three tiles, so every team streams the same number of bytes whatever the tile
-// count. A stage is 16 rows x 1024 columns of codes: 512 contiguous bytes of every row, fetched by one TMA copy, so
-// that DRAM sees long runs per row. Each team keeps a ring of four stages: lane 0 of its first warp issues the copies,
-// the four warps wait on the stage's `full` mbarrier, multiply two 128-column blocks each and arrive on its `empty`
+// count. A stage is 16 rows x 2048 columns of codes: 1024 contiguous bytes of every row, fetched by one TMA copy, so
+// that DRAM sees long runs per row. Each team keeps a ring of two stages: lane 0 of its first warp issues the copies,
+// the four warps wait on the stage's `full` mbarrier, multiply four 128-column blocks each and arrive on its `empty`
 // mbarrier. Per block a warp issues 8 MMAs (two chains) whose accumulators start at -(1024 + zero) * sum(x over the
 // block), then folds them into its running sums with the two rows' group scales. Partial sums meet in shared memory
 // and are added in warp order.
@@ -416,7 +419,7 @@ int launch_qgemv_mma(const QGemvParams& q, cudaStream_t stream) {
   const MmaGemvShape shape = mma_gemv_shape(q.M, q.N, q.K, swiglu);
   p.chunk_cols = shape.chunk_cols; p.max_tiles = shape.max_tiles;
   const bool f16 = q.scale_dtype == CACHEIR_B200_F16;
-  // the packed rows as a [N][K/8] matrix of 32-bit words, copied in tiles of 16 rows x 512 bytes; what lies past N or K reads as zero
+  // the packed rows as a [N][K/8] matrix of 32-bit words, copied in tiles of 16 rows x 1024 bytes; what lies past N or K reads as zero
   CUtensorMap tmap;
   if (!ptx::encode_u32_rows_plain(&tmap, q.packed, static_cast<uint64_t>(q.K / 8), static_cast<uint64_t>(q.N), static_cast<uint64_t>(q.K / 2),
                                   kStageRowBytes / 4, kTileRows))
