@@ -90,6 +90,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "cacheir_b200_dequantize_rows": (c_int, [c_void_p] * 4 + [c_int, c_int, c_int, c_int, c_void_p]),
     "cacheir_b200_rms_norm": (c_int, [c_void_p] * 5 + [c_int, c_int, c_float, c_int, c_void_p]),
     "cacheir_b200_rope_inplace": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p]),
+    "cacheir_b200_rope_append": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_longlong, c_void_p]),
     "cacheir_b200_kv_append": (
         c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p]),
     "cacheir_b200_kv_append_q8": (

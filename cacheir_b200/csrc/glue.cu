@@ -165,6 +165,39 @@ __global__ void kv_append_kernel(const T* __restrict__ k, const T* __restrict__ 
   v_cache[dst] = v[static_cast<size_t>(b) * v_stride + idx];
 }
 
+// ---- RoPE on the q and k heads of a fused [q | k | v] row and the append of the new k / v rows, one launch ----
+// The same arithmetic as rope_inplace_kernel followed by kv_append_kernel (the pool receives the rotated, rounded k).
+template <typename T>
+__global__ void rope_append_kernel(T* __restrict__ qkv, const int32_t* __restrict__ positions,
+                                   const int32_t* __restrict__ page_table, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                   int q_dim, int k_dim, int head_dim, float theta, int max_pages, int page_size, long long stride) {
+  const int b = blockIdx.y;
+  const int pair = blockIdx.x * blockDim.x + threadIdx.x;            // pair of adjacent elements of the row
+  if (pair >= (q_dim + 2 * k_dim) / 2) return;
+  const int col = 2 * pair;
+  const int pos = positions[b];
+  T* p = qkv + static_cast<size_t>(b) * stride + col;
+  T e0 = p[0], e1 = p[1];
+  if (col < q_dim + k_dim) {                                          // q and k heads rotate
+    float s, c, re, ro;
+    rope_cos_sin(pos, (col % head_dim) / 2, head_dim, theta, &c, &s);
+    rope_rotate(Elem<T>::ld(p), Elem<T>::ld(p + 1), c, s, &re, &ro);
+    Elem<T>::st(p, re);
+    Elem<T>::st(p + 1, ro);
+    e0 = p[0]; e1 = p[1];
+  }
+  if (col < q_dim) return;
+  const int page_idx = pos / page_size;
+  if (pos < 0 || page_idx >= max_pages) return;                       // no page reserved: drop rather than write out of range
+  const int kv_col = (col - q_dim) % k_dim;                           // v follows k and has the same width
+  const int page = page_table[static_cast<size_t>(b) * max_pages + page_idx];
+  const size_t dst = ((static_cast<size_t>(page) * (k_dim / head_dim) + kv_col / head_dim) * page_size + pos % page_size) *
+                         static_cast<size_t>(head_dim) + kv_col % head_dim;
+  T* pool = col < q_dim + k_dim ? k_cache : v_cache;
+  pool[dst] = e0;
+  pool[dst + 1] = e1;
+}
+
 // ---- KV append into 8-bit pools: each new row is quantised with its own scale --------------------
 // scale = fp16(max|row| / 127) (1 for an all-zero row), byte = clamp(rint(value / scale), -127, 127) + 128.
 // One CTA per (kv head, request); k and v rows of head_dim values each.
@@ -350,6 +383,23 @@ extern "C" int cacheir_b200_rope_table(float* table, int positions, int head_dim
   const size_t total = static_cast<size_t>(positions) * (head_dim / 2);
   rope_table_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(
       reinterpret_cast<float2*>(table), positions, head_dim, theta);
+  return launch_status();
+}
+
+extern "C" int cacheir_b200_rope_append(void* qkv, const int32_t* positions, const int32_t* page_table, void* k_cache,
+                                        void* v_cache, int batch_size, int q_dim, int k_dim, int head_dim, float theta,
+                                        int max_pages_per_seq, int page_size, int dtype, long long qkv_batch_stride,
+                                        void* stream) {
+  if (batch_size <= 0 || q_dim < 0 || k_dim <= 0 || head_dim <= 0) return 0;
+  if (!qkv || !positions || !page_table || !k_cache || !v_cache || max_pages_per_seq <= 0 || page_size <= 0 ||
+      batch_size > 65535 || (head_dim % 2) != 0 || q_dim % head_dim != 0 || k_dim % head_dim != 0)
+    return CACHEIR_B200_EINVAL;
+  const long long stride = qkv_batch_stride > 0 ? qkv_batch_stride : static_cast<long long>(q_dim) + 2 * k_dim;
+  const int pairs = (q_dim + 2 * k_dim) / 2;
+  const dim3 grid((pairs + 127) / 128, batch_size);
+  CB200_DISPATCH_DTYPE(dtype, (rope_append_kernel<T><<<grid, 128, 0, as_stream(stream)>>>(
+                                  static_cast<T*>(qkv), positions, page_table, static_cast<T*>(k_cache), static_cast<T*>(v_cache),
+                                  q_dim, k_dim, head_dim, theta, max_pages_per_seq, page_size, stride)));
   return launch_status();
 }
 

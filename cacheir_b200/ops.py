@@ -353,6 +353,24 @@ def kv_append(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: 
                                              k.stride(0), v.stride(0), _stream()), "kv_append")
 
 
+def rope_append(qkv: torch.Tensor, positions: torch.Tensor, page_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *,
+                q_dim: int, k_dim: int, head_dim: int, theta: float) -> None:
+    """`rope_inplace` on the q and k heads of the fused rows qkv [B, q_dim + 2*k_dim] followed by `kv_append` of the
+    rotated k and the v columns, in one launch (the same bits)."""
+    _require_cuda(qkv, positions, page_table, k_cache, v_cache)
+    _, kv_heads, page_size, pool_dim = (int(s) for s in k_cache.shape)
+    if qkv.dim() != 2 or int(qkv.shape[1]) != q_dim + 2 * k_dim or qkv.stride(1) != 1:
+        raise ValueError("qkv must be [B, q_dim + 2*k_dim] with dense rows")
+    if pool_dim != head_dim or kv_heads * head_dim != k_dim or v_cache.shape != k_cache.shape:
+        raise ValueError("the pools must hold k_dim / head_dim heads of head_dim values")
+    if qkv.dtype != k_cache.dtype or v_cache.dtype != k_cache.dtype or page_table.dtype != torch.int32 or positions.dtype != torch.int32:
+        raise TypeError("dtype mismatch in rope_append")
+    check(_lib.load().cacheir_b200_rope_append(qkv.data_ptr(), positions.data_ptr(), page_table.data_ptr(), k_cache.data_ptr(),
+                                               v_cache.data_ptr(), int(qkv.shape[0]), int(q_dim), int(k_dim), int(head_dim),
+                                               float(theta), int(page_table.shape[1]), page_size, dtype_code(qkv.dtype),
+                                               qkv.stride(0), _stream()), "rope_append")
+
+
 def kv_append_q8(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_scales: torch.Tensor,
                  page_table: torch.Tensor, positions: torch.Tensor) -> None:
     """`kv_append` into uint8 pools: each new row is quantised with its own fp16 scale (kv_scales [slots, KVH, 2, page])."""

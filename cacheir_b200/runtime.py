@@ -456,9 +456,19 @@ class _DecodePlan:
                     normed = self._buf(int(x.shape[1]))
                     self._emit(lambda x=x, w=norm_w, out=normed, eps=eps: ops.rms_norm(x, w, eps, out=out), "b200.rms_norm")
                     qkv = self._matmul(normed, weight)
-                qk = qkv[:, : q_dim + k_dim]   # q and k heads are adjacent: one RoPE launch covers both
-                self._emit(lambda qk=qk, hd=head_dim, theta=theta, nh=(q_dim + k_dim) // head_dim:
-                           ops.rope_inplace(qk, self.positions, num_heads=nh, head_dim=hd, theta=theta), "b200.rope")
+                pool = eng.allocator.pool_for_layer(int(consumer.attrs.get("layer", 0))) if consumer is not None else None
+                if (pool is not None and "scales" not in pool and pool["keys"].dtype == qkv.dtype and int(pool["keys"].shape[3]) == head_dim
+                        and int(pool["keys"].shape[1]) * head_dim == k_dim and int(qkv.shape[1]) == q_dim + 2 * k_dim):
+                    # RoPE on q|k and the append of the new k / v rows in one launch
+                    k_pool, v_pool = pool["keys"], pool["values"]
+                    self._emit(lambda qkv=qkv, k_pool=k_pool, v_pool=v_pool, hd=head_dim, theta=theta:
+                               ops.rope_append(qkv, self.positions, self.page_table, k_pool, v_pool, q_dim=q_dim, k_dim=k_dim,
+                                               head_dim=hd, theta=theta), "b200.rope_append")
+                    self._kv_appended.add(node.outputs[1])
+                else:
+                    qk = qkv[:, : q_dim + k_dim]   # q and k heads are adjacent: one RoPE launch covers both
+                    self._emit(lambda qk=qk, hd=head_dim, theta=theta, nh=(q_dim + k_dim) // head_dim:
+                               ops.rope_inplace(qk, self.positions, num_heads=nh, head_dim=hd, theta=theta), "b200.rope")
                 env[node.outputs[0]] = qkv[:, :q_dim]
                 env[node.outputs[1]] = qkv[:, q_dim:q_dim + k_dim]
                 env[node.outputs[2]] = qkv[:, q_dim + k_dim:]

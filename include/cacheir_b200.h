@@ -421,6 +421,14 @@ int cacheir_b200_kv_append(const void* k, const void* v, void* k_cache, void* v_
                            long long k_batch_stride, long long v_batch_stride,
                            void* stream);
 
+/* `_rope_with_offsets` on the q and k heads of a fused row [q | k | v] (in place) and the append of the new k / v rows
+ * (cacheir_b200_rope_inplace followed by cacheir_b200_kv_append, bit for bit) in one launch: qkv is
+ * [batch][q_dim + 2*k_dim] with `qkv_batch_stride` elements between rows (0 = dense), pools of the same dtype. */
+int cacheir_b200_rope_append(void* qkv, const int32_t* positions, const int32_t* page_table, void* k_cache,
+                             void* v_cache, int batch_size, int q_dim, int k_dim, int head_dim, float theta,
+                             int max_pages_per_seq, int page_size, int dtype, long long qkv_batch_stride,
+                             void* stream);
+
 /* The same into 8-bit pools (see cacheir_b200_paged_attention_decode_batch_ex): every new row is quantised with its
  * own scale, scale = fp16(max|row| / 127) (1 for an all-zero row), byte = clamp(rint(value / scale), -127, 127) + 128;
  * the scale goes to kv_scales[slot][kv_head][0 (K) | 1 (V)][pos % page_size] (fp16). head_dim <= 256.

@@ -343,6 +343,29 @@ def test_kv_append_writes_the_right_page_rows():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_rope_append_equals_rope_then_append(dtype):
+    """One launch for RoPE on q|k and the append of the new k / v rows: the bits of the two separate launches,
+    on a row-strided fused buffer, with a position past the reserved pages (dropped) and q wider than k (GQA)."""
+    ops = _ops()
+    rng = np.random.default_rng(11)
+    batch, heads, kvh, d, page = 5, 6, 2, 16, 4
+    q_dim, k_dim = heads * d, kvh * d
+    pool_shape = (12, kvh, page, d)
+    table = torch.tensor([[5, 1, 0], [2, 7, 9], [3, 0, 0], [4, 6, 8], [10, 11, 0]], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([6, 11, 0, 13, 5], dtype=torch.int32, device="cuda")     # row 3: page index 3 is not in the table
+    wide = torch.from_numpy(rng.standard_normal((batch, q_dim + 2 * k_dim + 8)).astype(np.float32)).to(dtype).cuda()
+    a, b = wide.clone(), wide.clone()
+    qkv_a, qkv_b = a[:, 4:4 + q_dim + 2 * k_dim], b[:, 4:4 + q_dim + 2 * k_dim]
+    ka, va = torch.zeros(pool_shape, device="cuda", dtype=dtype), torch.zeros(pool_shape, device="cuda", dtype=dtype)
+    kb, vb = torch.zeros_like(ka), torch.zeros_like(va)
+    ops.rope_inplace(qkv_a[:, : q_dim + k_dim], pos, num_heads=heads + kvh, head_dim=d, theta=10000.0)
+    ops.kv_append(qkv_a[:, q_dim:q_dim + k_dim], qkv_a[:, q_dim + k_dim:], ka, va, table[:, :3].contiguous(), pos)
+    ops.rope_append(qkv_b, pos, table[:, :3].contiguous(), kb, vb, q_dim=q_dim, k_dim=k_dim, head_dim=d, theta=10000.0)
+    assert torch.equal(a, b) and torch.equal(ka, kb) and torch.equal(va, vb)
+    assert ka.abs().sum() > 0 and not ka[0].any()                                 # rows were written; slot 0 was not touched
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_elementwise_embedding_argmax(dtype):
     ops = _ops()
     rng = np.random.default_rng(8)
