@@ -496,7 +496,8 @@ class _DecodePlan:
                         and uses.get(node.outputs[0], 0) == 1 and eng.fuse_attention_prepass and not eng.tp.enabled):
                     # (single GPU only: under tensor parallelism the o projection keeps its own pre-pass)
                     k_total = int(attrs["num_heads"]) * int(attrs["head_dim"])
-                    if self._i8_eligible(eng.matmul_weight((nxt.inputs[1],), True, self.batch, "replicated"), k_total):
+                    if (self._i8_eligible(eng.matmul_weight((nxt.inputs[1],), True, self.batch, "replicated"), k_total)
+                            and ops.qgemv_workspace_bytes(self.batch, k_total) <= self._gemm_ws.numel()):   # (never grows it here)
                         quant_ws = self._gemm_workspace(k_total)
                 out, fused = self._attention(env[node.inputs[0]], env[node.inputs[1]], env[node.inputs[2]], attrs,
                                              appended=node.inputs[1] in self._kv_appended, quant_ws=quant_ws)
